@@ -1,0 +1,116 @@
+/*
+ * qmm.h — C ABI of libqmm: GGUF-block quantized matmul for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a host program binds (Rust `unsafe extern "C"`, ctypes,
+ * cgo ...).  It follows the launcher convention of nm-z/nates-recipe-rs's
+ * gpu-core crate: one `launch_<op>` per operator, device pointers first, sizes
+ * as `int`/`long`, the stream last (gpu-core/src/kernels/gemm_f64.hip:48-54,
+ * gpu-core/src/kernels/f64_infer.hip:19, gpu-core/src/kernels/quantizedx.hip:25-28;
+ * Rust declarations gpu-core/src/infer_ops.rs:11-55).  One deliberate difference:
+ * every launcher returns an `int` status (0 = launched; negative = an argument
+ * was rejected on the host and nothing was launched) where the upstream returns
+ * void and relies on `check_launch` (gpu-core/src/kernels.rs:8-13).
+ *
+ * Conventions shared by all entry points
+ *   - every pointer is a DEVICE pointer unless the parameter says `host`;
+ *   - the caller owns every buffer; no entry point here allocates device memory;
+ *   - weights `w` are row-major (n, k): n rows of k/B packed blocks, exactly the
+ *     GGUF tensor bytes (the operand `b` of gpu_gemm_bt_f64_into,
+ *     gpu-core/src/infer_ops.rs:224-240);
+ *   - activations are row-major (m, k); outputs row-major (m, n), distinct from
+ *     the inputs;
+ *   - `stream` is a cudaStream_t passed as void*; NULL is the legacy default
+ *     stream, which is what the upstream's wrappers pass;
+ *   - weight buffers are read in whole 16-byte lines: up to 15 bytes before the
+ *     first and after the last byte of `w`, inside the same 16-byte line, may be
+ *     read (never written).  Any pointer inside a cudaMalloc allocation satisfies
+ *     this.
+ *
+ * Block formats (little endian; "fp16" = IEEE binary16)
+ *   Q8_0   32 elems, 34 B: fp16 d; int8 q[32]                     w = d*q
+ *   Q8_1   32 elems, 36 B: fp16 d; fp16 s; int8 q[32]             x = d*q, s = d*sum(q)
+ *   Q4_K  256 elems,144 B: fp16 d; fp16 dmin; u8 scales[12]; u8 qs[128]
+ *                                                                 w = (d*sc_j)*q - (dmin*m_j)
+ *   Q6_K  256 elems,210 B: u8 ql[128]; u8 qh[64]; int8 scales[16]; fp16 d
+ *                                                                 w = (d*scale_g)*(q-32)
+ */
+#ifndef QMM_H
+#define QMM_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* type tags (GGUF numbering) */
+#define QMM_TYPE_Q8_0 8
+#define QMM_TYPE_Q8_1 9
+#define QMM_TYPE_Q4_K 12
+#define QMM_TYPE_Q6_K 14
+
+/* status codes returned by the launchers */
+#define QMM_OK 0
+#define QMM_ERR_NULL (-1)        /* a required pointer is NULL                         */
+#define QMM_ERR_SHAPE (-2)       /* m, n or k is not positive, or k is not a whole number of blocks */
+#define QMM_ERR_UNSUPPORTED (-3) /* shape outside what the kernel can stage (see each entry point)  */
+#define QMM_ERR_ALIGN (-4)       /* a pointer is not aligned as documented             */
+#define QMM_ERR_TYPE (-5)        /* unknown type tag                                   */
+#define QMM_ERR_CUDA (-6)        /* the CUDA runtime refused the launch (see qmm_last_cuda_error) */
+#define QMM_ERR_SCRATCH (-7)     /* request exceeds a fixed scratch capacity           */
+
+const char* qmm_status_string(int status);
+/* cudaError_t of the most recent failed runtime call made by this library on this thread */
+int qmm_last_cuda_error(void);
+/* Reads and clears the device-side status word of the current device (synchronises
+ * the device).  0 = no kernel gave up on a bounded wait since the last call. */
+int qmm_device_status(int* host_status);
+/* bytes of one packed row of k elements, or a negative status */
+long qmm_row_bytes(int type, long k);
+/* Programmatic dependent launch: when on (default), the matvec kernels are
+ * launched so that they may begin streaming weights while the preceding kernel
+ * in the stream drains; they still wait for it to complete before touching
+ * activations or outputs.  Returns the previous setting. */
+int qmm_set_overlap(int on);
+
+/* ---- activations -> Q8_1.  No upstream counterpart (its quantizers are affine
+ * per-tensor: gpu-core/src/kernels/quantizedx.hip:12-33); rounding follows its
+ * half-away-from-zero rule (quantizedx.hip:8).  x (m,k) f32 -> xq m*(k/32)*36 bytes. */
+int launch_quantize_q8_1(const float* x, void* xq, int m, int k, void* stream);
+
+/* ---- weights f32 -> packed blocks (deterministic min/max quantizers; used to
+ * build synthetic models on the device).  No upstream counterpart. */
+int launch_quantize_q8_0(const float* w, void* out, long rows, int k, void* stream);
+int launch_quantize_q4_k(const float* w, void* out, long rows, int k, void* stream);
+int launch_quantize_q6_k(const float* w, void* out, long rows, int k, void* stream);
+
+/* ---- weight decode.  Replaces launch_widen_bf16_f64 (gpu-core/src/kernels/
+ * f64_infer.hip:12-23; Rust gpu_widen_bf16_into, gpu-core/src/infer_ops.rs:85-101):
+ * n_elems packed elements -> n_elems decoded values.  n_elems must be a whole
+ * number of blocks.  `_bf16` stores the round-to-nearest-even bf16 of the f32 value. */
+int launch_dequantize_q8_0_f32(const void* w, float* out, long n_elems, void* stream);
+int launch_dequantize_q4_k_f32(const void* w, float* out, long n_elems, void* stream);
+int launch_dequantize_q6_k_f32(const void* w, float* out, long n_elems, void* stream);
+int launch_dequantize_q8_0_bf16(const void* w, void* out, long n_elems, void* stream);
+int launch_dequantize_q4_k_bf16(const void* w, void* out, long n_elems, void* stream);
+int launch_dequantize_q6_k_bf16(const void* w, void* out, long n_elems, void* stream);
+
+/* ---- fused dequant-matvec for decode.  Replaces the pair launch_widen_bf16_f64 +
+ * launch_gemm_bt_f64 (gpu-core/src/kernels/gemm_f64.hip:14-54; Rust
+ * gpu_gemm_bt_f64_into, gpu-core/src/infer_ops.rs:224-240):
+ *   y(m,n) = xq(m,k) . w(n,k)^T,  xq = Q8_1 blocks from launch_quantize_q8_1.
+ * m >= 1 (small batches; weights are streamed once per 4 activation rows).
+ * k: whole blocks, at most 131072, and one packed row must fit a 48 KiB stage
+ * (QMM_ERR_UNSUPPORTED otherwise).  Bit-identical across reruns (no atomics). */
+int launch_qmatvec_q8_0(const void* w, const void* xq, float* y, int m, int n, int k, void* stream);
+int launch_qmatvec_q4_k(const void* w, const void* xq, float* y, int m, int n, int k, void* stream);
+int launch_qmatvec_q6_k(const void* w, const void* xq, float* y, int m, int n, int k, void* stream);
+int launch_qmatvec(int type, const void* w, const void* xq, float* y, int m, int n, int k, void* stream);
+
+/* ---- per-block integer dot sums (parity instrumentation; same device code as
+ * the matvec).  One Q8_1 row xq (k); out int32 (n, k/32) for Q8_0 and Q4_K,
+ * (n, k/16) for Q6_K. */
+int launch_qblock_dots(int type, const void* w, const void* xq, int32_t* out, int n, int k, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,68 @@
+"""ctypes binding of the C ABI in include/qmm.h.  There is no fallback: if
+``libqmm.so`` is missing the import of any operator raises."""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libqmm.so")
+
+Q8_0, Q8_1, Q4_K, Q6_K = 8, 9, 12, 14
+BLOCK_ELEMS = {Q8_0: 32, Q8_1: 32, Q4_K: 256, Q6_K: 256}
+BLOCK_BYTES = {Q8_0: 34, Q8_1: 36, Q4_K: 144, Q6_K: 210}
+TYPE_NAMES = {Q8_0: "q8_0", Q8_1: "q8_1", Q4_K: "q4_k", Q6_K: "q6_k"}
+
+vp, i32, i64 = C.c_void_p, C.c_int, C.c_long
+
+# name -> (restype, argtypes); must list every symbol include/qmm.h declares
+SIGNATURES = {
+    "qmm_status_string": (C.c_char_p, [i32]),
+    "qmm_last_cuda_error": (i32, []),
+    "qmm_device_status": (i32, [C.POINTER(i32)]),
+    "qmm_row_bytes": (i64, [i32, i64]),
+    "qmm_set_overlap": (i32, [i32]),
+    "launch_quantize_q8_1": (i32, [vp, vp, i32, i32, vp]),
+    "launch_quantize_q8_0": (i32, [vp, vp, i64, i32, vp]),
+    "launch_quantize_q4_k": (i32, [vp, vp, i64, i32, vp]),
+    "launch_quantize_q6_k": (i32, [vp, vp, i64, i32, vp]),
+    "launch_dequantize_q8_0_f32": (i32, [vp, vp, i64, vp]),
+    "launch_dequantize_q4_k_f32": (i32, [vp, vp, i64, vp]),
+    "launch_dequantize_q6_k_f32": (i32, [vp, vp, i64, vp]),
+    "launch_dequantize_q8_0_bf16": (i32, [vp, vp, i64, vp]),
+    "launch_dequantize_q4_k_bf16": (i32, [vp, vp, i64, vp]),
+    "launch_dequantize_q6_k_bf16": (i32, [vp, vp, i64, vp]),
+    "launch_qmatvec_q8_0": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "launch_qmatvec_q4_k": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "launch_qmatvec_q6_k": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "launch_qmatvec": (i32, [i32, vp, vp, vp, i32, i32, i32, vp]),
+    "launch_qblock_dots": (i32, [i32, vp, vp, vp, i32, i32, vp]),
+}
+
+_lib = None
+
+
+class QmmError(RuntimeError):
+    def __init__(self, status, what):
+        msg = lib().qmm_status_string(status).decode()
+        extra = f" (cudaError {lib().qmm_last_cuda_error()})" if status == -6 else ""
+        super().__init__(f"{what}: {msg}{extra} [status {status}]")
+        self.status = status
+
+
+def lib():
+    """The loaded library.  Raises if it has not been built (python -m nates_recipe_rs_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m nates_recipe_rs_b200.build` "
+                               "(there is no CPU or PyTorch fallback)")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def check(status, what):
+    if status != 0:
+        raise QmmError(status, what)

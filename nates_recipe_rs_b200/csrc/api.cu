@@ -1,0 +1,117 @@
+// extern "C" surface of libqmm (declared in include/qmm.h) and the few pieces of
+// host state shared by the launchers.
+#include "qmm_common.cuh"
+
+namespace qmm {
+
+static thread_local int t_last_cuda_error = 0;
+void set_last_cuda_error(cudaError_t e) { t_last_cuda_error = (int)e; }
+
+int sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        cached[dev] = v;
+    }
+    return cached[dev];
+}
+
+static int g_overlap = 1;
+bool overlap_enabled() { return g_overlap != 0; }
+
+int qmatvec_launch(int type, const void* w, const void* xq, float* y, int m, int n, int k, cudaStream_t stream);
+int qblock_dots_launch(int type, const void* w, const void* xq, int32_t* out, int n, int k, cudaStream_t stream);
+int quantize_q8_1_launch(const float* x, void* xq, int m, int k, cudaStream_t stream);
+int quantize_weights_launch(int type, const float* w, void* out, long rows, int k, cudaStream_t stream);
+int dequantize_f32_launch(int type, const void* w, float* out, long n_elems, cudaStream_t stream);
+int dequantize_bf16_launch(int type, const void* w, void* out, long n_elems, cudaStream_t stream);
+
+}  // namespace qmm
+
+using namespace qmm;
+
+extern "C" {
+
+const char* qmm_status_string(int status) {
+    switch (status) {
+    case QMM_OK: return "ok";
+    case QMM_ERR_NULL: return "null pointer";
+    case QMM_ERR_SHAPE: return "bad shape (non-positive size, or k not a whole number of blocks)";
+    case QMM_ERR_UNSUPPORTED: return "shape not supported by this kernel";
+    case QMM_ERR_ALIGN: return "pointer not aligned as documented";
+    case QMM_ERR_TYPE: return "unknown block type";
+    case QMM_ERR_CUDA: return "CUDA runtime error (see qmm_last_cuda_error)";
+    case QMM_ERR_SCRATCH: return "request exceeds the fixed scratch capacity";
+    }
+    return "unknown status";
+}
+
+int qmm_last_cuda_error(void) { return t_last_cuda_error; }
+
+int qmm_device_status(int* host_status) {
+    if (!host_status) return QMM_ERR_NULL;
+    QMM_CUDA_TRY(cudaDeviceSynchronize());
+    int v = 0;
+    QMM_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)));
+    if (v != 0) {
+        const int zero = 0;
+        QMM_CUDA_TRY(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
+    }
+    *host_status = v;
+    return QMM_OK;
+}
+
+long qmm_row_bytes(int type, long k) {
+    int be, bb;
+    switch (type) {
+    case QMM_TYPE_Q8_0: be = 32, bb = Q8_0_BYTES; break;
+    case QMM_TYPE_Q8_1: be = 32, bb = Q8_1_BYTES; break;
+    case QMM_TYPE_Q4_K: be = 256, bb = Q4_K_BYTES; break;
+    case QMM_TYPE_Q6_K: be = 256, bb = Q6_K_BYTES; break;
+    default: return QMM_ERR_TYPE;
+    }
+    if (k <= 0 || k % be != 0) return QMM_ERR_SHAPE;
+    return k / be * bb;
+}
+
+int qmm_set_overlap(int on) {
+    const int prev = g_overlap;
+    g_overlap = on ? 1 : 0;
+    return prev;
+}
+
+int launch_quantize_q8_1(const float* x, void* xq, int m, int k, void* stream) {
+    return quantize_q8_1_launch(x, xq, m, k, as_stream(stream));
+}
+int launch_quantize_q8_0(const float* w, void* out, long rows, int k, void* stream) {
+    return quantize_weights_launch(QMM_TYPE_Q8_0, w, out, rows, k, as_stream(stream));
+}
+int launch_quantize_q4_k(const float* w, void* out, long rows, int k, void* stream) {
+    return quantize_weights_launch(QMM_TYPE_Q4_K, w, out, rows, k, as_stream(stream));
+}
+int launch_quantize_q6_k(const float* w, void* out, long rows, int k, void* stream) {
+    return quantize_weights_launch(QMM_TYPE_Q6_K, w, out, rows, k, as_stream(stream));
+}
+
+int launch_dequantize_q8_0_f32(const void* w, float* out, long n, void* s) { return dequantize_f32_launch(QMM_TYPE_Q8_0, w, out, n, as_stream(s)); }
+int launch_dequantize_q4_k_f32(const void* w, float* out, long n, void* s) { return dequantize_f32_launch(QMM_TYPE_Q4_K, w, out, n, as_stream(s)); }
+int launch_dequantize_q6_k_f32(const void* w, float* out, long n, void* s) { return dequantize_f32_launch(QMM_TYPE_Q6_K, w, out, n, as_stream(s)); }
+int launch_dequantize_q8_0_bf16(const void* w, void* out, long n, void* s) { return dequantize_bf16_launch(QMM_TYPE_Q8_0, w, out, n, as_stream(s)); }
+int launch_dequantize_q4_k_bf16(const void* w, void* out, long n, void* s) { return dequantize_bf16_launch(QMM_TYPE_Q4_K, w, out, n, as_stream(s)); }
+int launch_dequantize_q6_k_bf16(const void* w, void* out, long n, void* s) { return dequantize_bf16_launch(QMM_TYPE_Q6_K, w, out, n, as_stream(s)); }
+
+int launch_qmatvec(int type, const void* w, const void* xq, float* y, int m, int n, int k, void* stream) {
+    return qmatvec_launch(type, w, xq, y, m, n, k, as_stream(stream));
+}
+int launch_qmatvec_q8_0(const void* w, const void* xq, float* y, int m, int n, int k, void* s) { return qmatvec_launch(QMM_TYPE_Q8_0, w, xq, y, m, n, k, as_stream(s)); }
+int launch_qmatvec_q4_k(const void* w, const void* xq, float* y, int m, int n, int k, void* s) { return qmatvec_launch(QMM_TYPE_Q4_K, w, xq, y, m, n, k, as_stream(s)); }
+int launch_qmatvec_q6_k(const void* w, const void* xq, float* y, int m, int n, int k, void* s) { return qmatvec_launch(QMM_TYPE_Q6_K, w, xq, y, m, n, k, as_stream(s)); }
+
+int launch_qblock_dots(int type, const void* w, const void* xq, int32_t* out, int n, int k, void* stream) {
+    return qblock_dots_launch(type, w, xq, out, n, k, as_stream(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,5 @@
+// Single translation unit of libqmm: the kernels share one device status word
+// and are compiled without relocatable device code.
+#include "api.cu"
+#include "quantize.cu"
+#include "qmatvec.cu"

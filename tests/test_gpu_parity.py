@@ -1,0 +1,233 @@
+"""CUDA kernels against the CPU oracle, through the C ABI.  Needs a B200.
+
+Bars: bit-exact for packed codes, dequantised values and per-block integer sums;
+fp32 matvec outputs within 1e-3 relative / 1e-4 absolute."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL, ABS_TOL = 1e-3, 1e-4
+TYPES = [oracle.Q8_0, oracle.Q4_K, oracle.Q6_K]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device")
+    from nates_recipe_rs_b200 import quant_ops
+    return quant_ops
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def assert_close(got, want, what=""):
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    bound = ABS_TOL + REL_TOL * np.abs(want.astype(np.float64))
+    bad = err > bound
+    assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} outside tolerance, max err {err.max():.3e}"
+
+
+def seeded_weights(qtype, n, k, seed):
+    return oracle.quantize(qtype, oracle.fill_normal(n * k, seed, 0.02).reshape(n, k))
+
+
+def random_byte_weights(qtype, n, k, seed):
+    """Raw random bytes with finite fp16 scales: reaches every code and scale pattern."""
+    rng = np.random.default_rng(seed)
+    bb = oracle.BLOCK_BYTES[qtype]
+    w = rng.integers(0, 256, (n * k // oracle.BLOCK_ELEMS[qtype], bb), dtype=np.uint8)
+    scale = (rng.normal(size=w.shape[0]) * 0.01).astype(np.float16).view(np.uint8).reshape(-1, 2)
+    if qtype == oracle.Q8_0:
+        w[:, 0:2] = scale
+    elif qtype == oracle.Q4_K:
+        w[:, 0:2] = scale
+        w[:, 2:4] = (rng.normal(size=w.shape[0]) * 0.01).astype(np.float16).view(np.uint8).reshape(-1, 2)
+    else:
+        w[:, 208:210] = scale
+    return w.reshape(n, -1)
+
+
+# ------------------------------------------------------------------ golden fixtures
+def test_golden_blocks_dequantize_bit_exact(ops, golden):
+    for case in golden["blocks"]:
+        t = case["type"]
+        blk = np.frombuffer(bytes.fromhex(case["bytes"]), dtype=np.uint8)
+        want = np.frombuffer(bytes.fromhex(case["f32_bits"]), dtype=np.uint32)
+        pad = np.zeros(256, dtype=np.uint8)          # the library reads whole 16-byte lines
+        buf = dev(np.concatenate([blk, pad]))
+        got = ops.gpu_dequantize(t, buf, oracle.BLOCK_ELEMS[t]).cpu().numpy().view(np.uint32)
+        assert np.array_equal(got, want), case["name"]
+        got16 = ops.gpu_dequantize(t, buf, oracle.BLOCK_ELEMS[t], torch.bfloat16).view(torch.int16).cpu().numpy().view(np.uint16)
+        assert np.array_equal(got16, oracle.f32_to_bf16_bits(want.view(np.float32))), case["name"]
+
+
+def test_golden_q8_1_quantizer(ops, golden):
+    for case in golden["q8_1"]:
+        x = np.frombuffer(bytes.fromhex(case["x_bits"]), dtype=np.uint32).view(np.float32)
+        got = ops.gpu_quantize_q8_1(dev(x)).cpu().numpy()
+        assert np.array_equal(got, np.frombuffer(bytes.fromhex(case["bytes"]), dtype=np.uint8)), case["name"]
+
+
+def test_golden_block_dots(ops, golden):
+    for case in golden["dots"]:
+        t, k = case["type"], case["k"]
+        w = np.frombuffer(bytes.fromhex(case["w"]), dtype=np.uint8)
+        xq = np.frombuffer(bytes.fromhex(case["xq"]), dtype=np.uint8)
+        n = w.size // oracle.row_bytes(t, k)
+        got = ops.gpu_qblock_dots(t, dev(w), dev(xq), n, k).cpu().numpy()
+        assert np.array_equal(got.reshape(-1), np.frombuffer(bytes.fromhex(case["sums"]), dtype=np.int32))
+
+
+# ------------------------------------------------------------------ quantizers
+@pytest.mark.parametrize("m,k", [(1, 32), (1, 4096), (3, 14336), (16, 4096)])
+def test_quantize_q8_1_bit_exact(ops, m, k):
+    x = oracle.fill_normal(m * k, 17 + m, 1.0).reshape(m, k)
+    x[0, :32] = 0.0  # an all-zero block
+    got = ops.gpu_quantize_q8_1(dev(x)).cpu().numpy()
+    assert np.array_equal(got, oracle.quantize(oracle.Q8_1, x).reshape(-1))
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+def test_weight_quantizers_bit_exact(ops, qtype):
+    n, k = 37, 2048
+    x = oracle.fill_normal(n * k, 0x5EED + qtype, 0.02).reshape(n, k)
+    x[3] = 0.0
+    x[5, :256] = np.abs(x[5, :256])      # a super-block with no negative value
+    x[6, :256] = -np.abs(x[6, :256])     # and one with no positive value
+    got = ops.gpu_quantize_weights(qtype, dev(x)).cpu().numpy()
+    assert np.array_equal(got, oracle.quantize(qtype, x).reshape(-1))
+
+
+# ------------------------------------------------------------------ dequantize
+@pytest.mark.parametrize("qtype", TYPES)
+@pytest.mark.parametrize("maker", [seeded_weights, random_byte_weights])
+def test_dequantize_bit_exact(ops, qtype, maker):
+    n, k = 64, 1024
+    w = maker(qtype, n, k, 123)
+    got = ops.gpu_dequantize(qtype, dev(w), n * k).cpu().numpy().view(np.uint32)
+    want = oracle.dequantize(qtype, w, k).reshape(-1).view(np.uint32)
+    assert np.array_equal(got, want)
+    got16 = ops.gpu_dequantize(qtype, dev(w), n * k, torch.bfloat16).view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got16, oracle.dequantize_bf16(qtype, w, k).reshape(-1))
+
+
+# ------------------------------------------------------------------ integer block sums
+@pytest.mark.parametrize("qtype", TYPES)
+@pytest.mark.parametrize("maker", [seeded_weights, random_byte_weights])
+def test_block_dots_bit_exact(ops, qtype, maker):
+    n, k = 48, 2048
+    w = maker(qtype, n, k, 7)
+    xq = oracle.quantize(oracle.Q8_1, oracle.fill_normal(k, 8, 1.0)).reshape(-1)
+    got = ops.gpu_qblock_dots(qtype, dev(w), dev(xq), n, k).cpu().numpy()
+    assert np.array_equal(got, oracle.block_dots(qtype, w, xq, k))
+
+
+# ------------------------------------------------------------------ matvec
+SHAPES = [
+    # (m, n, k)
+    (1, 1, 256), (1, 7, 256), (1, 33, 512), (1, 300, 1024), (2, 129, 2048), (3, 64, 4096),
+    (1, 1000, 4096), (4, 515, 4096), (1, 257, 14336), (5, 96, 8192), (1, 40, 28672), (9, 200, 1792),
+]
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_matvec_matches_oracle(ops, qtype, m, n, k):
+    w = seeded_weights(qtype, n, k, 1000 + n)
+    xq = oracle.quantize(oracle.Q8_1, oracle.fill_normal(m * k, 2000 + k, 1.0).reshape(m, k))
+    y = torch.full((m, n), float("nan"), device="cuda")
+    ops.gpu_qmatvec_into(qtype, dev(w), dev(xq), y, m, n, k)
+    ops.check_launch()
+    assert_close(y.cpu().numpy(), oracle.matvec(qtype, w, xq, k), f"{oracle.TYPE_NAMES[qtype]} {m}x{n}x{k}")
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+def test_matvec_random_byte_weights(ops, qtype):
+    m, n, k = 2, 77, 2048
+    w = random_byte_weights(qtype, n, k, 5)
+    xq = oracle.quantize(oracle.Q8_1, oracle.fill_normal(m * k, 6, 1.0).reshape(m, k))
+    y = ops.gpu_qmatvec(qtype, dev(w), dev(xq), m, n, k)
+    want = oracle.matvec(qtype, w, xq, k)
+    # terms cancel in these rows, so the bound is relative to the magnitude of the terms
+    wf = np.abs(oracle.dequantize(qtype, w, k)).astype(np.float64)
+    xf = np.abs(oracle.dequantize(oracle.Q8_1, xq, k)).astype(np.float64)
+    bound = ABS_TOL + REL_TOL * (xf @ wf.T)
+    assert (np.abs(y.cpu().numpy() - want) <= bound).all()
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+def test_matvec_unaligned_row_views(ops, qtype):
+    """Rows taken from the middle of a matrix: for Q6_K / Q8_0 the view starts on a
+    2-byte boundary only; the padding bytes around the output stay untouched."""
+    n, k, skip = 40, 1792 if qtype != oracle.Q8_0 else 1056, 3
+    w = seeded_weights(qtype, n + skip, k, 9)
+    xq = oracle.quantize(oracle.Q8_1, oracle.fill_normal(k, 10, 1.0))
+    wd = dev(w).reshape(-1)
+    rb = oracle.row_bytes(qtype, k)
+    view = wd[skip * rb:]
+    ybuf = torch.full((n + 64,), 12345.0, device="cuda")
+    from nates_recipe_rs_b200._lib import check, lib
+    check(lib().launch_qmatvec(qtype, view.data_ptr(), dev(xq).data_ptr(), ybuf[32:].data_ptr(), 1, n, k,
+                               torch.cuda.current_stream().cuda_stream), "launch_qmatvec")
+    ops.check_launch()
+    out = ybuf.cpu().numpy()
+    assert (out[:32] == 12345.0).all() and (out[32 + n:] == 12345.0).all()
+    assert_close(out[32:32 + n][None], oracle.matvec(qtype, w[skip:], xq, k))
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+def test_matvec_twice_bit_identical(ops, qtype):
+    """Rerun determinism, as examples/det_probe.rs:125-134 checks for the upstream's GEMM."""
+    m, n, k = 2, 4096, 4096
+    w = dev(seeded_weights(qtype, n, k, 3))
+    xq = dev(oracle.quantize(oracle.Q8_1, oracle.fill_normal(m * k, 4, 1.0).reshape(m, k)))
+    a = ops.gpu_qmatvec(qtype, w, xq, m, n, k)
+    b = ops.gpu_qmatvec(qtype, w, xq, m, n, k)
+    assert torch.equal(a.view(torch.int32), b.view(torch.int32))
+
+
+def test_config1_q8_0_4096(ops):
+    """BASELINE config 1: Q8_0 4096x4096, batch 1, x ~ N(0,1), w ~ N(0,0.02)."""
+    n = k = 4096
+    w = seeded_weights(oracle.Q8_0, n, k, 0x5EED)
+    x = oracle.fill_normal(k, 0x5EED + 1, 1.0)
+    xq = ops.gpu_quantize_q8_1(dev(x))
+    assert np.array_equal(xq.cpu().numpy(), oracle.quantize(oracle.Q8_1, x).reshape(-1))
+    y = ops.gpu_qmatvec(oracle.Q8_0, dev(w), xq, 1, n, k)
+    assert_close(y.cpu().numpy(), oracle.matvec(oracle.Q8_0, w, xq.cpu().numpy(), k))
+
+
+@pytest.mark.parametrize("qtype,n,k", [(oracle.Q4_K, 14336, 4096), (oracle.Q4_K, 4096, 14336), (oracle.Q6_K, 4096, 14336)])
+def test_config2_full_size(ops, qtype, n, k):
+    """BASELINE config 2 at full size: weights quantised on the device, checked against the
+    oracle on a sample of rows and through linearity: W.(x1) + W.(x2) vs rows of a 2-row batch."""
+    wf = torch.from_numpy(oracle.fill_normal(n * k, 0x5EED + n, 0.02).reshape(n, k)).cuda()
+    w = ops.gpu_quantize_weights(qtype, wf)
+    x = oracle.fill_normal(2 * k, 77, 1.0).reshape(2, k)
+    xq = ops.gpu_quantize_q8_1(dev(x))
+    y2 = ops.gpu_qmatvec(qtype, w, xq, 2, n, k)
+    rb = oracle.row_bytes(oracle.Q8_1, k)
+    y_a = ops.gpu_qmatvec(qtype, w, xq[:rb], 1, n, k)
+    y_b = ops.gpu_qmatvec(qtype, w, xq[rb:], 1, n, k)
+    ops.check_launch()
+    assert torch.equal(y2[0], y_a[0]) and torch.equal(y2[1], y_b[0])     # batch rows are independent
+    rows = np.r_[0:64, n // 2:n // 2 + 64, n - 64:n]
+    wrows = w.reshape(n, -1)[torch.from_numpy(rows).cuda()].cpu().numpy()
+    assert_close(y2.cpu().numpy()[:, rows], oracle.matvec(qtype, wrows, xq.cpu().numpy(), k))
+
+
+def test_bad_arguments_are_rejected_not_launched(ops):
+    w = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    y = torch.zeros(16, device="cuda")
+    from nates_recipe_rs_b200._lib import QmmError
+    with pytest.raises(QmmError):
+        ops.gpu_qmatvec_into(oracle.Q4_K, w, w, y, 1, 1, 100)
+    with pytest.raises(ValueError):
+        ops.gpu_qmatvec_into(oracle.Q4_K, w[:100], w, y, 1, 1, 256)
+    ops.check_launch()
