@@ -71,6 +71,11 @@ long qmm_row_bytes(int type, long k);
  * activations or outputs.  Returns the previous setting. */
 int qmm_set_overlap(int on);
 
+/* Tuning hook for the matvec launcher (benchmark sweeps; the defaults are the tuned
+ * values): "stage_bytes" (1024..49152), "ring_bytes" (8192..194560),
+ * "consumer_warps" (1..24).  Not thread-safe against concurrent launches. */
+int qmm_tune(const char* key, int value);
+
 /* ---- activations -> Q8_1.  No upstream counterpart (its quantizers are affine
  * per-tensor: gpu-core/src/kernels/quantizedx.hip:12-33); rounding follows its
  * half-away-from-zero rule (quantizedx.hip:8).  x (m,k) f32 -> xq m*(k/32)*36 bytes. */

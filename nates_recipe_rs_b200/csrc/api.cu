@@ -28,6 +28,7 @@ int quantize_q8_1_launch(const float* x, void* xq, int m, int k, cudaStream_t st
 int quantize_weights_launch(int type, const float* w, void* out, long rows, int k, cudaStream_t stream);
 int dequantize_f32_launch(int type, const void* w, float* out, long n_elems, cudaStream_t stream);
 int dequantize_bf16_launch(int type, const void* w, void* out, long n_elems, cudaStream_t stream);
+int matvec_tune(const char* key, int value);
 
 }  // namespace qmm
 
@@ -82,6 +83,8 @@ int qmm_set_overlap(int on) {
     g_overlap = on ? 1 : 0;
     return prev;
 }
+
+int qmm_tune(const char* key, int value) { return matvec_tune(key, value); }
 
 int launch_quantize_q8_1(const float* x, void* xq, int m, int k, void* stream) {
     return quantize_q8_1_launch(x, xq, m, k, as_stream(stream));

@@ -23,6 +23,7 @@
 //     while this one drains; only activations and outputs wait for the
 //     predecessor.
 #include "qmm_formats.cuh"
+#include <string>
 
 namespace qmm {
 
@@ -30,22 +31,24 @@ struct MatvecParams {
     const uint8_t* w;
     const uint8_t* xq;
     float* y;
-    int m;           // activation rows in this launch (<= M of the instantiation)
+    int m;            // activation rows in this launch (<= M of the instantiation)
     int n, k;
-    int row_bytes;   // packed bytes of one weight row
+    int row_bytes;    // packed bytes of one weight row
     int xq_row_bytes;
-    int units;       // k / UNIT_ELEMS
-    int kw;          // warps along K
-    int rg;          // row groups (warps along rows)
-    int rows_stage;  // rows per stage
-    int nst;         // stages in the ring
-    int slot_bytes;  // bytes per ring slot (128-aligned, >= rows_stage*row_bytes + 32)
-    int partial_off; // byte offset of the partial-sum area in dynamic shared memory
-    int ring_off;    // byte offset of the ring
+    int units;        // k / UNIT_ELEMS
+    int kw;           // warps along K
+    int rg;           // row groups (warps along rows)
+    int rows_stage;   // rows per stage, a multiple of rg * RB
+    int nst;          // stages in the ring
+    int slot_bytes;   // bytes per ring slot (128-aligned, >= rows_stage*row_bytes + 32)
+    int pstage;       // floats per partial-sum stage: rows_stage * kw * M
+    int partial_off;  // byte offset of the partial-sum area in dynamic shared memory
+    int ring_off;     // byte offset of the ring
+    int probe;        // 0 = normal; 1 = stream only: every wait and arrival happens, the arithmetic is skipped
 };
 
 constexpr int MAX_STAGES = 8;
-constexpr int MAX_CONSUMER_WARPS = 16;
+constexpr int MAX_CONSUMER_WARPS = 24;
 
 struct __align__(16) MatvecSmemHeader {
     uint64_t full[MAX_STAGES];
@@ -53,9 +56,34 @@ struct __align__(16) MatvecSmemHeader {
     int abort_flag;
 };
 
-template <int TYPE, int P, int M>
+// Sums V per-lane values across the warp at once: each round halves the number of
+// live values while doubling the lanes that share one, so V values cost
+// (V-1) + log2(32/V) shuffles instead of 5V.  On return v[0] of lane L holds the
+// warp total of value number L / (32/V).  The order of additions is fixed.
+template <int V>
+__device__ __forceinline__ void warp_multi_sum(float (&v)[V], int lane) {
+    int off = 16;
+#pragma unroll
+    for (int width = V; width > 1; width >>= 1, off >>= 1) {
+        const bool up = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < width / 2; ++i) {
+            const float send = up ? v[i] : v[i + width / 2];
+            const float keep = up ? v[i + width / 2] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+    }
+#pragma unroll
+    for (; off > 0; off >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+}
+
+// Partial sums live in shared memory as [stage % (2*nst)][row][kw][M]; the producer
+// warp adds the kw entries of a row in a fixed order.  Depth 2*nst because the
+// producer refills a ring slot before it folds the stage that just left it.
+template <int TYPE, int P, int M, int RB>
 __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kernel(const MatvecParams p) {
     using F = Fmt<TYPE>;
+    constexpr int V = M * RB;
     extern __shared__ __align__(128) uint8_t smem[];
     MatvecSmemHeader* hdr = reinterpret_cast<MatvecSmemHeader*>(smem);
     float* partial = reinterpret_cast<float*>(smem + p.partial_off);
@@ -70,6 +98,8 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
     const long row_end = (long)(blockIdx.x + 1) * p.n / gridDim.x;
     const int n_rows = (int)(row_end - row_begin);
     const int n_it = (n_rows + p.rows_stage - 1) / p.rows_stage;
+    const uintptr_t w_begin = reinterpret_cast<uintptr_t>(p.w) + (size_t)row_begin * p.row_bytes;
+    const uint32_t stage_bytes = (uint32_t)p.rows_stage * p.row_bytes;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.nst; ++s) {
@@ -86,9 +116,8 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
         // ------------------------------------------------------------ producer
         auto issue = [&](int it) {
             const int slot = it % p.nst;
-            const long r0 = row_begin + (long)it * p.rows_stage;
-            const int nr = min(p.rows_stage, (int)(row_end - r0));
-            const uintptr_t g = reinterpret_cast<uintptr_t>(p.w) + (size_t)r0 * p.row_bytes;
+            const int nr = min(p.rows_stage, n_rows - it * p.rows_stage);
+            const uintptr_t g = w_begin + (size_t)it * stage_bytes;
             const uint32_t head = (uint32_t)(g & 15);
             const uint32_t bytes = (head + (uint32_t)nr * p.row_bytes + 15u) & ~15u;
             const uint32_t bar = smem_u32(&hdr->full[slot]);
@@ -98,7 +127,6 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
         int issued = 0;
         if (lane == 0)
             for (; issued < n_it && issued < p.nst; ++issued) issue(issued);
-        issued = __shfl_sync(0xffffffffu, issued, 0);
         pdl_wait_prior_grids();  // y may still be read by the preceding kernel
         bool ok = true;
         for (int it = 0; it < n_it; ++it) {
@@ -111,28 +139,28 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
                 }
                 break;
             }
-            const long r0 = row_begin + (long)it * p.rows_stage;
-            const int nr = min(p.rows_stage, (int)(row_end - r0));
-            const float* ps = partial + (size_t)slot * p.rows_stage * p.kw * M;
-            for (int idx = lane; idx < nr * M; idx += 32) {
-                const int r = idx / M, mi = idx - r * M;
-                float acc = 0.f;
-                for (int q = 0; q < p.kw; ++q) acc += ps[(r * p.kw + q) * M + mi];
-                if (mi < p.m) p.y[(size_t)mi * p.n + r0 + r] = acc;
-            }
-            __syncwarp();
             if (lane == 0 && it + p.nst < n_it) {
                 issue(it + p.nst);
                 issued = it + p.nst + 1;
             }
+            const int nr = min(p.rows_stage, n_rows - it * p.rows_stage);
+            const float* ps = partial + (size_t)(it % (2 * p.nst)) * p.pstage;
+            float* yrow = p.y + row_begin + (long)it * p.rows_stage;
+            for (int idx = lane; idx < nr * M; idx += 32) {  // idx = r*M + mi
+                const int r = idx / M, mi = idx - r * M;
+                const float* src = ps + (size_t)r * p.kw * M + mi;
+                float acc = 0.f;
+                for (int q = 0; q < p.kw; ++q) acc += src[q * M];
+                if (mi < p.m) yrow[(size_t)mi * p.n + r] = acc;
+            }
         }
+        issued = __shfl_sync(0xffffffffu, issued, 0);
         if (!ok && lane == 0) {
             // wait (bounded) for copies still in flight before the CTA's shared memory is released
-            issued = max(issued, min(n_it, p.nst));
             for (int it = max(0, issued - p.nst); it < issued; ++it) {
-                const uint64_t t0 = globaltimer_ns();
+                const long long t0 = clock64();
                 while (!mbar_try_wait(smem_u32(&hdr->full[it % p.nst]), (it / p.nst) & 1)) {
-                    if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
                         atomicExch(&g_device_status, DEV_TIMEOUT_DRAIN);
                         break;
                     }
@@ -141,7 +169,6 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
         }
         return;
     }
-    if (warp > n_consumers) return;
 
     // ---------------------------------------------------------------- consumers
     const int kwi = warp % p.kw, rgi = warp / p.kw;
@@ -150,15 +177,25 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
     pdl_wait_prior_grids();  // activations come from the preceding kernel
 #pragma unroll
     for (int pp = 0; pp < P; ++pp) {
-        unit[pp] = (pp * p.kw + kwi) * 32 + lane;
+        const int u = (pp * p.kw + kwi) * 32 + lane;
+        // lanes past the end of the row re-read unit 0 against zero activations
+        unit[pp] = u < p.units ? u : 0;
 #pragma unroll
         for (int mi = 0; mi < M; ++mi) {
-            if (unit[pp] < p.units && mi < p.m)
-                F::load_x(p.xq + (size_t)mi * p.xq_row_bytes, unit[pp], x[mi][pp]);
+            if (u < p.units && mi < p.m)
+                F::load_x(p.xq + (size_t)mi * p.xq_row_bytes, u, x[mi][pp]);
             else
                 F::zero_x(x[mi][pp]);
         }
     }
+    // after warp_multi_sum lane L owns value number L / (32/V) = (row j of the batch, activation row mi)
+    constexpr int LANES_PER_VALUE = 32 / V;
+    const int my_val = lane / LANES_PER_VALUE, my_j = my_val / M, my_mi = my_val - my_j * M;
+    const bool writer = (lane % LANES_PER_VALUE) == 0;
+    const uint32_t row_step = (uint32_t)p.rg * p.row_bytes;
+    const int batch_rows = p.rg * RB;
+    const uint32_t w_begin_lo = (uint32_t)(w_begin & 15);
+    const uint32_t my_ps = ((uint32_t)(rgi + my_j * p.rg) * p.kw + kwi) * M + my_mi;
 
     for (int it = 0; it < n_it; ++it) {
         const int slot = it % p.nst;
@@ -169,30 +206,29 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
             }
             return;
         }
-        const long r0 = row_begin + (long)it * p.rows_stage;
-        const int nr = min(p.rows_stage, (int)(row_end - r0));
-        const uint32_t head = (uint32_t)((reinterpret_cast<uintptr_t>(p.w) + (size_t)r0 * p.row_bytes) & 15);
-        const uint8_t* base = ring + (size_t)slot * p.slot_bytes + head;
-        float* ps = partial + (size_t)slot * p.rows_stage * p.kw * M;
-        for (int r = rgi; r < nr; r += p.rg) {
-            const uint8_t* row = base + (size_t)r * p.row_bytes;
-            float acc[M];
+        const int nr = min(p.rows_stage, n_rows - it * p.rows_stage);
+        const uint32_t head = (w_begin_lo + (uint32_t)it * stage_bytes) & 15u;
+        const uint8_t* row0 = ring + (uint32_t)slot * p.slot_bytes + head + (uint32_t)rgi * p.row_bytes;
+        float* ps = partial + (uint32_t)(it % (2 * p.nst)) * p.pstage + my_ps;
+        // Whole batches only: rows past nr (last stage of the CTA) hold stale bytes of an
+        // earlier stage; their sums land in partial entries that nobody reads.
+        for (int rb = rgi; rb < nr && p.probe == 0; rb += batch_rows, row0 += row_step * RB, ps += batch_rows * p.kw * M) {
+            float acc[V];
 #pragma unroll
-            for (int mi = 0; mi < M; ++mi) acc[mi] = 0.f;
+            for (int v = 0; v < V; ++v) acc[v] = 0.f;
 #pragma unroll
-            for (int pp = 0; pp < P; ++pp) {
-                if (unit[pp] < p.units) {
+            for (int j = 0; j < RB; ++j) {
+                const uint8_t* row = row0 + j * row_step;
+#pragma unroll
+                for (int pp = 0; pp < P; ++pp) {
                     typename F::WRegs wr;
                     F::load_w(row, unit[pp], wr);
 #pragma unroll
-                    for (int mi = 0; mi < M; ++mi) acc[mi] += F::dot(wr, unit[pp], x[mi][pp], nullptr);
+                    for (int mi = 0; mi < M; ++mi) acc[j * M + mi] += F::dot(wr, unit[pp], x[mi][pp], nullptr);
                 }
             }
-#pragma unroll
-            for (int mi = 0; mi < M; ++mi) {
-                const float v = warp_sum(acc[mi]);
-                if (lane == 0) ps[(r * p.kw + kwi) * M + mi] = v;
-            }
+            warp_multi_sum<V>(acc, lane);
+            if (writer) *ps = acc[0];
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&hdr->empty[slot]));
@@ -210,13 +246,24 @@ static int type_geometry(int type, int& block_elems, int& block_bytes, int& unit
     return QMM_ERR_TYPE;
 }
 
-constexpr int STAGE_TARGET_BYTES = 18 * 1024;  // preferred bytes per stage
-constexpr int STAGE_MAX_BYTES = 48 * 1024;     // one packed row must fit this
-constexpr int RING_BUDGET_BYTES = 100 * 1024;  // ring size that still lets two CTAs share an SM
+constexpr int STAGE_MAX_BYTES = 48 * 1024;  // one packed row must fit this
+// tunables (qmm_tune): preferred bytes per stage, ring bytes per CTA, consumer warps per CTA
+static int g_stage_target = 36 * 1024;
+static int g_ring_budget = 150 * 1024;
+static int g_consumer_warps = 20;
+static int g_probe = 0;
+int matvec_tune(const char* key, int value) {
+    const std::string k(key ? key : "");
+    if (k == "stage_bytes" && value >= 1024 && value <= STAGE_MAX_BYTES) return g_stage_target = value, QMM_OK;
+    if (k == "ring_bytes" && value >= 8 * 1024 && value <= 190 * 1024) return g_ring_budget = value, QMM_OK;
+    if (k == "consumer_warps" && value >= 1 && value <= MAX_CONSUMER_WARPS) return g_consumer_warps = value, QMM_OK;
+    if (k == "probe" && value >= 0 && value <= 1) return g_probe = value, QMM_OK;
+    return QMM_ERR_UNSUPPORTED;
+}
 
-template <int TYPE, int P, int M>
+template <int TYPE, int P, int M, int RB>
 static int launch_inst(const MatvecParams& p, int grid, int threads, size_t smem, cudaStream_t stream) {
-    auto kern = qmatvec_kernel<TYPE, P, M>;
+    auto kern = qmatvec_kernel<TYPE, P, M, RB>;
     static size_t configured[64] = {};  // per instantiation and device; racing writers store the same facts
     int dev = 0;
     QMM_CUDA_TRY(cudaGetDevice(&dev));
@@ -238,21 +285,24 @@ static int launch_inst(const MatvecParams& p, int grid, int threads, size_t smem
     return QMM_OK;
 }
 
+// (activation-row tile M, rows per batch RB) pairs that are instantiated
+static int rows_per_batch(int mtile, int level) { return mtile == 1 ? (level == 0 ? 4 : (level == 1 ? 2 : 1)) : (mtile == 2 ? 2 : 1); }
+
 template <int TYPE, int P>
-static int launch_m(const MatvecParams& p, int grid, int threads, size_t smem, int mtile, cudaStream_t stream) {
-    switch (mtile) {
-    case 1: return launch_inst<TYPE, P, 1>(p, grid, threads, smem, stream);
-    case 2: return launch_inst<TYPE, P, 2>(p, grid, threads, smem, stream);
-    default: return launch_inst<TYPE, P, 4>(p, grid, threads, smem, stream);
-    }
+static int launch_m(const MatvecParams& p, int grid, int threads, size_t smem, int mtile, int rb, cudaStream_t stream) {
+    if (mtile == 1 && rb == 4) return launch_inst<TYPE, P, 1, 4>(p, grid, threads, smem, stream);
+    if (mtile == 1 && rb == 2) return launch_inst<TYPE, P, 1, 2>(p, grid, threads, smem, stream);
+    if (mtile == 1) return launch_inst<TYPE, P, 1, 1>(p, grid, threads, smem, stream);
+    if (mtile == 2) return launch_inst<TYPE, P, 2, 2>(p, grid, threads, smem, stream);
+    return launch_inst<TYPE, P, 4, 1>(p, grid, threads, smem, stream);
 }
 
 template <int TYPE>
-static int launch_p(const MatvecParams& p, int passes, int grid, int threads, size_t smem, int mtile, cudaStream_t stream) {
+static int launch_p(const MatvecParams& p, int passes, int grid, int threads, size_t smem, int mtile, int rb, cudaStream_t stream) {
     switch (passes) {
-    case 1: return launch_m<TYPE, 1>(p, grid, threads, smem, mtile, stream);
-    case 2: return launch_m<TYPE, 2>(p, grid, threads, smem, mtile, stream);
-    default: return launch_m<TYPE, 4>(p, grid, threads, smem, mtile, stream);
+    case 1: return launch_m<TYPE, 1>(p, grid, threads, smem, mtile, rb, stream);
+    case 2: return launch_m<TYPE, 2>(p, grid, threads, smem, mtile, rb, stream);
+    default: return launch_m<TYPE, 4>(p, grid, threads, smem, mtile, rb, stream);
     }
 }
 
@@ -272,29 +322,20 @@ int qmatvec_launch(int type, const void* w, const void* xq, float* y, int m, int
     p.row_bytes = k / block_elems * block_bytes;
     p.xq_row_bytes = k / QK8 * Q8_1_BYTES;
     p.units = k / unit_elems;
+    p.probe = g_probe;
     if (p.row_bytes > STAGE_MAX_BYTES) return QMM_ERR_UNSUPPORTED;
 
     // K split: the fewest passes that keep the K axis within MAX_CONSUMER_WARPS warps
     int passes = 1;
-    while (passes <= 4 && (p.units + 32 * passes - 1) / (32 * passes) > MAX_CONSUMER_WARPS) passes *= 2;
+    const int nw = g_consumer_warps;
+    while (passes <= 4 && (p.units + 32 * passes - 1) / (32 * passes) > nw) passes *= 2;
     if (passes > 4) return QMM_ERR_UNSUPPORTED;
     p.kw = (p.units + 32 * passes - 1) / (32 * passes);
-    p.rg = MAX_CONSUMER_WARPS / p.kw;
+    p.rg = nw / p.kw;
     const int sms = sm_count();
-    // rows per stage: a multiple of the row groups, near the target size, never more than a CTA's share
     const int rows_per_cta = (n + sms - 1) / sms;
-    int per_group = STAGE_TARGET_BYTES / (p.rg * p.row_bytes);
-    if (per_group < 1) per_group = 1;
-    p.rows_stage = p.rg * per_group;
-    while (p.rows_stage > p.rg && p.rows_stage - p.rg >= rows_per_cta) p.rows_stage -= p.rg;
-    while (p.rows_stage > 1 && p.rows_stage * p.row_bytes > STAGE_MAX_BYTES) --p.rows_stage;
-    p.slot_bytes = (p.rows_stage * p.row_bytes + 32 + 127) & ~127;
-    p.nst = RING_BUDGET_BYTES / p.slot_bytes;
-    if (p.nst < 2) p.nst = 2;
-    if (p.nst > MAX_STAGES) p.nst = MAX_STAGES;
-    const int threads = (p.kw * p.rg + 1) * 32;
-    int grid = (n + p.rows_stage - 1) / p.rows_stage;
-    if (grid > sms) grid = sms;
+    p.partial_off = (int)((sizeof(MatvecSmemHeader) + 127) & ~size_t(127));
+    constexpr size_t SMEM_LIMIT = 200 * 1024;
 
     for (int m0 = 0; m0 < m; m0 += 4) {
         const int left = m - m0;
@@ -302,16 +343,44 @@ int qmatvec_launch(int type, const void* w, const void* xq, float* y, int m, int
         p.m = left < mt ? left : mt;
         p.xq = static_cast<const uint8_t*>(xq) + (size_t)m0 * p.xq_row_bytes;
         p.y = y + (size_t)m0 * n;
-        p.partial_off = (int)((sizeof(MatvecSmemHeader) + 127) & ~size_t(127));
-        const size_t partial_bytes = (size_t)p.nst * p.rows_stage * p.kw * mt * sizeof(float);
+        // rows per stage: whole batches of rg*RB rows, near the target size, no more than a CTA's share.
+        // Rows per batch per warp: the larger tile unless it overshoots the stage or the CTA's rows;
+        // row groups are halved until one batch fits a stage.
+        p.rg = nw / p.kw;
+        int rb = rows_per_batch(mt, 0);
+        for (int level = 1; level <= 2 && mt == 1; ++level)
+            if (p.rg * rb * p.row_bytes > STAGE_MAX_BYTES || p.rg * rb / 2 >= rows_per_cta) rb = rows_per_batch(mt, level);
+        while (p.rg > 1 && p.rg * rb * p.row_bytes > STAGE_MAX_BYTES) p.rg /= 2;
+        const int batch = p.rg * rb;
+        if (batch * p.row_bytes > STAGE_MAX_BYTES) return QMM_ERR_UNSUPPORTED;
+        int batches = g_stage_target / (batch * p.row_bytes);
+        if (batches < 1) batches = 1;
+        while (batches > 1 && (batches - 1) * batch >= rows_per_cta) --batches;
+        p.rows_stage = batch * batches;
+        p.slot_bytes = (p.rows_stage * p.row_bytes + 32 + 127) & ~127;
+        const int threads = (p.kw * p.rg + 1) * 32;
+        int grid = (n + p.rows_stage - 1) / p.rows_stage;
+        if (grid > sms) grid = sms;
+        p.pstage = p.rows_stage * p.kw * mt;
+        // stages: as many as the ring budget allows, fewer if the partial sums (two per stage) crowd them out
+        const size_t per_stage = (size_t)p.slot_bytes + 2 * (size_t)p.pstage * sizeof(float);
+        p.nst = g_ring_budget / p.slot_bytes;
+        const int fit = (int)((SMEM_LIMIT - p.partial_off - 256) / per_stage);
+        if (p.nst > fit) p.nst = fit;
+        if (p.nst > MAX_STAGES) p.nst = MAX_STAGES;
+        if (p.nst < 2) {
+            if (fit < 2) return QMM_ERR_UNSUPPORTED;
+            p.nst = 2;
+        }
+        const size_t partial_bytes = (size_t)2 * p.nst * p.pstage * sizeof(float);
         p.ring_off = (int)((p.partial_off + partial_bytes + 127) & ~size_t(127));
         const size_t smem = (size_t)p.ring_off + (size_t)p.nst * p.slot_bytes;
-        if (smem > 200 * 1024) return QMM_ERR_UNSUPPORTED;
+        if (smem > SMEM_LIMIT) return QMM_ERR_UNSUPPORTED;
         int st;
         switch (type) {
-        case QMM_TYPE_Q8_0: st = launch_p<QMM_TYPE_Q8_0>(p, passes, grid, threads, smem, mt, stream); break;
-        case QMM_TYPE_Q4_K: st = launch_p<QMM_TYPE_Q4_K>(p, passes, grid, threads, smem, mt, stream); break;
-        default: st = launch_p<QMM_TYPE_Q6_K>(p, passes, grid, threads, smem, mt, stream); break;
+        case QMM_TYPE_Q8_0: st = launch_p<QMM_TYPE_Q8_0>(p, passes, grid, threads, smem, mt, rb, stream); break;
+        case QMM_TYPE_Q4_K: st = launch_p<QMM_TYPE_Q4_K>(p, passes, grid, threads, smem, mt, rb, stream); break;
+        default: st = launch_p<QMM_TYPE_Q6_K>(p, passes, grid, threads, smem, mt, rb, stream); break;
         }
         if (st) return st;
     }

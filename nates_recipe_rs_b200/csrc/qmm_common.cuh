@@ -87,18 +87,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait: polls the barrier; gives up after ~2 s of wall clock (or at once
-// when another thread of the CTA has already given up), in which case the caller
-// records a status code and unwinds without touching the data.
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+// Bounded wait: polls the barrier; gives up after WAIT_LIMIT_CYCLES of the SM clock
+// (about 2 s at the boost clock, longer at lower clocks, never unbounded) or at once
+// when another thread of the CTA has already given up; the caller then records a
+// status code and unwinds without touching the data.  The SM cycle counter is used
+// because it is a plain register read; the global nanosecond timer is not.
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* cta_abort) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
+    const long long t0 = clock64();
     for (;;) {
-        for (int i = 0; i < 64; ++i)
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*cta_abort) return false;
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
     }
 }
 

@@ -20,6 +20,12 @@ __device__ __forceinline__ int dp4a_u8s8(uint32_t a, int b, int c) {
     return d;
 }
 
+// Exact int -> float without the conversion unit (which runs at a quarter of the
+// arithmetic rate): for |i| < 2^22, float(i) = as_float(0x4B400000 + i) - 1.5*2^23.
+__device__ __forceinline__ float small_int_to_float(int i) {
+    return __int_as_float(0x4B400000 + i) - 12582912.0f;
+}
+
 // four consecutive 32-bit words starting at a 2-byte aligned address
 __device__ __forceinline__ void ld_words4_align2(const uint8_t* p, uint32_t (&o)[4]) {
     const uintptr_t a = reinterpret_cast<uintptr_t>(p);
@@ -122,8 +128,10 @@ struct Fmt<QMM_TYPE_Q4_K> {
         uint32_t sc2, m2;
         scale_codes(wr.hdr, u & 3, sc2, m2);
         const float d = f16_bits_to_f32(wr.hdr.x & 0xFFFFu), dmin = f16_bits_to_f32(wr.hdr.x >> 16);
-        const float accd = x.xs[0] * (float)((int)(sc2 & 0xFFu) * sum0) + x.xs[1] * (float)((int)(sc2 >> 8) * sum1);
-        const float accm = x.xs[2] * (float)(m2 & 0xFFu) + x.xs[3] * (float)(m2 >> 8);
+        // |sc*sum| <= 63*32*15*127 < 2^22
+        const float accd = x.xs[0] * small_int_to_float((int)(sc2 & 0xFFu) * sum0) +
+                           x.xs[1] * small_int_to_float((int)(sc2 >> 8) * sum1);
+        const float accm = x.xs[2] * small_int_to_float((int)(m2 & 0xFFu)) + x.xs[3] * small_int_to_float((int)(m2 >> 8));
         return d * accd - dmin * accm;
     }
 };
@@ -192,10 +200,13 @@ struct Fmt<QMM_TYPE_Q6_K> {
         const int bsh = 8 * (u & 1);
         const int c0 = (int)(int8_t)(wr.sc[0] >> bsh), c1 = (int)(int8_t)(wr.sc[0] >> (16 + bsh));
         const int c2 = (int)(int8_t)(wr.sc[1] >> bsh), c3 = (int)(int8_t)(wr.sc[1] >> (16 + bsh));
-        float acc = x.xs[0] * (float)(c0 * s[0]);
-        acc += x.xs[1] * (float)(c1 * s[1]);
-        acc += x.xs[2] * (float)(c2 * s[2]);
-        acc += x.xs[3] * (float)(c3 * s[3]);
+        // |scale*sum| can reach 2^24, so the two factors are converted separately (each exact)
+        // and multiplied in float: the product of two exact integers below 2^24 in magnitude
+        // is rounded once, like the int->float conversion of the integer product would be.
+        float acc = x.xs[0] * (small_int_to_float(c0) * small_int_to_float(s[0]));
+        acc += x.xs[1] * (small_int_to_float(c1) * small_int_to_float(s[1]));
+        acc += x.xs[2] * (small_int_to_float(c2) * small_int_to_float(s[2]));
+        acc += x.xs[3] * (small_int_to_float(c3) * small_int_to_float(s[3]));
         return f16_bits_to_f32(wr.d) * acc;
     }
 };
@@ -237,7 +248,7 @@ struct Fmt<QMM_TYPE_Q8_0> {
         }
         const int sum = s0 + s1;
         if (sums) sums[0] = sum;
-        return (f16_bits_to_f32(wr.d) * x.xs[0]) * (float)sum;
+        return (f16_bits_to_f32(wr.d) * x.xs[0]) * small_int_to_float(sum);
     }
 };
 
