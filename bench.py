@@ -62,7 +62,7 @@ class ClockSampler:
         try:
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=self.out, stderr=subprocess.DEVNULL)
+                                          "-lms", "20"], stdout=self.out, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
@@ -119,7 +119,7 @@ def cpu_time_sample(budget_s=12.0):
         one()
         reps += 1
         dt = time.perf_counter() - t0
-        if dt > budget_s or reps >= 200:
+        if dt > budget_s or reps >= 5000:
             break
     return {"value": total * reps / dt / 1e9, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
             "sample": f"{reps} passes over one layer set (gate, up, down Q4_K, down Q6_K = {total} B) in {dt:.1f} s, "
@@ -246,10 +246,10 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     with torch.cuda.stream(stream):
+        sampler = ClockSampler(local) if rank == 0 else None  # spans warm-up, the timed steps and the two legs below
         for _ in range(max(args.warmup, 3)):
             run_step()
         barrier()
-        sampler = ClockSampler(local) if rank == 0 else None
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record(stream)
