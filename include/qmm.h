@@ -73,8 +73,13 @@ int qmm_set_overlap(int on);
 
 /* Tuning hook for the matvec launcher (benchmark sweeps; the defaults are the tuned
  * values): "stage_bytes" (1024..49152), "ring_bytes" (8192..194560),
- * "consumer_warps" (1..24).  Not thread-safe against concurrent launches. */
+ * "consumer_warps" (1..24), "q4k_unit" (0 = automatic, 1, 2, 4: 32-byte groups of a
+ * Q4_K super-block per lane), "rb_max" (1, 2, 4: rows reduced together per warp).  Not thread-safe against concurrent launches. */
 int qmm_tune(const char* key, int value);
+/* Tuning aid: while buf is non-NULL, matvec launch number i (counted from this call) stores four
+ * global-timer stamps per CTA (start, dependency released, first stage landed, end) as 64-bit
+ * words at buf + i*stride_words.  buf = NULL switches it off. */
+int qmm_trace(void* buf, int stride_words);
 
 /* ---- activations -> Q8_1.  No upstream counterpart (its quantizers are affine
  * per-tensor: gpu-core/src/kernels/quantizedx.hip:12-33); rounding follows its

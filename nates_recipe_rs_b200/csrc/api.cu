@@ -29,6 +29,7 @@ int quantize_weights_launch(int type, const float* w, void* out, long rows, int 
 int dequantize_f32_launch(int type, const void* w, float* out, long n_elems, cudaStream_t stream);
 int dequantize_bf16_launch(int type, const void* w, void* out, long n_elems, cudaStream_t stream);
 int matvec_tune(const char* key, int value);
+void matvec_set_trace(unsigned long long* buf, int stride_words);
 
 }  // namespace qmm
 
@@ -85,6 +86,7 @@ int qmm_set_overlap(int on) {
 }
 
 int qmm_tune(const char* key, int value) { return matvec_tune(key, value); }
+int qmm_trace(void* buf, int stride_words) { matvec_set_trace(static_cast<unsigned long long*>(buf), stride_words); return QMM_OK; }
 
 int launch_quantize_q8_1(const float* x, void* xq, int m, int k, void* stream) {
     return quantize_q8_1_launch(x, xq, m, k, as_stream(stream));

@@ -14,10 +14,12 @@
 //   * the activations never touch shared memory: the K axis is split over KW
 //     warps x 32 lanes x P passes, each lane keeps the Q8_1 words of its own
 //     slices in registers for the whole kernel and meets every row there;
-//   * each lane unpacks its slice of a row with a handful of logic ops and
-//     accumulates with dp4a; a row's KW partial sums are combined in a fixed
-//     order by the producer warp, which is idle between copies (no atomics:
-//     reruns are bit-identical, the upstream's determinism rule,
+//   * rows are dealt to the row-group warps in batches of RB consecutive rows,
+//     round-robin over the whole CTA range, so the stage size is independent of
+//     the warp count; the RB x M partial sums of a batch are reduced across the
+//     warp together (warp_multi_sum);
+//   * a row's KW partial sums are combined in a fixed order by the producer warp
+//     (no atomics: reruns are bit-identical, the upstream's determinism rule,
 //     gpu-core/src/kernels/gemm_f64.hip:12);
 //   * with programmatic dependent launch the next kernel's weight stream starts
 //     while this one drains; only activations and outputs wait for the
@@ -38,13 +40,14 @@ struct MatvecParams {
     int units;        // k / UNIT_ELEMS
     int kw;           // warps along K
     int rg;           // row groups (warps along rows)
-    int rows_stage;   // rows per stage, a multiple of rg * RB
+    int rows_stage;   // rows per stage, a multiple of RB
     int nst;          // stages in the ring
     int slot_bytes;   // bytes per ring slot (128-aligned, >= rows_stage*row_bytes + 32)
     int pstage;       // floats per partial-sum stage: rows_stage * kw * M
     int partial_off;  // byte offset of the partial-sum area in dynamic shared memory
     int ring_off;     // byte offset of the ring
     int probe;        // 0 = normal; 1 = stream only: every wait and arrival happens, the arithmetic is skipped
+    unsigned long long* trace;  // optional (tuning aid): 4 global-timer stamps per CTA
 };
 
 constexpr int MAX_STAGES = 8;
@@ -80,9 +83,9 @@ __device__ __forceinline__ void warp_multi_sum(float (&v)[V], int lane) {
 // Partial sums live in shared memory as [stage % (2*nst)][row][kw][M]; the producer
 // warp adds the kw entries of a row in a fixed order.  Depth 2*nst because the
 // producer refills a ring slot before it folds the stage that just left it.
-template <int TYPE, int P, int M, int RB>
+template <int TYPE, int UW, int P, int M, int RB>
 __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kernel(const MatvecParams p) {
-    using F = Fmt<TYPE>;
+    using F = Fmt<TYPE, UW>;
     constexpr int V = M * RB;
     extern __shared__ __align__(128) uint8_t smem[];
     MatvecSmemHeader* hdr = reinterpret_cast<MatvecSmemHeader*>(smem);
@@ -111,6 +114,7 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
     }
     __syncthreads();
     pdl_release_dependents();
+    if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 4 + 0] = globaltimer_ns();
 
     if (warp == n_consumers) {
         // ------------------------------------------------------------ producer
@@ -155,6 +159,7 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
             }
         }
         issued = __shfl_sync(0xffffffffu, issued, 0);
+        if (p.trace && lane == 0) p.trace[blockIdx.x * 4 + 3] = globaltimer_ns();
         if (!ok && lane == 0) {
             // wait (bounded) for copies still in flight before the CTA's shared memory is released
             for (int it = max(0, issued - p.nst); it < issued; ++it) {
@@ -172,9 +177,10 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
 
     // ---------------------------------------------------------------- consumers
     const int kwi = warp % p.kw, rgi = warp / p.kw;
-    XRegs x[M][P];
+    typename F::XRegs x[M][P];
     int unit[P];
     pdl_wait_prior_grids();  // activations come from the preceding kernel
+    if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 4 + 1] = globaltimer_ns();
 #pragma unroll
     for (int pp = 0; pp < P; ++pp) {
         const int u = (pp * p.kw + kwi) * 32 + lane;
@@ -192,43 +198,65 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
     constexpr int LANES_PER_VALUE = 32 / V;
     const int my_val = lane / LANES_PER_VALUE, my_j = my_val / M, my_mi = my_val - my_j * M;
     const bool writer = (lane % LANES_PER_VALUE) == 0;
-    const uint32_t row_step = (uint32_t)p.rg * p.row_bytes;
-    const int batch_rows = p.rg * RB;
     const uint32_t w_begin_lo = (uint32_t)(w_begin & 15);
-    const uint32_t my_ps = ((uint32_t)(rgi + my_j * p.rg) * p.kw + kwi) * M + my_mi;
+    const uint32_t my_ps = ((uint32_t)my_j * p.kw + kwi) * M + my_mi;
+    const uint32_t batch_bytes = (uint32_t)RB * p.row_bytes;
+    const uint32_t batch_ps = (uint32_t)RB * p.kw * M;
+    const int bps = p.rows_stage / RB;  // batches per full stage
+    // batches are numbered over the CTA's whole row range; batch g belongs to row group g % rg
+    int next_b = rgi;                   // this warp's next batch, relative to the current stage
 
     for (int it = 0; it < n_it; ++it) {
         const int slot = it % p.nst;
-        if (!mbar_wait_bounded(smem_u32(&hdr->full[slot]), (it / p.nst) & 1, cta_abort)) {
+        const int nr = min(p.rows_stage, n_rows - it * p.rows_stage);
+        const int nb = (nr + RB - 1) / RB;
+        if (next_b < nb) {
+            if (!mbar_wait_bounded(smem_u32(&hdr->full[slot]), (it / p.nst) & 1, cta_abort)) {
+                if (lane == 0 && !*cta_abort) {
+                    atomicExch(&g_device_status, DEV_TIMEOUT_FULL);
+                    *cta_abort = 1;
+                }
+                return;
+            }
+            if (p.trace && threadIdx.x == 0 && it == 0) p.trace[blockIdx.x * 4 + 2] = globaltimer_ns();
+            const uint32_t head = (w_begin_lo + (uint32_t)it * stage_bytes) & 15u;
+            const uint8_t* base = ring + (uint32_t)slot * p.slot_bytes + head;
+            float* ps = partial + (uint32_t)(it % (2 * p.nst)) * p.pstage + my_ps;
+            // Whole batches only: rows past nr (last stage of the CTA) hold stale bytes of an
+            // earlier stage; their sums land in partial entries that nobody reads.
+            if (p.probe == 0) {
+                for (; next_b < nb; next_b += p.rg) {
+                    const uint8_t* row0 = base + (uint32_t)next_b * batch_bytes;
+                    float acc[V];
+#pragma unroll
+                    for (int v = 0; v < V; ++v) acc[v] = 0.f;
+#pragma unroll
+                    for (int j = 0; j < RB; ++j) {
+                        const uint8_t* row = row0 + (uint32_t)j * p.row_bytes;
+#pragma unroll
+                        for (int pp = 0; pp < P; ++pp) {
+                            typename F::WRegs wr;
+                            F::load_w(row, unit[pp], wr);
+#pragma unroll
+                            for (int mi = 0; mi < M; ++mi) acc[j * M + mi] += F::dot(wr, unit[pp], x[mi][pp], nullptr);
+                        }
+                    }
+                    warp_multi_sum<V>(acc, lane);
+                    if (writer) ps[(uint32_t)next_b * batch_ps] = acc[0];
+                }
+            } else {
+                next_b += ((nb - next_b + p.rg - 1) / p.rg) * p.rg;
+            }
+        }
+        next_b -= bps;  // renumber relative to the next stage (only the last stage is short)
+        // A warp without work in a stage gets here without waiting for the stage's data; it must
+        // not arrive for this use of the slot before every warp has released the previous use.
+        if (it >= p.nst && !mbar_wait_bounded(smem_u32(&hdr->empty[slot]), ((it / p.nst) - 1) & 1, cta_abort)) {
             if (lane == 0 && !*cta_abort) {
-                atomicExch(&g_device_status, DEV_TIMEOUT_FULL);
+                atomicExch(&g_device_status, DEV_TIMEOUT_EMPTY);
                 *cta_abort = 1;
             }
             return;
-        }
-        const int nr = min(p.rows_stage, n_rows - it * p.rows_stage);
-        const uint32_t head = (w_begin_lo + (uint32_t)it * stage_bytes) & 15u;
-        const uint8_t* row0 = ring + (uint32_t)slot * p.slot_bytes + head + (uint32_t)rgi * p.row_bytes;
-        float* ps = partial + (uint32_t)(it % (2 * p.nst)) * p.pstage + my_ps;
-        // Whole batches only: rows past nr (last stage of the CTA) hold stale bytes of an
-        // earlier stage; their sums land in partial entries that nobody reads.
-        for (int rb = rgi; rb < nr && p.probe == 0; rb += batch_rows, row0 += row_step * RB, ps += batch_rows * p.kw * M) {
-            float acc[V];
-#pragma unroll
-            for (int v = 0; v < V; ++v) acc[v] = 0.f;
-#pragma unroll
-            for (int j = 0; j < RB; ++j) {
-                const uint8_t* row = row0 + j * row_step;
-#pragma unroll
-                for (int pp = 0; pp < P; ++pp) {
-                    typename F::WRegs wr;
-                    F::load_w(row, unit[pp], wr);
-#pragma unroll
-                    for (int mi = 0; mi < M; ++mi) acc[j * M + mi] += F::dot(wr, unit[pp], x[mi][pp], nullptr);
-                }
-            }
-            warp_multi_sum<V>(acc, lane);
-            if (writer) *ps = acc[0];
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&hdr->empty[slot]));
@@ -247,23 +275,32 @@ static int type_geometry(int type, int& block_elems, int& block_bytes, int& unit
 }
 
 constexpr int STAGE_MAX_BYTES = 48 * 1024;  // one packed row must fit this
-// tunables (qmm_tune): preferred bytes per stage, ring bytes per CTA, consumer warps per CTA
-static int g_stage_target = 36 * 1024;
+// tunables (qmm_tune): preferred bytes per stage, ring bytes per CTA, consumer warps per CTA,
+// Q4_K unit width (0 = automatic), upper bound on rows per batch
+static int g_stage_target = 24 * 1024;
 static int g_ring_budget = 150 * 1024;
 static int g_consumer_warps = 20;
+static int g_q4k_unit = 0;
+static int g_rb_max = 4;
 static int g_probe = 0;
+static unsigned long long* g_trace = nullptr;
+static int g_trace_stride = 0, g_trace_count = 0;
+// tuning aid: the next launches write 4 time stamps per CTA at trace + launch_index * stride
+void matvec_set_trace(unsigned long long* buf, int stride_words) { g_trace = buf; g_trace_stride = stride_words; g_trace_count = 0; }
 int matvec_tune(const char* key, int value) {
     const std::string k(key ? key : "");
     if (k == "stage_bytes" && value >= 1024 && value <= STAGE_MAX_BYTES) return g_stage_target = value, QMM_OK;
     if (k == "ring_bytes" && value >= 8 * 1024 && value <= 190 * 1024) return g_ring_budget = value, QMM_OK;
     if (k == "consumer_warps" && value >= 1 && value <= MAX_CONSUMER_WARPS) return g_consumer_warps = value, QMM_OK;
+    if (k == "q4k_unit" && (value == 0 || value == 1 || value == 2 || value == 4)) return g_q4k_unit = value, QMM_OK;
+    if (k == "rb_max" && (value == 1 || value == 2 || value == 4)) return g_rb_max = value, QMM_OK;
     if (k == "probe" && value >= 0 && value <= 1) return g_probe = value, QMM_OK;
     return QMM_ERR_UNSUPPORTED;
 }
 
-template <int TYPE, int P, int M, int RB>
+template <int TYPE, int UW, int P, int M, int RB>
 static int launch_inst(const MatvecParams& p, int grid, int threads, size_t smem, cudaStream_t stream) {
-    auto kern = qmatvec_kernel<TYPE, P, M, RB>;
+    auto kern = qmatvec_kernel<TYPE, UW, P, M, RB>;
     static size_t configured[64] = {};  // per instantiation and device; racing writers store the same facts
     int dev = 0;
     QMM_CUDA_TRY(cudaGetDevice(&dev));
@@ -285,25 +322,24 @@ static int launch_inst(const MatvecParams& p, int grid, int threads, size_t smem
     return QMM_OK;
 }
 
-// (activation-row tile M, rows per batch RB) pairs that are instantiated
-static int rows_per_batch(int mtile, int level) { return mtile == 1 ? (level == 0 ? 4 : (level == 1 ? 2 : 1)) : (mtile == 2 ? 2 : 1); }
-
-template <int TYPE, int P>
+// Instantiated (activation-row tile M, rows per batch RB) pairs: M=1: RB 4, 2, 1; M=2: RB 2, 1; M=4: RB 1.
+template <int TYPE, int UW, int P>
 static int launch_m(const MatvecParams& p, int grid, int threads, size_t smem, int mtile, int rb, cudaStream_t stream) {
-    if (mtile == 1 && rb == 4) return launch_inst<TYPE, P, 1, 4>(p, grid, threads, smem, stream);
-    if (mtile == 1 && rb == 2) return launch_inst<TYPE, P, 1, 2>(p, grid, threads, smem, stream);
-    if (mtile == 1) return launch_inst<TYPE, P, 1, 1>(p, grid, threads, smem, stream);
-    if (mtile == 2) return launch_inst<TYPE, P, 2, 2>(p, grid, threads, smem, stream);
-    return launch_inst<TYPE, P, 4, 1>(p, grid, threads, smem, stream);
+    if (mtile == 1 && rb == 4) return launch_inst<TYPE, UW, P, 1, 4>(p, grid, threads, smem, stream);
+    if (mtile == 1 && rb == 2) return launch_inst<TYPE, UW, P, 1, 2>(p, grid, threads, smem, stream);
+    if (mtile == 1) return launch_inst<TYPE, UW, P, 1, 1>(p, grid, threads, smem, stream);
+    if (mtile == 2 && rb == 2) return launch_inst<TYPE, UW, P, 2, 2>(p, grid, threads, smem, stream);
+    if (mtile == 2) return launch_inst<TYPE, UW, P, 2, 1>(p, grid, threads, smem, stream);
+    return launch_inst<TYPE, UW, P, 4, 1>(p, grid, threads, smem, stream);
 }
 
-template <int TYPE>
+template <int TYPE, int UW>
 static int launch_p(const MatvecParams& p, int passes, int grid, int threads, size_t smem, int mtile, int rb, cudaStream_t stream) {
-    switch (passes) {
-    case 1: return launch_m<TYPE, 1>(p, grid, threads, smem, mtile, rb, stream);
-    case 2: return launch_m<TYPE, 2>(p, grid, threads, smem, mtile, rb, stream);
-    default: return launch_m<TYPE, 4>(p, grid, threads, smem, mtile, rb, stream);
+    if constexpr (UW == 1) {
+        if (passes == 2) return launch_m<TYPE, UW, 2>(p, grid, threads, smem, mtile, rb, stream);
+        if (passes == 4) return launch_m<TYPE, UW, 4>(p, grid, threads, smem, mtile, rb, stream);
     }
+    return launch_m<TYPE, UW, 1>(p, grid, threads, smem, mtile, rb, stream);
 }
 
 int qmatvec_launch(int type, const void* w, const void* xq, float* y, int m, int n, int k, cudaStream_t stream) {
@@ -321,17 +357,10 @@ int qmatvec_launch(int type, const void* w, const void* xq, float* y, int m, int
     p.k = k;
     p.row_bytes = k / block_elems * block_bytes;
     p.xq_row_bytes = k / QK8 * Q8_1_BYTES;
-    p.units = k / unit_elems;
     p.probe = g_probe;
+    p.trace = g_trace ? g_trace + (size_t)(g_trace_count++) * g_trace_stride : nullptr;
     if (p.row_bytes > STAGE_MAX_BYTES) return QMM_ERR_UNSUPPORTED;
-
-    // K split: the fewest passes that keep the K axis within MAX_CONSUMER_WARPS warps
-    int passes = 1;
     const int nw = g_consumer_warps;
-    while (passes <= 4 && (p.units + 32 * passes - 1) / (32 * passes) > nw) passes *= 2;
-    if (passes > 4) return QMM_ERR_UNSUPPORTED;
-    p.kw = (p.units + 32 * passes - 1) / (32 * passes);
-    p.rg = nw / p.kw;
     const int sms = sm_count();
     const int rows_per_cta = (n + sms - 1) / sms;
     p.partial_off = (int)((sizeof(MatvecSmemHeader) + 127) & ~size_t(127));
@@ -343,20 +372,41 @@ int qmatvec_launch(int type, const void* w, const void* xq, float* y, int m, int
         p.m = left < mt ? left : mt;
         p.xq = static_cast<const uint8_t*>(xq) + (size_t)m0 * p.xq_row_bytes;
         p.y = y + (size_t)m0 * n;
-        // rows per stage: whole batches of rg*RB rows, near the target size, no more than a CTA's share.
-        // Rows per batch per warp: the larger tile unless it overshoots the stage or the CTA's rows;
-        // row groups are halved until one batch fits a stage.
+
+        // Q4_K unit width: the widest unit that keeps the activation registers within budget
+        // (UW * M <= 2 unless forced) and at least 7/8 of the lanes busy; other formats use 1.
+        int uw = 1;
+        if (type == QMM_TYPE_Q4_K) {
+            if (g_q4k_unit) {
+                uw = g_q4k_unit;
+            } else {
+                for (int cand = 2; cand >= 1; cand /= 2) {
+                    const int u = k / (64 * cand), lanes = ((u + 31) / 32) * 32;
+                    if (cand * mt <= 2 && u * 8 >= lanes * 7) {
+                        uw = cand;
+                        break;
+                    }
+                }
+            }
+            if (uw * mt > 4) uw = 4 / mt;
+        }
+        p.units = k / (unit_elems * uw);
+        // K split: the fewest passes that keep the K axis within the consumer warps (passes > 1 only for UW = 1)
+        int passes = 1;
+        while (passes <= 4 && (p.units + 32 * passes - 1) / (32 * passes) > nw) passes *= 2;
+        if (passes > 4 || (passes > 1 && uw > 1)) return QMM_ERR_UNSUPPORTED;
+        p.kw = (p.units + 32 * passes - 1) / (32 * passes);
         p.rg = nw / p.kw;
-        int rb = rows_per_batch(mt, 0);
-        for (int level = 1; level <= 2 && mt == 1; ++level)
-            if (p.rg * rb * p.row_bytes > STAGE_MAX_BYTES || p.rg * rb / 2 >= rows_per_cta) rb = rows_per_batch(mt, level);
-        while (p.rg > 1 && p.rg * rb * p.row_bytes > STAGE_MAX_BYTES) p.rg /= 2;
-        const int batch = p.rg * rb;
-        if (batch * p.row_bytes > STAGE_MAX_BYTES) return QMM_ERR_UNSUPPORTED;
-        int batches = g_stage_target / (batch * p.row_bytes);
+
+        // rows per batch: as many as instantiated for this M, not beyond what keeps every row group busy
+        int rb = mt == 1 ? 4 : (mt == 2 ? 2 : 1);
+        if (rb > g_rb_max) rb = g_rb_max;
+        while (rb > 1 && (p.rg * rb > rows_per_cta * 2 || rb * p.row_bytes > STAGE_MAX_BYTES)) rb /= 2;
+        // rows per stage: whole batches, near the target size, at most a CTA's share
+        int batches = g_stage_target / (rb * p.row_bytes);
         if (batches < 1) batches = 1;
-        while (batches > 1 && (batches - 1) * batch >= rows_per_cta) --batches;
-        p.rows_stage = batch * batches;
+        while (batches > 1 && (batches - 1) * rb >= rows_per_cta) --batches;
+        p.rows_stage = rb * batches;
         p.slot_bytes = (p.rows_stage * p.row_bytes + 32 + 127) & ~127;
         const int threads = (p.kw * p.rg + 1) * 32;
         int grid = (n + p.rows_stage - 1) / p.rows_stage;
@@ -377,11 +427,11 @@ int qmatvec_launch(int type, const void* w, const void* xq, float* y, int m, int
         const size_t smem = (size_t)p.ring_off + (size_t)p.nst * p.slot_bytes;
         if (smem > SMEM_LIMIT) return QMM_ERR_UNSUPPORTED;
         int st;
-        switch (type) {
-        case QMM_TYPE_Q8_0: st = launch_p<QMM_TYPE_Q8_0>(p, passes, grid, threads, smem, mt, rb, stream); break;
-        case QMM_TYPE_Q4_K: st = launch_p<QMM_TYPE_Q4_K>(p, passes, grid, threads, smem, mt, rb, stream); break;
-        default: st = launch_p<QMM_TYPE_Q6_K>(p, passes, grid, threads, smem, mt, rb, stream); break;
-        }
+        if (type == QMM_TYPE_Q8_0) st = launch_p<QMM_TYPE_Q8_0, 1>(p, passes, grid, threads, smem, mt, rb, stream);
+        else if (type == QMM_TYPE_Q6_K) st = launch_p<QMM_TYPE_Q6_K, 1>(p, passes, grid, threads, smem, mt, rb, stream);
+        else if (uw == 4) st = launch_p<QMM_TYPE_Q4_K, 4>(p, passes, grid, threads, smem, mt, rb, stream);
+        else if (uw == 2) st = launch_p<QMM_TYPE_Q4_K, 2>(p, passes, grid, threads, smem, mt, rb, stream);
+        else st = launch_p<QMM_TYPE_Q4_K, 1>(p, passes, grid, threads, smem, mt, rb, stream);
         if (st) return st;
     }
     return QMM_OK;
@@ -390,12 +440,11 @@ int qmatvec_launch(int type, const void* w, const void* xq, float* y, int m, int
 // ------------------------------------------- per-block integer sums (parity)
 template <int TYPE>
 __global__ void qblock_dots_kernel(const uint8_t* w, const uint8_t* xq, int32_t* out, int n, int units, int row_bytes) {
-    using F = Fmt<TYPE>;
+    using F = Fmt<TYPE, 1>;
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long)n * units) return;
     const int r = (int)(idx / units), u = (int)(idx - (long)r * units);
-    XRegs x;
-    F::zero_x(x);
+    typename F::XRegs x;
     F::load_x(xq, u, x);
     typename F::WRegs wr;
     F::load_w(w + (size_t)r * row_bytes, u, wr);

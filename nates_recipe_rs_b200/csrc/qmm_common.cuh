@@ -77,6 +77,10 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
     asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
+// One potentially-blocking probe of a phase: the hardware parks the thread until the
+// phase completes or a short time slice ends, so a waiting warp costs almost no issue
+// slots (a test_wait polling loop was measured to execute 4x more instructions than
+// the arithmetic of the whole kernel).
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(

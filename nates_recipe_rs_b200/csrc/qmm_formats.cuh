@@ -3,7 +3,7 @@
 //
 // A "unit" is the slice of one weight row that one lane handles against
 // activations it keeps in registers for the whole kernel:
-//   Q4_K  64 elements = one 32-byte group of qs = sub-blocks 2g (low nibbles), 2g+1 (high)
+//   Q4_K  64*UW elements = UW 32-byte groups of qs; group g = sub-blocks 2g (low nibbles), 2g+1 (high)
 //   Q6_K  64 elements = 16 consecutive l of one half: 4 quarter-runs of 16 elements,
 //                       each run is exactly one 16-element scale group
 //   Q8_0  32 elements = one block
@@ -41,14 +41,6 @@ __device__ __forceinline__ uint32_t ld_u16(const uint8_t* p) {
     return *reinterpret_cast<const uint16_t*>(p);
 }
 
-// Activation registers of one unit: xw = packed int8 words, xs = float scales,
-// xb = integer biases folded into the dot accumulators.
-struct XRegs {
-    int xw[16];
-    float xs[4];
-    int xb[4];
-};
-
 // Q8_1 accessors (row pointer 4-byte aligned)
 __device__ __forceinline__ int q81_word(const uint8_t* xq, int blk, int w) {
     return *reinterpret_cast<const int*>(xq + (size_t)blk * Q8_1_BYTES + 4 + 4 * w);
@@ -60,88 +52,122 @@ __device__ __forceinline__ float q81_s(const uint8_t* xq, int blk) {
     return f16_bits_to_f32(ld_u16(xq + (size_t)blk * Q8_1_BYTES + 2));
 }
 
-template <int TYPE>
+// byte `idx` (0..3, may be a run-time value) of w, zero-extended: one PRMT
+__device__ __forceinline__ uint32_t byte_of(uint32_t w, uint32_t idx) { return __byte_perm(w, 0u, 0x4440u | idx); }
+// float(byte idx of w), exact: PRMT builds the bits of 2^23 + byte, one subtraction removes 2^23
+__device__ __forceinline__ float byte_to_float(uint32_t w, uint32_t idx) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | idx)) - 8388608.0f;
+}
+
+// Fmt<TYPE, UW>: UW is the unit width, used by Q4_K only (UW = 1, 2 or 4 consecutive
+// 32-byte groups of qs, i.e. 64, 128 or 256 elements per lane); wider units decode the
+// packed 6-bit scales once for more weights at the price of more activation registers.
+template <int TYPE, int UW>
 struct Fmt;
 
 // ----------------------------------------------------------------- Q4_K
-template <>
-struct Fmt<QMM_TYPE_Q4_K> {
-    static constexpr int BLOCK_ELEMS = 256, BLOCK_BYTES = Q4_K_BYTES, UNIT_ELEMS = 64, SUMS_PER_UNIT = 2;
+template <int UW>
+struct Fmt<QMM_TYPE_Q4_K, UW> {
+    static_assert(UW == 1 || UW == 2 || UW == 4, "unit = 1, 2 or 4 groups of a super-block");
+    static constexpr int BLOCK_ELEMS = 256, BLOCK_BYTES = Q4_K_BYTES, UNIT_ELEMS = 64 * UW, SUMS_PER_UNIT = 2 * UW;
     static constexpr int W_ALIGN = 16;  // required alignment of the weight pointer
+    static constexpr int UNITS_PER_BLOCK = 4 / UW;
 
+    // activations of unit u: the 2*UW Q8_1 blocks 2*UW*u .. of the row
+    struct XRegs {
+        int xw[16 * UW];
+        float xd[2 * UW], xs[2 * UW];
+    };
     __device__ static __forceinline__ void load_x(const uint8_t* xq, int u, XRegs& r) {
-        const int j0 = 2 * u;  // = 8*(u>>2) + 2*(u&3)
+        const int j0 = 2 * UW * u;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) {
-            r.xw[w] = q81_word(xq, j0, w);
-            r.xw[8 + w] = q81_word(xq, j0 + 1, w);
+        for (int j = 0; j < 2 * UW; ++j) {
+#pragma unroll
+            for (int w = 0; w < 8; ++w) r.xw[8 * j + w] = q81_word(xq, j0 + j, w);
+            r.xd[j] = q81_d(xq, j0 + j);
+            r.xs[j] = q81_s(xq, j0 + j);
         }
-        r.xs[0] = q81_d(xq, j0);
-        r.xs[1] = q81_d(xq, j0 + 1);
-        r.xs[2] = q81_s(xq, j0);
-        r.xs[3] = q81_s(xq, j0 + 1);
     }
     __device__ static __forceinline__ void zero_x(XRegs& r) {
 #pragma unroll
-        for (int w = 0; w < 16; ++w) r.xw[w] = 0;
+        for (int w = 0; w < 16 * UW; ++w) r.xw[w] = 0;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) r.xs[w] = 0.f, r.xb[w] = 0;
+        for (int w = 0; w < 2 * UW; ++w) r.xd[w] = 0.f, r.xs[w] = 0.f;
     }
 
     struct WRegs {  // the weight words of one unit, fetched once and reused per activation row
-        uint4 hdr, qa, qb;
+        uint4 hdr, q[2 * UW];
     };
     __device__ static __forceinline__ void load_w(const uint8_t* row, int u, WRegs& wr) {
-        const uint8_t* blk = row + (size_t)(u >> 2) * Q4_K_BYTES;
+        const uint8_t* blk = row + (uint32_t)(u / UNITS_PER_BLOCK) * Q4_K_BYTES;
         wr.hdr = *reinterpret_cast<const uint4*>(blk);
-        const uint4* q = reinterpret_cast<const uint4*>(blk + 16 + 32 * (u & 3));
-        wr.qa = q[0];
-        wr.qb = q[1];
-    }
-    // 6-bit scale / min codes of sub-blocks 2g and 2g+1, packed as two bytes each
-    __device__ static __forceinline__ void scale_codes(const uint4& hdr, int g, uint32_t& sc2, uint32_t& m2) {
-        const int sh = 16 * (g & 1);
-        const uint32_t a = hdr.y >> sh, b = hdr.z >> sh, c = hdr.w >> sh;
-        const uint32_t sc_lo = a & 0x3F3Fu, m_lo = b & 0x3F3Fu;
-        const uint32_t sc_hi = (c & 0x0F0Fu) | ((a >> 2) & 0x3030u);
-        const uint32_t m_hi = ((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u);
-        sc2 = (g < 2) ? sc_lo : sc_hi;
-        m2 = (g < 2) ? m_lo : m_hi;
+        const uint4* q = reinterpret_cast<const uint4*>(blk + 16 + 32 * UW * (u % UNITS_PER_BLOCK));
+#pragma unroll
+        for (int i = 0; i < 2 * UW; ++i) wr.q[i] = q[i];
     }
     __device__ static __forceinline__ float dot(const WRegs& wr, int u, const XRegs& x, int* sums) {
-        const uint32_t qa[4] = {wr.qa.x, wr.qa.y, wr.qa.z, wr.qa.w};
-        const uint32_t qb[4] = {wr.qb.x, wr.qb.y, wr.qb.z, wr.qb.w};
-        int s0 = 0, s0b = 0, s1 = 0, s1b = 0;
+        // integer sums of the 2*UW sub-blocks
+        int sum[2 * UW];
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            s0 = dp4a_ss((int)(qa[w] & 0x0F0F0F0Fu), x.xw[w], s0);
-            s0b = dp4a_ss((int)(qb[w] & 0x0F0F0F0Fu), x.xw[4 + w], s0b);
-            s1 = dp4a_u8s8(qa[w] & 0xF0F0F0F0u, x.xw[8 + w], s1);  // 16 * (high nibble) . x
-            s1b = dp4a_u8s8(qb[w] & 0xF0F0F0F0u, x.xw[12 + w], s1b);
+        for (int g = 0; g < UW; ++g) {
+            const uint32_t qa[4] = {wr.q[2 * g].x, wr.q[2 * g].y, wr.q[2 * g].z, wr.q[2 * g].w};
+            const uint32_t qb[4] = {wr.q[2 * g + 1].x, wr.q[2 * g + 1].y, wr.q[2 * g + 1].z, wr.q[2 * g + 1].w};
+            const int* xl = x.xw + 16 * g;  // sub-block 2g (low nibbles); +8: sub-block 2g+1 (high nibbles)
+            int s0 = 0, s0b = 0, s1 = 0, s1b = 0;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                s0 = dp4a_ss((int)(qa[w] & 0x0F0F0F0Fu), xl[w], s0);
+                s0b = dp4a_ss((int)(qb[w] & 0x0F0F0F0Fu), xl[4 + w], s0b);
+                s1 = dp4a_u8s8(qa[w] & 0xF0F0F0F0u, xl[8 + w], s1);  // 16 * (high nibble) . x
+                s1b = dp4a_u8s8(qb[w] & 0xF0F0F0F0u, xl[12 + w], s1b);
+            }
+            sum[2 * g] = s0 + s0b;
+            sum[2 * g + 1] = (s1 + s1b) >> 4;  // exact: a multiple of 16
         }
-        const int sum0 = s0 + s0b;
-        const int sum1 = (s1 + s1b) >> 4;  // exact: a multiple of 16
         if (sums) {
-            sums[0] = sum0;
-            sums[1] = sum1;
+#pragma unroll
+            for (int j = 0; j < 2 * UW; ++j) sums[j] = sum[j];
         }
-        uint32_t sc2, m2;
-        scale_codes(wr.hdr, u & 3, sc2, m2);
+        // 6-bit scale / min codes, four per word: A = sub-blocks 0..3, B = sub-blocks 4..7
+        const uint32_t scA = wr.hdr.y & 0x3F3F3F3Fu, mA = wr.hdr.z & 0x3F3F3F3Fu;
+        const uint32_t scB = (wr.hdr.w & 0x0F0F0F0Fu) | ((wr.hdr.y >> 2) & 0x30303030u);
+        const uint32_t mB = ((wr.hdr.w >> 4) & 0x0F0F0F0Fu) | ((wr.hdr.z >> 2) & 0x30303030u);
+        float accd = 0.f, accm = 0.f;
+        if constexpr (UW == 4) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t sc4 = j < 4 ? scA : scB, m4 = j < 4 ? mA : mB;
+                accd += x.xd[j] * small_int_to_float((int)byte_of(sc4, j & 3) * sum[j]);  // |sc*sum| < 2^22
+                accm += x.xs[j] * byte_to_float(m4, j & 3);
+            }
+        } else {
+            // first sub-block of the unit: j0 = 2*UW*(u % UNITS_PER_BLOCK); lanes differ, a lane never changes
+            const int j0 = 2 * UW * (u % UNITS_PER_BLOCK);
+            const uint32_t sc4 = j0 < 4 ? scA : scB, m4 = j0 < 4 ? mA : mB;
+#pragma unroll
+            for (int j = 0; j < 2 * UW; ++j) {
+                const uint32_t idx = (uint32_t)(j0 + j) & 3u;
+                accd += x.xd[j] * small_int_to_float((int)byte_of(sc4, idx) * sum[j]);
+                accm += x.xs[j] * byte_to_float(m4, idx);
+            }
+        }
         const float d = f16_bits_to_f32(wr.hdr.x & 0xFFFFu), dmin = f16_bits_to_f32(wr.hdr.x >> 16);
-        // |sc*sum| <= 63*32*15*127 < 2^22
-        const float accd = x.xs[0] * small_int_to_float((int)(sc2 & 0xFFu) * sum0) +
-                           x.xs[1] * small_int_to_float((int)(sc2 >> 8) * sum1);
-        const float accm = x.xs[2] * small_int_to_float((int)(m2 & 0xFFu)) + x.xs[3] * small_int_to_float((int)(m2 >> 8));
         return d * accd - dmin * accm;
     }
 };
 
 // ----------------------------------------------------------------- Q6_K
-template <>
-struct Fmt<QMM_TYPE_Q6_K> {
+template <int UW>
+struct Fmt<QMM_TYPE_Q6_K, UW> {
+    static_assert(UW == 1, "Q6_K has one unit width");
     static constexpr int BLOCK_ELEMS = 256, BLOCK_BYTES = Q6_K_BYTES, UNIT_ELEMS = 64, SUMS_PER_UNIT = 4;
     static constexpr int W_ALIGN = 2;
 
+    struct XRegs {
+        int xw[16];
+        float xd[4];
+        int xb[4];  // -32 * sum of the activations of a run, folded into the dot accumulator
+    };
     // unit u: block b = u>>2, half h = (u>>1)&1, l0 = 16*(u&1); run t covers x block 8b+4h+t, elements l0..l0+15
     __device__ static __forceinline__ void load_x(const uint8_t* xq, int u, XRegs& r) {
         const int j0 = 8 * (u >> 2) + 4 * ((u >> 1) & 1);
@@ -154,7 +180,7 @@ struct Fmt<QMM_TYPE_Q6_K> {
                 r.xw[4 * t + w] = q81_word(xq, j0 + t, w0 + w);
                 sx = dp4a_ss(0x01010101, r.xw[4 * t + w], sx);
             }
-            r.xs[t] = q81_d(xq, j0 + t);
+            r.xd[t] = q81_d(xq, j0 + t);
             r.xb[t] = -32 * sx;  // sum((q-32)*x) = sum(q*x) - 32*sum(x)
         }
     }
@@ -162,14 +188,14 @@ struct Fmt<QMM_TYPE_Q6_K> {
 #pragma unroll
         for (int w = 0; w < 16; ++w) r.xw[w] = 0;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) r.xs[w] = 0.f, r.xb[w] = 0;
+        for (int w = 0; w < 4; ++w) r.xd[w] = 0.f, r.xb[w] = 0;
     }
 
     struct WRegs {
         uint32_t a[4], b[4], h[4], sc[2], d;
     };
     __device__ static __forceinline__ void load_w(const uint8_t* row, int u, WRegs& wr) {
-        const uint8_t* blk = row + (size_t)(u >> 2) * Q6_K_BYTES;
+        const uint8_t* blk = row + (uint32_t)(u >> 2) * Q6_K_BYTES;
         const int h = (u >> 1) & 1, l0 = 16 * (u & 1);
         ld_words4_align2(blk + 64 * h + l0, wr.a);
         ld_words4_align2(blk + 64 * h + 32 + l0, wr.b);
@@ -200,38 +226,42 @@ struct Fmt<QMM_TYPE_Q6_K> {
         const int bsh = 8 * (u & 1);
         const int c0 = (int)(int8_t)(wr.sc[0] >> bsh), c1 = (int)(int8_t)(wr.sc[0] >> (16 + bsh));
         const int c2 = (int)(int8_t)(wr.sc[1] >> bsh), c3 = (int)(int8_t)(wr.sc[1] >> (16 + bsh));
-        // |scale*sum| can reach 2^24, so the two factors are converted separately (each exact)
-        // and multiplied in float: the product of two exact integers below 2^24 in magnitude
-        // is rounded once, like the int->float conversion of the integer product would be.
-        float acc = x.xs[0] * (small_int_to_float(c0) * small_int_to_float(s[0]));
-        acc += x.xs[1] * (small_int_to_float(c1) * small_int_to_float(s[1]));
-        acc += x.xs[2] * (small_int_to_float(c2) * small_int_to_float(s[2]));
-        acc += x.xs[3] * (small_int_to_float(c3) * small_int_to_float(s[3]));
+        // |scale*sum| can reach 2^23, so the two factors are converted separately (each exact)
+        // and multiplied in float; the product of two integers stays below 2^24 and is exact.
+        float acc = x.xd[0] * (small_int_to_float(c0) * small_int_to_float(s[0]));
+        acc += x.xd[1] * (small_int_to_float(c1) * small_int_to_float(s[1]));
+        acc += x.xd[2] * (small_int_to_float(c2) * small_int_to_float(s[2]));
+        acc += x.xd[3] * (small_int_to_float(c3) * small_int_to_float(s[3]));
         return f16_bits_to_f32(wr.d) * acc;
     }
 };
 
 // ----------------------------------------------------------------- Q8_0
-template <>
-struct Fmt<QMM_TYPE_Q8_0> {
+template <int UW>
+struct Fmt<QMM_TYPE_Q8_0, UW> {
+    static_assert(UW == 1, "Q8_0 has one unit width");
     static constexpr int BLOCK_ELEMS = 32, BLOCK_BYTES = Q8_0_BYTES, UNIT_ELEMS = 32, SUMS_PER_UNIT = 1;
     static constexpr int W_ALIGN = 2;
 
+    struct XRegs {
+        int xw[8];
+        float xd;
+    };
     __device__ static __forceinline__ void load_x(const uint8_t* xq, int u, XRegs& r) {
 #pragma unroll
         for (int w = 0; w < 8; ++w) r.xw[w] = q81_word(xq, u, w);
-        r.xs[0] = q81_d(xq, u);
+        r.xd = q81_d(xq, u);
     }
     __device__ static __forceinline__ void zero_x(XRegs& r) {
 #pragma unroll
         for (int w = 0; w < 8; ++w) r.xw[w] = 0;
-        r.xs[0] = 0.f;
+        r.xd = 0.f;
     }
     struct WRegs {
         uint32_t q[8], d;
     };
     __device__ static __forceinline__ void load_w(const uint8_t* row, int u, WRegs& wr) {
-        const uint8_t* blk = row + (size_t)u * Q8_0_BYTES;
+        const uint8_t* blk = row + (uint32_t)u * Q8_0_BYTES;
         wr.d = ld_u16(blk);
         uint32_t lo[4], hi[4];
         ld_words4_align2(blk + 2, lo);
@@ -246,9 +276,9 @@ struct Fmt<QMM_TYPE_Q8_0> {
             s0 = dp4a_ss((int)wr.q[w], x.xw[w], s0);
             s1 = dp4a_ss((int)wr.q[4 + w], x.xw[4 + w], s1);
         }
-        const int sum = s0 + s1;
+        const int sum = s0 + s1;  // |sum| <= 32*128*127 < 2^22
         if (sums) sums[0] = sum;
-        return (f16_bits_to_f32(wr.d) * x.xs[0]) * small_int_to_float(sum);
+        return (f16_bits_to_f32(wr.d) * x.xd) * small_int_to_float(sum);
     }
 };
 

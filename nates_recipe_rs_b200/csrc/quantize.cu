@@ -180,7 +180,7 @@ __global__ void quantize_q6_k_kernel(const float* __restrict__ x, uint8_t* __res
 // ---- element-wise dequantization: one thread per element, coalesced stores ----
 template <int TYPE, typename OUT>
 __global__ void dequantize_kernel(const uint8_t* __restrict__ w, OUT* __restrict__ out, long n_elems) {
-    using F = Fmt<TYPE>;
+    using F = Fmt<TYPE, 1>;
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n_elems) return;
     const long blk = idx / F::BLOCK_ELEMS;

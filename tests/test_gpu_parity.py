@@ -216,7 +216,9 @@ def test_config2_full_size(ops, qtype, n, k):
     y_a = ops.gpu_qmatvec(qtype, w, xq[:rb], 1, n, k)
     y_b = ops.gpu_qmatvec(qtype, w, xq[rb:], 1, n, k)
     ops.check_launch()
-    assert torch.equal(y2[0], y_a[0]) and torch.equal(y2[1], y_b[0])     # batch rows are independent
+    # batch rows are independent (the batched launch may use another summation order, hence a tolerance)
+    assert_close(y2[0].cpu().numpy(), y_a[0].cpu().numpy())
+    assert_close(y2[1].cpu().numpy(), y_b[0].cpu().numpy())
     rows = np.r_[0:64, n // 2:n // 2 + 64, n - 64:n]
     wrows = w.reshape(n, -1)[torch.from_numpy(rows).cuda()].cpu().numpy()
     assert_close(y2.cpu().numpy()[:, rows], oracle.matvec(qtype, wrows, xq.cpu().numpy(), k))
