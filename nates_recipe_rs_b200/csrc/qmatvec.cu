@@ -210,6 +210,18 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
         const int slot = it % p.nst;
         const int nr = min(p.rows_stage, n_rows - it * p.rows_stage);
         const int nb = (nr + RB - 1) / RB;
+        // Every warp passes every stage but only waits for the data of stages it has work in, so
+        // it can run ahead of the copies.  Before touching this use of the slot it waits until all
+        // warps have released the previous use: that keeps its arrival in the right phase, makes
+        // the parity test on the data barrier below unambiguous (the barrier cannot still be one
+        // phase behind), and means no copy can still be in flight when the CTA exits.
+        if (it >= p.nst && !mbar_wait_bounded(smem_u32(&hdr->empty[slot]), ((it / p.nst) - 1) & 1, cta_abort)) {
+            if (lane == 0 && !*cta_abort) {
+                atomicExch(&g_device_status, DEV_TIMEOUT_EMPTY);
+                *cta_abort = 1;
+            }
+            return;
+        }
         if (next_b < nb) {
             if (!mbar_wait_bounded(smem_u32(&hdr->full[slot]), (it / p.nst) & 1, cta_abort)) {
                 if (lane == 0 && !*cta_abort) {
@@ -249,15 +261,6 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
             }
         }
         next_b -= bps;  // renumber relative to the next stage (only the last stage is short)
-        // A warp without work in a stage gets here without waiting for the stage's data; it must
-        // not arrive for this use of the slot before every warp has released the previous use.
-        if (it >= p.nst && !mbar_wait_bounded(smem_u32(&hdr->empty[slot]), ((it / p.nst) - 1) & 1, cta_abort)) {
-            if (lane == 0 && !*cta_abort) {
-                atomicExch(&g_device_status, DEV_TIMEOUT_EMPTY);
-                *cta_abort = 1;
-            }
-            return;
-        }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&hdr->empty[slot]));
     }
@@ -277,9 +280,9 @@ static int type_geometry(int type, int& block_elems, int& block_bytes, int& unit
 constexpr int STAGE_MAX_BYTES = 48 * 1024;  // one packed row must fit this
 // tunables (qmm_tune): preferred bytes per stage, ring bytes per CTA, consumer warps per CTA,
 // Q4_K unit width (0 = automatic), upper bound on rows per batch
-static int g_stage_target = 24 * 1024;
+static int g_stage_target = 48 * 1024;
 static int g_ring_budget = 150 * 1024;
-static int g_consumer_warps = 20;
+static int g_consumer_warps = 16;
 static int g_q4k_unit = 0;
 static int g_rb_max = 4;
 static int g_probe = 0;

@@ -224,6 +224,37 @@ def test_config2_full_size(ops, qtype, n, k):
     assert_close(y2.cpu().numpy()[:, rows], oracle.matvec(qtype, wrows, xq.cpu().numpy(), k))
 
 
+@pytest.mark.parametrize("qtype,n,k", [(oracle.Q4_K, 14336, 4096), (oracle.Q4_K, 4096, 14336), (oracle.Q6_K, 4096, 14336),
+                                       (oracle.Q8_0, 4096, 4096), (oracle.Q4_K, 28672, 8192)])
+def test_full_size_every_row_back_to_back(ops, qtype, n, k):
+    """Every output row of full-size launches issued back to back over rotating weight buffers
+    (so each launch overlaps the tail of the previous one) against float64 products of the
+    dequantised operands; the dequantisers are checked bit for bit against the oracle elsewhere."""
+    copies = 4
+    ws, refs = [], []
+    x = torch.from_numpy(oracle.fill_normal(k, 91, 1.0)).cuda()
+    xq = ops.gpu_quantize_q8_1(x)
+    # Q8_1 decode on the host (small): d * q
+    xf = torch.from_numpy(oracle.dequantize(oracle.Q8_1, xq.cpu().numpy(), k).reshape(-1)).cuda().double()
+    for c in range(copies):
+        wf = torch.randn(n, k, device="cuda", generator=torch.Generator(device="cuda").manual_seed(c)) * 0.02
+        w = ops.gpu_quantize_weights(qtype, wf)
+        wd = ops.gpu_dequantize(qtype, w, n * k).reshape(n, k)
+        refs.append(((wd.double() @ xf), (wd.double().abs() @ xf.abs())))
+        ws.append(w)
+        del wf, wd
+    ys = [torch.empty(1, n, device="cuda") for _ in range(3 * copies)]
+    for i, y in enumerate(ys):
+        ops.gpu_qmatvec_into(qtype, ws[i % copies], xq, y, 1, n, k)
+    ops.check_launch()
+    for i, y in enumerate(ys):
+        ref, mag = refs[i % copies]
+        # Q4_K subtracts dmin*m*s with the fp16-rounded block sums s of Q8_1: bound relative to the term magnitudes
+        bound = ABS_TOL + (4e-3 if qtype == oracle.Q4_K else REL_TOL) * mag
+        err = (y[0].double() - ref).abs()
+        assert bool((err <= bound).all()), f"launch {i}: {int((err > bound).sum())} rows off, max err {float(err.max()):.3e}"
+
+
 def test_bad_arguments_are_rejected_not_launched(ops):
     w = torch.zeros(4096, dtype=torch.uint8, device="cuda")
     y = torch.zeros(16, device="cuda")
