@@ -24,8 +24,13 @@ __device__ __forceinline__ void st_u16(uint8_t* p, uint16_t v) { *reinterpret_ca
 // ---- 32-element blocks: one warp per block, one element per lane ----
 template <bool WITH_SUM>
 __global__ void quantize_q8_kernel(const float* __restrict__ x, uint8_t* __restrict__ out, long n_blocks) {
-    pdl_release_dependents();
-    pdl_wait_prior_grids();
+    // Only the activation quantizer takes part in programmatic dependent launch: the kernel after
+    // it (a matvec) may start streaming its weights early.  The Q8_0 weight quantizer must not
+    // release dependents early, since what follows may read the weights it is still writing.
+    if (WITH_SUM) {
+        pdl_release_dependents();
+        pdl_wait_prior_grids();
+    }
     const int lane = threadIdx.x & 31;
     const long blk = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (blk >= n_blocks) return;
