@@ -115,6 +115,15 @@ int launch_qmatvec_q4_k(const void* w, const void* xq, float* y, int m, int n, i
 int launch_qmatvec_q6_k(const void* w, const void* xq, float* y, int m, int n, int k, void* stream);
 int launch_qmatvec(int type, const void* w, const void* xq, float* y, int m, int n, int k, void* stream);
 
+/* ---- dequant-GEMM for prefill on the tcgen05 tensor cores.  Same operator shape as
+ * launch_gemm_bt_f64 (gpu-core/src/kernels/gemm_f64.hip:48-54; gpu-core/src/infer_ops.rs:224-240) with
+ * m in the hundreds:  y(m,n) = bf16( sum_k x(m,k) * bf16(w(n,k)) ), x and y bf16 row-major, w Q4_K
+ * rows, fp32 accumulation; bf16(w) is the round-to-nearest-even bf16 of the value
+ * launch_dequantize_q4_k_f32 produces.  x and w 16-byte aligned, k a multiple of 256.
+ * `_f32acc` stores the fp32 accumulators instead of rounding them (parity instrumentation). */
+int launch_qgemm_q4_k_bf16(const void* w, const void* x, void* y, int m, int n, int k, void* stream);
+int launch_qgemm_q4_k_bf16_f32acc(const void* w, const void* x, float* yf, int m, int n, int k, void* stream);
+
 /* ---- per-block integer dot sums (parity instrumentation; same device code as
  * the matvec).  One Q8_1 row xq (k); out int32 (n, k/32) for Q8_0 and Q4_K,
  * (n, k/16) for Q6_K. */

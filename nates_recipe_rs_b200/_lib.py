@@ -36,6 +36,8 @@ SIGNATURES = {
     "launch_qmatvec_q4_k": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "launch_qmatvec_q6_k": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "launch_qmatvec": (i32, [i32, vp, vp, vp, i32, i32, i32, vp]),
+    "launch_qgemm_q4_k_bf16": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "launch_qgemm_q4_k_bf16_f32acc": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "launch_qblock_dots": (i32, [i32, vp, vp, vp, i32, i32, vp]),
 }
 

@@ -28,6 +28,7 @@ int quantize_q8_1_launch(const float* x, void* xq, int m, int k, cudaStream_t st
 int quantize_weights_launch(int type, const float* w, void* out, long rows, int k, cudaStream_t stream);
 int dequantize_f32_launch(int type, const void* w, float* out, long n_elems, cudaStream_t stream);
 int dequantize_bf16_launch(int type, const void* w, void* out, long n_elems, cudaStream_t stream);
+int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, int n, int k, cudaStream_t stream);
 int matvec_tune(const char* key, int value);
 void matvec_set_trace(unsigned long long* buf, int stride_words);
 
@@ -114,6 +115,15 @@ int launch_qmatvec(int type, const void* w, const void* xq, float* y, int m, int
 int launch_qmatvec_q8_0(const void* w, const void* xq, float* y, int m, int n, int k, void* s) { return qmatvec_launch(QMM_TYPE_Q8_0, w, xq, y, m, n, k, as_stream(s)); }
 int launch_qmatvec_q4_k(const void* w, const void* xq, float* y, int m, int n, int k, void* s) { return qmatvec_launch(QMM_TYPE_Q4_K, w, xq, y, m, n, k, as_stream(s)); }
 int launch_qmatvec_q6_k(const void* w, const void* xq, float* y, int m, int n, int k, void* s) { return qmatvec_launch(QMM_TYPE_Q6_K, w, xq, y, m, n, k, as_stream(s)); }
+
+int launch_qgemm_q4_k_bf16(const void* w, const void* x, void* y, int m, int n, int k, void* stream) {
+    if (!y) return QMM_ERR_NULL;
+    return qgemm_q4k_launch(w, x, y, nullptr, m, n, k, as_stream(stream));
+}
+int launch_qgemm_q4_k_bf16_f32acc(const void* w, const void* x, float* yf, int m, int n, int k, void* stream) {
+    if (!yf) return QMM_ERR_NULL;
+    return qgemm_q4k_launch(w, x, nullptr, yf, m, n, k, as_stream(stream));
+}
 
 int launch_qblock_dots(int type, const void* w, const void* xq, int32_t* out, int n, int k, void* stream) {
     return qblock_dots_launch(type, w, xq, out, n, k, as_stream(stream));

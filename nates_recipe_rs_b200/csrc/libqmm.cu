@@ -3,3 +3,4 @@
 #include "api.cu"
 #include "quantize.cu"
 #include "qmatvec.cu"
+#include "qgemm.cu"

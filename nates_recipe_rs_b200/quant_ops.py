@@ -23,6 +23,7 @@ __all__ = [
     "Q8_0", "Q8_1", "Q4_K", "Q6_K", "row_bytes", "check_launch",
     "gpu_quantize_q8_1_into", "gpu_quantize_q8_1", "gpu_quantize_weights_into", "gpu_quantize_weights",
     "gpu_dequantize_into", "gpu_dequantize", "gpu_qmatvec_into", "gpu_qmatvec", "gpu_qblock_dots",
+    "gpu_qgemm_q4_k_bf16_into", "gpu_qgemm_q4_k_bf16",
     "gpu_qlinear",
 ]
 
@@ -130,6 +131,28 @@ def gpu_qblock_dots(qtype, w, xq, n, k):
     group = 16 if qtype == Q6_K else 32
     out = torch.empty((n, k // group), dtype=torch.int32, device=w.device)
     check(lib().launch_qblock_dots(qtype, _ptr(w), _ptr(xq), _ptr(out), n, k, _stream()), "launch_qblock_dots")
+    return out
+
+
+def gpu_qgemm_q4_k_bf16_into(w, x, out, m, n, k):
+    """out(m,n) = x(m,k) . bf16(w(n,k))^T on the tensor cores; x bf16, w Q4_K rows, out bf16 (or
+    float32: the unrounded accumulators).  The prefill form of gpu_gemm_bt_f64_into."""
+    _need(w, n * row_bytes(Q4_K, k), "w")
+    _need(x, m * k * 2, "x")
+    if x.dtype != torch.bfloat16:
+        raise ValueError("x must be bfloat16")
+    _need(out, m * n * out.element_size(), "out")
+    name = "launch_qgemm_q4_k_bf16" if out.dtype == torch.bfloat16 else "launch_qgemm_q4_k_bf16_f32acc"
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("out must be bfloat16 or float32")
+    check(getattr(lib(), name)(_ptr(w), _ptr(x), _ptr(out), m, n, k, _stream()), name)
+
+
+def gpu_qgemm_q4_k_bf16(w, x, n, k, dtype=torch.bfloat16):
+    x = x.contiguous()
+    m = x.shape[0]
+    out = torch.empty((m, n), dtype=dtype, device=x.device)
+    gpu_qgemm_q4_k_bf16_into(w, x, out, m, n, k)
     return out
 
 
