@@ -1,0 +1,74 @@
+/*
+ * qmm_decoder.h — C ABI of the decode engine of libqmm.
+ *
+ * The engine plays the role examples/gemma4.rs plays in nm-z/nates-recipe-rs (model held in VRAM,
+ * every activation buffer allocated once, one projection after another per layer, greedy
+ * sampling: examples/gemma4.rs:231-271, 638-742, 758-783, 1021-1057) for a Llama/Gemma-style
+ * decoder whose weights are random-init GGUF blocks.  All allocation happens in
+ * qmm_decoder_create; qmm_decoder_step only launches kernels on the given stream.
+ */
+#ifndef QMM_DECODER_H
+#define QMM_DECODER_H
+#include "qmm.h"
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QMM_DECODER_MAX_TP 8
+#define QMM_ACT_GELU_TANH 0
+#define QMM_ACT_SILU 1
+
+/* tensor ids for qmm_decoder_get_tensor (layer = -1 for the last three) */
+#define QMM_T_ATTN_NORM 0
+#define QMM_T_WQ 1     /* returned as the fused [Wq ; Wk] block of this rank */
+#define QMM_T_WK 2     /* not a separate tensor: use QMM_T_WQ */
+#define QMM_T_WV 3
+#define QMM_T_WO 4
+#define QMM_T_FFN_NORM 5
+#define QMM_T_WGATE 6  /* returned as the fused [Wgate ; Wup] block of this rank */
+#define QMM_T_WUP 7    /* not a separate tensor: use QMM_T_WGATE */
+#define QMM_T_WDOWN 8
+#define QMM_T_FINAL_NORM 9
+#define QMM_T_HEAD 10
+#define QMM_T_EMBED 11
+
+typedef struct {
+    int n_layers, hidden, n_q_heads, n_kv_heads, head_dim, ffn, vocab, ctx_len;
+    float rope_theta, rms_eps;
+    int act;                                  /* QMM_ACT_* */
+    int type_attn_qk, type_attn_v, type_attn_o, type_ffn_gate_up, type_ffn_down, type_head; /* QMM_TYPE_* */
+    int max_batch;
+    int tp_rank, tp_size;                     /* tensor-parallel rank / world (1 = single GPU) */
+    unsigned long long seed;
+} qmm_decoder_config;
+
+/* Builds the model on the current device: allocates and fills weights (seeded closed-form normal,
+ * sigma 0.02, quantized on the device), KV cache (fp16, zeroed) and every activation buffer. */
+int qmm_decoder_create(const qmm_decoder_config* cfg, void** handle);
+int qmm_decoder_destroy(void* handle);
+/* packed weight bytes this rank streams per decoded token (all layers + head) */
+long qmm_decoder_weight_bytes(void* handle);
+/* device pointer and byte size of a tensor (norm weights are f32, matrices packed blocks) */
+int qmm_decoder_get_tensor(void* handle, int layer, int which, void** ptr, long* bytes);
+/* copies a tensor to host memory (synchronises the device); capacity in bytes */
+int qmm_decoder_read_tensor(void* handle, int layer, int which, void* host_dst, long capacity);
+/* fills the whole KV cache with seeded N(0,1) values (emulates a full context for benchmarks) */
+int qmm_decoder_fill_cache(void* handle, unsigned long long seed, void* stream);
+
+/* Tensor-parallel wiring.  Each rank exports the handle of its exchange area (64 bytes, a
+ * cudaIpcMemHandle_t), the host program gathers them, and every rank imports its peers'. */
+int qmm_decoder_ipc_export(void* handle, void* out_handle_64_bytes);
+int qmm_decoder_ipc_import(void* handle, int peer_rank, const void* handle_64_bytes);
+int qmm_decoder_tp_ready(void* handle); /* call once after all imports (uploads the pointer tables) */
+
+/* One decode step: tokens (device, batch ints) at position pos -> next_tokens (device, batch ints,
+ * greedy).  logits (optional, device, batch x vocab_local f32) receives this rank's slice of the
+ * logits.  With tensor parallelism the ranks exchange their slice's best candidate inside the
+ * step, so next_tokens holds the same global token on every rank; best (optional, device, batch
+ * f32) receives this rank's own best logit.  batch <= 1024. */
+int qmm_decoder_step(void* handle, const int* tokens, int batch, int pos, int* next_tokens, float* logits, float* best, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

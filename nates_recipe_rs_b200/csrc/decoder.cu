@@ -1,0 +1,520 @@
+// Decode engine: the caller-side glue of the quantized path, in the role examples/gemma4.rs plays
+// upstream (Arena::new: every activation buffer once, :231-271; layer(): the projection call sites,
+// :638-742; lm_head + sampling, :758-783, 1021-1057), for a Llama/Gemma-style decoder with
+// random-init GGUF-block weights.  One token per sequence per step; nothing is allocated after
+// qmm_decoder_create.  Tensor parallel: Q/K/V/gate/up split by output rows, O/down by input
+// columns; the partial outputs of a row-parallel projection are summed inside the next
+// residual-add + RMSNorm + Q8_1 kernel, which reads the peers' partial buffers directly.
+#include "qmm_formats.cuh"
+#include "../../include/qmm_decoder.h"
+#include <vector>
+#include <cstring>
+
+namespace qmm {
+
+int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, cudaStream_t stream);
+int quantize_weights_launch(int type, const float* w, void* out, long rows, int k, cudaStream_t stream);
+
+struct LayerWeights {
+    float *attn_norm, *ffn_norm;
+    uint8_t *wqk, *wv, *wo, *wgu, *wdown;
+};
+
+struct Decoder {
+    qmm_decoder_config c;
+    int dev;
+    int nq, nkv;          // local heads
+    int ffn_l, vocab_l;   // local ffn width and vocabulary slice
+    int qk_rows, v_rows, qkv_cols;
+    std::vector<LayerWeights> layers;
+    float* final_norm = nullptr;
+    uint8_t *head = nullptr, *embed = nullptr;  // embed == head when tp_size == 1
+    __half *kcache = nullptr, *vcache = nullptr;
+    // activations (allocated once)
+    float *x = nullptr, *qkv = nullptr, *gu = nullptr, *logits = nullptr, *attn_scratch = nullptr, *best_val = nullptr;
+    uint8_t *xq_h = nullptr, *xq_attn = nullptr, *xq_ffn = nullptr;
+    // tensor-parallel exchange area (one IPC-able allocation): partial outputs A (after O), B (after down), flags
+    uint8_t* xchg = nullptr;
+    size_t xchg_bytes = 0, part_bytes = 0, cand_bytes = 0;
+    Candidate** cand_dev = nullptr;            // device array of tp_size pointers to the ranks' candidate areas
+    float* part[2] = {nullptr, nullptr};
+    unsigned* flags = nullptr;                 // [2][tp_size] arrival counters written by the peers
+    std::vector<uint8_t*> peer_xchg;           // mapped peers (own entry = xchg)
+    const float** parts_dev[2] = {nullptr, nullptr};  // device arrays of tp_size pointers
+    unsigned** peer_flags_dev = nullptr;       // device array of tp_size pointers to the peers' flag areas
+    unsigned* step_counter = nullptr;          // device word: decode steps so far
+    int handshake_index = 0;                   // handshake number within the step being launched
+    int attn_splits = 1, attn_chunk = 0;
+    std::vector<void*> allocs;
+    long weight_bytes_per_token = 0;
+};
+
+static int type_row_bytes(int type, long k) {
+    switch (type) {
+    case QMM_TYPE_Q8_0: return (int)(k / 32 * Q8_0_BYTES);
+    case QMM_TYPE_Q4_K: return (int)(k / 256 * Q4_K_BYTES);
+    case QMM_TYPE_Q6_K: return (int)(k / 256 * Q6_K_BYTES);
+    }
+    return -1;
+}
+
+// rows x k slice of a (., k_full) matrix: element (r, c) = sigma * z(seed, (row0 + r) * k_full + col0 + c)
+__global__ void fill_normal_2d_kernel(float* out, long rows, int k, uint64_t seed, float sigma, long row0, int col0, int k_full) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * k) return;
+    const long r = i / k;
+    const int c = (int)(i - r * k);
+    const uint64_t h1 = mix64(seed * 0xD1342543DE82EF95ull + (uint64_t)((row0 + r) * (long)k_full + col0 + c));
+    const uint64_t h2 = mix64(h1);
+    int s = 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) s += (int)((h1 >> (16 * q)) & 0xFFFFu) + (int)((h2 >> (16 * q)) & 0xFFFFu);
+    out[i] = __fmul_rn(__fmul_rn((float)(s - 262140), __fdiv_rn(1.0f, 53510.0f)), sigma);
+}
+__global__ void add_scalar_kernel(float* x, long n, float v) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += v;
+}
+__global__ void f32_to_f16_kernel(const float* in, __half* out, long n) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2half_rn(in[i]);
+}
+
+template <typename T>
+static int dev_alloc(Decoder* d, T** p, size_t bytes) {
+    void* q = nullptr;
+    QMM_CUDA_TRY(cudaMalloc(&q, bytes ? bytes : 16));
+    d->allocs.push_back(q);
+    *p = static_cast<T*>(q);
+    return QMM_OK;
+}
+
+// Tensor ids for seeding and for qmm_decoder_get_tensor.
+static uint64_t tensor_seed(const Decoder* d, int layer, int which) {
+    return d->c.seed * 1000003ull + (uint64_t)(layer + 1) * 64ull + (uint64_t)which;
+}
+
+// Fills a packed (rows, k) matrix with quantized N(0, sigma) values.  Element (r, col) of the FULL
+// (unsharded) matrix is fill_normal(seed, r * k_full + col); a shard takes rows [row0, row0+rows) and
+// columns [col0, col0+k) of it, so every tensor-parallel layout holds the same model.
+static int init_matrix(Decoder* d, uint8_t* dst, int type, long rows, int k, long row0, int col0, int k_full, uint64_t seed, float* tmp,
+                       long tmp_elems, cudaStream_t s) {
+    const long rows_per = tmp_elems / k;
+    const int rb = type_row_bytes(type, k);
+    for (long r = 0; r < rows; r += rows_per) {
+        const long nr = rows - r < rows_per ? rows - r : rows_per;
+        const long n = nr * k;
+        fill_normal_2d_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(tmp, nr, k, seed, 0.02f, row0 + r, col0, k_full);
+        QMM_CUDA_TRY(cudaGetLastError());
+        if (int st = quantize_weights_launch(type, tmp, dst + (size_t)r * rb, nr, k, s)) return st;
+    }
+    return QMM_OK;
+}
+
+static int init_gamma(Decoder* d, float* g, int n, uint64_t seed, cudaStream_t s) {
+    fill_normal_kernel<<<(n + 255) / 256, 256, 0, s>>>(g, n, seed, 0.1f, 0);
+    add_scalar_kernel<<<(n + 255) / 256, 256, 0, s>>>(g, n, 1.0f);
+    QMM_CUDA_TRY(cudaGetLastError());
+    return QMM_OK;
+}
+
+static void destroy(Decoder* d) {
+    if (!d) return;
+    for (size_t r = 0; r < d->peer_xchg.size(); ++r)
+        if (d->peer_xchg[r] && d->peer_xchg[r] != d->xchg) cudaIpcCloseMemHandle(d->peer_xchg[r]);
+    for (void* p : d->allocs) cudaFree(p);
+    delete d;
+}
+
+static int create(const qmm_decoder_config* cfg, Decoder** out) {
+    const qmm_decoder_config& c = *cfg;
+    if (c.n_layers <= 0 || c.hidden <= 0 || c.head_dim <= 0 || c.n_q_heads <= 0 || c.n_kv_heads <= 0 || c.ffn <= 0 || c.vocab <= 0 ||
+        c.ctx_len <= 0 || c.max_batch <= 0 || c.tp_size <= 0 || c.tp_rank < 0 || c.tp_rank >= c.tp_size)
+        return QMM_ERR_SHAPE;
+    if (c.hidden % 256 || c.head_dim % 8 || c.head_dim > 256 || (c.n_q_heads * c.head_dim) % (256 * c.tp_size) || c.ffn % (256 * c.tp_size) ||
+        c.n_q_heads % c.n_kv_heads || c.n_kv_heads % c.tp_size || c.vocab % c.tp_size || c.hidden > NORM_MAX_PER_THREAD * 1024 ||
+        c.n_q_heads / c.n_kv_heads > ATTN_MAX_GROUP || c.tp_size > QMM_DECODER_MAX_TP)
+        return QMM_ERR_UNSUPPORTED;
+    Decoder* d = new Decoder();
+    d->c = c;
+    cudaGetDevice(&d->dev);
+    d->nq = c.n_q_heads / c.tp_size;
+    d->nkv = c.n_kv_heads / c.tp_size;
+    d->ffn_l = c.ffn / c.tp_size;
+    d->vocab_l = c.vocab / c.tp_size;
+    d->qk_rows = (d->nq + d->nkv) * c.head_dim;
+    d->v_rows = d->nkv * c.head_dim;
+    d->qkv_cols = (d->nq + 2 * d->nkv) * c.head_dim;
+    const int H = c.hidden, B = c.max_batch, hd = c.head_dim;
+    const int ao = d->nq * hd;  // local attention output width = K of the O projection shard
+    cudaStream_t s = nullptr;
+    int st = QMM_OK;
+#define TRY(e)                \
+    do {                      \
+        if ((st = (e)) != 0) { \
+            destroy(d);       \
+            return st;        \
+        }                     \
+    } while (0)
+    const long tmp_elems = 32l << 20;  // 128 MB of f32 staging for initialisation
+    float* tmp = nullptr;
+    TRY(dev_alloc(d, &tmp, tmp_elems * sizeof(float)));
+    const int r = c.tp_rank;
+    d->layers.resize(c.n_layers);
+    long per_token = 0;
+    for (int l = 0; l < c.n_layers; ++l) {
+        LayerWeights& L = d->layers[l];
+        TRY(dev_alloc(d, &L.attn_norm, H * sizeof(float)));
+        TRY(dev_alloc(d, &L.ffn_norm, H * sizeof(float)));
+        TRY(init_gamma(d, L.attn_norm, H, tensor_seed(d, l, QMM_T_ATTN_NORM), s));
+        TRY(init_gamma(d, L.ffn_norm, H, tensor_seed(d, l, QMM_T_FFN_NORM), s));
+        // [q heads | k heads] of this rank: rows of the full Wq then rows of the full Wk
+        const size_t qk_b = (size_t)d->qk_rows * type_row_bytes(c.type_attn_qk, H);
+        TRY(dev_alloc(d, &L.wqk, qk_b));
+        TRY(init_matrix(d, L.wqk, c.type_attn_qk, (long)d->nq * hd, H, (long)r * d->nq * hd, 0, H, tensor_seed(d, l, QMM_T_WQ), tmp, tmp_elems, s));
+        TRY(init_matrix(d, L.wqk + (size_t)d->nq * hd * type_row_bytes(c.type_attn_qk, H), c.type_attn_qk, (long)d->nkv * hd, H,
+                        (long)r * d->nkv * hd, 0, H, tensor_seed(d, l, QMM_T_WK), tmp, tmp_elems, s));
+        const size_t v_b = (size_t)d->v_rows * type_row_bytes(c.type_attn_v, H);
+        TRY(dev_alloc(d, &L.wv, v_b));
+        TRY(init_matrix(d, L.wv, c.type_attn_v, d->v_rows, H, (long)r * d->v_rows, 0, H, tensor_seed(d, l, QMM_T_WV), tmp, tmp_elems, s));
+        const size_t o_b = (size_t)H * type_row_bytes(c.type_attn_o, ao);
+        TRY(dev_alloc(d, &L.wo, o_b));
+        TRY(init_matrix(d, L.wo, c.type_attn_o, H, ao, 0, r * ao, c.n_q_heads * hd, tensor_seed(d, l, QMM_T_WO), tmp, tmp_elems, s));
+        const size_t gu_b = (size_t)2 * d->ffn_l * type_row_bytes(c.type_ffn_gate_up, H);
+        TRY(dev_alloc(d, &L.wgu, gu_b));
+        TRY(init_matrix(d, L.wgu, c.type_ffn_gate_up, d->ffn_l, H, (long)r * d->ffn_l, 0, H, tensor_seed(d, l, QMM_T_WGATE), tmp, tmp_elems, s));
+        TRY(init_matrix(d, L.wgu + (size_t)d->ffn_l * type_row_bytes(c.type_ffn_gate_up, H), c.type_ffn_gate_up, d->ffn_l, H,
+                        (long)r * d->ffn_l, 0, H, tensor_seed(d, l, QMM_T_WUP), tmp, tmp_elems, s));
+        const size_t dn_b = (size_t)H * type_row_bytes(c.type_ffn_down, d->ffn_l);
+        TRY(dev_alloc(d, &L.wdown, dn_b));
+        TRY(init_matrix(d, L.wdown, c.type_ffn_down, H, d->ffn_l, 0, r * d->ffn_l, c.ffn, tensor_seed(d, l, QMM_T_WDOWN), tmp, tmp_elems, s));
+        per_token += (long)(qk_b + v_b + o_b + gu_b + dn_b);
+    }
+    TRY(dev_alloc(d, &d->final_norm, H * sizeof(float)));
+    TRY(init_gamma(d, d->final_norm, H, tensor_seed(d, -1, QMM_T_FINAL_NORM), s));
+    const size_t head_b = (size_t)d->vocab_l * type_row_bytes(c.type_head, H);
+    TRY(dev_alloc(d, &d->head, head_b));
+    TRY(init_matrix(d, d->head, c.type_head, d->vocab_l, H, (long)r * d->vocab_l, 0, H, tensor_seed(d, -1, QMM_T_HEAD), tmp, tmp_elems, s));
+    per_token += (long)head_b;
+    if (c.tp_size == 1) {
+        d->embed = d->head;  // tied embedding
+    } else {                 // every rank needs every row of the embedding
+        TRY(dev_alloc(d, &d->embed, (size_t)c.vocab * type_row_bytes(c.type_head, H)));
+        TRY(init_matrix(d, d->embed, c.type_head, c.vocab, H, 0, 0, H, tensor_seed(d, -1, QMM_T_HEAD), tmp, tmp_elems, s));
+    }
+    d->weight_bytes_per_token = per_token;
+
+    const size_t cache_elems = (size_t)c.n_layers * B * c.ctx_len * d->nkv * hd;
+    TRY(dev_alloc(d, &d->kcache, cache_elems * sizeof(__half)));
+    TRY(dev_alloc(d, &d->vcache, cache_elems * sizeof(__half)));
+    QMM_CUDA_TRY(cudaMemsetAsync(d->kcache, 0, cache_elems * sizeof(__half), s));
+    QMM_CUDA_TRY(cudaMemsetAsync(d->vcache, 0, cache_elems * sizeof(__half), s));
+
+    TRY(dev_alloc(d, &d->x, (size_t)B * H * sizeof(float)));
+    TRY(dev_alloc(d, &d->qkv, (size_t)B * d->qkv_cols * sizeof(float)));
+    TRY(dev_alloc(d, &d->gu, (size_t)B * 2 * d->ffn_l * sizeof(float)));
+    TRY(dev_alloc(d, &d->logits, (size_t)B * d->vocab_l * sizeof(float)));
+    TRY(dev_alloc(d, &d->best_val, (size_t)B * sizeof(float)));
+    TRY(dev_alloc(d, &d->xq_h, (size_t)B * (H / 32) * Q8_1_BYTES));
+    TRY(dev_alloc(d, &d->xq_attn, (size_t)B * (ao / 32) * Q8_1_BYTES));
+    TRY(dev_alloc(d, &d->xq_ffn, (size_t)B * (d->ffn_l / 32) * Q8_1_BYTES));
+    // context splits: enough CTAs to pull the cache at HBM speed, chunks of at least 64 positions
+    const int sms = sm_count();
+    int splits = (2 * sms + d->nkv * B - 1) / (d->nkv * B);
+    const int max_splits = (c.ctx_len + 63) / 64;
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    d->attn_chunk = (((c.ctx_len + splits - 1) / splits) + 7) & ~7;
+    d->attn_splits = (c.ctx_len + d->attn_chunk - 1) / d->attn_chunk;
+    TRY(dev_alloc(d, &d->attn_scratch, (size_t)B * d->nq * d->attn_splits * (hd + 2) * sizeof(float)));
+
+    // exchange area: [part A][part B][token candidates][flags], 256-aligned pieces
+    d->part_bytes = (((size_t)B * H * sizeof(float)) + 255) & ~size_t(255);
+    d->cand_bytes = (((size_t)B * sizeof(Candidate)) + 255) & ~size_t(255);
+    d->xchg_bytes = 2 * d->part_bytes + d->cand_bytes + 256 * 2;
+    TRY(dev_alloc(d, &d->xchg, d->xchg_bytes));
+    QMM_CUDA_TRY(cudaMemsetAsync(d->xchg, 0, d->xchg_bytes, s));
+    d->part[0] = reinterpret_cast<float*>(d->xchg);
+    d->part[1] = reinterpret_cast<float*>(d->xchg + d->part_bytes);
+    d->flags = reinterpret_cast<unsigned*>(d->xchg + 2 * d->part_bytes + d->cand_bytes);
+    TRY(dev_alloc(d, &d->cand_dev, QMM_DECODER_MAX_TP * sizeof(Candidate*)));
+    d->peer_xchg.assign(c.tp_size, nullptr);
+    d->peer_xchg[r] = d->xchg;
+    TRY(dev_alloc(d, &d->parts_dev[0], QMM_DECODER_MAX_TP * sizeof(float*)));
+    TRY(dev_alloc(d, &d->parts_dev[1], QMM_DECODER_MAX_TP * sizeof(float*)));
+    TRY(dev_alloc(d, &d->peer_flags_dev, QMM_DECODER_MAX_TP * sizeof(unsigned*)));
+    TRY(dev_alloc(d, &d->step_counter, 256));
+    QMM_CUDA_TRY(cudaMemsetAsync(d->step_counter, 0, 256, s));
+    QMM_CUDA_TRY(cudaStreamSynchronize(s));
+#undef TRY
+    *out = d;
+    return QMM_OK;
+}
+
+
+template <typename... KArgs, typename... Args>
+static int launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap_enabled() ? 1 : 0;
+    QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...));
+    return QMM_OK;
+}
+
+static int norm_threads(int hidden) {
+    int t = (hidden + NORM_MAX_PER_THREAD - 1) / NORM_MAX_PER_THREAD;
+    t = (t + 31) & ~31;
+    if (t < 256) t = 256;
+    while (hidden % t != 0 && t < 1024) t += 32;  // whole warps of valid elements in every pass
+    return t > 1024 ? 1024 : t;
+}
+
+// residual add of the partial outputs in buffer `which` (or none), RMSNorm with gamma, Q8_1 into xq_h
+static int add_norm(Decoder* d, int which, const float* gamma, int batch, cudaStream_t s) {
+    const int tp = d->c.tp_size;
+    TpSync sync = {};
+    int n_parts = 0;
+    const float* const* parts = nullptr;
+    if (which >= 0) {
+        n_parts = tp;
+        parts = d->parts_dev[which];
+        if (tp > 1) {
+            sync.peer_flags = d->peer_flags_dev;
+            sync.my_flags = d->flags;
+            sync.rank = d->c.tp_rank;
+            sync.which = which;
+            sync.step_counter = d->step_counter;
+            sync.per_step = 2 * d->c.n_layers + 2;
+            sync.index = d->handshake_index++;
+        }
+    }
+    return launch_pdl(add_rmsnorm_q8_kernel, dim3(batch), dim3(norm_threads(d->c.hidden)), 0, s, d->x, parts, n_parts, (long)d->c.hidden,
+                      gamma, d->xq_h, d->c.hidden, d->c.rms_eps, sync);
+}
+
+static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tokens, float* logits_out, float* best_out, cudaStream_t s) {
+    const qmm_decoder_config& c = d->c;
+    if (!tokens || !next_tokens) return QMM_ERR_NULL;
+    if (batch <= 0 || batch > c.max_batch || pos < 0 || pos >= c.ctx_len) return QMM_ERR_SHAPE;
+    const int H = c.hidden, hd = c.head_dim, ao = d->nq * hd;
+    int st;
+#define TRY(e) \
+    do {       \
+        if ((st = (e)) != 0) return st; \
+    } while (0)
+    d->handshake_index = 0;
+    {   // embedding
+        const int rb = type_row_bytes(c.type_head, H);
+        const dim3 grid((H + 255) / 256, batch);
+        if (c.type_head == QMM_TYPE_Q6_K) TRY(launch_pdl(embed_rows_kernel<QMM_TYPE_Q6_K>, grid, dim3(256), 0, s, d->embed, tokens, d->x, H, rb, c.vocab, d->step_counter));
+        else if (c.type_head == QMM_TYPE_Q4_K) TRY(launch_pdl(embed_rows_kernel<QMM_TYPE_Q4_K>, grid, dim3(256), 0, s, d->embed, tokens, d->x, H, rb, c.vocab, d->step_counter));
+        else TRY(launch_pdl(embed_rows_kernel<QMM_TYPE_Q8_0>, grid, dim3(256), 0, s, d->embed, tokens, d->x, H, rb, c.vocab, d->step_counter));
+    }
+    const size_t cache_layer = (size_t)c.max_batch * c.ctx_len * d->nkv * hd;
+    const int len = pos + 1;
+    const int splits = (len + d->attn_chunk - 1) / d->attn_chunk;
+    const int group = d->nq / d->nkv;
+    const size_t attn_smem = (size_t)(group * hd + group * d->attn_chunk) * sizeof(float);
+    for (int l = 0; l < c.n_layers; ++l) {
+        const LayerWeights& L = d->layers[l];
+        TRY(add_norm(d, l == 0 ? -1 : 1, L.attn_norm, batch, s));
+        TRY(qmatvec_launch_strided(c.type_attn_qk, L.wqk, d->xq_h, d->qkv, d->qkv_cols, batch, d->qk_rows, H, s));
+        TRY(qmatvec_launch_strided(c.type_attn_v, L.wv, d->xq_h, d->qkv + d->qk_rows, d->qkv_cols, batch, d->v_rows, H, s));
+        __half* kc = d->kcache + (size_t)l * cache_layer;
+        __half* vc = d->vcache + (size_t)l * cache_layer;
+        TRY(launch_pdl(rope_kv_append_kernel, dim3(8, batch), dim3(256), 0, s, d->qkv, kc, vc, d->nq, d->nkv, hd, pos, c.ctx_len, c.rope_theta));
+        TRY(launch_pdl(attn_decode_split_kernel, dim3(d->nkv, batch, splits), dim3(ATTN_THREADS), attn_smem, s, (const float*)d->qkv,
+                       (const __half*)kc, (const __half*)vc, d->attn_scratch, d->nq, d->nkv, hd, len, c.ctx_len, d->attn_chunk, splits));
+        TRY(launch_pdl(attn_combine_q8_kernel, dim3((ao / 32 + 3) / 4, batch), dim3(128), 0, s, (const float*)d->attn_scratch, d->xq_attn,
+                       (float*)nullptr, d->nq, hd, splits));
+        TRY(qmatvec_launch_strided(c.type_attn_o, L.wo, d->xq_attn, d->part[0], H, batch, H, ao, s));
+        TRY(add_norm(d, 0, L.ffn_norm, batch, s));
+        TRY(qmatvec_launch_strided(c.type_ffn_gate_up, L.wgu, d->xq_h, d->gu, 2 * d->ffn_l, batch, 2 * d->ffn_l, H, s));
+        TRY(launch_pdl(act_mul_q8_kernel, dim3((d->ffn_l / 32 + 3) / 4, batch), dim3(128), 0, s, (const float*)d->gu, d->xq_ffn, d->ffn_l, c.act));
+        TRY(qmatvec_launch_strided(c.type_ffn_down, L.wdown, d->xq_ffn, d->part[1], H, batch, H, d->ffn_l, s));
+    }
+    TRY(add_norm(d, 1, d->final_norm, batch, s));
+    float* lg = logits_out ? logits_out : d->logits;
+    TRY(qmatvec_launch_strided(c.type_head, d->head, d->xq_h, lg, d->vocab_l, batch, d->vocab_l, H, s));
+    float* bv = best_out ? best_out : d->best_val;
+    TRY(launch_pdl(argmax_kernel, dim3(batch), dim3(1024), 0, s, (const float*)lg, next_tokens, d->vocab_l, c.tp_rank * d->vocab_l, bv));
+    if (c.tp_size > 1) {
+        TpSync sync = {};
+        sync.peer_flags = d->peer_flags_dev;
+        sync.my_flags = d->flags;
+        sync.rank = c.tp_rank;
+        sync.which = 2;
+        sync.step_counter = d->step_counter;
+        sync.per_step = 2 * c.n_layers + 2;
+        sync.index = d->handshake_index++;
+        TRY(launch_pdl(tp_pick_token_kernel, dim3(1), dim3(batch < 32 ? 32 : ((batch + 31) & ~31)), 0, s, (const float*)bv, next_tokens,
+                       (Candidate* const*)d->cand_dev, c.tp_size, batch, sync));
+    }
+#undef TRY
+    return QMM_OK;
+}
+
+}  // namespace qmm
+
+using namespace qmm;
+
+extern "C" {
+
+int qmm_decoder_create(const qmm_decoder_config* cfg, void** handle) {
+    if (!cfg || !handle) return QMM_ERR_NULL;
+    Decoder* d = nullptr;
+    const int st = create(cfg, &d);
+    if (st) return st;
+    // attention kernel: opt in to the shared memory its largest context split needs
+    const int group = d->nq / d->nkv;
+    const size_t attn_smem = (size_t)(group * cfg->head_dim + group * d->attn_chunk) * sizeof(float);
+    if (attn_smem > 200 * 1024) {
+        destroy(d);
+        return QMM_ERR_UNSUPPORTED;
+    }
+    if (cudaFuncSetAttribute(attn_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem) != cudaSuccess) {
+        destroy(d);
+        return cuda_fail(cudaGetLastError());
+    }
+    // single GPU: the pointer tables hold only this rank's buffers
+    if (cfg->tp_size == 1) {
+        const int rc = qmm_decoder_tp_ready(d);
+        if (rc) {
+            destroy(d);
+            return rc;
+        }
+    }
+    *handle = d;
+    return QMM_OK;
+}
+
+int qmm_decoder_destroy(void* handle) {
+    if (!handle) return QMM_ERR_NULL;
+    cudaDeviceSynchronize();
+    destroy(static_cast<Decoder*>(handle));
+    return QMM_OK;
+}
+
+long qmm_decoder_weight_bytes(void* handle) { return handle ? static_cast<Decoder*>(handle)->weight_bytes_per_token : QMM_ERR_NULL; }
+
+int qmm_decoder_get_tensor(void* handle, int layer, int which, void** ptr, long* bytes) {
+    if (!handle || !ptr || !bytes) return QMM_ERR_NULL;
+    Decoder* d = static_cast<Decoder*>(handle);
+    const qmm_decoder_config& c = d->c;
+    const int H = c.hidden, ao = d->nq * c.head_dim;
+    if (layer >= c.n_layers) return QMM_ERR_SHAPE;
+    if (layer >= 0) {
+        const LayerWeights& L = d->layers[layer];
+        switch (which) {
+        case QMM_T_ATTN_NORM: *ptr = L.attn_norm, *bytes = H * 4l; return QMM_OK;
+        case QMM_T_FFN_NORM: *ptr = L.ffn_norm, *bytes = H * 4l; return QMM_OK;
+        case QMM_T_WQ: *ptr = L.wqk, *bytes = (long)d->qk_rows * type_row_bytes(c.type_attn_qk, H); return QMM_OK;
+        case QMM_T_WV: *ptr = L.wv, *bytes = (long)d->v_rows * type_row_bytes(c.type_attn_v, H); return QMM_OK;
+        case QMM_T_WO: *ptr = L.wo, *bytes = (long)H * type_row_bytes(c.type_attn_o, ao); return QMM_OK;
+        case QMM_T_WGATE: *ptr = L.wgu, *bytes = 2l * d->ffn_l * type_row_bytes(c.type_ffn_gate_up, H); return QMM_OK;
+        case QMM_T_WDOWN: *ptr = L.wdown, *bytes = (long)H * type_row_bytes(c.type_ffn_down, d->ffn_l); return QMM_OK;
+        }
+        return QMM_ERR_TYPE;
+    }
+    switch (which) {
+    case QMM_T_FINAL_NORM: *ptr = d->final_norm, *bytes = H * 4l; return QMM_OK;
+    case QMM_T_HEAD: *ptr = d->head, *bytes = (long)d->vocab_l * type_row_bytes(c.type_head, H); return QMM_OK;
+    case QMM_T_EMBED: *ptr = d->embed, *bytes = (long)c.vocab * type_row_bytes(c.type_head, H); return QMM_OK;
+    }
+    return QMM_ERR_TYPE;
+}
+
+int qmm_decoder_read_tensor(void* handle, int layer, int which, void* host_dst, long capacity) {
+    void* p = nullptr;
+    long n = 0;
+    if (!host_dst) return QMM_ERR_NULL;
+    if (int st = qmm_decoder_get_tensor(handle, layer, which, &p, &n)) return st;
+    if (n > capacity) return QMM_ERR_SHAPE;
+    QMM_CUDA_TRY(cudaDeviceSynchronize());
+    QMM_CUDA_TRY(cudaMemcpy(host_dst, p, (size_t)n, cudaMemcpyDeviceToHost));
+    return QMM_OK;
+}
+
+int qmm_decoder_fill_cache(void* handle, unsigned long long seed, void* stream) {
+    if (!handle) return QMM_ERR_NULL;
+    Decoder* d = static_cast<Decoder*>(handle);
+    cudaStream_t s = as_stream(stream);
+    const size_t total = (size_t)d->c.n_layers * d->c.max_batch * d->c.ctx_len * d->nkv * d->c.head_dim;
+    const size_t chunk = 16u << 20;
+    float* tmp = nullptr;
+    QMM_CUDA_TRY(cudaMalloc(&tmp, chunk * sizeof(float)));
+    int rc = QMM_OK;
+    for (int which = 0; which < 2 && rc == QMM_OK; ++which) {
+        __half* dst = which ? d->vcache : d->kcache;
+        for (size_t off = 0; off < total; off += chunk) {
+            const long n = (long)(total - off < chunk ? total - off : chunk);
+            fill_normal_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(tmp, n, seed + which, 1.0f, (long)off);
+            f32_to_f16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(tmp, dst + off, n);
+            if (cudaGetLastError() != cudaSuccess) {
+                rc = cuda_fail(cudaErrorLaunchFailure);
+                break;
+            }
+        }
+    }
+    cudaStreamSynchronize(s);
+    cudaFree(tmp);
+    return rc;
+}
+
+int qmm_decoder_ipc_export(void* handle, void* out_handle_64_bytes) {
+    if (!handle || !out_handle_64_bytes) return QMM_ERR_NULL;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    QMM_CUDA_TRY(cudaIpcGetMemHandle(&h, static_cast<Decoder*>(handle)->xchg));
+    std::memcpy(out_handle_64_bytes, &h, 64);
+    return QMM_OK;
+}
+
+int qmm_decoder_ipc_import(void* handle, int peer_rank, const void* handle_64_bytes) {
+    if (!handle || !handle_64_bytes) return QMM_ERR_NULL;
+    Decoder* d = static_cast<Decoder*>(handle);
+    if (peer_rank < 0 || peer_rank >= d->c.tp_size) return QMM_ERR_SHAPE;
+    if (peer_rank == d->c.tp_rank) return QMM_OK;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle_64_bytes, 64);
+    void* p = nullptr;
+    QMM_CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    d->peer_xchg[peer_rank] = static_cast<uint8_t*>(p);
+    return QMM_OK;
+}
+
+int qmm_decoder_tp_ready(void* handle) {
+    if (!handle) return QMM_ERR_NULL;
+    Decoder* d = static_cast<Decoder*>(handle);
+    const int tp = d->c.tp_size;
+    const float* pa[QMM_DECODER_MAX_TP] = {};
+    const float* pb[QMM_DECODER_MAX_TP] = {};
+    unsigned* pf[QMM_DECODER_MAX_TP] = {};
+    Candidate* pc[QMM_DECODER_MAX_TP] = {};
+    for (int r = 0; r < tp; ++r) {
+        if (!d->peer_xchg[r]) return QMM_ERR_NULL;  // a peer has not been imported
+        pa[r] = reinterpret_cast<const float*>(d->peer_xchg[r]);
+        pb[r] = reinterpret_cast<const float*>(d->peer_xchg[r] + d->part_bytes);
+        pf[r] = reinterpret_cast<unsigned*>(d->peer_xchg[r] + 2 * d->part_bytes + d->cand_bytes);
+        pc[r] = reinterpret_cast<Candidate*>(d->peer_xchg[r] + 2 * d->part_bytes);
+    }
+    QMM_CUDA_TRY(cudaMemcpy(d->cand_dev, pc, sizeof(pc), cudaMemcpyHostToDevice));
+    QMM_CUDA_TRY(cudaMemcpy(d->parts_dev[0], pa, sizeof(pa), cudaMemcpyHostToDevice));
+    QMM_CUDA_TRY(cudaMemcpy(d->parts_dev[1], pb, sizeof(pb), cudaMemcpyHostToDevice));
+    QMM_CUDA_TRY(cudaMemcpy(d->peer_flags_dev, pf, sizeof(pf), cudaMemcpyHostToDevice));
+    return QMM_OK;
+}
+
+int qmm_decoder_step(void* handle, const int* tokens, int batch, int pos, int* next_tokens, float* logits, float* best, void* stream) {
+    if (!handle) return QMM_ERR_NULL;
+    return step(static_cast<Decoder*>(handle), tokens, batch, pos, next_tokens, logits, best, as_stream(stream));
+}
+
+}  // extern "C"

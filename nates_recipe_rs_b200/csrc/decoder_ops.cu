@@ -1,0 +1,418 @@
+// The small per-layer operators of the decode stack, fused so that every matvec finds its
+// activations already in Q8_1: counterparts of the upstream's f64 operators
+//   rmsnorm      normx_rmsnorm_kernel   gpu-core/src/kernels/normx.hip:135-159
+//   rope         rope_partial           gpu-core/src/kernels/f64_infer.hip:107-132 (rotary_dim == head_dim)
+//   attention    gqa_masked_attn        gpu-core/src/kernels/f64_infer.hip:49-100 (one query token, fp16 KV cache)
+//   gated act    gelu_mul / glu_gelu    gpu-core/src/kernels/f64_infer.hip:134-166
+//   add          add_kernel             gpu-core/src/kernels/elementwise.hip:13
+// in fp32 with fp16 KV, as the decode configurations ask.  All of them take part in
+// programmatic dependent launch so the following matvec can prefetch its weights.
+#include "qmm_formats.cuh"
+
+namespace qmm {
+
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+// out[i] = sigma * z(seed, first_index + i): sum of eight 16-bit uniforms, centred and scaled;
+// integer hashing only, so the CPU oracle reproduces every value bit for bit.
+__global__ void fill_normal_kernel(float* __restrict__ out, long n, uint64_t seed, float sigma, long first_index) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t h1 = mix64(seed * 0xD1342543DE82EF95ull + (uint64_t)(first_index + i));
+    const uint64_t h2 = mix64(h1);
+    int s = 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) s += (int)((h1 >> (16 * c)) & 0xFFFFu) + (int)((h2 >> (16 * c)) & 0xFFFFu);
+    const float z = __fmul_rn((float)(s - 262140), __fdiv_rn(1.0f, 53510.0f));
+    out[i] = __fmul_rn(z, sigma);
+}
+
+// x[b][:] = decoded row tokens[b] of a packed (vocab, hidden) matrix
+template <int TYPE>
+__global__ void embed_rows_kernel(const uint8_t* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x, int hidden,
+                                  int row_bytes, int vocab, unsigned* step_counter) {
+    using F = Fmt<TYPE, 1>;
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    if (step_counter && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *step_counter += 1;  // first kernel of a step
+    const int b = blockIdx.y;
+    int tok = tokens[b];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    const uint8_t* row = table + (size_t)tok * row_bytes;
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < hidden; e += gridDim.x * blockDim.x) {
+        const int blk = e / F::BLOCK_ELEMS;
+        x[(size_t)b * hidden + e] = dequant_elem<TYPE>(row + (size_t)blk * F::BLOCK_BYTES, e - blk * F::BLOCK_ELEMS);
+    }
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < nw) ? red[lane] : 0.f;
+    t = warp_sum(t);
+    __syncthreads();
+    return t;
+}
+
+__device__ __forceinline__ uint16_t f32_to_f16_bits_rn(float f) { return __half_as_ushort(__float2half_rn(f)); }
+
+// One Q8_1 block from the 32 values held one per lane (same arithmetic as quantize_q8_kernel).
+__device__ __forceinline__ void warp_store_q8_1(float v, uint8_t* blk, int lane) {
+    float amax = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const uint16_t dh = f32_to_f16_bits_rn(fminf(__fdiv_rn(amax, 127.0f), 65504.0f));
+    const float df = f16_bits_to_f32(dh);
+    int q = (df > 0.0f) ? (int)roundf(__fdiv_rn(v, df)) : 0;
+    q = q < -127 ? -127 : (q > 127 ? 127 : q);
+    blk[4 + lane] = (uint8_t)(int8_t)q;
+    int sum = q;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) {
+        *reinterpret_cast<uint16_t*>(blk) = dh;
+        *reinterpret_cast<uint16_t*>(blk + 2) = f32_to_f16_bits_rn(__fmul_rn(df, (float)sum));
+    }
+}
+
+// Residual update + RMSNorm + Q8_1 in one pass over a row, fused with the tensor-parallel sum:
+//   x += sum_{r < n_parts} part[r]          (n_parts = 0: no update.  The parts are the partial outputs of
+//                                            the preceding row-parallel projection, one per rank; the
+//                                            peers' buffers are read in place over NVLink)
+//   xq = Q8_1( x * rsqrt(mean(x^2) + eps) * gamma )
+// Handshake when n_parts > 1: CTA 0 publishes this rank's arrival number `seq` in every peer's flag
+// area (after a system-scope fence: its own partial was written by the preceding kernel), then every
+// CTA waits, with a bound, until all peers have published `seq` here.  Two partial buffers alternate
+// (after O, after down), so a buffer is rewritten only after a later handshake has shown that every
+// peer finished reading it.
+// One CTA per activation row, one element per thread per pass (hidden <= 8 * blockDim.x).
+constexpr int NORM_MAX_PER_THREAD = 8;
+struct TpSync {
+    unsigned* const* peer_flags;  // [n_parts] flag areas of all ranks (own included), each [3][QMM_TP_SLOTS]
+    unsigned* my_flags;
+    const unsigned* step_counter;  // device word, incremented once per decode step (graph replays included)
+    int rank, which;
+    int index, per_step;           // handshake number within a step, handshakes per step
+};
+constexpr int QMM_TP_SLOTS = 8;
+__global__ void add_rmsnorm_q8_kernel(float* __restrict__ x, const float* const* __restrict__ parts, int n_parts, long part_stride,
+                                      const float* __restrict__ gamma, uint8_t* __restrict__ xq, int hidden, float eps, TpSync tp) {
+    __shared__ float red[32];
+    __shared__ int peers_ok;
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    const int b = blockIdx.x, lane = threadIdx.x & 31;
+    if (n_parts > 1) {
+        const unsigned seq = *tp.step_counter * (unsigned)tp.per_step + (unsigned)tp.index;
+        if (threadIdx.x == 0) peers_ok = 1;
+        __syncthreads();
+        if (b == 0 && threadIdx.x < n_parts && (int)threadIdx.x != tp.rank) {
+            __threadfence_system();
+            *reinterpret_cast<volatile unsigned*>(tp.peer_flags[threadIdx.x] + tp.which * QMM_TP_SLOTS + tp.rank) = seq;
+        }
+        if (threadIdx.x < n_parts && (int)threadIdx.x != tp.rank) {
+            const volatile unsigned* f = tp.my_flags + tp.which * QMM_TP_SLOTS + threadIdx.x;
+            const long long t0 = clock64();
+            while ((int)(*f - seq) < 0) {
+                if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                    atomicExch(&g_device_status, DEV_TIMEOUT_PEER);
+                    peers_ok = 0;
+                    break;
+                }
+            }
+            __threadfence_system();
+        }
+        __syncthreads();
+        if (!peers_ok) return;
+    }
+    float* xr = x + (size_t)b * hidden;
+    float v[NORM_MAX_PER_THREAD];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_PER_THREAD; ++i) {
+        const int e = i * blockDim.x + threadIdx.x;
+        v[i] = 0.f;
+        if (e < hidden) {
+            float t = xr[e];
+            for (int r = 0; r < n_parts; ++r) t += __ldcv(parts[r] + (size_t)b * part_stride + e);  // never from a stale cache line
+            if (n_parts > 0) xr[e] = t;
+            v[i] = t;
+            ss += t * t;
+        }
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)hidden + eps);
+    uint8_t* qrow = xq + (size_t)b * (hidden / 32) * Q8_1_BYTES;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_PER_THREAD; ++i) {
+        const int e = i * blockDim.x + threadIdx.x;  // a warp covers 32 consecutive elements = one block
+        if (e < hidden) warp_store_q8_1(v[i] * inv * gamma[e], qrow + (size_t)(e >> 5) * Q8_1_BYTES, lane);
+    }
+}
+
+// NeoX rotary embedding of q (in place, fp32) and k, then k and v appended to the fp16 cache at `pos`.
+// qkv row layout: [q: nqh*hd | k: nkv*hd | v: nkv*hd].  cache layout: (batch, ctx_cap, nkv, hd).
+__global__ void rope_kv_append_kernel(float* __restrict__ qkv, __half* __restrict__ kcache, __half* __restrict__ vcache, int nqh, int nkv,
+                                      int hd, int pos, int ctx_cap, float theta) {
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    const int b = blockIdx.y;
+    const int half = hd / 2;
+    const int pairs = (nqh + nkv) * half;
+    float* row = qkv + (size_t)b * (nqh + 2 * nkv) * hd;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < pairs + nkv * hd; idx += gridDim.x * blockDim.x) {
+        if (idx < pairs) {
+            const int head = idx / half, i = idx - head * half;
+            const float freq = powf(theta, -2.0f * (float)i / (float)hd);
+            float sn, cs;
+            sincosf((float)pos * freq, &sn, &cs);
+            float* h = row + (size_t)head * hd;
+            const float a = h[i], c = h[i + half];
+            const float ra = a * cs - c * sn, rc = a * sn + c * cs;
+            if (head < nqh) {
+                h[i] = ra;
+                h[i + half] = rc;
+            } else {
+                __half* dst = kcache + (((size_t)b * ctx_cap + pos) * nkv + (head - nqh)) * hd;
+                dst[i] = __float2half_rn(ra);
+                dst[i + half] = __float2half_rn(rc);
+            }
+        } else {
+            const int j = idx - pairs;  // element of v
+            vcache[((size_t)b * ctx_cap + pos) * nkv * hd + j] = __float2half_rn(row[(size_t)(nqh + nkv) * hd + j]);
+        }
+    }
+}
+
+// Single-query GQA attention over the fp16 cache, split over the context: CTA (kv head, batch, split)
+// handles positions [split*chunk, ...) for the `group` query heads of its kv head and writes, per
+// query head, the running maximum, the sum of exponentials and the unnormalised output (hd floats)
+// to the scratch area; attn_combine_q8_kernel merges the splits.
+// scratch layout: (batch, nqh, splits, hd + 2) floats.
+constexpr int ATTN_THREADS = 128;
+constexpr int ATTN_MAX_GROUP = 8;
+__global__ void __launch_bounds__(ATTN_THREADS) attn_decode_split_kernel(const float* __restrict__ qkv, const __half* __restrict__ kcache,
+                                                                        const __half* __restrict__ vcache, float* __restrict__ scratch,
+                                                                        int nqh, int nkv, int hd, int len, int ctx_cap, int chunk,
+                                                                        int splits) {
+    extern __shared__ float att_sm[];  // q: group*hd | p: group*chunk
+    __shared__ float red[32];
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    const int kvh = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
+    const int group = nqh / nkv;
+    const int t0 = sp * chunk, t1 = min(len, t0 + chunk);
+    float* qs = att_sm;
+    float* ps = att_sm + group * hd;
+    const float scale = rsqrtf((float)hd);
+    const float* qrow = qkv + (size_t)b * (nqh + 2 * nkv) * hd + (size_t)kvh * group * hd;
+    for (int i = threadIdx.x; i < group * hd; i += blockDim.x) qs[i] = qrow[i] * scale;
+    __syncthreads();
+    const int nt = max(t1 - t0, 0);
+    // scores: one thread per position, all query heads of the group against one pass over the K row
+    float mx[ATTN_MAX_GROUP];
+#pragma unroll
+    for (int g = 0; g < ATTN_MAX_GROUP; ++g) mx[g] = -INFINITY;
+    for (int t = threadIdx.x; t < nt; t += blockDim.x) {
+        const uint4* kr = reinterpret_cast<const uint4*>(kcache + (((size_t)b * ctx_cap + t0 + t) * nkv + kvh) * hd);
+        float acc[ATTN_MAX_GROUP];
+#pragma unroll
+        for (int g = 0; g < ATTN_MAX_GROUP; ++g) acc[g] = 0.f;
+        for (int c = 0; c < hd / 8; ++c) {
+            const uint4 kk = kr[c];
+            const __half2* h2 = reinterpret_cast<const __half2*>(&kk);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h2[j]);
+#pragma unroll
+                for (int g = 0; g < ATTN_MAX_GROUP; ++g)
+                    if (g < group) acc[g] += f.x * qs[g * hd + 8 * c + 2 * j] + f.y * qs[g * hd + 8 * c + 2 * j + 1];
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < ATTN_MAX_GROUP; ++g)
+            if (g < group) {
+                ps[g * chunk + t] = acc[g];
+                mx[g] = fmaxf(mx[g], acc[g]);
+            }
+    }
+    // per query head: block max, exponentials, block sum
+    float lsum[ATTN_MAX_GROUP], gmax[ATTN_MAX_GROUP];
+#pragma unroll
+    for (int g = 0; g < ATTN_MAX_GROUP; ++g) {
+        lsum[g] = 0.f;
+        gmax[g] = -INFINITY;
+        if (g < group) {
+            float m = mx[g];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+            __syncthreads();
+            m = red[0];
+            for (int w = 1; w < (int)(blockDim.x >> 5); ++w) m = fmaxf(m, red[w]);
+            __syncthreads();
+            gmax[g] = m;
+            float s = 0.f;
+            for (int t = threadIdx.x; t < nt; t += blockDim.x) {
+                const float e = __expf(ps[g * chunk + t] - m);
+                ps[g * chunk + t] = e;
+                s += e;
+            }
+            lsum[g] = block_sum(s, red);
+        }
+    }
+    __syncthreads();
+    // outputs: thread d accumulates over the positions (coalesced across d)
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float o[ATTN_MAX_GROUP];
+#pragma unroll
+        for (int g = 0; g < ATTN_MAX_GROUP; ++g) o[g] = 0.f;
+        const __half* vr = vcache + (((size_t)b * ctx_cap + t0) * nkv + kvh) * hd + d;
+        for (int t = 0; t < nt; ++t) {
+            const float vv = __half2float(vr[(size_t)t * nkv * hd]);
+#pragma unroll
+            for (int g = 0; g < ATTN_MAX_GROUP; ++g)
+                if (g < group) o[g] += ps[g * chunk + t] * vv;
+        }
+#pragma unroll
+        for (int g = 0; g < ATTN_MAX_GROUP; ++g)
+            if (g < group) {
+                float* dst = scratch + (((size_t)b * nqh + kvh * group + g) * splits + sp) * (hd + 2);
+                dst[2 + d] = o[g];
+                if (d == 0) {
+                    dst[0] = gmax[g];
+                    dst[1] = lsum[g];
+                }
+            }
+    }
+}
+
+// Merge of the context splits + Q8_1 of the attention output (the activations of the O projection).
+// One warp per 32 output elements: grid (nqh*hd/32/warps_per_cta, batch).
+__global__ void attn_combine_q8_kernel(const float* __restrict__ scratch, uint8_t* __restrict__ xq, float* __restrict__ out_f32, int nqh,
+                                       int hd, int splits) {
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    const int b = blockIdx.y, lane = threadIdx.x & 31;
+    const int blk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // Q8_1 block index within the row
+    if (blk >= nqh * hd / 32) return;
+    const int e = blk * 32 + lane, head = e / hd, d = e - head * hd;
+    const float* src = scratch + ((size_t)b * nqh + head) * splits * (hd + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, src[(size_t)s * (hd + 2)]);
+    float den = 0.f, num = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float* ps = src + (size_t)s * (hd + 2);
+        const float wgt = (ps[1] > 0.f) ? __expf(ps[0] - m) : 0.f;
+        den += wgt * ps[1];
+        num += wgt * ps[2 + d];
+    }
+    const float v = den > 0.f ? num / den : 0.f;
+    if (out_f32) out_f32[(size_t)b * nqh * hd + e] = v;
+    warp_store_q8_1(v, xq + ((size_t)b * (nqh * hd / 32) + blk) * Q8_1_BYTES, lane);
+}
+
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+
+// gated activation on the fused [gate | up] projection output + Q8_1: act(gate) * up -> xq (ffn per row)
+__global__ void act_mul_q8_kernel(const float* __restrict__ gate_up, uint8_t* __restrict__ xq, int ffn, int act) {
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    const int b = blockIdx.y, lane = threadIdx.x & 31;
+    const int blk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (blk >= ffn / 32) return;
+    const float* row = gate_up + (size_t)b * 2 * ffn;
+    const float g = row[blk * 32 + lane], u = row[ffn + blk * 32 + lane];
+    const float a = act == 0 ? gelu_tanh_f(g) : g / (1.0f + __expf(-g));
+    warp_store_q8_1(a * u, xq + ((size_t)b * (ffn / 32) + blk) * Q8_1_BYTES, lane);
+}
+
+// argmax over a row of logits (first index wins ties); one CTA per row
+__global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, int index_offset, float* __restrict__ best_val) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    const int b = blockIdx.x;
+    const float* row = logits + (size_t)b * vocab;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (v > bv) bv = v, bi = i;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+    }
+    if ((threadIdx.x & 31) == 0) sv[threadIdx.x >> 5] = bv, si[threadIdx.x >> 5] = bi;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) bv = sv[w], bi = si[w];
+        out[b] = bi + index_offset;
+        if (best_val) best_val[b] = bv;
+    }
+}
+
+// Tensor-parallel greedy pick: every rank has the argmax of its vocabulary slice (global index and
+// value) in cand[rank]; after the same bounded handshake as the residual kernel each rank reads all
+// candidates and keeps the best (lowest index on ties), so all ranks continue with the same token.
+// cand areas: per rank `max_batch` pairs {float value, int index}.  One CTA, one thread per row.
+struct Candidate {
+    float value;
+    int index;
+};
+__global__ void tp_pick_token_kernel(const float* __restrict__ best_val, int* __restrict__ tokens_io, Candidate* const* __restrict__ cand,
+                                     int n_ranks, int batch, TpSync tp) {
+    __shared__ int peers_ok;
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    const unsigned seq = *tp.step_counter * (unsigned)tp.per_step + (unsigned)tp.index;
+    if (threadIdx.x == 0) peers_ok = 1;
+    if ((int)threadIdx.x < batch) {
+        Candidate c;
+        c.value = best_val[threadIdx.x];
+        c.index = tokens_io[threadIdx.x];
+        cand[tp.rank][threadIdx.x] = c;
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < n_ranks && (int)threadIdx.x != tp.rank) {
+        __threadfence_system();
+        *reinterpret_cast<volatile unsigned*>(tp.peer_flags[threadIdx.x] + tp.which * QMM_TP_SLOTS + tp.rank) = seq;
+        const volatile unsigned* f = tp.my_flags + tp.which * QMM_TP_SLOTS + threadIdx.x;
+        const long long t0 = clock64();
+        while ((int)(*f - seq) < 0) {
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                atomicExch(&g_device_status, DEV_TIMEOUT_PEER);
+                peers_ok = 0;
+                break;
+            }
+        }
+        __threadfence_system();
+    }
+    __syncthreads();
+    if (!peers_ok || (int)threadIdx.x >= batch) return;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int r = 0; r < n_ranks; ++r) {
+        const volatile Candidate* c = cand[r] + threadIdx.x;
+        const float v = c->value;
+        const int i = c->index;
+        if (v > bv || (v == bv && i < bi)) bv = v, bi = i;
+    }
+    tokens_io[threadIdx.x] = bi;
+}
+
+}  // namespace qmm

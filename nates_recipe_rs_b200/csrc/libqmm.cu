@@ -4,3 +4,5 @@
 #include "quantize.cu"
 #include "qmatvec.cu"
 #include "qgemm.cu"
+#include "decoder_ops.cu"
+#include "decoder.cu"

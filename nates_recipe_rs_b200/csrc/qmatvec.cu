@@ -33,6 +33,7 @@ struct MatvecParams {
     const uint8_t* w;
     const uint8_t* xq;
     float* y;
+    long y_stride;    // floats between output rows (>= n)
     int m;            // activation rows in this launch (<= M of the instantiation)
     int n, k;
     int row_bytes;    // packed bytes of one weight row
@@ -155,7 +156,7 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
                 const float* src = ps + (size_t)r * p.kw * M + mi;
                 float acc = 0.f;
                 for (int q = 0; q < p.kw; ++q) acc += src[q * M];
-                if (mi < p.m) yrow[(size_t)mi * p.n + r] = acc;
+                if (mi < p.m) yrow[(size_t)mi * p.y_stride + r] = acc;
             }
         }
         issued = __shfl_sync(0xffffffffu, issued, 0);
@@ -345,8 +346,15 @@ static int launch_p(const MatvecParams& p, int passes, int grid, int threads, si
     return launch_m<TYPE, UW, 1>(p, grid, threads, smem, mtile, rb, stream);
 }
 
+int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, cudaStream_t stream);
 int qmatvec_launch(int type, const void* w, const void* xq, float* y, int m, int n, int k, cudaStream_t stream) {
+    return qmatvec_launch_strided(type, w, xq, y, n, m, n, k, stream);
+}
+
+// y_stride: floats between consecutive output rows (lets several projections write slices of one row)
+int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, cudaStream_t stream) {
     if (!w || !xq || !y) return QMM_ERR_NULL;
+    if (y_stride < n) return QMM_ERR_SHAPE;
     int block_elems, block_bytes, unit_elems, w_align;
     if (int st = type_geometry(type, block_elems, block_bytes, unit_elems, w_align)) return st;
     if (m <= 0 || n <= 0 || k <= 0 || k % block_elems != 0) return QMM_ERR_SHAPE;
@@ -374,7 +382,8 @@ int qmatvec_launch(int type, const void* w, const void* xq, float* y, int m, int
         const int mt = left >= 3 ? 4 : left;  // register tile of 1, 2 or 4 activation rows
         p.m = left < mt ? left : mt;
         p.xq = static_cast<const uint8_t*>(xq) + (size_t)m0 * p.xq_row_bytes;
-        p.y = y + (size_t)m0 * n;
+        p.y = y + (size_t)m0 * y_stride;
+        p.y_stride = y_stride;
 
         // Q4_K unit width: the widest unit that keeps the activation registers within budget
         // (UW * M <= 2 unless forced) and at least 7/8 of the lanes busy; other formats use 1.

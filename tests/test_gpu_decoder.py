@@ -1,0 +1,129 @@
+"""Decode engine against a numpy composition of the CPU oracle's pieces on the engine's own
+packed weights.  Needs a B200."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def tiny_cfg(dec, **kw):
+    c = dict(n_layers=2, hidden=256, n_q_heads=4, n_kv_heads=2, head_dim=64, ffn=512, vocab=1024, ctx_len=48,
+             rope_theta=10000.0, rms_eps=1e-6, act=dec.ACT_GELU_TANH, type_attn_qk=oracle.Q4_K, type_attn_v=oracle.Q6_K,
+             type_attn_o=oracle.Q4_K, type_ffn_gate_up=oracle.Q4_K, type_ffn_down=oracle.Q6_K, type_head=oracle.Q6_K,
+             max_batch=3, tp_rank=0, tp_size=1, seed=77)
+    c.update(kw)
+    return dec.DecoderConfig(**c)
+
+
+class RefModel:
+    """Straight-loop restatement of one decode step from oracle pieces."""
+
+    def __init__(self, d, dec):
+        c = d.cfg
+        self.c, self.dec = c, dec
+        H = c.hidden
+        f32 = lambda b: b.view(np.float32)
+        self.layers = []
+        for l in range(c.n_layers):
+            self.layers.append(dict(
+                attn_norm=f32(d.tensor(l, dec.T_ATTN_NORM)), ffn_norm=f32(d.tensor(l, dec.T_FFN_NORM)),
+                wqk=d.tensor(l, dec.T_WQK), wv=d.tensor(l, dec.T_WV), wo=d.tensor(l, dec.T_WO), wgu=d.tensor(l, dec.T_WGU),
+                wdown=d.tensor(l, dec.T_WDOWN)))
+        self.final_norm = f32(d.tensor(-1, dec.T_FINAL_NORM))
+        self.head = d.tensor(-1, dec.T_HEAD)
+        hd = c.head_dim
+        self.kc = np.zeros((c.n_layers, c.max_batch, c.ctx_len, c.n_kv_heads, hd), dtype=np.float16)
+        self.vc = np.zeros_like(self.kc)
+
+    def q8(self, v):
+        return oracle.quantize(oracle.Q8_1, v.reshape(1, -1)).reshape(-1)
+
+    def step(self, b, token, pos):
+        c = self.c
+        H, hd, nq, nkv = c.hidden, c.head_dim, c.n_q_heads, c.n_kv_heads
+        rb = oracle.row_bytes(c.type_head, H)
+        x = oracle.dequantize(c.type_head, self.head[token * rb:(token + 1) * rb], H).reshape(-1).copy()
+        for l, L in enumerate(self.layers):
+            xq = self.q8(oracle.rmsnorm(x[None], L["attn_norm"], c.rms_eps)[0])
+            qk = oracle.matvec(c.type_attn_qk, L["wqk"], xq, H)[0]
+            v = oracle.matvec(c.type_attn_v, L["wv"], xq, H)[0]
+            q = oracle.rope_neox(qk[:nq * hd], hd, nq, pos, c.rope_theta)           # rows = heads of one token at `pos`
+            k = oracle.rope_neox(qk[nq * hd:], hd, nkv, pos, c.rope_theta)
+            self.kc[l, b, pos] = k.reshape(nkv, hd).astype(np.float16)
+            self.vc[l, b, pos] = v.reshape(nkv, hd).astype(np.float16)
+            att = oracle.attn_decode(q, self.kc[l, b], self.vc[l, b], nq, nkv, hd, pos + 1)
+            x = x + oracle.matvec(c.type_attn_o, L["wo"], self.q8(att), nq * hd)[0]
+            xq = self.q8(oracle.rmsnorm(x[None], L["ffn_norm"], c.rms_eps)[0])
+            gu = oracle.matvec(c.type_ffn_gate_up, L["wgu"], xq, H)[0]
+            act = oracle.gelu_mul if c.act == self.dec.ACT_GELU_TANH else oracle.silu_mul
+            hq = self.q8(act(gu[:c.ffn], gu[c.ffn:]))
+            x = x + oracle.matvec(c.type_ffn_down, L["wdown"], hq, c.ffn)[0]
+        xq = self.q8(oracle.rmsnorm(x[None], self.final_norm, c.rms_eps)[0])
+        return oracle.matvec(c.type_head, self.head, xq, H)[0]
+
+
+@pytest.fixture(scope="module")
+def dec():
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device")
+    from nates_recipe_rs_b200 import decoder
+    return decoder
+
+
+def test_model_bytes_are_the_seeded_quantized_normal(dec):
+    """The engine's weights are reproducible on the CPU: fill_normal(seed, index) quantized by the oracle."""
+    d = dec.Decoder(tiny_cfg(dec))
+    c = d.cfg
+    seed = lambda layer, which: (c.seed * 1000003 + (layer + 1) * 64 + which) & ((1 << 64) - 1)
+    got = d.tensor(1, dec.T_WDOWN)
+    want = oracle.quantize(c.type_ffn_down, oracle.fill_normal(c.hidden * c.ffn, seed(1, 8), 0.02).reshape(c.hidden, c.ffn)).reshape(-1)
+    assert np.array_equal(got, want)
+    got = d.tensor(0, dec.T_WQK)
+    rows_q = c.n_q_heads * c.head_dim
+    wq = oracle.quantize(c.type_attn_qk, oracle.fill_normal(rows_q * c.hidden, seed(0, 1), 0.02).reshape(rows_q, c.hidden)).reshape(-1)
+    assert np.array_equal(got[:wq.size], wq)
+    g = d.tensor(0, dec.T_ATTN_NORM).view(np.float32)
+    assert np.array_equal(g, oracle.fill_normal(c.hidden, seed(0, 0), 0.1) + np.float32(1.0))
+    d.close()
+
+
+@pytest.mark.parametrize("act", ["gelu", "silu"])
+def test_decode_steps_match_reference(dec, act):
+    d = dec.Decoder(tiny_cfg(dec, act=dec.ACT_GELU_TANH if act == "gelu" else dec.ACT_SILU))
+    c = d.cfg
+    ref = RefModel(d, dec)
+    from nates_recipe_rs_b200 import quant_ops as ops
+    B = c.max_batch
+    toks = np.array([5, 700, 123], dtype=np.int32)
+    logits = torch.empty(B, c.vocab, device="cuda")
+    for pos in range(6):
+        d.tokens.copy_(torch.from_numpy(toks))
+        d.step(B, pos, logits)
+        ops.check_launch()
+        got = logits.cpu().numpy()
+        nxt = d.next_tokens.cpu().numpy()
+        new = []
+        for b in range(B):
+            want = ref.step(b, int(toks[b]), pos)
+            scale = np.abs(want).max()
+            assert np.abs(got[b] - want).max() <= 2e-2 * scale, (pos, b, float(np.abs(got[b] - want).max()), float(scale))
+            assert int(nxt[b]) == int(np.argmax(got[b]))
+            top2 = np.sort(want)[-2:]
+            if top2[1] - top2[0] > 4e-2 * scale:
+                assert int(nxt[b]) == int(np.argmax(want))
+            new.append(int(np.argmax(want)))      # both sides continue from the reference's token
+        toks = np.array(new, dtype=np.int32)
+    d.close()
+
+
+def test_step_rejects_bad_arguments(dec):
+    d = dec.Decoder(tiny_cfg(dec))
+    from nates_recipe_rs_b200._lib import QmmError
+    with pytest.raises(QmmError):
+        d.step(4, 0)            # batch above max_batch
+    with pytest.raises(QmmError):
+        d.step(1, 48)           # position beyond the context
+    d.close()
