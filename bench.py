@@ -316,6 +316,7 @@ def run_ours(args):
     q4_algo = q4_bytes + (HID // 32 * 36 * 2 + FFN // 32 * 36) / 3 + (FFN * 4 * 2 + HID * 4) / 3
     achieved = q4_algo / (q4_us * 1e-6) / 1e9
 
+    decode = None if args.no_decode else run_decode(world, rank, dev, args.quick_decode)
     if rank == 0:
         cpu, _ = cpu_time_sample() if world == 1 else (None, None)
         out = {
@@ -337,9 +338,75 @@ def run_ours(args):
         }
         if cpu:
             out["cpu_baseline"] = cpu
+        if decode is not None:
+            out["decode"] = decode
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_decode(world, rank, dev, quick):
+    """Greedy decode tok/s of the random-init 8B- and 70B-class stacks (BASELINE configs[3], [4]):
+    whole steps (embedding .. argmax) captured as a CUDA graph, KV cache filled with seeded values,
+    positions at the end of the context.  Tensor parallel over all ranks when world > 1."""
+    import torch
+    import torch.distributed as dist
+    from nates_recipe_rs_b200 import decoder as dec, quant_ops as ops
+    cases = [("8b", 1), ("8b", 16), ("70b", 1), ("70b", 8)]
+    if quick:
+        cases = [("8b", 1)]
+    out = []
+    for name, batch in cases:
+        make = dec.config_8b if name == "8b" else dec.config_70b
+        cfg = make(max_batch=batch, tp_rank=rank, tp_size=world)
+        if cfg.n_kv_heads % world != 0:
+            continue
+        try:
+            d = dec.Decoder(cfg)
+        except Exception as e:  # e.g. not enough memory for the 70B stack on this GPU
+            out.append({"stack": name, "batch": batch, "error": f"{type(e).__name__}: {e}"[:120]})
+            continue
+        d.fill_cache(3)
+        steps_per_graph = 8
+        pos0 = cfg.ctx_len - steps_per_graph - 1
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            d.tokens.fill_(11)
+
+            def body():
+                for i in range(steps_per_graph):
+                    d.step(batch, pos0 + i)
+                    d.tokens.copy_(d.next_tokens)
+            body()
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                body()
+            graph.replay()
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 4
+            e0.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e-3 / (reps * steps_per_graph)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec = float(t.item())
+        ops.check_launch()
+        wb = d.weight_bytes * world
+        out.append({"stack": name, "batch": batch, "context": cfg.ctx_len, "ms_per_step": sec * 1e3, "tok_s": batch / sec,
+                    "weight_GB_per_token": wb / 1e9, "weight_GBps": wb / sec / 1e9, "tp": world})
+        d.close()
+        del d
+        torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -348,6 +415,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode tok/s section")
+    ap.add_argument("--quick-decode", action="store_true", help="decode section: 8B batch 1 only")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -15,6 +15,8 @@ namespace qmm {
 int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, cudaStream_t stream);
 int quantize_weights_launch(int type, const float* w, void* out, long rows, int k, cudaStream_t stream);
 
+constexpr int ARGMAX_PARTS = 256;
+
 struct LayerWeights {
     float *attn_norm, *ffn_norm;
     uint8_t *wqk, *wv, *wo, *wgu, *wdown;
@@ -40,7 +42,8 @@ struct Decoder {
     float* part[2] = {nullptr, nullptr};
     unsigned* flags = nullptr;                 // [2][tp_size] arrival counters written by the peers
     std::vector<uint8_t*> peer_xchg;           // mapped peers (own entry = xchg)
-    const float** parts_dev[2] = {nullptr, nullptr};  // device arrays of tp_size pointers
+    PartPtrs parts_host[2] = {};               // the ranks' partial buffers A and B (own included)
+    Candidate* argmax_cand = nullptr;          // argmax stage-one candidates: max_batch x ARGMAX_PARTS
     unsigned** peer_flags_dev = nullptr;       // device array of tp_size pointers to the peers' flag areas
     unsigned* step_counter = nullptr;          // device word: decode steps so far
     int handshake_index = 0;                   // handshake number within the step being launched
@@ -218,14 +221,13 @@ static int create(const qmm_decoder_config* cfg, Decoder** out) {
     TRY(dev_alloc(d, &d->xq_h, (size_t)B * (H / 32) * Q8_1_BYTES));
     TRY(dev_alloc(d, &d->xq_attn, (size_t)B * (ao / 32) * Q8_1_BYTES));
     TRY(dev_alloc(d, &d->xq_ffn, (size_t)B * (d->ffn_l / 32) * Q8_1_BYTES));
-    // context splits: enough CTAs to pull the cache at HBM speed, chunks of at least 64 positions
-    const int sms = sm_count();
-    int splits = (2 * sms + d->nkv * B - 1) / (d->nkv * B);
-    const int max_splits = (c.ctx_len + 63) / 64;
-    if (splits > max_splits) splits = max_splits;
-    if (splits < 1) splits = 1;
-    d->attn_chunk = (((c.ctx_len + splits - 1) / splits) + 7) & ~7;
-    d->attn_splits = (c.ctx_len + d->attn_chunk - 1) / d->attn_chunk;
+    // context splits of ATTN_CHUNK positions
+    d->attn_chunk = ATTN_CHUNK;
+    d->attn_splits = (c.ctx_len + ATTN_CHUNK - 1) / ATTN_CHUNK;
+    if (d->attn_splits > ATTN_MAX_SPLITS) {
+        destroy(d);
+        return QMM_ERR_UNSUPPORTED;
+    }
     TRY(dev_alloc(d, &d->attn_scratch, (size_t)B * d->nq * d->attn_splits * (hd + 2) * sizeof(float)));
 
     // exchange area: [part A][part B][token candidates][flags], 256-aligned pieces
@@ -240,8 +242,7 @@ static int create(const qmm_decoder_config* cfg, Decoder** out) {
     TRY(dev_alloc(d, &d->cand_dev, QMM_DECODER_MAX_TP * sizeof(Candidate*)));
     d->peer_xchg.assign(c.tp_size, nullptr);
     d->peer_xchg[r] = d->xchg;
-    TRY(dev_alloc(d, &d->parts_dev[0], QMM_DECODER_MAX_TP * sizeof(float*)));
-    TRY(dev_alloc(d, &d->parts_dev[1], QMM_DECODER_MAX_TP * sizeof(float*)));
+    TRY(dev_alloc(d, &d->argmax_cand, (size_t)B * ARGMAX_PARTS * sizeof(Candidate)));
     TRY(dev_alloc(d, &d->peer_flags_dev, QMM_DECODER_MAX_TP * sizeof(unsigned*)));
     TRY(dev_alloc(d, &d->step_counter, 256));
     QMM_CUDA_TRY(cudaMemsetAsync(d->step_counter, 0, 256, s));
@@ -269,11 +270,11 @@ static int launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem
 }
 
 static int norm_threads(int hidden) {
-    int t = (hidden + NORM_MAX_PER_THREAD - 1) / NORM_MAX_PER_THREAD;
-    t = (t + 31) & ~31;
-    if (t < 256) t = 256;
-    while (hidden % t != 0 && t < 1024) t += 32;  // whole warps of valid elements in every pass
-    return t > 1024 ? 1024 : t;
+    // whole warps of valid elements in every pass (hidden is a multiple of 256): 1024 threads when they
+    // divide the row, else the largest multiple of 256 that does
+    for (int t = 1024; t >= 256; t -= 256)
+        if (hidden % t == 0 && hidden <= NORM_MAX_PER_THREAD * t) return t;
+    return 256;
 }
 
 // residual add of the partial outputs in buffer `which` (or none), RMSNorm with gamma, Q8_1 into xq_h
@@ -281,10 +282,10 @@ static int add_norm(Decoder* d, int which, const float* gamma, int batch, cudaSt
     const int tp = d->c.tp_size;
     TpSync sync = {};
     int n_parts = 0;
-    const float* const* parts = nullptr;
+    PartPtrs parts = {};
     if (which >= 0) {
         n_parts = tp;
-        parts = d->parts_dev[which];
+        parts = d->parts_host[which];
         if (tp > 1) {
             sync.peer_flags = d->peer_flags_dev;
             sync.my_flags = d->flags;
@@ -321,7 +322,7 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
     const int len = pos + 1;
     const int splits = (len + d->attn_chunk - 1) / d->attn_chunk;
     const int group = d->nq / d->nkv;
-    const size_t attn_smem = (size_t)(group * hd + group * d->attn_chunk) * sizeof(float);
+    const size_t attn_smem = (size_t)ATTN_CHUNK * (2 * hd + 8) * sizeof(__half) + (size_t)group * (hd + ATTN_CHUNK + 2) * sizeof(float);
     for (int l = 0; l < c.n_layers; ++l) {
         const LayerWeights& L = d->layers[l];
         TRY(add_norm(d, l == 0 ? -1 : 1, L.attn_norm, batch, s));
@@ -331,8 +332,8 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
         __half* vc = d->vcache + (size_t)l * cache_layer;
         TRY(launch_pdl(rope_kv_append_kernel, dim3(8, batch), dim3(256), 0, s, d->qkv, kc, vc, d->nq, d->nkv, hd, pos, c.ctx_len, c.rope_theta));
         TRY(launch_pdl(attn_decode_split_kernel, dim3(d->nkv, batch, splits), dim3(ATTN_THREADS), attn_smem, s, (const float*)d->qkv,
-                       (const __half*)kc, (const __half*)vc, d->attn_scratch, d->nq, d->nkv, hd, len, c.ctx_len, d->attn_chunk, splits));
-        TRY(launch_pdl(attn_combine_q8_kernel, dim3((ao / 32 + 3) / 4, batch), dim3(128), 0, s, (const float*)d->attn_scratch, d->xq_attn,
+                       (const __half*)kc, (const __half*)vc, d->attn_scratch, d->nq, d->nkv, hd, len, c.ctx_len, splits));
+        TRY(launch_pdl(attn_combine_q8_kernel, dim3(d->nq, batch), dim3(hd < 128 ? hd : 128), 0, s, (const float*)d->attn_scratch, d->xq_attn,
                        (float*)nullptr, d->nq, hd, splits));
         TRY(qmatvec_launch_strided(c.type_attn_o, L.wo, d->xq_attn, d->part[0], H, batch, H, ao, s));
         TRY(add_norm(d, 0, L.ffn_norm, batch, s));
@@ -344,7 +345,9 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
     float* lg = logits_out ? logits_out : d->logits;
     TRY(qmatvec_launch_strided(c.type_head, d->head, d->xq_h, lg, d->vocab_l, batch, d->vocab_l, H, s));
     float* bv = best_out ? best_out : d->best_val;
-    TRY(launch_pdl(argmax_kernel, dim3(batch), dim3(1024), 0, s, (const float*)lg, next_tokens, d->vocab_l, c.tp_rank * d->vocab_l, bv));
+    TRY(launch_pdl(argmax_partial_kernel, dim3(ARGMAX_PARTS, batch), dim3(256), 0, s, (const float*)lg, d->argmax_cand, d->vocab_l));
+    TRY(launch_pdl(argmax_final_kernel, dim3(batch), dim3(256), 0, s, (const Candidate*)d->argmax_cand, ARGMAX_PARTS, next_tokens,
+                   c.tp_rank * d->vocab_l, bv));
     if (c.tp_size > 1) {
         TpSync sync = {};
         sync.peer_flags = d->peer_flags_dev;
@@ -374,7 +377,8 @@ int qmm_decoder_create(const qmm_decoder_config* cfg, void** handle) {
     if (st) return st;
     // attention kernel: opt in to the shared memory its largest context split needs
     const int group = d->nq / d->nkv;
-    const size_t attn_smem = (size_t)(group * cfg->head_dim + group * d->attn_chunk) * sizeof(float);
+    const size_t attn_smem = (size_t)ATTN_CHUNK * (2 * cfg->head_dim + 8) * sizeof(__half) +
+                             (size_t)group * (cfg->head_dim + ATTN_CHUNK + 2) * sizeof(float);
     if (attn_smem > 200 * 1024) {
         destroy(d);
         return QMM_ERR_UNSUPPORTED;
@@ -506,8 +510,7 @@ int qmm_decoder_tp_ready(void* handle) {
         pc[r] = reinterpret_cast<Candidate*>(d->peer_xchg[r] + 2 * d->part_bytes);
     }
     QMM_CUDA_TRY(cudaMemcpy(d->cand_dev, pc, sizeof(pc), cudaMemcpyHostToDevice));
-    QMM_CUDA_TRY(cudaMemcpy(d->parts_dev[0], pa, sizeof(pa), cudaMemcpyHostToDevice));
-    QMM_CUDA_TRY(cudaMemcpy(d->parts_dev[1], pb, sizeof(pb), cudaMemcpyHostToDevice));
+    for (int r = 0; r < QMM_DECODER_MAX_TP; ++r) d->parts_host[0].p[r] = pa[r], d->parts_host[1].p[r] = pb[r];
     QMM_CUDA_TRY(cudaMemcpy(d->peer_flags_dev, pf, sizeof(pf), cudaMemcpyHostToDevice));
     return QMM_OK;
 }

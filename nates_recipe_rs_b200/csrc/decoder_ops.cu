@@ -94,6 +94,9 @@ __device__ __forceinline__ void warp_store_q8_1(float v, uint8_t* blk, int lane)
 // peer finished reading it.
 // One CTA per activation row, one element per thread per pass (hidden <= 8 * blockDim.x).
 constexpr int NORM_MAX_PER_THREAD = 8;
+struct PartPtrs {
+    const float* p[8];  // the ranks' partial-output buffers (own included), passed by value: no pointer chase
+};
 struct TpSync {
     unsigned* const* peer_flags;  // [n_parts] flag areas of all ranks (own included), each [3][QMM_TP_SLOTS]
     unsigned* my_flags;
@@ -102,7 +105,7 @@ struct TpSync {
     int index, per_step;           // handshake number within a step, handshakes per step
 };
 constexpr int QMM_TP_SLOTS = 8;
-__global__ void add_rmsnorm_q8_kernel(float* __restrict__ x, const float* const* __restrict__ parts, int n_parts, long part_stride,
+__global__ void __launch_bounds__(1024) add_rmsnorm_q8_kernel(float* __restrict__ x, const PartPtrs parts, int n_parts, long part_stride,
                                       const float* __restrict__ gamma, uint8_t* __restrict__ xq, int hidden, float eps, TpSync tp) {
     __shared__ float red[32];
     __shared__ int peers_ok;
@@ -141,7 +144,9 @@ __global__ void add_rmsnorm_q8_kernel(float* __restrict__ x, const float* const*
         v[i] = 0.f;
         if (e < hidden) {
             float t = xr[e];
-            for (int r = 0; r < n_parts; ++r) t += __ldcv(parts[r] + (size_t)b * part_stride + e);  // never from a stale cache line
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+                if (r < n_parts) t += __ldcv(parts.p[r] + (size_t)b * part_stride + e);  // never from a stale cache line
             if (n_parts > 0) xr[e] = t;
             v[i] = t;
             ss += t * t;
@@ -192,131 +197,148 @@ __global__ void rope_kv_append_kernel(float* __restrict__ qkv, __half* __restric
 }
 
 // Single-query GQA attention over the fp16 cache, split over the context: CTA (kv head, batch, split)
-// handles positions [split*chunk, ...) for the `group` query heads of its kv head and writes, per
-// query head, the running maximum, the sum of exponentials and the unnormalised output (hd floats)
-// to the scratch area; attn_combine_q8_kernel merges the splits.
+// handles ATTN_CHUNK positions for the `group` query heads of its kv head.  The K and V rows of
+// the chunk are staged in shared memory with coalesced 16-byte loads (all in flight at once), the
+// scores are one thread per (position, half of the heads), the outputs one thread per head
+// dimension.  Per query head the CTA writes the running maximum, the sum of exponentials and
+// the unnormalised output (hd floats); attn_combine_q8_kernel merges the splits.
 // scratch layout: (batch, nqh, splits, hd + 2) floats.
 constexpr int ATTN_THREADS = 128;
 constexpr int ATTN_MAX_GROUP = 8;
+constexpr int ATTN_CHUNK = 64;
 __global__ void __launch_bounds__(ATTN_THREADS) attn_decode_split_kernel(const float* __restrict__ qkv, const __half* __restrict__ kcache,
                                                                         const __half* __restrict__ vcache, float* __restrict__ scratch,
-                                                                        int nqh, int nkv, int hd, int len, int ctx_cap, int chunk,
-                                                                        int splits) {
-    extern __shared__ float att_sm[];  // q: group*hd | p: group*chunk
-    __shared__ float red[32];
+                                                                        int nqh, int nkv, int hd, int len, int ctx_cap, int splits) {
+    extern __shared__ __align__(16) uint8_t att_raw[];
+    // layout: K rows (ATTN_CHUNK x (hd+8) halves, padded against bank conflicts) | V rows (ATTN_CHUNK x hd halves)
+    //         | q (group x hd floats) | p (group x ATTN_CHUNK floats) | stats (2 x group floats)
+    const int kpitch = hd + 8;
+    __half* ks = reinterpret_cast<__half*>(att_raw);
+    __half* vs = ks + ATTN_CHUNK * kpitch;
+    float* qs = reinterpret_cast<float*>(vs + ATTN_CHUNK * hd);
+    const int group = nqh / nkv;
+    float* ps = qs + group * hd;
+    float* stat = ps + group * ATTN_CHUNK;
     pdl_release_dependents();
     pdl_wait_prior_grids();
     const int kvh = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
-    const int group = nqh / nkv;
-    const int t0 = sp * chunk, t1 = min(len, t0 + chunk);
-    float* qs = att_sm;
-    float* ps = att_sm + group * hd;
+    const int t0 = sp * ATTN_CHUNK, nt = max(min(len - t0, ATTN_CHUNK), 0);
+    const int tid = threadIdx.x;
     const float scale = rsqrtf((float)hd);
     const float* qrow = qkv + (size_t)b * (nqh + 2 * nkv) * hd + (size_t)kvh * group * hd;
-    for (int i = threadIdx.x; i < group * hd; i += blockDim.x) qs[i] = qrow[i] * scale;
+    // stage K and V: hd/8 16-byte pieces per row
+    const int pieces = hd / 8;
+    const size_t row_stride = (size_t)nkv * hd;  // halves between consecutive positions
+    const __half* kbase = kcache + (((size_t)b * ctx_cap + t0) * nkv + kvh) * hd;
+    const __half* vbase = vcache + (((size_t)b * ctx_cap + t0) * nkv + kvh) * hd;
+    for (int i = tid; i < nt * pieces; i += ATTN_THREADS) {
+        const int t = i / pieces, c = i - t * pieces;
+        *reinterpret_cast<uint4*>(ks + t * kpitch + 8 * c) = *reinterpret_cast<const uint4*>(kbase + t * row_stride + 8 * c);
+        *reinterpret_cast<uint4*>(vs + t * hd + 8 * c) = *reinterpret_cast<const uint4*>(vbase + t * row_stride + 8 * c);
+    }
+    for (int i = tid; i < group * hd; i += ATTN_THREADS) qs[i] = qrow[i] * scale;
     __syncthreads();
-    const int nt = max(t1 - t0, 0);
-    // scores: one thread per position, all query heads of the group against one pass over the K row
-    float mx[ATTN_MAX_GROUP];
+    // scores: thread = (position t, head parity): heads g = par, par+2, ...
+    {
+        const int t = tid & (ATTN_CHUNK - 1), par = tid / ATTN_CHUNK;
+        float acc[ATTN_MAX_GROUP / 2];
 #pragma unroll
-    for (int g = 0; g < ATTN_MAX_GROUP; ++g) mx[g] = -INFINITY;
-    for (int t = threadIdx.x; t < nt; t += blockDim.x) {
-        const uint4* kr = reinterpret_cast<const uint4*>(kcache + (((size_t)b * ctx_cap + t0 + t) * nkv + kvh) * hd);
-        float acc[ATTN_MAX_GROUP];
+        for (int g = 0; g < ATTN_MAX_GROUP / 2; ++g) acc[g] = 0.f;
+        if (t < nt) {
+            const __half2* kr = reinterpret_cast<const __half2*>(ks + t * kpitch);
+            for (int c = 0; c < hd / 2; ++c) {
+                const float2 f = __half22float2(kr[c]);
 #pragma unroll
-        for (int g = 0; g < ATTN_MAX_GROUP; ++g) acc[g] = 0.f;
-        for (int c = 0; c < hd / 8; ++c) {
-            const uint4 kk = kr[c];
-            const __half2* h2 = reinterpret_cast<const __half2*>(&kk);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 f = __half22float2(h2[j]);
-#pragma unroll
-                for (int g = 0; g < ATTN_MAX_GROUP; ++g)
-                    if (g < group) acc[g] += f.x * qs[g * hd + 8 * c + 2 * j] + f.y * qs[g * hd + 8 * c + 2 * j + 1];
+                for (int g = 0; g < ATTN_MAX_GROUP / 2; ++g) {
+                    const int head = 2 * g + par;
+                    if (head < group) acc[g] += f.x * qs[head * hd + 2 * c] + f.y * qs[head * hd + 2 * c + 1];
+                }
             }
         }
 #pragma unroll
-        for (int g = 0; g < ATTN_MAX_GROUP; ++g)
-            if (g < group) {
-                ps[g * chunk + t] = acc[g];
-                mx[g] = fmaxf(mx[g], acc[g]);
-            }
+        for (int g = 0; g < ATTN_MAX_GROUP / 2; ++g) {
+            const int head = 2 * g + par;
+            if (head < group) ps[head * ATTN_CHUNK + t] = (t < nt) ? acc[g] : -INFINITY;
+        }
     }
-    // per query head: block max, exponentials, block sum
-    float lsum[ATTN_MAX_GROUP], gmax[ATTN_MAX_GROUP];
-#pragma unroll
-    for (int g = 0; g < ATTN_MAX_GROUP; ++g) {
-        lsum[g] = 0.f;
-        gmax[g] = -INFINITY;
-        if (g < group) {
-            float m = mx[g];
+    __syncthreads();
+    // per head: max, exponentials, sum; warp w handles heads w, w+4, ... (ATTN_CHUNK = 64 = two values per lane)
+    {
+        const int warp = tid >> 5, lane = tid & 31;
+        for (int head = warp; head < group; head += ATTN_THREADS / 32) {
+            float a = ps[head * ATTN_CHUNK + lane], c = ps[head * ATTN_CHUNK + 32 + lane];
+            float m = fmaxf(a, c);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
-            __syncthreads();
-            m = red[0];
-            for (int w = 1; w < (int)(blockDim.x >> 5); ++w) m = fmaxf(m, red[w]);
-            __syncthreads();
-            gmax[g] = m;
-            float s = 0.f;
-            for (int t = threadIdx.x; t < nt; t += blockDim.x) {
-                const float e = __expf(ps[g * chunk + t] - m);
-                ps[g * chunk + t] = e;
-                s += e;
-            }
-            lsum[g] = block_sum(s, red);
+            a = (lane < nt) ? __expf(a - m) : 0.f;
+            c = (32 + lane < nt) ? __expf(c - m) : 0.f;
+            ps[head * ATTN_CHUNK + lane] = a;
+            ps[head * ATTN_CHUNK + 32 + lane] = c;
+            const float sum = warp_sum(a + c);
+            if (lane == 0) stat[2 * head] = m, stat[2 * head + 1] = sum;
         }
     }
     __syncthreads();
-    // outputs: thread d accumulates over the positions (coalesced across d)
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    // outputs: thread d accumulates over the positions for every head of the group
+    for (int d = tid; d < hd; d += ATTN_THREADS) {
         float o[ATTN_MAX_GROUP];
 #pragma unroll
         for (int g = 0; g < ATTN_MAX_GROUP; ++g) o[g] = 0.f;
-        const __half* vr = vcache + (((size_t)b * ctx_cap + t0) * nkv + kvh) * hd + d;
         for (int t = 0; t < nt; ++t) {
-            const float vv = __half2float(vr[(size_t)t * nkv * hd]);
+            const float vv = __half2float(vs[t * hd + d]);
 #pragma unroll
             for (int g = 0; g < ATTN_MAX_GROUP; ++g)
-                if (g < group) o[g] += ps[g * chunk + t] * vv;
+                if (g < group) o[g] += ps[g * ATTN_CHUNK + t] * vv;
         }
 #pragma unroll
         for (int g = 0; g < ATTN_MAX_GROUP; ++g)
             if (g < group) {
                 float* dst = scratch + (((size_t)b * nqh + kvh * group + g) * splits + sp) * (hd + 2);
                 dst[2 + d] = o[g];
-                if (d == 0) {
-                    dst[0] = gmax[g];
-                    dst[1] = lsum[g];
-                }
+                if (d == 0) dst[0] = stat[2 * g], dst[1] = stat[2 * g + 1];
             }
     }
 }
 
 // Merge of the context splits + Q8_1 of the attention output (the activations of the O projection).
-// One warp per 32 output elements: grid (nqh*hd/32/warps_per_cta, batch).
+// One CTA per (query head, batch): the split weights are computed once into shared memory, then
+// every thread merges its output element with independent loads.
+constexpr int ATTN_MAX_SPLITS = 512;
 __global__ void attn_combine_q8_kernel(const float* __restrict__ scratch, uint8_t* __restrict__ xq, float* __restrict__ out_f32, int nqh,
                                        int hd, int splits) {
+    __shared__ float wgt[ATTN_MAX_SPLITS];
+    __shared__ float red[32];
     pdl_release_dependents();
     pdl_wait_prior_grids();
-    const int b = blockIdx.y, lane = threadIdx.x & 31;
-    const int blk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // Q8_1 block index within the row
-    if (blk >= nqh * hd / 32) return;
-    const int e = blk * 32 + lane, head = e / hd, d = e - head * hd;
+    const int head = blockIdx.x, b = blockIdx.y, lane = threadIdx.x & 31;
     const float* src = scratch + ((size_t)b * nqh + head) * splits * (hd + 2);
     float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, src[(size_t)s * (hd + 2)]);
-    float den = 0.f, num = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float* ps = src + (size_t)s * (hd + 2);
-        const float wgt = (ps[1] > 0.f) ? __expf(ps[0] - m) : 0.f;
-        den += wgt * ps[1];
-        num += wgt * ps[2 + d];
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) m = fmaxf(m, src[(size_t)s * (hd + 2)]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = red[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) m = fmaxf(m, red[w]);
+    __syncthreads();
+    float den = 0.f;
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+        const float l = src[(size_t)s * (hd + 2) + 1];
+        const float w = l > 0.f ? __expf(src[(size_t)s * (hd + 2)] - m) : 0.f;
+        wgt[s] = w;
+        den += w * l;
     }
-    const float v = den > 0.f ? num / den : 0.f;
-    if (out_f32) out_f32[(size_t)b * nqh * hd + e] = v;
-    warp_store_q8_1(v, xq + ((size_t)b * (nqh * hd / 32) + blk) * Q8_1_BYTES, lane);
+    den = block_sum(den, red);
+    const float inv = den > 0.f ? 1.0f / den : 0.f;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {  // hd is a multiple of 32: whole warps
+        float num = 0.f;
+#pragma unroll 8
+        for (int s = 0; s < splits; ++s) num += wgt[s] * src[(size_t)s * (hd + 2) + 2 + d];
+        const float v = num * inv;
+        const int e = head * hd + d;
+        if (out_f32) out_f32[(size_t)b * nqh * hd + e] = v;
+        warp_store_q8_1(v, xq + ((size_t)b * (nqh * hd / 32) + (e >> 5)) * Q8_1_BYTES, lane);
+    }
 }
 
 __device__ __forceinline__ float gelu_tanh_f(float x) {
@@ -336,31 +358,54 @@ __global__ void act_mul_q8_kernel(const float* __restrict__ gate_up, uint8_t* __
     warp_store_q8_1(a * u, xq + ((size_t)b * (ffn / 32) + blk) * Q8_1_BYTES, lane);
 }
 
-// argmax over a row of logits (first index wins ties); one CTA per row
-__global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, int index_offset, float* __restrict__ best_val) {
+// argmax over rows of logits (lowest index wins ties), two stages: grid (parts, batch) CTAs each scan a
+// contiguous slice and write one candidate {value, index}; the second kernel reduces the candidates.
+struct Candidate {
+    float value;
+    int index;
+};
+__device__ __forceinline__ void better(float& bv, int& bi, float v, int i) {
+    if (v > bv || (v == bv && i < bi)) bv = v, bi = i;
+}
+__device__ __forceinline__ void block_argmax(float& bv, int& bi, float* sv, int* si) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        better(bv, bi, ov, oi);
+    }
+    if ((threadIdx.x & 31) == 0) sv[threadIdx.x >> 5] = bv, si[threadIdx.x >> 5] = bi;
+    __syncthreads();
+    if (threadIdx.x == 0)
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) better(bv, bi, sv[w], si[w]);
+}
+__global__ void argmax_partial_kernel(const float* __restrict__ logits, Candidate* __restrict__ cand, int vocab) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    const int b = blockIdx.y, parts = gridDim.x;
+    const int per = (vocab + parts - 1) / parts;
+    const int i0 = blockIdx.x * per, i1 = min(vocab, i0 + per);
+    const float* row = logits + (size_t)b * vocab;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) better(bv, bi, row[i], i);
+    block_argmax(bv, bi, sv, si);
+    if (threadIdx.x == 0) cand[(size_t)b * parts + blockIdx.x] = Candidate{bv, bi};
+}
+__global__ void argmax_final_kernel(const Candidate* __restrict__ cand, int parts, int* __restrict__ out, int index_offset,
+                                    float* __restrict__ best_val) {
     __shared__ float sv[32];
     __shared__ int si[32];
     pdl_release_dependents();
     pdl_wait_prior_grids();
     const int b = blockIdx.x;
-    const float* row = logits + (size_t)b * vocab;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i];
-        if (v > bv) bv = v, bi = i;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
-    }
-    if ((threadIdx.x & 31) == 0) sv[threadIdx.x >> 5] = bv, si[threadIdx.x >> 5] = bi;
-    __syncthreads();
+    for (int i = threadIdx.x; i < parts; i += blockDim.x) better(bv, bi, cand[(size_t)b * parts + i].value, cand[(size_t)b * parts + i].index);
+    block_argmax(bv, bi, sv, si);
     if (threadIdx.x == 0) {
-        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
-            if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) bv = sv[w], bi = si[w];
         out[b] = bi + index_offset;
         if (best_val) best_val[b] = bv;
     }
@@ -370,10 +415,6 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict_
 // value) in cand[rank]; after the same bounded handshake as the residual kernel each rank reads all
 // candidates and keeps the best (lowest index on ties), so all ranks continue with the same token.
 // cand areas: per rank `max_batch` pairs {float value, int index}.  One CTA, one thread per row.
-struct Candidate {
-    float value;
-    int index;
-};
 __global__ void tp_pick_token_kernel(const float* __restrict__ best_val, int* __restrict__ tokens_io, Candidate* const* __restrict__ cand,
                                      int n_ranks, int batch, TpSync tp) {
     __shared__ int peers_ok;
