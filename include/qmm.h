@@ -124,6 +124,18 @@ int launch_qmatvec(int type, const void* w, const void* xq, float* y, int m, int
 int launch_qgemm_q4_k_bf16(const void* w, const void* x, void* y, int m, int n, int k, void* stream);
 int launch_qgemm_q4_k_bf16_f32acc(const void* w, const void* x, float* yf, int m, int n, int k, void* stream);
 
+/* ---- decode attention: one query token per sequence against an fp16 KV cache, grouped-query.
+ * Counterpart of launch_gqa_masked_attn (gpu-core/src/kernels/f64_infer.hip:49-100; Rust
+ * gpu_gqa_attn_into, gpu-core/src/infer_ops.rs:11-55) for the decode case: qkv (batch, (n_q_heads +
+ * 2*n_kv_heads)*head_dim) f32, of which the first n_q_heads*head_dim entries of a row are the
+ * queries; kcache/vcache (batch, ctx_cap, n_kv_heads, head_dim) fp16; positions [0, len) are
+ * attended with scale 1/sqrt(head_dim).  out_f32 (batch, n_q_heads*head_dim) and/or out_q8 (the same
+ * values as Q8_1 blocks, ready for the output projection); either may be NULL, not both.
+ * scratch: qmm_attn_decode_scratch_bytes(...) bytes of device memory owned by the caller. */
+long qmm_attn_decode_scratch_bytes(int batch, int n_q_heads, int head_dim, int len);
+int launch_attn_decode(const float* qkv, const void* kcache, const void* vcache, float* scratch, float* out_f32, void* out_q8,
+                       int batch, int n_q_heads, int n_kv_heads, int head_dim, int len, int ctx_cap, void* stream);
+
 /* ---- per-block integer dot sums (parity instrumentation; same device code as
  * the matvec).  One Q8_1 row xq (k); out int32 (n, k/32) for Q8_0 and Q4_K,
  * (n, k/16) for Q6_K. */

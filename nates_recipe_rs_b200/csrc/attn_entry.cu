@@ -1,0 +1,67 @@
+// Stand-alone entry points for the decode attention (the engine calls the same kernels directly).
+#include "qmm_formats.cuh"
+
+namespace qmm {
+
+static int attn_check(const float* qkv, const void* kc, const void* vc, const void* out_f32, const void* out_q8, int batch, int nqh, int nkv,
+                      int hd, int len, int ctx_cap, int& splits, size_t& smem) {
+    if (!qkv || !kc || !vc || (!out_f32 && !out_q8)) return QMM_ERR_NULL;
+    if (batch <= 0 || nqh <= 0 || nkv <= 0 || hd <= 0 || len <= 0 || ctx_cap < len) return QMM_ERR_SHAPE;
+    if (nqh % nkv || hd % 32 || hd > 256 || nqh / nkv > ATTN_MAX_GROUP) return QMM_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(kc) % 16 || reinterpret_cast<uintptr_t>(vc) % 16 || reinterpret_cast<uintptr_t>(out_q8) % 4)
+        return QMM_ERR_ALIGN;
+    splits = (len + ATTN_CHUNK - 1) / ATTN_CHUNK;
+    if (splits > ATTN_MAX_SPLITS) return QMM_ERR_UNSUPPORTED;
+    const int group = nqh / nkv;
+    smem = (size_t)ATTN_CHUNK * (2 * hd + 8) * sizeof(__half) + (size_t)group * (hd + ATTN_CHUNK + 2) * sizeof(float);
+    return QMM_OK;
+}
+
+static int attn_run(const float* qkv, const void* kc, const void* vc, float* scratch, float* out_f32, void* out_q8, int batch, int nqh, int nkv,
+                    int hd, int len, int ctx_cap, int splits, size_t smem, cudaStream_t s) {
+    static size_t configured[64] = {};
+    int dev = 0;
+    QMM_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || smem > configured[dev]) {
+        QMM_CUDA_TRY(cudaFuncSetAttribute(attn_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (dev >= 0 && dev < 64) configured[dev] = smem;
+    }
+    attn_decode_split_kernel<<<dim3(nkv, batch, splits), ATTN_THREADS, smem, s>>>(qkv, static_cast<const __half*>(kc),
+                                                                                   static_cast<const __half*>(vc), scratch, nqh, nkv, hd,
+                                                                                   len, ctx_cap, splits);
+    QMM_CUDA_TRY(cudaGetLastError());
+    // the merge always produces Q8_1 blocks; a caller that only wants f32 gets them in a throw-away tail of the scratch
+    uint8_t* q8 = static_cast<uint8_t*>(out_q8);
+    if (!q8) q8 = reinterpret_cast<uint8_t*>(scratch + (size_t)batch * nqh * splits * (hd + 2));
+    attn_combine_q8_kernel<<<dim3(nqh, batch), hd < 128 ? hd : 128, 0, s>>>(scratch, q8, out_f32, nqh, hd, splits);
+    QMM_CUDA_TRY(cudaGetLastError());
+    return QMM_OK;
+}
+
+static size_t attn_scratch_floats(int batch, int nqh, int hd, int splits) {
+    // split results + room for a row of Q8_1 blocks per sequence (used when the caller passes no out_q8)
+    return (size_t)batch * nqh * splits * (hd + 2) + ((size_t)batch * (nqh * hd / 32) * Q8_1_BYTES + 3) / 4;
+}
+
+}  // namespace qmm
+
+using namespace qmm;
+
+extern "C" {
+
+long qmm_attn_decode_scratch_bytes(int batch, int n_q_heads, int head_dim, int len) {
+    if (batch <= 0 || n_q_heads <= 0 || head_dim <= 0 || len <= 0) return QMM_ERR_SHAPE;
+    return (long)(attn_scratch_floats(batch, n_q_heads, head_dim, (len + ATTN_CHUNK - 1) / ATTN_CHUNK) * sizeof(float));
+}
+
+int launch_attn_decode(const float* qkv, const void* kcache, const void* vcache, float* scratch, float* out_f32, void* out_q8, int batch,
+                       int n_q_heads, int n_kv_heads, int head_dim, int len, int ctx_cap, void* stream) {
+    int splits = 0;
+    size_t smem = 0;
+    if (!scratch) return QMM_ERR_NULL;
+    if (int st = attn_check(qkv, kcache, vcache, out_f32, out_q8, batch, n_q_heads, n_kv_heads, head_dim, len, ctx_cap, splits, smem)) return st;
+    return attn_run(qkv, kcache, vcache, scratch, out_f32, out_q8, batch, n_q_heads, n_kv_heads, head_dim, len, ctx_cap, splits, smem,
+                    as_stream(stream));
+}
+
+}  // extern "C"

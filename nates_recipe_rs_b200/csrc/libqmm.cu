@@ -5,4 +5,5 @@
 #include "qmatvec.cu"
 #include "qgemm.cu"
 #include "decoder_ops.cu"
+#include "attn_entry.cu"
 #include "decoder.cu"

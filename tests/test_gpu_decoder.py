@@ -127,3 +127,29 @@ def test_step_rejects_bad_arguments(dec):
     with pytest.raises(QmmError):
         d.step(1, 48)           # position beyond the context
     d.close()
+
+
+@pytest.mark.parametrize("batch,nqh,nkv,hd,length", [(1, 4, 2, 64, 1), (2, 8, 2, 128, 70), (3, 32, 8, 128, 300), (1, 8, 8, 32, 129)])
+def test_attention_entry_matches_oracle(dec, batch, nqh, nkv, hd, length):
+    """launch_attn_decode through the C ABI against the oracle's straight-loop attention."""
+    from nates_recipe_rs_b200._lib import check, lib
+    L = lib()
+    cap = length + 5
+    rng = np.random.default_rng(batch * 1000 + length)
+    qkv = rng.normal(size=(batch, (nqh + 2 * nkv) * hd)).astype(np.float32)
+    kc = rng.normal(size=(batch, cap, nkv, hd)).astype(np.float16)
+    vc = rng.normal(size=(batch, cap, nkv, hd)).astype(np.float16)
+    dq, dk, dv = (torch.from_numpy(a).cuda() for a in (qkv, kc, vc))
+    nbytes = L.qmm_attn_decode_scratch_bytes(batch, nqh, hd, length)
+    scratch = torch.empty(nbytes // 4, dtype=torch.float32, device="cuda")
+    out = torch.full((batch, nqh * hd), float("nan"), device="cuda")
+    q8 = torch.zeros(batch * (nqh * hd // 32) * 36, dtype=torch.uint8, device="cuda")
+    check(L.launch_attn_decode(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), scratch.data_ptr(), out.data_ptr(), q8.data_ptr(), batch, nqh, nkv,
+                               hd, length, cap, torch.cuda.current_stream().cuda_stream), "launch_attn_decode")
+    got = out.cpu().numpy()
+    for b in range(batch):
+        want = oracle.attn_decode(qkv[b, :nqh * hd].reshape(nqh, hd), kc[b], vc[b], nqh, nkv, hd, length).reshape(-1)
+        assert np.abs(got[b] - want).max() <= 1e-4 + 1e-3 * np.abs(want).max()
+    # the Q8_1 output is the library's own quantization of the f32 output
+    from nates_recipe_rs_b200 import quant_ops as ops
+    assert torch.equal(q8, ops.gpu_quantize_q8_1(out))
