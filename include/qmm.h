@@ -136,6 +136,22 @@ long qmm_attn_decode_scratch_bytes(int batch, int n_q_heads, int head_dim, int l
 int launch_attn_decode(const float* qkv, const void* kcache, const void* vcache, float* scratch, float* out_f32, void* out_q8,
                        int batch, int n_q_heads, int n_kv_heads, int head_dim, int len, int ctx_cap, void* stream);
 
+/* ---- the same attention for callers that cannot allocate.  This entry point has no counterpart in
+ * the upstream project.  It takes no scratch pointer: the split results go to a fixed 4 MiB array
+ * that lives inside the library on every GPU that loads it (held until the process exits).  It is
+ * meant for hosts that must not call an allocator where they need attention: code running inside a
+ * frozen no-allocation loop (the upstream aborts on any allocation once its steady state is
+ * frozen), a plugin that only owns the buffers its host handed over, a caller that has already
+ * handed all of its memory to other uses.  It never calls cudaMalloc, cudaFree or any allocating
+ * routine.  Requests whose scratch need (qmm_attn_decode_scratch_bytes) exceeds 4 MiB are rejected
+ * with QMM_ERR_SCRATCH and nothing is launched.  The first call on a device looks up the array's
+ * device address (a one-time set-up); make that first call outside any stream capture.  All calls
+ * share the one array and it keeps what the last call left there: nothing in it needs clearing
+ * (each call overwrites every word it reads), but two calls that overlap on the GPU, from any
+ * streams or threads, race on it and must be ordered by the caller. */
+int launch_attn_decode_static(const float* qkv, const void* kcache, const void* vcache, float* out_f32, void* out_q8, int batch,
+                              int n_q_heads, int n_kv_heads, int head_dim, int len, int ctx_cap, void* stream);
+
 /* ---- per-block integer dot sums (parity instrumentation; same device code as
  * the matvec).  One Q8_1 row xq (k); out int32 (n, k/32) for Q8_0 and Q4_K,
  * (n, k/16) for Q6_K. */

@@ -40,6 +40,7 @@ SIGNATURES = {
     "launch_qgemm_q4_k_bf16_f32acc": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "qmm_attn_decode_scratch_bytes": (i64, [i32, i32, i32, i32]),
     "launch_attn_decode": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
+    "launch_attn_decode_static": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
     "launch_qblock_dots": (i32, [i32, vp, vp, vp, i32, i32, vp]),
 }
 

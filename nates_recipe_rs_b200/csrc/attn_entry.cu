@@ -43,6 +43,34 @@ static size_t attn_scratch_floats(int batch, int nqh, int hd, int splits) {
     return (size_t)batch * nqh * splits * (hd + 2) + ((size_t)batch * (nqh * hd / 32) * Q8_1_BYTES + 3) / 4;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Scratch that belongs to the library instead of the caller.  Some hosts of this code may not
+// allocate device memory at the moment they need attention: a caller inside a frozen steady
+// state (the upstream's AllocGuard panics on any allocation once a loop is frozen), a plugin
+// that was handed fixed buffers by its host application, code running between the capture and
+// the replay of a work graph.  For them one entry point works out of a fixed array that every
+// GPU loading this library carries until the process exits.
+constexpr size_t ATTN_STATIC_FLOATS = 1u << 20;  // 4 MiB per GPU
+static __device__ __align__(256) float g_attn_static_scratch[ATTN_STATIC_FLOATS];
+
+// `g_attn_static_scratch` is only a stand-in on the host side: it is not a device address and must
+// never be handed to a kernel.  The device address is asked for once per device, with that device
+// current, and remembered.
+static int attn_static_scratch_ptr(float** out) {
+    static float* cached[64] = {};
+    int dev = 0;
+    QMM_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return QMM_ERR_UNSUPPORTED;
+    if (!cached[dev]) {
+        float* p = nullptr;
+        QMM_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_attn_static_scratch));
+        if (!p) return cuda_fail(cudaErrorInvalidSymbol);
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return QMM_OK;
+}
+
 }  // namespace qmm
 
 using namespace qmm;
@@ -60,6 +88,18 @@ int launch_attn_decode(const float* qkv, const void* kcache, const void* vcache,
     size_t smem = 0;
     if (!scratch) return QMM_ERR_NULL;
     if (int st = attn_check(qkv, kcache, vcache, out_f32, out_q8, batch, n_q_heads, n_kv_heads, head_dim, len, ctx_cap, splits, smem)) return st;
+    return attn_run(qkv, kcache, vcache, scratch, out_f32, out_q8, batch, n_q_heads, n_kv_heads, head_dim, len, ctx_cap, splits, smem,
+                    as_stream(stream));
+}
+
+int launch_attn_decode_static(const float* qkv, const void* kcache, const void* vcache, float* out_f32, void* out_q8, int batch, int n_q_heads,
+                              int n_kv_heads, int head_dim, int len, int ctx_cap, void* stream) {
+    int splits = 0;
+    size_t smem = 0;
+    if (int st = attn_check(qkv, kcache, vcache, out_f32, out_q8, batch, n_q_heads, n_kv_heads, head_dim, len, ctx_cap, splits, smem)) return st;
+    if (attn_scratch_floats(batch, n_q_heads, head_dim, splits) > ATTN_STATIC_FLOATS) return QMM_ERR_SCRATCH;
+    float* scratch = nullptr;
+    if (int st = attn_static_scratch_ptr(&scratch)) return st;
     return attn_run(qkv, kcache, vcache, scratch, out_f32, out_q8, batch, n_q_heads, n_kv_heads, head_dim, len, ctx_cap, splits, smem,
                     as_stream(stream));
 }
