@@ -223,8 +223,10 @@ def run_ours(args):
                 body()
         return gr
 
+    note("model built; first eager step")
     step_body(count=True)
     torch.cuda.synchronize()
+    note("capturing the step graph")
     use_graph = True
     try:
         graph = make_graph(step_body)
@@ -245,6 +247,7 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    note(f"graph={use_graph}; warm-up")
     with torch.cuda.stream(stream):
         sampler = ClockSampler(local) if rank == 0 else None  # spans warm-up, the timed steps and the two legs below
         for _ in range(max(args.warmup, 3)):
@@ -258,6 +261,7 @@ def run_ours(args):
         e1.record(stream)
         barrier()
         elapsed_ms = e0.elapsed_time(e1)
+        note("timed steps done; Q4_K-only graph")
 
         # ---- dominant kernel alone: the Q4_K matvec launches of the same step, same rotation of weights
         def q4_body():
@@ -280,6 +284,7 @@ def run_ours(args):
 
         # ---- end to end through the C ABI with host buffers: activations come from pinned host
         # memory and the projections go back to it every step; the weights stay resident in HBM
+        note("end-to-end leg")
         hx = torch.randn(1, HID).pin_memory()
         hh = torch.randn(1, FFN).pin_memory()
         hy = torch.empty(2, HID).pin_memory()
@@ -316,6 +321,7 @@ def run_ours(args):
     q4_algo = q4_bytes + (HID // 32 * 36 * 2 + FFN // 32 * 36) / 3 + (FFN * 4 * 2 + HID * 4) / 3
     achieved = q4_algo / (q4_us * 1e-6) / 1e9
 
+    note("FFN legs done")
     decode = None if args.no_decode else run_decode(world, rank, dev, args.quick_decode)
     if rank == 0:
         cpu, _ = cpu_time_sample() if world == 1 else (None, None)
@@ -340,9 +346,23 @@ def run_ours(args):
             out["cpu_baseline"] = cpu
         if decode is not None:
             out["decode"] = decode
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if world > 1:
+        # The NCCL communicator is referenced by the captured graphs: release them first, and do not let
+        # a slow teardown outlive the measurement (the line above is already printed).
+        import threading
+        graph = q4_graph = None
+        torch.cuda.synchronize()
+        dist.barrier()
+        threading.Timer(20.0, lambda: os._exit(0)).start()
         dist.destroy_process_group()
+        os._exit(0)
+
+
+def note(msg):
+    """Progress line on stderr (QMM_BENCH_VERBOSE=1): where a multi-rank run is, should it stall."""
+    if os.environ.get("QMM_BENCH_VERBOSE"):
+        print(f"[bench rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
 
 
 def run_decode(world, rank, dev, quick):
@@ -361,6 +381,7 @@ def run_decode(world, rank, dev, quick):
         cfg = make(max_batch=batch, tp_rank=rank, tp_size=world)
         if cfg.n_kv_heads % world != 0:
             continue
+        note(f"decode {name} batch {batch}: building")
         try:
             d = dec.Decoder(cfg)
         except Exception as e:  # e.g. not enough memory for the 70B stack on this GPU
@@ -377,17 +398,21 @@ def run_decode(world, rank, dev, quick):
                 for i in range(steps_per_graph):
                     d.step(batch, pos0 + i)
                     d.tokens.copy_(d.next_tokens)
+            note("decode: eager steps")
             body()
             stream.synchronize()
             if world > 1:
                 dist.barrier()
+            note("decode: capture")
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 body()
+            note("decode: first replay")
             graph.replay()
             stream.synchronize()
             if world > 1:
                 dist.barrier()
+            note("decode: timed replays")
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             reps = 4
             e0.record(stream)
