@@ -74,7 +74,9 @@ int qmm_set_overlap(int on);
 /* Tuning hook for the matvec launcher (benchmark sweeps; the defaults are the tuned
  * values): "stage_bytes" (1024..49152), "ring_bytes" (8192..194560),
  * "consumer_warps" (1..24), "q4k_unit" (0 = automatic, 1, 2, 4: 32-byte groups of a
- * Q4_K super-block per lane), "rb_max" (1, 2, 4: rows reduced together per warp).  Not thread-safe against concurrent launches. */
+ * Q4_K super-block per lane), "rb_max" (1, 2, 4: rows reduced together per warp), "probe" (0/1: 1 = the
+ * matvec streams and synchronises but skips its arithmetic), "gemm_probe" (0/1/2: the GEMM skips its unpack
+ * arithmetic / its tensor-core instructions).  Probe modes produce wrong results by design.  Not thread-safe against concurrent launches. */
 int qmm_tune(const char* key, int value);
 /* Tuning aid: while buf is non-NULL, matvec launch number i (counted from this call) stores four
  * global-timer stamps per CTA (start, dependency released, first stage landed, end) as 64-bit

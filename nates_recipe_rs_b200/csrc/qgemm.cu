@@ -8,8 +8,8 @@
 // unpacked once per 512 tokens.  Warp roles:
 //   warp 0      TMA producer: x tiles (128 rows x 64 k, 128-byte swizzle) through a 6-slot ring
 //   warp 1      TMEM allocation; one lane issues tcgen05.mma (128x128x16, bf16 -> f32 in TMEM)
-//   warps 2..9  unpack one 32-byte group of qs per row and k-step (= 64 weights = one 128-byte
-//               swizzled row of the B tile) into a 3-slot ring, then run the epilogue
+//   warps 2..17 unpack one 32-byte group of qs per row and k-step (= 64 weights = one 128-byte
+//               swizzled row of the B tile) into a 6-slot ring, then run the epilogue
 // A k-step is 64 elements: exactly one group of a Q4_K super-block, so the B tile row of a
 // weight row is one group of that row's current super-block.
 // Accumulators: up to four 128x128 f32 blocks = all 512 TMEM columns; the epilogue reads them
@@ -22,9 +22,9 @@
 namespace qmm {
 
 constexpr int GEMM_BN = 128, GEMM_BK = 64, GEMM_MB_MAX = 4;
-constexpr int GEMM_SA = 6, GEMM_SB = 3;
+constexpr int GEMM_SA = 6, GEMM_SB = 6;
 constexpr int GEMM_TILE_BYTES = 128 * GEMM_BK * 2;  // 16 KB: 128 rows x 128 bytes
-constexpr int GEMM_DEQ_WARPS = 8;
+constexpr int GEMM_DEQ_WARPS = 16;
 constexpr int GEMM_THREADS = (2 + GEMM_DEQ_WARPS) * 32;
 constexpr uint32_t GEMM_TMEM_COLS = 512;
 // instruction descriptor: D f32, A bf16, B bf16, both K-major, N = 128, M = 128
@@ -36,6 +36,7 @@ struct GemmParams {
     float* yf;            // optional (m, n) f32 copy of the accumulators
     int m, n, k;
     int row_bytes;
+    int probe;            // tuning aid: 0 normal, 1 = unpack arithmetic skipped, 2 = tensor-core work skipped
 };
 
 struct __align__(16) GemmSmemHeader {
@@ -81,12 +82,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// 16 weights of one sub-block from four words of nibbles already reduced to one nibble per byte:
-// value = (ds*q) - off with each operation rounded, then pairs rounded to bf16 (RNE).
-__device__ __forceinline__ void q4k_to_bf16x16(const uint32_t (&t)[4], float ds, float off, uint4& c0, uint4& c1) {
-    uint32_t o[8];
+// 8 weights of one sub-block from two words holding one nibble per byte:
+// value = (ds*q) - off with each operation rounded, then pairs rounded to bf16 (RNE) = one 16-byte chunk.
+__device__ __forceinline__ uint4 q4k_to_bf16x8(uint32_t t0, uint32_t t1, float ds, float off) {
+    uint32_t o[4];
+    const uint32_t t[2] = {t0, t1};
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < 2; ++w) {
         float v[4];
 #pragma unroll
         for (int b = 0; b < 4; ++b) v[b] = __fsub_rn(__fmul_rn(ds, byte_to_float(t[w], b)), off);
@@ -94,8 +96,7 @@ __device__ __forceinline__ void q4k_to_bf16x16(const uint32_t (&t)[4], float ds,
         o[2 * w] = *reinterpret_cast<const uint32_t*>(&p0);
         o[2 * w + 1] = *reinterpret_cast<const uint32_t*>(&p1);
     }
-    c0 = make_uint4(o[0], o[1], o[2], o[3]);
-    c1 = make_uint4(o[4], o[5], o[6], o[7]);
+    return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
@@ -196,7 +197,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
                     const uint64_t adesc = umma_desc_sw128(smem_u32(a_ring + sa * GEMM_TILE_BYTES));
 #pragma unroll
                     for (int k16 = 0; k16 < GEMM_BK / 16; ++k16)  // 32 bytes of K per instruction: +2 in 16-byte units
-                        umma_bf16(tmem_base + (uint32_t)mb * GEMM_BN, adesc + 2 * k16, bdesc + 2 * k16, GEMM_IDESC,
+                        if (p.probe != 2) umma_bf16(tmem_base + (uint32_t)mb * GEMM_BN, adesc + 2 * k16, bdesc + 2 * k16, GEMM_IDESC,
                                   (ks > 0 || k16 > 0) ? 1u : 0u);
                     umma_commit(smem_u32(&hdr->a_empty[sa]));  // frees the x slot when these MMAs retire
                 }
@@ -206,21 +207,38 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
         }
     } else {
         // ------------------------------------------------------------ unpack warps, then epilogue
-        const int t = threadIdx.x - 64;          // 0..255
-        const int row = t >> 1, h = t & 1;       // weight row of the tile, which 16 bytes of the group
+        // thread = (weight row of the tile, which 8 bytes of the 32-byte group): consecutive lanes take
+        // consecutive rows, so the eight lanes of a store phase hit eight different swizzle positions
+        const int t = threadIdx.x - 64;          // 0..511
+        const int row = t & 127, part = t >> 7;  // part 0..3
         const int wrow = min(n0 + row, p.n - 1); // rows past n are unpacked from the last row and never stored
         const uint8_t* wr = p.w + (size_t)wrow * p.row_bytes;
         const uint32_t row_off = (uint32_t)row * 128u, swz = (uint32_t)(row & 7);
-        uint4 hdr_next = *reinterpret_cast<const uint4*>(wr);
-        uint4 qs_next = *reinterpret_cast<const uint4*>(wr + 16 + 16 * h);
+        // two k-steps of packed words in flight ahead of the one being unpacked
+        // A super-block serves four k-steps: its header and this thread's four 8-byte pieces are fetched
+        // together, one whole super-block (four k-steps) ahead of their use.
+        struct Packed {
+            uint4 hdr;
+            uint2 q[4];
+        };
+        auto fetch = [&](int sbi, Packed& pk) {
+            const uint8_t* blk = wr + (size_t)sbi * Q4_K_BYTES;
+            pk.hdr = *reinterpret_cast<const uint4*>(blk);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) pk.q[g] = *reinterpret_cast<const uint2*>(blk + 16 + 32 * g + 8 * part);
+        };
+        Packed cur, nxt;
+        fetch(0, cur);
+        nxt = cur;
         bool ok = true;
         for (int ks = 0; ks < kt; ++ks) {
-            const uint4 hd = hdr_next, qs = qs_next;
-            if (ks + 1 < kt) {  // fetch the next group while this one is unpacked
-                const uint8_t* blk = wr + (size_t)((ks + 1) >> 2) * Q4_K_BYTES;
-                hdr_next = *reinterpret_cast<const uint4*>(blk);
-                qs_next = *reinterpret_cast<const uint4*>(blk + 16 + 32 * ((ks + 1) & 3) + 16 * h);
+            if ((ks & 3) == 0) {
+                if (ks > 0) cur = nxt;
+                if (ks + 4 < kt) fetch((ks >> 2) + 1, nxt);
             }
+            const uint4 hd = cur.hdr;
+            const int gsel = ks & 3;
+            const uint2 qs = gsel == 0 ? cur.q[0] : (gsel == 1 ? cur.q[1] : (gsel == 2 ? cur.q[2] : cur.q[3]));
             // scale / min codes of sub-blocks 2g (low nibbles) and 2g+1 (high nibbles); g is uniform over the CTA
             const int g = ks & 3;
             const uint32_t scA = hd.y & 0x3F3F3F3Fu, mA = hd.z & 0x3F3F3F3Fu;
@@ -231,13 +249,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
             const float d = f16_bits_to_f32(hd.x & 0xFFFFu), dmin = f16_bits_to_f32(hd.x >> 16);
             const float ds0 = __fmul_rn(d, byte_to_float(sc4, i0)), off0 = __fmul_rn(dmin, byte_to_float(m4, i0));
             const float ds1 = __fmul_rn(d, byte_to_float(sc4, i0 + 1)), off1 = __fmul_rn(dmin, byte_to_float(m4, i0 + 1));
-            const uint32_t v[4] = {qs.x, qs.y, qs.z, qs.w};
-            uint32_t lo[4], hi[4];
-#pragma unroll
-            for (int w = 0; w < 4; ++w) lo[w] = v[w] & 0x0F0F0F0Fu, hi[w] = (v[w] >> 4) & 0x0F0F0F0Fu;
-            uint4 c_lo0, c_lo1, c_hi0, c_hi1;
-            q4k_to_bf16x16(lo, ds0, off0, c_lo0, c_lo1);  // elements 16h .. 16h+15       -> chunks 2h, 2h+1
-            q4k_to_bf16x16(hi, ds1, off1, c_hi0, c_hi1);  // elements 32+16h .. 32+16h+15 -> chunks 4+2h, 5+2h
+            // bytes 8*part .. 8*part+7 of the group: low nibbles = elements 8*part.. (chunk part),
+            // high nibbles = elements 32+8*part.. (chunk 4+part)
+            uint4 c_lo, c_hi;
+            if (p.probe != 1) {
+                c_lo = q4k_to_bf16x8(qs.x & 0x0F0F0F0Fu, qs.y & 0x0F0F0F0Fu, ds0, off0);
+                c_hi = q4k_to_bf16x8((qs.x >> 4) & 0x0F0F0F0Fu, (qs.y >> 4) & 0x0F0F0F0Fu, ds1, off1);
+            } else {
+                c_lo = make_uint4(qs.x, qs.y, hd.x, hd.y);
+                c_hi = c_lo;
+            }
 
             const int sb = ks % GEMM_SB, use = ks / GEMM_SB;
             if (use > 0 && !mbar_wait_bounded(smem_u32(&hdr->b_empty[sb]), (use - 1) & 1, cta_abort)) {
@@ -246,11 +267,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
                 break;
             }
             uint8_t* tile = b_ring + sb * GEMM_TILE_BYTES + row_off;
-            const uint32_t c = 2u * h;
-            *reinterpret_cast<uint4*>(tile + (((c + 0) ^ swz) << 4)) = c_lo0;
-            *reinterpret_cast<uint4*>(tile + (((c + 1) ^ swz) << 4)) = c_lo1;
-            *reinterpret_cast<uint4*>(tile + (((c + 4) ^ swz) << 4)) = c_hi0;
-            *reinterpret_cast<uint4*>(tile + (((c + 5) ^ swz) << 4)) = c_hi1;
+            *reinterpret_cast<uint4*>(tile + ((((uint32_t)part + 0) ^ swz) << 4)) = c_lo;
+            *reinterpret_cast<uint4*>(tile + ((((uint32_t)part + 4) ^ swz) << 4)) = c_hi;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&hdr->b_full[sb]));
@@ -259,12 +277,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
         if (ok && mbar_wait_bounded(smem_u32(&hdr->acc_full), 0, cta_abort) && !*cta_abort) {
             tc_fence_after();
             const int q = warp & 3;                 // TMEM lane quarter this warp may read
-            const int half = (warp - 2) >> 2;       // the two warps of a quarter split the 128 columns
+            const int cq = (warp - 2) >> 2;         // the four warps of a quarter take 32 columns each
             for (int mb = 0; mb < mb_count; ++mb) {
                 const int grow = m0 + mb * 128 + 32 * q + lane;
-#pragma unroll
-                for (int c0 = 0; c0 < 64; c0 += 32) {
-                    const int col = 64 * half + c0;
+                {
+                    const int col = 32 * cq;
                     uint32_t r[32];
                     tmem_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(mb * GEMM_BN + col), r);
                     if (grow < p.m) {
@@ -327,6 +344,9 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+static int g_gemm_probe = 0;
+void gemm_set_probe(int v) { g_gemm_probe = v; }
+
 int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, int n, int k, cudaStream_t stream) {
     if (!w || !x || (!y && !yf)) return QMM_ERR_NULL;
     if (m <= 0 || n <= 0 || k <= 0 || k % 256 != 0) return QMM_ERR_SHAPE;
@@ -350,6 +370,7 @@ int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, in
     p.yf = yf;
     p.m = m, p.n = n, p.k = k;
     p.row_bytes = k / 256 * Q4_K_BYTES;
+    p.probe = g_gemm_probe;
     const size_t smem = (size_t)(GEMM_SA + GEMM_SB) * GEMM_TILE_BYTES + sizeof(GemmSmemHeader) + 1024;
     static bool configured[64] = {};
     int dev = 0;

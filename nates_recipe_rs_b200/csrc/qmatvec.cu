@@ -291,8 +291,10 @@ static unsigned long long* g_trace = nullptr;
 static int g_trace_stride = 0, g_trace_count = 0;
 // tuning aid: the next launches write 4 time stamps per CTA at trace + launch_index * stride
 void matvec_set_trace(unsigned long long* buf, int stride_words) { g_trace = buf; g_trace_stride = stride_words; g_trace_count = 0; }
+void gemm_set_probe(int v);
 int matvec_tune(const char* key, int value) {
     const std::string k(key ? key : "");
+    if (k == "gemm_probe" && value >= 0 && value <= 2) return gemm_set_probe(value), QMM_OK;
     if (k == "stage_bytes" && value >= 1024 && value <= STAGE_MAX_BYTES) return g_stage_target = value, QMM_OK;
     if (k == "ring_bytes" && value >= 8 * 1024 && value <= 190 * 1024) return g_ring_budget = value, QMM_OK;
     if (k == "consumer_warps" && value >= 1 && value <= MAX_CONSUMER_WARPS) return g_consumer_warps = value, QMM_OK;

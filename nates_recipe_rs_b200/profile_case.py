@@ -1,6 +1,7 @@
-"""Small driver for profiler captures of one matvec shape.
+"""Small driver for profiler captures of one matvec or GEMM shape.
 
     python -m nates_recipe_rs_b200.profile_case <q8_0|q4_k|q6_k> <n> <k> <m> [launches]
+    python -m nates_recipe_rs_b200.profile_case gemm <n> <k> <m> [launches]      (Q4_K x bf16 prefill GEMM)
 
 Allocates enough distinct random weight matrices to exceed L2 (about 300 MB in
 total, never more), quantizes random activations and launches the matvec on the
@@ -15,8 +16,9 @@ from . import _lib, quant_ops as ops
 
 
 def main(argv):
-    names = {"q8_0": _lib.Q8_0, "q4_k": _lib.Q4_K, "q6_k": _lib.Q6_K}
+    names = {"q8_0": _lib.Q8_0, "q4_k": _lib.Q4_K, "q6_k": _lib.Q6_K, "gemm": _lib.Q4_K}
     qt = names[argv[0]]
+    gemm = argv[0] == "gemm"
     n, k, m = int(argv[1]), int(argv[2]), int(argv[3])
     reps = int(argv[4]) if len(argv) > 4 else 4
     torch.cuda.set_device(0)
@@ -30,11 +32,18 @@ def main(argv):
     ws = [torch.randint(0, 255, (n * rb,), dtype=torch.uint8, device="cuda") for _ in range(ncopy)]
     for w in ws:  # finite fp16 scales
         ops.gpu_quantize_weights_into(qt, torch.randn(n, k, device="cuda") * 0.02, w, n, k)
-    xq = ops.gpu_quantize_q8_1(torch.randn(m, k, device="cuda"))
-    y = torch.empty(m, n, device="cuda")
-    torch.cuda.synchronize()
-    for i in range(reps):
-        ops.gpu_qmatvec_into(qt, ws[i % ncopy], xq, y, m, n, k)
+    if gemm:
+        x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        y = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        torch.cuda.synchronize()
+        for i in range(reps):
+            ops.gpu_qgemm_q4_k_bf16_into(ws[i % ncopy], x, y, m, n, k)
+    else:
+        xq = ops.gpu_quantize_q8_1(torch.randn(m, k, device="cuda"))
+        y = torch.empty(m, n, device="cuda")
+        torch.cuda.synchronize()
+        for i in range(reps):
+            ops.gpu_qmatvec_into(qt, ws[i % ncopy], xq, y, m, n, k)
     torch.cuda.synchronize()
     ops.check_launch()
     print("done")
