@@ -387,22 +387,12 @@ int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, lo
         p.y = y + (size_t)m0 * y_stride;
         p.y_stride = y_stride;
 
-        // Q4_K unit width: the widest unit that keeps the activation registers within budget
-        // (UW * M <= 2 unless forced) and at least 7/8 of the lanes busy; other formats use 1.
+        // Q4_K unit width: one 32-byte group per lane measured fastest on every decode shape (wider units
+        // decode the packed scales less often but cost registers and occupancy); "q4k_unit" overrides.
         int uw = 1;
-        if (type == QMM_TYPE_Q4_K) {
-            if (g_q4k_unit) {
-                uw = g_q4k_unit;
-            } else {
-                for (int cand = 2; cand >= 1; cand /= 2) {
-                    const int u = k / (64 * cand), lanes = ((u + 31) / 32) * 32;
-                    if (cand * mt <= 2 && u * 8 >= lanes * 7) {
-                        uw = cand;
-                        break;
-                    }
-                }
-            }
-            if (uw * mt > 4) uw = 4 / mt;
+        if (type == QMM_TYPE_Q4_K && g_q4k_unit) {
+            uw = g_q4k_unit;
+            while (uw > 1 && (uw * mt > 4 || k % (64 * uw) != 0)) uw /= 2;
         }
         p.units = k / (unit_elems * uw);
         // K split: the fewest passes that keep the K axis within the consumer warps (passes > 1 only for UW = 1)
