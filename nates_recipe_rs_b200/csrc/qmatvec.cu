@@ -292,6 +292,9 @@ static int g_trace_stride = 0, g_trace_count = 0;
 // tuning aid: the next launches write 4 time stamps per CTA at trace + launch_index * stride
 void matvec_set_trace(unsigned long long* buf, int stride_words) { g_trace = buf; g_trace_stride = stride_words; g_trace_count = 0; }
 void gemm_set_probe(int v);
+int mma_set_min_m(int v);
+int mma_min_m();
+int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, cudaStream_t stream);
 int matvec_tune(const char* key, int value) {
     const std::string k(key ? key : "");
     if (k == "gemm_probe" && value >= 0 && value <= 2) return gemm_set_probe(value), QMM_OK;
@@ -301,6 +304,7 @@ int matvec_tune(const char* key, int value) {
     if (k == "q4k_unit" && (value == 0 || value == 1 || value == 2 || value == 4)) return g_q4k_unit = value, QMM_OK;
     if (k == "rb_max" && (value == 1 || value == 2 || value == 4)) return g_rb_max = value, QMM_OK;
     if (k == "probe" && value >= 0 && value <= 1) return g_probe = value, QMM_OK;
+    if (k == "mma_min_m") return mma_set_min_m(value);
     return QMM_ERR_UNSUPPORTED;
 }
 
@@ -379,7 +383,21 @@ int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, lo
     p.partial_off = (int)((sizeof(MatvecSmemHeader) + 127) & ~size_t(127));
     constexpr size_t SMEM_LIMIT = 200 * 1024;
 
-    for (int m0 = 0; m0 < m; m0 += 4) {
+    // From mma_min_m activation rows on, groups of up to 16 rows go to the tensor-core kernel where it
+    // supports the shape; what is left (fewer rows, other types and shapes) takes the dp4a kernel below.
+    int m_done = 0;
+    if (mma_min_m() > 0 && !g_probe && !g_trace) {
+        while (m - m_done >= mma_min_m()) {
+            const int mg = m - m_done < 16 ? m - m_done : 16;
+            const int st = qmatvec_mma_launch(type, w, static_cast<const uint8_t*>(xq) + (size_t)m_done * p.xq_row_bytes,
+                                              y + (size_t)m_done * y_stride, y_stride, mg, n, k, stream);
+            if (st == QMM_ERR_UNSUPPORTED) break;
+            if (st) return st;
+            m_done += mg;
+        }
+    }
+
+    for (int m0 = m_done; m0 < m; m0 += 4) {
         const int left = m - m0;
         const int mt = left >= 3 ? 4 : left;  // register tile of 1, 2 or 4 activation rows
         p.m = left < mt ? left : mt;

@@ -133,6 +133,10 @@ SHAPES = [
     # (m, n, k)
     (1, 1, 256), (1, 7, 256), (1, 33, 512), (1, 300, 1024), (2, 129, 2048), (3, 64, 4096),
     (1, 1000, 4096), (4, 515, 4096), (1, 257, 14336), (5, 96, 8192), (1, 40, 28672), (9, 200, 1792),
+    # three rows and more: Q4_K takes the tensor-core kernel where the shape allows (one or two tiles of
+    # eight activation rows, one or several K chunks, ragged last row tile and last chunk), else dp4a
+    (8, 300, 4096), (16, 1000, 4096), (13, 257, 14336), (21, 100, 8192), (16, 40, 28672), (7, 17, 256),
+    (6, 50, 1024), (12, 50, 1024), (3, 4099, 2048), (10, 333, 4608),
 ]
 
 
@@ -147,9 +151,30 @@ def test_matvec_matches_oracle(ops, qtype, m, n, k):
     assert_close(y.cpu().numpy(), oracle.matvec(qtype, w, xq, k), f"{oracle.TYPE_NAMES[qtype]} {m}x{n}x{k}")
 
 
+@pytest.mark.parametrize("m,n,k", [(3, 515, 4096), (8, 4096, 4096), (16, 1031, 14336), (11, 2048, 8192)])
+def test_small_batch_tensor_core_kernel_matches_dp4a_kernel(ops, m, n, k):
+    """The same launch through both Q4_K kernels (the threshold is a tunable), twice each."""
+    from nates_recipe_rs_b200 import _lib
+    L = _lib.lib()
+    w = dev(seeded_weights(oracle.Q4_K, n, k, 77))
+    xq = ops.gpu_quantize_q8_1(torch.from_numpy(oracle.fill_normal(m * k, 78, 1.0).reshape(m, k)).cuda())
+    try:
+        _lib.check(L.qmm_tune(b"mma_min_m", 0), "tune")
+        y_dp4a = ops.gpu_qmatvec(oracle.Q4_K, w, xq, m, n, k)
+        _lib.check(L.qmm_tune(b"mma_min_m", 1), "tune")
+        y_mma = ops.gpu_qmatvec(oracle.Q4_K, w, xq, m, n, k)
+        y_mma2 = ops.gpu_qmatvec(oracle.Q4_K, w, xq, m, n, k)
+    finally:
+        _lib.check(L.qmm_tune(b"mma_min_m", 3), "tune")
+    ops.check_launch()
+    assert torch.equal(y_mma, y_mma2)
+    assert_close(y_mma.cpu().numpy(), y_dp4a.cpu().numpy())
+
+
 @pytest.mark.parametrize("qtype", TYPES)
-def test_matvec_random_byte_weights(ops, qtype):
-    m, n, k = 2, 77, 2048
+@pytest.mark.parametrize("m", [2, 8, 16])
+def test_matvec_random_byte_weights(ops, qtype, m):
+    n, k = 77, 2048
     w = random_byte_weights(qtype, n, k, 5)
     xq = oracle.quantize(oracle.Q8_1, oracle.fill_normal(m * k, 6, 1.0).reshape(m, k))
     y = ops.gpu_qmatvec(qtype, dev(w), dev(xq), m, n, k)
