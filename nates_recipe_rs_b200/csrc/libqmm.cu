@@ -3,8 +3,8 @@
 #include "api.cu"
 #include "quantize.cu"
 #include "qmatvec.cu"
-#include "qmatvec_mma.cu"
 #include "qgemm.cu"
+#include "qmatvec_mma.cu"
 #include "decoder_ops.cu"
 #include "attn_entry.cu"
 #include "decoder.cu"

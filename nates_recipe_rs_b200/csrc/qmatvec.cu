@@ -294,7 +294,8 @@ void matvec_set_trace(unsigned long long* buf, int stride_words) { g_trace = buf
 void gemm_set_probe(int v);
 int mma_set_min_m(int v);
 int mma_min_m();
-int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, cudaStream_t stream);
+int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k,
+                       unsigned long long* trace, cudaStream_t stream);
 int matvec_tune(const char* key, int value) {
     const std::string k(key ? key : "");
     if (k == "gemm_probe" && value >= 0 && value <= 2) return gemm_set_probe(value), QMM_OK;
@@ -386,11 +387,11 @@ int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, lo
     // From mma_min_m activation rows on, groups of up to 16 rows go to the tensor-core kernel where it
     // supports the shape; what is left (fewer rows, other types and shapes) takes the dp4a kernel below.
     int m_done = 0;
-    if (mma_min_m() > 0 && !g_probe && !g_trace) {
+    if (mma_min_m() > 0 && !g_probe) {
         while (m - m_done >= mma_min_m()) {
             const int mg = m - m_done < 16 ? m - m_done : 16;
             const int st = qmatvec_mma_launch(type, w, static_cast<const uint8_t*>(xq) + (size_t)m_done * p.xq_row_bytes,
-                                              y + (size_t)m_done * y_stride, y_stride, mg, n, k, stream);
+                                              y + (size_t)m_done * y_stride, y_stride, mg, n, k, p.trace, stream);
             if (st == QMM_ERR_UNSUPPORTED) break;
             if (st) return st;
             m_done += mg;

@@ -8,17 +8,18 @@
 //
 //   * one persistent CTA per SM owns a contiguous range of 16-row tiles; the K axis is cut into
 //     chunks of CW super-block columns (CW = consumer warps).  A ring stage holds the pieces
-//     (16 rows x CW super-blocks) of one tile and one chunk, fetched with one 1-D bulk copy per row
-//     (cp.async.bulk + mbarrier, issued by warp 0 between its tiles); the row pitch in shared
-//     memory is chosen so that the 8-byte fragment loads of a half-warp touch 32 different banks;
+//     (16 rows x CW super-blocks) of one tile and one chunk, fetched with one 3-D tensor copy
+//     (cp.async.bulk.tensor + mbarrier) whose box is a little wider than the columns, which makes the
+//     row pitch in shared memory one that spreads the 8-byte fragment loads of a half-warp over all banks;
 //   * consumer warp c owns super-block column c of the chunk and keeps the Q8_1 words, scales
 //     and sums of that column for all activation rows in registers, already in B-fragment order
-//     (reloaded once per chunk); the 4-bit weights are masked straight into A fragments;
+//     (reloaded once per chunk through a small staging area filled a chunk ahead); the 4-bit weights are masked straight into A fragments;
 //   * the per-sub-block integer sums are scaled in float (6-bit scale as an integer multiply-add
 //     onto a magic constant, then the activation scale), the mins term  sum_j m_j * s_j  of a
 //     super-block is one f16 mma (6-bit mins and the fp16 sums of Q8_1 are exact in f16);
-//   * the CW partial tiles of a stage are added in a fixed order after a named barrier (no atomics);
-//     with several chunks the running sums wait in shared memory until the last chunk.
+//   * the CW partial tiles of a stage are added in a fixed order (no atomics), one stage behind the
+//     arithmetic and spread over all warps, synchronised by an mbarrier that every warp arrives on once
+//     per stage; with several chunks the running sums wait in shared memory until the last chunk.
 #include "qmm_formats.cuh"
 
 namespace qmm {
@@ -34,10 +35,14 @@ struct MmaParams {
     int cw;            // consumer warps = super-block columns per chunk
     int n_chunks;
     int pitch;         // bytes between the row pieces of a stage
+    int chunk_groups;  // 96-byte groups per chunk of columns
     int nst;           // ring stages
     int stage_bytes;   // 16 * pitch
     int tiles_total;   // ceil(n / 16)
-    int part_off, yacc_off, ring_off;
+    int part_off, yacc_off, ring_off, xstage_off;
+    int opw, opw_p;    // outputs of a tile folded per warp, and the next power of two (<= 32)
+    int pstride;       // floats between the partial tiles of two warps
+    unsigned long long* trace;  // optional (tuning aid): per stage and warp of CTA 0, four SM-clock stamps
 };
 
 constexpr int MMA_MAX_STAGES = 8;
@@ -45,7 +50,9 @@ constexpr int MMA_MAX_CW = 16;
 
 struct __align__(16) MmaSmemHeader {
     uint64_t full[MMA_MAX_STAGES];
+    uint64_t pfull[4];
     int abort_flag;
+    int refill_next;  // first stage whose ring slot has not been handed back to the copies yet
 };
 
 __device__ __forceinline__ void mma_u8s8_k32(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -62,13 +69,6 @@ __device__ __forceinline__ void mma_f16_k16_lo(float (&d)[4], uint32_t a0, uint3
         : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
         : "r"(a0), "r"(a1), "r"(0), "r"(b0), "f"(0.f));
 }
-__device__ __forceinline__ void named_bar_sync(int id, int threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-// exact float of sum * scale for |sum * scale| < 2^22: integer multiply-add onto 1.5 * 2^23, then subtract it
-__device__ __forceinline__ float scaled_sum_to_float(int sum, int scale) {
-    return __int_as_float(sum * scale + 0x4B400000) - 12582912.f;
-}
 // two 6-bit codes (bytes 0 and 1 of v) as f16x2: 0x6400 | c is 1024 + c
 __device__ __forceinline__ uint32_t codes_to_half2(uint32_t v) {
     const uint32_t biased = __byte_perm(v, 0x64646464u, 0x4140);
@@ -76,21 +76,70 @@ __device__ __forceinline__ uint32_t codes_to_half2(uint32_t v) {
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-__device__ __forceinline__ bool mma_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort) {
-    if (*cta_abort) return false;
-    return mbar_wait_bounded(bar, parity, cta_abort);
+// packed pairs of floats (one 64-bit register): d = a * b + c and d = a + b on both halves
+__device__ __forceinline__ uint64_t pack_b64(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
 }
+__device__ __forceinline__ void unpack_f2(uint64_t v, float& lo, float& hi) {
+    uint32_t a, b;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+    lo = __uint_as_float(a), hi = __uint_as_float(b);
+}
+__device__ __forceinline__ uint64_t pack_f2(float lo, float hi) { return pack_b64(__float_as_uint(lo), __float_as_uint(hi)); }
+__device__ __forceinline__ uint64_t fma_f2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_f2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+// shared-memory accesses by 32-bit shared address (no 64-bit address arithmetic in the inner loops)
+__device__ __forceinline__ uint4 lds_v4(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds_v2(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
+    uint32_t v;
+    asm volatile("{ .reg .b16 h; ld.shared.u16 h, [%1]; cvt.u32.u16 %0, h; }" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float lds_f32(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void sts_f32(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory"); }
+__device__ __forceinline__ uint32_t byte_n(uint32_t v, int n) { return __byte_perm(v, 0, 0x4440 + n); }
+
+constexpr int PART_DEPTH = 3;  // partial-sum tiles in flight (see the ordering argument in the kernel)
 
 // NT: activation rows in tiles of eight (1: m <= 8, 2: m <= 16)
 template <int NT>
-__global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_q4k_kernel(const MmaParams p) {
+__global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_q4k_kernel(const __grid_constant__ CUtensorMap wmap, const MmaParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     MmaSmemHeader* hdr = reinterpret_cast<MmaSmemHeader*>(smem);
-    float* part = reinterpret_cast<float*>(smem + p.part_off);   // [2][cw][128*NT]
-    float* yacc = reinterpret_cast<float*>(smem + p.yacc_off);   // [tiles][128*NT], several chunks only
-    uint8_t* ring = smem + p.ring_off;
     volatile int* cta_abort = &hdr->abort_flag;
     constexpr int OUTS = 128 * NT;  // values of one 16 x (8*NT) output tile, in fragment order
+    const uint32_t part_s = smem_u32(smem + p.part_off);  // [PART_DEPTH][cw][pstride] floats
+    const uint32_t yacc_s = smem_u32(smem + p.yacc_off);  // [tiles][OUTS] floats, several chunks only
+    const uint32_t ring_s = (smem_u32(smem + p.ring_off) + 127u) & ~127u;  // tensor copies land on 128-byte boundaries
+    const uint32_t full_s = smem_u32(&hdr->full[0]), pfull_s = smem_u32(&hdr->pfull[0]);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t_begin = (int)((long)blockIdx.x * p.tiles_total / gridDim.x);
@@ -100,44 +149,122 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_q4k_kernel(const M
     const int rows_cta = min(p.n, t_end * 16) - row0;
     const int n_it = p.n_chunks * tiles;
 
+    // tuning aid: wall-clock stamps of CTA 0 (entry, predecessor done, activations in registers, exit)
+    unsigned long long* trg = (p.trace && blockIdx.x == 0 && threadIdx.x == 0) ? p.trace + (size_t)63 * p.cw * 8 : nullptr;
+    if (trg) trg[0] = globaltimer_ns(), trg[5] = clock64();
     if (threadIdx.x == 0) {
-        for (int s = 0; s < p.nst; ++s) mbar_init(smem_u32(&hdr->full[s]), 1);
+        for (int s = 0; s < p.nst; ++s) mbar_init(full_s + 8 * s, 1);
+        for (int s = 0; s < PART_DEPTH; ++s) mbar_init(pfull_s + 8 * s, p.cw);
         hdr->abort_flag = 0;
+        hdr->refill_next = 0;
         mbar_fence_init();
     }
     __syncthreads();
     pdl_release_dependents();
 
-    // Stage `it` = (chunk it / tiles, tile it % tiles).  Warp 0 issues the copies: the named barrier that
-    // every warp passes once per stage (below) also tells it that the slot of the stage just finished
-    // is free, so the ring needs no second set of barriers and no warp of its own.
+    // Stage `it` = (chunk it / tiles, tile it % tiles): one 3-D tensor copy of 16 rows x pitch bytes, the
+    // row as (96-byte groups, group index).  The box is wider than the chunk's columns so that the rows
+    // land pitch bytes apart; what it fetches beyond them (the next columns, or zeros past the end of the
+    // row or of the matrix) is never read.
     auto issue = [&](int it) {
-        const int slot = it % p.nst;
-        const int c = it / tiles, ti = it - c * tiles;
-        const int cols = min(p.cw, p.k_blocks - c * p.cw);
-        const uint32_t piece = (uint32_t)cols * Q4_K_BYTES;
-        const int nr = min(16, rows_cta - ti * 16);
-        const uint32_t bar = smem_u32(&hdr->full[slot]);
-        if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)nr * piece);
-        __syncwarp();
-        if (lane < nr)
-            bulk_g2s(smem_u32(ring + (size_t)slot * p.stage_bytes + (size_t)lane * p.pitch),
-                     p.w + (size_t)(row0 + ti * 16 + lane) * p.row_bytes + (size_t)c * p.cw * Q4_K_BYTES, piece, bar);
+        if (lane == 0) {
+            const int slot = it % p.nst;
+            const int c = it / tiles, ti = it - c * tiles;
+            const uint32_t bar = full_s + 8 * slot;
+            mbar_arrive_expect_tx(bar, (uint32_t)p.stage_bytes);
+            asm volatile(
+                "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+                    ring_s + (uint32_t)slot * p.stage_bytes),
+                "l"(reinterpret_cast<uint64_t>(&wmap)), "r"(0), "r"(c * p.chunk_groups), "r"(row0 + ti * 16), "r"(bar)
+                : "memory");
+        }
     };
-    int issued = 0;
     if (warp == 0)
-        for (; issued < n_it && issued < p.nst; ++issued) issue(issued);
+        for (int s = 0; s < n_it && s < p.nst; ++s) issue(s);
 
-    // Every warp passes every stage and every named barrier, also after a timeout (it then skips
-    // the waits and the arithmetic), so no warp is left behind at a barrier.
+    auto give_up = [&](int code) {
+        if (lane == 0 && !*cta_abort) {
+            atomicExch(&g_device_status, code);
+            *cta_abort = 1;
+        }
+    };
+
+    // Fold of a stage: the cw partial tiles are added in a fixed order.  Warp w owns outputs w*opw ..
+    // w*opw+opw-1 of the tile (fragment order); the lanes of a warp split the partial tiles 32/opw_p ways
+    // and meet in a shuffle.  A timed-out wait only skips work: every warp still makes every arrival.
+    const int ol = lane & (p.opw_p - 1), sub = lane / p.opw_p, subs = 32 / p.opw_p;
+    const int my_o = warp * p.opw + ol;
+    const bool o_valid = ol < p.opw && my_o < OUTS;
+    // output my_o is register my_o / 32 of lane my_o % 32 of the accumulator fragments
+    const int o_row = ((my_o & 31) >> 2) + 8 * ((my_o >> 6) & 1);
+    const int o_bt = 8 * (my_o >> 7) + 2 * (my_o & 3) + ((my_o >> 5) & 1);
+    const uint32_t pstride_b = (uint32_t)p.pstride * 4u;
+    unsigned long long* trw = nullptr;
+    auto fold = [&](int pbuf, uint32_t ppar, int c, int ti, int cols) {
+        if (!mbar_wait_bounded(pfull_s + 8 * pbuf, ppar, cta_abort)) {
+            give_up(DEV_TIMEOUT_EMPTY);
+            return false;
+        }
+        if (trw) trw[4] = clock64();
+        // all loads first (up to four partial tiles per lane, and the running sum), then the additions
+        const uint32_t src = part_s + ((uint32_t)(pbuf * p.cw + sub) * p.pstride + my_o) * 4u;
+        const uint32_t ya = yacc_s + (uint32_t)(ti * OUTS + my_o) * 4u;
+        float v[4], run = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = (o_valid && sub + i * subs < cols) ? lds_f32(src + (uint32_t)(i * subs) * pstride_b) : 0.f;
+        if (o_valid && sub == 0 && c > 0) run = lds_f32(ya);
+        float sum = (v[0] + v[1]) + (v[2] + v[3]);
+        for (int wv = sub + 4 * subs; wv < cols; wv += subs) sum += lds_f32(src + (uint32_t)(wv - sub) * pstride_b);  // subs == 1 only
+        for (int off = p.opw_p; off < 32; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        sum += run;
+        if (o_valid && sub == 0) {
+            if (c + 1 < p.n_chunks) sts_f32(ya, sum);
+            if (c + 1 == p.n_chunks) {
+                const int row = ti * 16 + o_row;
+                if (row < rows_cta && o_bt < p.m) p.y[(size_t)o_bt * p.y_stride + row0 + row] = sum;
+            }
+        }
+        return true;
+    };
+
     const int q = lane >> 2, pq = lane & 3;
-    const int tid = threadIdx.x;
     pdl_wait_prior_grids();  // activations come from the preceding kernel, y may still be read by it
+
+    // Activations of a warp's column reach its registers through a private staging area: eight rows x
+    // 288 bytes fetched with 16-byte asynchronous copies (whole lines, a fraction of the requests that
+    // per-lane fragment loads would make), requested one chunk ahead, then read in fragment order.
+    constexpr uint32_t X_COL_BYTES = 8 * Q8_1_BYTES;  // one super-block column of one activation row
+    const uint32_t xst_s = smem_u32(smem + p.xstage_off) + (uint32_t)warp * 8 * X_COL_BYTES;
+    auto stage_x = [&](int col, int t) {
+        for (int i = lane; i < 8 * 18; i += 32) {
+            const int r = i / 18, piece = i - r * 18;
+            if (8 * t + r < p.m) {
+                const uint8_t* src = p.xq + (size_t)(8 * t + r) * p.xq_row_bytes + (size_t)col * X_COL_BYTES + piece * 16;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(xst_s + r * X_COL_BYTES + piece * 16), "l"(src) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (trg) trg[1] = globaltimer_ns();
+    if (warp < p.k_blocks) stage_x(warp, 0);
 
     uint32_t xb0[NT][8], xb1[NT][8];  // B fragments: sub-block j, activation row 8t+q, elements 8pq.. and 8pq+4..
     uint32_t xdh[NT][8];              // NT == 2: fp16 scales of activation rows 8t+2pq (low half) and 8t+2pq+1
-    float xda[NT][8], xdb[NT][8];     // NT == 1: the same scales as floats
+    uint64_t xdf[NT][8];              // NT == 1: the same scales as a pair of floats
     uint32_t xsf[NT];                 // f16x2: Q8_1 sums of sub-blocks 2pq, 2pq+1 of activation row 8t+q
+    const uint64_t minus_magic = pack_f2(-12582912.f, -12582912.f);
+    const uint32_t my_row_off = (uint32_t)q * p.pitch + (uint32_t)warp * Q4_K_BYTES;
+    const uint32_t my_part_off = ((uint32_t)warp * p.pstride + lane) * 4u;
+    const uint32_t part_buf_b = (uint32_t)p.cw * pstride_b;
+    const uint32_t sh_m = 16u * (pq & 1);
+
+    // running indices of the current stage `it` (ring slot and phase, partial tile and phase) and of the
+    // stage before it (what the fold needs), kept incrementally: no divisions in the loop
+    int it = 0, slot = 0, pbuf = 0;
+    uint32_t full_par = 0, ppar = 0;
+    int prev_pbuf = 0, prev_c = 0, prev_ti = 0, prev_cols = 0;
+    uint32_t prev_ppar = 0;
+    bool dead = false;
 
     for (int c = 0; c < p.n_chunks; ++c) {
         const int col = c * p.cw + warp;
@@ -146,133 +273,141 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_q4k_kernel(const M
         if (active) {
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
+                if (t > 0) stage_x(col, t);  // the first tile of eight rows was requested a chunk ahead
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                __syncwarp();
                 const int bq = 8 * t + q, ba = 8 * t + 2 * pq;
-                const uint8_t* rq = p.xq + (size_t)bq * p.xq_row_bytes + (size_t)col * 8 * Q8_1_BYTES;
-                const uint8_t* ra = p.xq + (size_t)ba * p.xq_row_bytes + (size_t)col * 8 * Q8_1_BYTES;
-                const uint8_t* rb = ra + p.xq_row_bytes;
+                const uint32_t rq = xst_s + (uint32_t)q * X_COL_BYTES, ra = xst_s + (uint32_t)(2 * pq) * X_COL_BYTES;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     uint32_t w0 = 0, w1 = 0, da = 0, db = 0;
-                    if (bq < p.m) {
-                        const uint32_t* qs = reinterpret_cast<const uint32_t*>(rq + j * Q8_1_BYTES + 4 + 8 * pq);
-                        w0 = qs[0], w1 = qs[1];
-                    }
-                    if (ba < p.m) da = *reinterpret_cast<const uint16_t*>(ra + j * Q8_1_BYTES);
-                    if (ba + 1 < p.m) db = *reinterpret_cast<const uint16_t*>(rb + j * Q8_1_BYTES);
+                    if (bq < p.m) w0 = lds_u32(rq + j * Q8_1_BYTES + 4 + 8 * pq), w1 = lds_u32(rq + j * Q8_1_BYTES + 8 + 8 * pq);
+                    if (ba < p.m) da = lds_u16(ra + j * Q8_1_BYTES);
+                    if (ba + 1 < p.m) db = lds_u16(ra + X_COL_BYTES + j * Q8_1_BYTES);
                     xb0[t][j] = w0, xb1[t][j] = w1;
                     if constexpr (NT == 1) {
-                        xda[t][j] = f16_bits_to_f32(da), xdb[t][j] = f16_bits_to_f32(db);
+                        xdf[t][j] = pack_f2(f16_bits_to_f32(da), f16_bits_to_f32(db));
                     } else {
                         xdh[t][j] = da | (db << 16);
                     }
                 }
                 uint32_t s = 0;
-                if (bq < p.m) {
-                    const uint32_t s0 = *reinterpret_cast<const uint16_t*>(rq + (2 * pq) * Q8_1_BYTES + 2);
-                    const uint32_t s1 = *reinterpret_cast<const uint16_t*>(rq + (2 * pq + 1) * Q8_1_BYTES + 2);
-                    s = s0 | (s1 << 16);
-                }
+                if (bq < p.m) s = lds_u16(rq + (2 * pq) * Q8_1_BYTES + 2) | (lds_u16(rq + (2 * pq + 1) * Q8_1_BYTES + 2) << 16);
                 xsf[t] = s;
+                __syncwarp();  // the staging area is overwritten next
             }
         }
+        if (c + 1 < p.n_chunks && col + p.cw < p.k_blocks) stage_x(col + p.cw, 0);
+        if (trg && c == 0) trg[2] = globaltimer_ns(), trg[6] = clock64();
 
         for (int ti = 0; ti < tiles; ++ti) {
-            const int it = c * tiles + ti, slot = it % p.nst;
-            bool ok = mma_wait(smem_u32(&hdr->full[slot]), (it / p.nst) & 1, cta_abort);
-            if (!ok && lane == 0 && !*cta_abort) {
-                atomicExch(&g_device_status, DEV_TIMEOUT_FULL);
-                *cta_abort = 1;
+            const long long t_top = p.trace ? clock64() : 0;
+            bool ok = !dead;  // after a timeout only the arrivals remain
+            if (ok && !mbar_wait_bounded(full_s + 8 * slot, full_par, cta_abort)) {
+                give_up(DEV_TIMEOUT_FULL);
+                ok = false, dead = true;
             }
-            float* my_part = part + ((size_t)(it & 1) * p.cw + warp) * OUTS + lane;
+            const bool tr = p.trace && blockIdx.x == 0 && lane == 0;
+            unsigned long long* trp = p.trace + ((size_t)it * p.cw + warp) * 8;
+            if (tr) trp[0] = clock64(), trp[5] = t_top;
+            trw = tr ? trp : nullptr;
             if (ok && active) {
-                const uint8_t* r0 = ring + (size_t)slot * p.stage_bytes + (size_t)q * p.pitch + (size_t)warp * Q4_K_BYTES;
-                const uint8_t* r1 = r0 + 8 * (size_t)p.pitch;
-                const uint4 h0 = *reinterpret_cast<const uint4*>(r0);
-                const uint4 h1 = *reinterpret_cast<const uint4*>(r1);
+                const uint32_t r0 = ring_s + (uint32_t)slot * p.stage_bytes + my_row_off;
+                const uint32_t r1 = r0 + 8u * p.pitch;
+                const uint4 h0 = lds_v4(r0), h1 = lds_v4(r1);
                 // 6-bit codes, one per byte: A = sub-blocks 0..3, B = 4..7
                 const uint32_t scA0 = h0.y & 0x3F3F3F3Fu, scB0 = (h0.w & 0x0F0F0F0Fu) | ((h0.y >> 2) & 0x30303030u);
                 const uint32_t scA1 = h1.y & 0x3F3F3F3Fu, scB1 = (h1.w & 0x0F0F0F0Fu) | ((h1.y >> 2) & 0x30303030u);
                 const uint32_t mA0 = h0.z & 0x3F3F3F3Fu, mB0 = ((h0.w >> 4) & 0x0F0F0F0Fu) | ((h0.z >> 2) & 0x30303030u);
                 const uint32_t mA1 = h1.z & 0x3F3F3F3Fu, mB1 = ((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u);
                 // mins of sub-blocks 2pq, 2pq+1 of both rows as f16x2 A fragments
-                const uint32_t sh = 16u * (pq & 1);
-                const uint32_t ma0 = codes_to_half2(((pq < 2) ? mA0 : mB0) >> sh);
-                const uint32_t ma1 = codes_to_half2(((pq < 2) ? mA1 : mB1) >> sh);
-                float cm[NT][4], acc[NT][4];
+                const uint32_t ma0 = codes_to_half2(((pq < 2) ? mA0 : mB0) >> sh_m);
+                const uint32_t ma1 = codes_to_half2(((pq < 2) ? mA1 : mB1) >> sh_m);
+                float cm[NT][4];
+                uint64_t acc01[NT], acc23[NT];  // (row q: activation rows 2pq, 2pq+1), (row q+8: the same two)
 #pragma unroll
                 for (int t = 0; t < NT; ++t) {
                     mma_f16_k16_lo(cm[t], ma0, ma1, xsf[t]);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
+                    acc01[t] = 0, acc23[t] = 0;
                 }
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
-                    const uint2 w0 = *reinterpret_cast<const uint2*>(r0 + 16 + 32 * g + 8 * pq);
-                    const uint2 w1 = *reinterpret_cast<const uint2*>(r1 + 16 + 32 * g + 8 * pq);
+                    const uint2 w0 = lds_v2(r0 + 16 + 32 * g + 8 * pq);
+                    const uint2 w1 = lds_v2(r1 + 16 + 32 * g + 8 * pq);
 #pragma unroll
                     for (int hi = 0; hi < 2; ++hi) {
                         const int j = 2 * g + hi;
                         const uint32_t a0 = (hi ? (w0.x >> 4) : w0.x) & 0x0F0F0F0Fu, a2 = (hi ? (w0.y >> 4) : w0.y) & 0x0F0F0F0Fu;
                         const uint32_t a1 = (hi ? (w1.x >> 4) : w1.x) & 0x0F0F0F0Fu, a3 = (hi ? (w1.y >> 4) : w1.y) & 0x0F0F0F0Fu;
-                        const int sc0 = (int)(((j < 4 ? scA0 : scB0) >> (8 * (j & 3))) & 0xFFu);
-                        const int sc1 = (int)(((j < 4 ? scA1 : scB1) >> (8 * (j & 3))) & 0xFFu);
+                        const int sc0 = (int)byte_n(j < 4 ? scA0 : scB0, j & 3);
+                        const int sc1 = (int)byte_n(j < 4 ? scA1 : scB1, j & 3);
 #pragma unroll
                         for (int t = 0; t < NT; ++t) {
                             int d[4];
                             mma_u8s8_k32(d, a0, a1, a2, a3, xb0[t][j], xb1[t][j]);
-                            float da, db;
+                            uint64_t dab;
                             if constexpr (NT == 1) {
-                                da = xda[t][j], db = xdb[t][j];
+                                dab = xdf[t][j];
                             } else {
                                 const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xdh[t][j]));
-                                da = f.x, db = f.y;
+                                dab = pack_f2(f.x, f.y);
                             }
-                            acc[t][0] += da * scaled_sum_to_float(d[0], sc0);
-                            acc[t][1] += db * scaled_sum_to_float(d[1], sc0);
-                            acc[t][2] += da * scaled_sum_to_float(d[2], sc1);
-                            acc[t][3] += db * scaled_sum_to_float(d[3], sc1);
+                            // sum * scale as exact floats: integer multiply-add onto 1.5 * 2^23, then subtract it
+                            const uint64_t v01 = pack_b64((uint32_t)(d[0] * sc0 + 0x4B400000), (uint32_t)(d[1] * sc0 + 0x4B400000));
+                            const uint64_t v23 = pack_b64((uint32_t)(d[2] * sc1 + 0x4B400000), (uint32_t)(d[3] * sc1 + 0x4B400000));
+                            acc01[t] = fma_f2(dab, add_f2(v01, minus_magic), acc01[t]);
+                            acc23[t] = fma_f2(dab, add_f2(v23, minus_magic), acc23[t]);
                         }
                     }
                 }
                 const float d0 = f16_bits_to_f32(h0.x & 0xFFFFu), dmin0 = f16_bits_to_f32(h0.x >> 16);
                 const float d1 = f16_bits_to_f32(h1.x & 0xFFFFu), dmin1 = f16_bits_to_f32(h1.x >> 16);
+                const uint32_t mp = part_s + (uint32_t)pbuf * part_buf_b + my_part_off;
 #pragma unroll
                 for (int t = 0; t < NT; ++t) {
-                    my_part[(4 * t + 0) * 32] = d0 * acc[t][0] - dmin0 * cm[t][0];
-                    my_part[(4 * t + 1) * 32] = d0 * acc[t][1] - dmin0 * cm[t][1];
-                    my_part[(4 * t + 2) * 32] = d1 * acc[t][2] - dmin1 * cm[t][2];
-                    my_part[(4 * t + 3) * 32] = d1 * acc[t][3] - dmin1 * cm[t][3];
+                    float a, b, e, f;
+                    unpack_f2(acc01[t], a, b);
+                    unpack_f2(acc23[t], e, f);
+                    sts_f32(mp + (4 * t + 0) * 128, d0 * a - dmin0 * cm[t][0]);
+                    sts_f32(mp + (4 * t + 1) * 128, d0 * b - dmin0 * cm[t][1]);
+                    sts_f32(mp + (4 * t + 2) * 128, d1 * e - dmin1 * cm[t][2]);
+                    sts_f32(mp + (4 * t + 3) * 128, d1 * f - dmin1 * cm[t][3]);
                 }
             }
-            named_bar_sync(1, p.cw * 32);
-            if (warp == 0 && it + p.nst < n_it && !*cta_abort) {
-                issue(it + p.nst);
-                issued = it + p.nst + 1;
+            // Order within an iteration: arithmetic of stage `it`, fold of stage it-1, then the arrival for
+            // stage `it`.  A warp thus runs at most one stage ahead of the slowest one, and when it writes
+            // partial tile it % 3 every warp has made its arrival for stage it-2, i.e. finished folding
+            // stage it-3, the previous user of that tile.
+            if (tr) trp[1] = clock64();
+            if (it > 0 && !dead && !fold(prev_pbuf, prev_ppar, prev_c, prev_ti, prev_cols)) dead = true;
+            if (tr) trp[2] = clock64();
+            __syncwarp();
+            // Once the arrivals of a stage are complete nobody reads its weights any more.  The warp that
+            // arrives last sees the phase complete at once and refills the ring slot; if two warps see it,
+            // the compare-and-swap picks one.
+            int refill = 0;
+            if (lane == 0) {
+                const uint32_t bar = pfull_s + 8 * pbuf;
+                mbar_arrive(bar);
+                if (it + p.nst < n_it && !dead && mbar_test_wait(bar, ppar)) refill = atomicCAS(&hdr->refill_next, it, it + 1) == it;
             }
-            // fold: thread tid owns value tid of the tile (fragment order: register tid/32 of lane tid%32)
-            if (tid < OUTS && !*cta_abort) {
-                const float* src = part + (size_t)(it & 1) * p.cw * OUTS + tid;
-                float s = 0.f;
-                for (int wv = 0; wv < cols; ++wv) s += src[(size_t)wv * OUTS];
-                if (p.n_chunks > 1) {
-                    float* ya = yacc + (size_t)ti * OUTS + tid;
-                    if (c > 0) s += *ya;
-                    if (c + 1 < p.n_chunks) *ya = s;
-                }
-                if (c + 1 == p.n_chunks) {
-                    const int i = tid >> 5, l = tid & 31;
-                    const int row = ti * 16 + (l >> 2) + 8 * ((i >> 1) & 1);
-                    const int b = 8 * (i >> 2) + 2 * (l & 3) + (i & 1);
-                    if (row < rows_cta && b < p.m) p.y[(size_t)b * p.y_stride + row0 + row] = s;
-                }
-            }
+            if (refill) issue(it + p.nst);
+            if (tr) trp[3] = clock64();
+            prev_pbuf = pbuf, prev_ppar = ppar, prev_c = c, prev_ti = ti, prev_cols = cols;
+            ++it;
+            if (++slot == p.nst) slot = 0, full_par ^= 1;
+            if (++pbuf == PART_DEPTH) pbuf = 0, ppar ^= 1;
         }
     }
+    if (n_it > 0 && !dead) (void)fold(prev_pbuf, prev_ppar, prev_c, prev_ti, prev_cols);
+    if (trg) trg[3] = globaltimer_ns(), trg[7] = clock64();
+    __syncthreads();  // every warp is here (timed-out waits only skip work), so refill_next is final
     if (warp == 0 && lane == 0 && *cta_abort) {
         // wait (bounded) for copies still in flight before the CTA's shared memory is released
-        for (int it = max(0, issued - p.nst); it < issued; ++it) {
+        const int issued = min(n_it, hdr->refill_next + p.nst);
+        for (int s = max(0, issued - p.nst); s < issued; ++s) {
             const long long t0 = clock64();
-            while (!mbar_try_wait(smem_u32(&hdr->full[it % p.nst]), (it / p.nst) & 1)) {
+            while (!mbar_try_wait(full_s + 8 * (s % p.nst), (s / p.nst) & 1)) {
                 if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
                     atomicExch(&g_device_status, DEV_TIMEOUT_DRAIN);
                     break;
@@ -292,7 +427,7 @@ int mma_set_min_m(int v) {
 int mma_min_m() { return g_mma_min_m; }
 
 template <int NT>
-static int mma_launch_inst(const MmaParams& p, int grid, int threads, size_t smem, cudaStream_t stream) {
+static int mma_launch_inst(const CUtensorMap& wmap, const MmaParams& p, int grid, int threads, size_t smem, cudaStream_t stream) {
     auto kern = qmv_mma_q4k_kernel<NT>;
     static size_t configured[64] = {};
     int dev = 0;
@@ -311,14 +446,16 @@ static int mma_launch_inst(const MmaParams& p, int grid, int threads, size_t sme
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap_enabled() ? 1 : 0;
-    QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
+    QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, wmap, p));
     return QMM_OK;
 }
 
 // Returns QMM_ERR_UNSUPPORTED (nothing launched) when the shape does not fit this kernel; the caller
 // then uses the dp4a kernel.  m <= 16.
-int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, cudaStream_t stream) {
+int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k,
+                       unsigned long long* trace, cudaStream_t stream) {
     if (type != QMM_TYPE_Q4_K || m < 1 || m > 16 || k % QKK != 0) return QMM_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(xq) % 16 != 0) return QMM_ERR_UNSUPPORTED;  // 16-byte asynchronous copies
     MmaParams p = {};
     p.w = static_cast<const uint8_t*>(w);
     p.xq = static_cast<const uint8_t*>(xq);
@@ -326,13 +463,16 @@ int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y
     p.y_stride = y_stride;
     p.m = m;
     p.n = n;
+    p.trace = trace;
     p.k_blocks = k / QKK;
     p.row_bytes = p.k_blocks * Q4_K_BYTES;
     p.xq_row_bytes = k / QK8 * Q8_1_BYTES;
     const int nt = m > 8 ? 2 : 1;
-    // consumer warps: a divisor of the super-blocks per row in 12..16 if there is one (no ragged last chunk)
+    // consumer warps: an even divisor of the super-blocks per row in 12..16 if there is one (no ragged last
+    // chunk); even because a chunk of columns must start on a 96-byte group of the row (see below)
+    if (p.k_blocks % 2 != 0) return QMM_ERR_UNSUPPORTED;
     int cw = p.k_blocks < MMA_MAX_CW ? p.k_blocks : MMA_MAX_CW;
-    for (int c = MMA_MAX_CW; c >= 12; --c)
+    for (int c = MMA_MAX_CW; c >= 12; c -= 2)
         if (p.k_blocks >= c && p.k_blocks % c == 0) {
             cw = c;
             break;
@@ -340,25 +480,55 @@ int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y
     if (cw < 4 * nt) return QMM_ERR_UNSUPPORTED;  // the fold needs 128*nt threads
     p.cw = cw;
     p.n_chunks = (p.k_blocks + cw - 1) / cw;
+    // Row pitch in shared memory: the columns of a chunk plus padding, a multiple of the 96-byte group
+    // and 32 or 96 modulo 128, which puts the 8-byte fragment loads of a half-warp (four rows, 32
+    // consecutive bytes each) on 32 different banks.
+    constexpr int GROUP = 96;
     const int piece = cw * Q4_K_BYTES;
-    p.pitch = piece + ((32 - piece % 128) + 128) % 128;  // pitch % 128 == 32: conflict-free 8-byte fragment loads
+    p.pitch = 0;
+    for (int pad = GROUP; pad <= 4 * GROUP; pad += GROUP)
+        if ((piece + pad) % 128 == 32 || (piece + pad) % 128 == 96) {
+            p.pitch = piece + pad;
+            break;
+        }
+    if (!p.pitch) return QMM_ERR_UNSUPPORTED;
+    p.chunk_groups = piece / GROUP;
     p.stage_bytes = 16 * p.pitch;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return cuda_fail(cudaErrorNotSupported);
+    CUtensorMap wmap;
+    {
+        const cuuint64_t dims[3] = {GROUP / 4, (cuuint64_t)(p.row_bytes / GROUP), (cuuint64_t)n};
+        const cuuint64_t strides[2] = {GROUP, (cuuint64_t)p.row_bytes};
+        const cuuint32_t box[3] = {GROUP / 4, (cuuint32_t)(p.pitch / GROUP), 16};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cuda_fail(cudaErrorInvalidValue);
+    }
     p.tiles_total = (n + 15) / 16;
     const int sms = sm_count();
     const int grid = p.tiles_total < sms ? p.tiles_total : sms;
     const int tiles_max = (p.tiles_total + grid - 1) / grid;
-    constexpr size_t SMEM_LIMIT = 200 * 1024;
+    constexpr size_t SMEM_LIMIT = 220 * 1024;
     p.part_off = 256;
-    const size_t part_bytes = (size_t)2 * cw * 128 * nt * sizeof(float);
-    p.yacc_off = (int)(p.part_off + part_bytes);
+    const int outs = 128 * nt;
+    p.opw = (outs + cw - 1) / cw;
+    p.opw_p = 8;
+    while (p.opw_p < p.opw) p.opw_p *= 2;
+    // lanes that fold different partial tiles of the same outputs read pstride floats apart: different banks
+    p.pstride = outs + (p.opw_p < 32 ? p.opw_p : 0);
+    const size_t part_bytes = (size_t)PART_DEPTH * cw * p.pstride * sizeof(float);
+    p.xstage_off = (int)(p.part_off + part_bytes);  // 8 rows x 288 bytes per warp
+    p.yacc_off = p.xstage_off + cw * 8 * 8 * Q8_1_BYTES;
     const size_t yacc_bytes = p.n_chunks > 1 ? (size_t)tiles_max * 128 * nt * sizeof(float) : 0;
     p.ring_off = (int)((p.yacc_off + yacc_bytes + 127) & ~size_t(127));
-    if ((size_t)p.ring_off + 2 * (size_t)p.stage_bytes > SMEM_LIMIT) return QMM_ERR_UNSUPPORTED;
-    p.nst = (int)((SMEM_LIMIT - p.ring_off) / p.stage_bytes);
+    if ((size_t)p.ring_off + 128 + 2 * (size_t)p.stage_bytes > SMEM_LIMIT) return QMM_ERR_UNSUPPORTED;
+    p.nst = (int)((SMEM_LIMIT - p.ring_off - 128) / p.stage_bytes);
     if (p.nst > MMA_MAX_STAGES) p.nst = MMA_MAX_STAGES;
-    const size_t smem = (size_t)p.ring_off + (size_t)p.nst * p.stage_bytes;
+    const size_t smem = (size_t)p.ring_off + 128 + (size_t)p.nst * p.stage_bytes;
     const int threads = cw * 32;
-    return nt == 1 ? mma_launch_inst<1>(p, grid, threads, smem, stream) : mma_launch_inst<2>(p, grid, threads, smem, stream);
+    return nt == 1 ? mma_launch_inst<1>(wmap, p, grid, threads, smem, stream) : mma_launch_inst<2>(wmap, p, grid, threads, smem, stream);
 }
 
 }  // namespace qmm
