@@ -1,5 +1,5 @@
-// Small-batch decode matvec on the int8 tensor cores:  y(m,n) = xq(m,k) . w(n,k)^T  for 5..16
-// activation rows per launch, w in Q4_K super-blocks, xq in Q8_1 blocks.
+// Small-batch decode matvec on the int8 tensor cores:  y(m,n) = xq(m,k) . w(n,k)^T  for 3..16
+// activation rows per launch, w in Q4_K or Q6_K super-blocks, xq in Q8_1 blocks.
 //
 // The dp4a kernel (qmatvec.cu) pays its integer dot products once per activation row; from a
 // handful of rows on it is bound by instruction issue and re-streams the weights for every four
@@ -62,6 +62,18 @@ __device__ __forceinline__ void mma_u8s8_k32(int (&d)[4], uint32_t a0, uint32_t 
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
+// k = 16, accumulating onto c: one 16-element scale group of Q6_K
+__device__ __forceinline__ void mma_u8s8_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, const int (&c)[4]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+// the same with signed weights and every accumulator input equal to c
+__device__ __forceinline__ void mma_s8s8_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, int c) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(c));
+}
 // k = 16 with the upper eight k zero on both sides
 __device__ __forceinline__ void mma_f16_k16_lo(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
     asm volatile(
@@ -93,6 +105,11 @@ __device__ __forceinline__ uint64_t fma_f2(uint64_t a, uint64_t b, uint64_t c) {
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     return d;
 }
+__device__ __forceinline__ uint64_t mul_f2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ uint64_t add_f2(uint64_t a, uint64_t b) {
     uint64_t d;
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
@@ -119,6 +136,8 @@ __device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
     asm volatile("{ .reg .b16 h; ld.shared.u16 h, [%1]; cvt.u32.u16 %0, h; }" : "=r"(v) : "r"(a));
     return v;
 }
+// two 16-bit loads (addresses a and a+8) packed into one word: bytes a, a+1, a+8, a+9
+__device__ __forceinline__ uint32_t lds_h2(uint32_t a) { return __byte_perm(lds_u16(a), lds_u16(a + 8), 0x5410); }
 __device__ __forceinline__ float lds_f32(uint32_t a) {
     float v;
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
@@ -129,13 +148,14 @@ __device__ __forceinline__ uint32_t byte_n(uint32_t v, int n) { return __byte_pe
 
 constexpr int PART_DEPTH = 3;  // partial-sum tiles in flight (see the ordering argument in the kernel)
 
-// NT: activation rows in tiles of eight (1: m <= 8, 2: m <= 16)
-template <int NT>
-__global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_q4k_kernel(const __grid_constant__ CUtensorMap wmap, const MmaParams p) {
+// TYPE: Q4_K or Q6_K weights.  NT: activation rows in tiles of eight (1: m <= 8, 2: m <= 16)
+template <int TYPE, int NT>
+__global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __grid_constant__ CUtensorMap wmap, const MmaParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     MmaSmemHeader* hdr = reinterpret_cast<MmaSmemHeader*>(smem);
     volatile int* cta_abort = &hdr->abort_flag;
     constexpr int OUTS = 128 * NT;  // values of one 16 x (8*NT) output tile, in fragment order
+    constexpr int BLOCK_BYTES = TYPE == QMM_TYPE_Q4_K ? Q4_K_BYTES : Q6_K_BYTES;
     const uint32_t part_s = smem_u32(smem + p.part_off);  // [PART_DEPTH][cw][pstride] floats
     const uint32_t yacc_s = smem_u32(smem + p.yacc_off);  // [tiles][OUTS] floats, several chunks only
     const uint32_t ring_s = (smem_u32(smem + p.ring_off) + 127u) & ~127u;  // tensor copies land on 128-byte boundaries
@@ -253,7 +273,7 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_q4k_kernel(const _
     uint64_t xdf[NT][8];              // NT == 1: the same scales as a pair of floats
     uint32_t xsf[NT];                 // f16x2: Q8_1 sums of sub-blocks 2pq, 2pq+1 of activation row 8t+q
     const uint64_t minus_magic = pack_f2(-12582912.f, -12582912.f);
-    const uint32_t my_row_off = (uint32_t)q * p.pitch + (uint32_t)warp * Q4_K_BYTES;
+    const uint32_t my_row_off = (uint32_t)q * p.pitch + (uint32_t)warp * BLOCK_BYTES;
     const uint32_t my_part_off = ((uint32_t)warp * p.pstride + lane) * 4u;
     const uint32_t part_buf_b = (uint32_t)p.cw * pstride_b;
     const uint32_t sh_m = 16u * (pq & 1);
@@ -281,7 +301,13 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_q4k_kernel(const _
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     uint32_t w0 = 0, w1 = 0, da = 0, db = 0;
-                    if (bq < p.m) w0 = lds_u32(rq + j * Q8_1_BYTES + 4 + 8 * pq), w1 = lds_u32(rq + j * Q8_1_BYTES + 8 + 8 * pq);
+                    if (bq < p.m) {
+                        if constexpr (TYPE == QMM_TYPE_Q4_K) {
+                            w0 = lds_u32(rq + j * Q8_1_BYTES + 4 + 8 * pq), w1 = lds_u32(rq + j * Q8_1_BYTES + 8 + 8 * pq);
+                        } else {  // 16-element run s of the block: elements 2pq, 2pq+1, 8+2pq, 9+2pq of the run
+                            w0 = lds_h2(rq + j * Q8_1_BYTES + 4 + 2 * pq), w1 = lds_h2(rq + j * Q8_1_BYTES + 4 + 16 + 2 * pq);
+                        }
+                    }
                     if (ba < p.m) da = lds_u16(ra + j * Q8_1_BYTES);
                     if (ba + 1 < p.m) db = lds_u16(ra + X_COL_BYTES + j * Q8_1_BYTES);
                     xb0[t][j] = w0, xb1[t][j] = w1;
@@ -292,7 +318,8 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_q4k_kernel(const _
                     }
                 }
                 uint32_t s = 0;
-                if (bq < p.m) s = lds_u16(rq + (2 * pq) * Q8_1_BYTES + 2) | (lds_u16(rq + (2 * pq + 1) * Q8_1_BYTES + 2) << 16);
+                if (TYPE == QMM_TYPE_Q4_K && bq < p.m)
+                    s = lds_u16(rq + (2 * pq) * Q8_1_BYTES + 2) | (lds_u16(rq + (2 * pq + 1) * Q8_1_BYTES + 2) << 16);
                 xsf[t] = s;
                 __syncwarp();  // the staging area is overwritten next
             }
@@ -314,64 +341,130 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_q4k_kernel(const _
             if (ok && active) {
                 const uint32_t r0 = ring_s + (uint32_t)slot * p.stage_bytes + my_row_off;
                 const uint32_t r1 = r0 + 8u * p.pitch;
-                const uint4 h0 = lds_v4(r0), h1 = lds_v4(r1);
-                // 6-bit codes, one per byte: A = sub-blocks 0..3, B = 4..7
-                const uint32_t scA0 = h0.y & 0x3F3F3F3Fu, scB0 = (h0.w & 0x0F0F0F0Fu) | ((h0.y >> 2) & 0x30303030u);
-                const uint32_t scA1 = h1.y & 0x3F3F3F3Fu, scB1 = (h1.w & 0x0F0F0F0Fu) | ((h1.y >> 2) & 0x30303030u);
-                const uint32_t mA0 = h0.z & 0x3F3F3F3Fu, mB0 = ((h0.w >> 4) & 0x0F0F0F0Fu) | ((h0.z >> 2) & 0x30303030u);
-                const uint32_t mA1 = h1.z & 0x3F3F3F3Fu, mB1 = ((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u);
-                // mins of sub-blocks 2pq, 2pq+1 of both rows as f16x2 A fragments
-                const uint32_t ma0 = codes_to_half2(((pq < 2) ? mA0 : mB0) >> sh_m);
-                const uint32_t ma1 = codes_to_half2(((pq < 2) ? mA1 : mB1) >> sh_m);
-                float cm[NT][4];
-                uint64_t acc01[NT], acc23[NT];  // (row q: activation rows 2pq, 2pq+1), (row q+8: the same two)
-#pragma unroll
-                for (int t = 0; t < NT; ++t) {
-                    mma_f16_k16_lo(cm[t], ma0, ma1, xsf[t]);
-                    acc01[t] = 0, acc23[t] = 0;
-                }
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const uint2 w0 = lds_v2(r0 + 16 + 32 * g + 8 * pq);
-                    const uint2 w1 = lds_v2(r1 + 16 + 32 * g + 8 * pq);
-#pragma unroll
-                    for (int hi = 0; hi < 2; ++hi) {
-                        const int j = 2 * g + hi;
-                        const uint32_t a0 = (hi ? (w0.x >> 4) : w0.x) & 0x0F0F0F0Fu, a2 = (hi ? (w0.y >> 4) : w0.y) & 0x0F0F0F0Fu;
-                        const uint32_t a1 = (hi ? (w1.x >> 4) : w1.x) & 0x0F0F0F0Fu, a3 = (hi ? (w1.y >> 4) : w1.y) & 0x0F0F0F0Fu;
-                        const int sc0 = (int)byte_n(j < 4 ? scA0 : scB0, j & 3);
-                        const int sc1 = (int)byte_n(j < 4 ? scA1 : scB1, j & 3);
-#pragma unroll
-                        for (int t = 0; t < NT; ++t) {
-                            int d[4];
-                            mma_u8s8_k32(d, a0, a1, a2, a3, xb0[t][j], xb1[t][j]);
-                            uint64_t dab;
-                            if constexpr (NT == 1) {
-                                dab = xdf[t][j];
-                            } else {
-                                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xdh[t][j]));
-                                dab = pack_f2(f.x, f.y);
+                const uint32_t mp = part_s + (uint32_t)pbuf * part_buf_b + my_part_off;
+                if constexpr (TYPE == QMM_TYPE_Q4_K) {
+                    const uint4 h0 = lds_v4(r0), h1 = lds_v4(r1);
+                    // 6-bit codes, one per byte: A = sub-blocks 0..3, B = 4..7
+                    const uint32_t scA0 = h0.y & 0x3F3F3F3Fu, scB0 = (h0.w & 0x0F0F0F0Fu) | ((h0.y >> 2) & 0x30303030u);
+                    const uint32_t scA1 = h1.y & 0x3F3F3F3Fu, scB1 = (h1.w & 0x0F0F0F0Fu) | ((h1.y >> 2) & 0x30303030u);
+                    const uint32_t mA0 = h0.z & 0x3F3F3F3Fu, mB0 = ((h0.w >> 4) & 0x0F0F0F0Fu) | ((h0.z >> 2) & 0x30303030u);
+                    const uint32_t mA1 = h1.z & 0x3F3F3F3Fu, mB1 = ((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u);
+                    // mins of sub-blocks 2pq, 2pq+1 of both rows as f16x2 A fragments
+                    const uint32_t ma0 = codes_to_half2(((pq < 2) ? mA0 : mB0) >> sh_m);
+                    const uint32_t ma1 = codes_to_half2(((pq < 2) ? mA1 : mB1) >> sh_m);
+                    float cm[NT][4];
+                    uint64_t acc01[NT], acc23[NT];  // (row q: activation rows 2pq, 2pq+1), (row q+8: the same two)
+    #pragma unroll
+                    for (int t = 0; t < NT; ++t) {
+                        mma_f16_k16_lo(cm[t], ma0, ma1, xsf[t]);
+                        acc01[t] = 0, acc23[t] = 0;
+                    }
+    #pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const uint2 w0 = lds_v2(r0 + 16 + 32 * g + 8 * pq);
+                        const uint2 w1 = lds_v2(r1 + 16 + 32 * g + 8 * pq);
+    #pragma unroll
+                        for (int hi = 0; hi < 2; ++hi) {
+                            const int j = 2 * g + hi;
+                            const uint32_t a0 = (hi ? (w0.x >> 4) : w0.x) & 0x0F0F0F0Fu, a2 = (hi ? (w0.y >> 4) : w0.y) & 0x0F0F0F0Fu;
+                            const uint32_t a1 = (hi ? (w1.x >> 4) : w1.x) & 0x0F0F0F0Fu, a3 = (hi ? (w1.y >> 4) : w1.y) & 0x0F0F0F0Fu;
+                            const int sc0 = (int)byte_n(j < 4 ? scA0 : scB0, j & 3);
+                            const int sc1 = (int)byte_n(j < 4 ? scA1 : scB1, j & 3);
+    #pragma unroll
+                            for (int t = 0; t < NT; ++t) {
+                                int d[4];
+                                mma_u8s8_k32(d, a0, a1, a2, a3, xb0[t][j], xb1[t][j]);
+                                uint64_t dab;
+                                if constexpr (NT == 1) {
+                                    dab = xdf[t][j];
+                                } else {
+                                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xdh[t][j]));
+                                    dab = pack_f2(f.x, f.y);
+                                }
+                                // sum * scale as exact floats: integer multiply-add onto 1.5 * 2^23, then subtract it
+                                const uint64_t v01 = pack_b64((uint32_t)(d[0] * sc0 + 0x4B400000), (uint32_t)(d[1] * sc0 + 0x4B400000));
+                                const uint64_t v23 = pack_b64((uint32_t)(d[2] * sc1 + 0x4B400000), (uint32_t)(d[3] * sc1 + 0x4B400000));
+                                acc01[t] = fma_f2(dab, add_f2(v01, minus_magic), acc01[t]);
+                                acc23[t] = fma_f2(dab, add_f2(v23, minus_magic), acc23[t]);
                             }
-                            // sum * scale as exact floats: integer multiply-add onto 1.5 * 2^23, then subtract it
-                            const uint64_t v01 = pack_b64((uint32_t)(d[0] * sc0 + 0x4B400000), (uint32_t)(d[1] * sc0 + 0x4B400000));
-                            const uint64_t v23 = pack_b64((uint32_t)(d[2] * sc1 + 0x4B400000), (uint32_t)(d[3] * sc1 + 0x4B400000));
-                            acc01[t] = fma_f2(dab, add_f2(v01, minus_magic), acc01[t]);
-                            acc23[t] = fma_f2(dab, add_f2(v23, minus_magic), acc23[t]);
                         }
                     }
-                }
-                const float d0 = f16_bits_to_f32(h0.x & 0xFFFFu), dmin0 = f16_bits_to_f32(h0.x >> 16);
-                const float d1 = f16_bits_to_f32(h1.x & 0xFFFFu), dmin1 = f16_bits_to_f32(h1.x >> 16);
-                const uint32_t mp = part_s + (uint32_t)pbuf * part_buf_b + my_part_off;
+                    const float d0 = f16_bits_to_f32(h0.x & 0xFFFFu), dmin0 = f16_bits_to_f32(h0.x >> 16);
+                    const float d1 = f16_bits_to_f32(h1.x & 0xFFFFu), dmin1 = f16_bits_to_f32(h1.x >> 16);
+    #pragma unroll
+                    for (int t = 0; t < NT; ++t) {
+                        float a, b, e, f;
+                        unpack_f2(acc01[t], a, b);
+                        unpack_f2(acc23[t], e, f);
+                        sts_f32(mp + (4 * t + 0) * 128, d0 * a - dmin0 * cm[t][0]);
+                        sts_f32(mp + (4 * t + 1) * 128, d0 * b - dmin0 * cm[t][1]);
+                        sts_f32(mp + (4 * t + 2) * 128, d1 * e - dmin1 * cm[t][2]);
+                        sts_f32(mp + (4 * t + 3) * 128, d1 * f - dmin1 * cm[t][3]);
+                    }
+                } else {
+                    // ---- Q6_K: sixteen runs of 16 weights with one int8 scale each, one k = 16 mma per run.
+                    // The codes stay unsigned (low nibble | two high bits); their offset of 32 enters through
+                    // a first mma of the constant -32 against the same activations, which also plants the
+                    // float magic 1.5 * 2^23 in the accumulator, so the result is the exact sum as a float.
+                    uint32_t sw0[4], sw1[4];  // the sixteen scales of both rows, biased to unsigned
 #pragma unroll
-                for (int t = 0; t < NT; ++t) {
-                    float a, b, e, f;
-                    unpack_f2(acc01[t], a, b);
-                    unpack_f2(acc23[t], e, f);
-                    sts_f32(mp + (4 * t + 0) * 128, d0 * a - dmin0 * cm[t][0]);
-                    sts_f32(mp + (4 * t + 1) * 128, d0 * b - dmin0 * cm[t][1]);
-                    sts_f32(mp + (4 * t + 2) * 128, d1 * e - dmin1 * cm[t][2]);
-                    sts_f32(mp + (4 * t + 3) * 128, d1 * f - dmin1 * cm[t][3]);
+                    for (int i = 0; i < 4; ++i) {
+                        sw0[i] = __byte_perm(lds_u16(r0 + 192 + 4 * i), lds_u16(r0 + 194 + 4 * i), 0x5410) ^ 0x80808080u;
+                        sw1[i] = __byte_perm(lds_u16(r1 + 192 + 4 * i), lds_u16(r1 + 194 + 4 * i), 0x5410) ^ 0x80808080u;
+                    }
+                    const uint64_t minus_bias = pack_f2(-(12582912.f + 128.f), -(12582912.f + 128.f));
+                    uint64_t acc01[NT], acc23[NT];
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) acc01[t] = 0, acc23[t] = 0;
+#pragma unroll
+                    for (int hs = 0; hs < 4; ++hs) {
+                        const int h = hs >> 1, s = hs & 1;
+                        const uint32_t oa = 64 * h + 16 * s + 2 * pq, oh = 128 + 32 * h + 16 * s + 2 * pq;
+                        const uint32_t A0 = lds_h2(r0 + oa), B0 = lds_h2(r0 + oa + 32), H0 = lds_h2(r0 + oh);
+                        const uint32_t A1 = lds_h2(r1 + oa), B1 = lds_h2(r1 + oa + 32), H1 = lds_h2(r1 + oh);
+#pragma unroll
+                        for (int t4 = 0; t4 < 4; ++t4) {
+                            const uint32_t s0 = (t4 & 1) ? B0 : A0, s1 = (t4 & 1) ? B1 : A1;
+                            const uint32_t n0 = (t4 < 2 ? s0 : s0 >> 4) & 0x0F0F0F0Fu, n1 = (t4 < 2 ? s1 : s1 >> 4) & 0x0F0F0F0Fu;
+                            const uint32_t g0 = t4 == 0 ? H0 << 4 : t4 == 1 ? H0 << 2 : t4 == 2 ? H0 : H0 >> 2;
+                            const uint32_t g1 = t4 == 0 ? H1 << 4 : t4 == 1 ? H1 << 2 : t4 == 2 ? H1 : H1 >> 2;
+                            const uint32_t qa0 = n0 | (g0 & 0x30303030u), qa1 = n1 | (g1 & 0x30303030u);
+                            const int idx = 8 * h + 2 * t4 + s, j = 4 * h + t4;
+                            // (scale + 128) as a float by byte insertion into the magic constant, twice in a pair
+                            const uint32_t v0 = __byte_perm(sw0[idx >> 2], 0x4B400000u, 0x7640 + (idx & 3));
+                            const uint32_t v1 = __byte_perm(sw1[idx >> 2], 0x4B400000u, 0x7640 + (idx & 3));
+                            const uint64_t S0 = add_f2(pack_b64(v0, v0), minus_bias), S1 = add_f2(pack_b64(v1, v1), minus_bias);
+#pragma unroll
+                            for (int t = 0; t < NT; ++t) {
+                                const uint32_t xw = s ? xb1[t][j] : xb0[t][j];
+                                int d1[4], d[4];
+                                mma_s8s8_k16(d1, 0xE0E0E0E0u, 0xE0E0E0E0u, xw, 0x4B400000);
+                                mma_u8s8_k16(d, qa0, qa1, xw, d1);
+                                uint64_t dab;
+                                if constexpr (NT == 1) {
+                                    dab = xdf[t][j];
+                                } else {
+                                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xdh[t][j]));
+                                    dab = pack_f2(f.x, f.y);
+                                }
+                                const uint64_t f01 = add_f2(pack_b64((uint32_t)d[0], (uint32_t)d[1]), minus_magic);
+                                const uint64_t f23 = add_f2(pack_b64((uint32_t)d[2], (uint32_t)d[3]), minus_magic);
+                                acc01[t] = fma_f2(mul_f2(dab, S0), f01, acc01[t]);
+                                acc23[t] = fma_f2(mul_f2(dab, S1), f23, acc23[t]);
+                            }
+                        }
+                    }
+                    const float d0 = f16_bits_to_f32(lds_u16(r0 + 208)), d1f = f16_bits_to_f32(lds_u16(r1 + 208));
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) {
+                        float a, b, e, f;
+                        unpack_f2(acc01[t], a, b);
+                        unpack_f2(acc23[t], e, f);
+                        sts_f32(mp + (4 * t + 0) * 128, d0 * a);
+                        sts_f32(mp + (4 * t + 1) * 128, d0 * b);
+                        sts_f32(mp + (4 * t + 2) * 128, d1f * e);
+                        sts_f32(mp + (4 * t + 3) * 128, d1f * f);
+                    }
                 }
             }
             // Order within an iteration: arithmetic of stage `it`, fold of stage it-1, then the arrival for
@@ -426,9 +519,9 @@ int mma_set_min_m(int v) {
 }
 int mma_min_m() { return g_mma_min_m; }
 
-template <int NT>
+template <int TYPE, int NT>
 static int mma_launch_inst(const CUtensorMap& wmap, const MmaParams& p, int grid, int threads, size_t smem, cudaStream_t stream) {
-    auto kern = qmv_mma_q4k_kernel<NT>;
+    auto kern = qmv_mma_kernel<TYPE, NT>;
     static size_t configured[64] = {};
     int dev = 0;
     QMM_CUDA_TRY(cudaGetDevice(&dev));
@@ -450,12 +543,15 @@ static int mma_launch_inst(const CUtensorMap& wmap, const MmaParams& p, int grid
     return QMM_OK;
 }
 
-// Returns QMM_ERR_UNSUPPORTED (nothing launched) when the shape does not fit this kernel; the caller
-// then uses the dp4a kernel.  m <= 16.
+// Returns QMM_ERR_UNSUPPORTED (nothing launched) when the type or shape does not fit this kernel; the
+// caller then uses the dp4a kernel.  m <= 16.
 int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k,
                        unsigned long long* trace, cudaStream_t stream) {
-    if (type != QMM_TYPE_Q4_K || m < 1 || m > 16 || k % QKK != 0) return QMM_ERR_UNSUPPORTED;
-    if (reinterpret_cast<uintptr_t>(xq) % 16 != 0) return QMM_ERR_UNSUPPORTED;  // 16-byte asynchronous copies
+    if ((type != QMM_TYPE_Q4_K && type != QMM_TYPE_Q6_K) || m < 1 || m > 16 || k % QKK != 0) return QMM_ERR_UNSUPPORTED;
+    // 16-byte asynchronous copies of the activations, tensor copies of the weights
+    if (reinterpret_cast<uintptr_t>(xq) % 16 != 0 || reinterpret_cast<uintptr_t>(w) % 16 != 0) return QMM_ERR_UNSUPPORTED;
+    const bool q4 = type == QMM_TYPE_Q4_K;
+    const int block_bytes = q4 ? Q4_K_BYTES : Q6_K_BYTES;
     MmaParams p = {};
     p.w = static_cast<const uint8_t*>(w);
     p.xq = static_cast<const uint8_t*>(xq);
@@ -465,14 +561,19 @@ int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y
     p.n = n;
     p.trace = trace;
     p.k_blocks = k / QKK;
-    p.row_bytes = p.k_blocks * Q4_K_BYTES;
+    p.row_bytes = p.k_blocks * block_bytes;
     p.xq_row_bytes = k / QK8 * Q8_1_BYTES;
     const int nt = m > 8 ? 2 : 1;
-    // consumer warps: an even divisor of the super-blocks per row in 12..16 if there is one (no ragged last
-    // chunk); even because a chunk of columns must start on a 96-byte group of the row (see below)
-    if (p.k_blocks % 2 != 0) return QMM_ERR_UNSUPPORTED;
+    // The weights arrive by tensor copies whose innermost extent is a group of GROUP bytes; a row and a
+    // chunk of columns must both be whole groups.  Q4_K: 96 bytes (even column counts), Q6_K: 48 bytes
+    // (multiples of eight columns).
+    const int group = q4 ? 96 : 48;
+    const int col_step = q4 ? 2 : 8;
+    if (p.k_blocks % col_step != 0) return QMM_ERR_UNSUPPORTED;
+    // consumer warps = columns per chunk: a divisor of the super-blocks per row in 12..16 if there is one
+    // (no ragged last chunk), else 16
     int cw = p.k_blocks < MMA_MAX_CW ? p.k_blocks : MMA_MAX_CW;
-    for (int c = MMA_MAX_CW; c >= 12; c -= 2)
+    for (int c = MMA_MAX_CW; c >= 12; c -= col_step)
         if (p.k_blocks >= c && p.k_blocks % c == 0) {
             cw = c;
             break;
@@ -480,27 +581,29 @@ int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y
     if (cw < 4 * nt) return QMM_ERR_UNSUPPORTED;  // the fold needs 128*nt threads
     p.cw = cw;
     p.n_chunks = (p.k_blocks + cw - 1) / cw;
-    // Row pitch in shared memory: the columns of a chunk plus padding, a multiple of the 96-byte group
-    // and 32 or 96 modulo 128, which puts the 8-byte fragment loads of a half-warp (four rows, 32
-    // consecutive bytes each) on 32 different banks.
-    constexpr int GROUP = 96;
-    const int piece = cw * Q4_K_BYTES;
+    // Row pitch in shared memory: the columns of a chunk plus padding, in whole groups, such that the
+    // fragment loads of the eight rows a warp reads at once spread over the banks: Q4_K reads 32
+    // consecutive bytes per row per half-warp (pitch 32 or 96 modulo 128), Q6_K reads 8 bytes per row per
+    // warp (pitch an odd multiple of 16).
+    const int piece = cw * block_bytes;
     p.pitch = 0;
-    for (int pad = GROUP; pad <= 4 * GROUP; pad += GROUP)
-        if ((piece + pad) % 128 == 32 || (piece + pad) % 128 == 96) {
-            p.pitch = piece + pad;
+    for (int pad = 0; pad <= 8 * group; pad += group) {
+        const int cand = piece + pad;
+        if (q4 ? (pad > 0 && (cand % 128 == 32 || cand % 128 == 96)) : (cand % 32 == 16)) {
+            p.pitch = cand;
             break;
         }
+    }
     if (!p.pitch) return QMM_ERR_UNSUPPORTED;
-    p.chunk_groups = piece / GROUP;
+    p.chunk_groups = piece / group;
     p.stage_bytes = 16 * p.pitch;
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return cuda_fail(cudaErrorNotSupported);
     CUtensorMap wmap;
     {
-        const cuuint64_t dims[3] = {GROUP / 4, (cuuint64_t)(p.row_bytes / GROUP), (cuuint64_t)n};
-        const cuuint64_t strides[2] = {GROUP, (cuuint64_t)p.row_bytes};
-        const cuuint32_t box[3] = {GROUP / 4, (cuuint32_t)(p.pitch / GROUP), 16};
+        const cuuint64_t dims[3] = {(cuuint64_t)(group / 4), (cuuint64_t)(p.row_bytes / group), (cuuint64_t)n};
+        const cuuint64_t strides[2] = {(cuuint64_t)group, (cuuint64_t)p.row_bytes};
+        const cuuint32_t box[3] = {(cuuint32_t)(group / 4), (cuuint32_t)(p.pitch / group), 16};
         const cuuint32_t estr[3] = {1, 1, 1};
         if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -528,7 +631,11 @@ int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y
     if (p.nst > MMA_MAX_STAGES) p.nst = MMA_MAX_STAGES;
     const size_t smem = (size_t)p.ring_off + 128 + (size_t)p.nst * p.stage_bytes;
     const int threads = cw * 32;
-    return nt == 1 ? mma_launch_inst<1>(wmap, p, grid, threads, smem, stream) : mma_launch_inst<2>(wmap, p, grid, threads, smem, stream);
+    if (q4)
+        return nt == 1 ? mma_launch_inst<QMM_TYPE_Q4_K, 1>(wmap, p, grid, threads, smem, stream)
+                       : mma_launch_inst<QMM_TYPE_Q4_K, 2>(wmap, p, grid, threads, smem, stream);
+    return nt == 1 ? mma_launch_inst<QMM_TYPE_Q6_K, 1>(wmap, p, grid, threads, smem, stream)
+                   : mma_launch_inst<QMM_TYPE_Q6_K, 2>(wmap, p, grid, threads, smem, stream);
 }
 
 }  // namespace qmm

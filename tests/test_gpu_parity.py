@@ -151,19 +151,20 @@ def test_matvec_matches_oracle(ops, qtype, m, n, k):
     assert_close(y.cpu().numpy(), oracle.matvec(qtype, w, xq, k), f"{oracle.TYPE_NAMES[qtype]} {m}x{n}x{k}")
 
 
-@pytest.mark.parametrize("m,n,k", [(3, 515, 4096), (8, 4096, 4096), (16, 1031, 14336), (11, 2048, 8192)])
-def test_small_batch_tensor_core_kernel_matches_dp4a_kernel(ops, m, n, k):
-    """The same launch through both Q4_K kernels (the threshold is a tunable), twice each."""
+@pytest.mark.parametrize("qtype", [oracle.Q4_K, oracle.Q6_K])
+@pytest.mark.parametrize("m,n,k", [(3, 515, 4096), (8, 4096, 4096), (16, 1031, 14336), (11, 2048, 8192), (16, 77, 6144)])
+def test_small_batch_tensor_core_kernel_matches_dp4a_kernel(ops, qtype, m, n, k):
+    """The same launch through both kernels of a type (the threshold is a tunable), twice each."""
     from nates_recipe_rs_b200 import _lib
     L = _lib.lib()
-    w = dev(seeded_weights(oracle.Q4_K, n, k, 77))
+    w = dev(seeded_weights(qtype, n, k, 77))
     xq = ops.gpu_quantize_q8_1(torch.from_numpy(oracle.fill_normal(m * k, 78, 1.0).reshape(m, k)).cuda())
     try:
         _lib.check(L.qmm_tune(b"mma_min_m", 0), "tune")
-        y_dp4a = ops.gpu_qmatvec(oracle.Q4_K, w, xq, m, n, k)
+        y_dp4a = ops.gpu_qmatvec(qtype, w, xq, m, n, k)
         _lib.check(L.qmm_tune(b"mma_min_m", 1), "tune")
-        y_mma = ops.gpu_qmatvec(oracle.Q4_K, w, xq, m, n, k)
-        y_mma2 = ops.gpu_qmatvec(oracle.Q4_K, w, xq, m, n, k)
+        y_mma = ops.gpu_qmatvec(qtype, w, xq, m, n, k)
+        y_mma2 = ops.gpu_qmatvec(qtype, w, xq, m, n, k)
     finally:
         _lib.check(L.qmm_tune(b"mma_min_m", 3), "tune")
     ops.check_launch()
