@@ -236,22 +236,34 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_decode_split_kernel(const f
         *reinterpret_cast<uint4*>(ks + t * kpitch + 8 * c) = *reinterpret_cast<const uint4*>(kbase + t * row_stride + 8 * c);
         *reinterpret_cast<uint4*>(vs + t * hd + 8 * c) = *reinterpret_cast<const uint4*>(vbase + t * row_stride + 8 * c);
     }
+    // V rows past the end of the context are multiplied by zero probabilities below: make them finite
+    for (int i = nt * pieces + tid; i < ATTN_CHUNK * pieces; i += ATTN_THREADS)
+        *reinterpret_cast<uint4*>(vs + (i / pieces) * hd + 8 * (i % pieces)) = make_uint4(0, 0, 0, 0);
     for (int i = tid; i < group * hd; i += ATTN_THREADS) qs[i] = qrow[i] * scale;
     __syncthreads();
-    // scores: thread = (position t, head parity): heads g = par, par+2, ...
+    // scores: thread = (position t, head parity): heads g = par, par+2, ...; eight elements per step, the
+    // K row as one 16-byte load, q as 16-byte broadcast loads
     {
         const int t = tid & (ATTN_CHUNK - 1), par = tid / ATTN_CHUNK;
         float acc[ATTN_MAX_GROUP / 2];
 #pragma unroll
         for (int g = 0; g < ATTN_MAX_GROUP / 2; ++g) acc[g] = 0.f;
         if (t < nt) {
-            const __half2* kr = reinterpret_cast<const __half2*>(ks + t * kpitch);
-            for (int c = 0; c < hd / 2; ++c) {
-                const float2 f = __half22float2(kr[c]);
+            const uint4* kr = reinterpret_cast<const uint4*>(ks + t * kpitch);
+            for (int c = 0; c < hd / 8; ++c) {
+                const uint4 kk = kr[c];
+                const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kk.x));
+                const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kk.y));
+                const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kk.z));
+                const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kk.w));
 #pragma unroll
                 for (int g = 0; g < ATTN_MAX_GROUP / 2; ++g) {
                     const int head = 2 * g + par;
-                    if (head < group) acc[g] += f.x * qs[head * hd + 2 * c] + f.y * qs[head * hd + 2 * c + 1];
+                    if (head < group) {
+                        const float4 qa = *reinterpret_cast<const float4*>(qs + head * hd + 8 * c);
+                        const float4 qb = *reinterpret_cast<const float4*>(qs + head * hd + 8 * c + 4);
+                        acc[g] += k0.x * qa.x + k0.y * qa.y + k1.x * qa.z + k1.y * qa.w + k2.x * qb.x + k2.y * qb.y + k3.x * qb.z + k3.y * qb.w;
+                    }
                 }
             }
         }
@@ -279,7 +291,53 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_decode_split_kernel(const f
         }
     }
     __syncthreads();
-    // outputs: thread d accumulates over the positions for every head of the group
+    // outputs, head dimensions up to the thread count: thread = (pair of head dimensions, half of the
+    // positions); four positions per step, the probabilities as 16-byte broadcast loads; the two halves
+    // meet in shared memory (the K area is free)
+    if (hd <= ATTN_THREADS) {
+        float* osum = reinterpret_cast<float*>(ks);  // (group x hd) floats of the upper half
+        const int pairs = hd / 2;
+        const int th = tid / pairs >= 1 ? 1 : 0, dp = tid - th * pairs;
+        const bool worker = tid < 2 * pairs;
+        float2 o[ATTN_MAX_GROUP];
+#pragma unroll
+        for (int g = 0; g < ATTN_MAX_GROUP; ++g) o[g] = make_float2(0.f, 0.f);
+        if (worker) {
+            const int tb = th * (ATTN_CHUNK / 2);
+            for (int t = tb; t < tb + ATTN_CHUNK / 2; t += 4) {  // probabilities past nt are zero, V rows past nt hold finite stale values
+                float2 vv[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) vv[u] = __half22float2(*reinterpret_cast<const __half2*>(vs + (t + u) * hd + 2 * dp));
+#pragma unroll
+                for (int g = 0; g < ATTN_MAX_GROUP; ++g)
+                    if (g < group) {
+                        const float4 pp = *reinterpret_cast<const float4*>(ps + g * ATTN_CHUNK + t);
+                        o[g].x += pp.x * vv[0].x + pp.y * vv[1].x + pp.z * vv[2].x + pp.w * vv[3].x;
+                        o[g].y += pp.x * vv[0].y + pp.y * vv[1].y + pp.z * vv[2].y + pp.w * vv[3].y;
+                    }
+            }
+        }
+        __syncthreads();  // everybody is done with K
+        if (worker && th == 1) {
+#pragma unroll
+            for (int g = 0; g < ATTN_MAX_GROUP; ++g)
+                if (g < group) *reinterpret_cast<float2*>(osum + g * hd + 2 * dp) = o[g];
+        }
+        __syncthreads();
+        if (worker && th == 0) {
+#pragma unroll
+            for (int g = 0; g < ATTN_MAX_GROUP; ++g)
+                if (g < group) {
+                    const float2 u = *reinterpret_cast<const float2*>(osum + g * hd + 2 * dp);
+                    float* dst = scratch + (((size_t)b * nqh + kvh * group + g) * splits + sp) * (hd + 2);
+                    dst[2 + 2 * dp] = o[g].x + u.x;
+                    dst[3 + 2 * dp] = o[g].y + u.y;
+                    if (dp == 0) dst[0] = stat[2 * g], dst[1] = stat[2 * g + 1];
+                }
+        }
+        return;
+    }
+    // wider heads: thread d accumulates over the positions for every head of the group
     for (int d = tid; d < hd; d += ATTN_THREADS) {
         float o[ATTN_MAX_GROUP];
 #pragma unroll
