@@ -287,6 +287,7 @@ static int g_consumer_warps = 16;
 static int g_q4k_unit = 0;
 static int g_rb_max = 4;
 static int g_probe = 0;
+static int g_ctas_per_sm = 1;  // persistent CTAs per SM (2 needs a ring and a warp count that fit twice)
 static unsigned long long* g_trace = nullptr;
 static int g_trace_stride = 0, g_trace_count = 0;
 // tuning aid: the next launches write 4 time stamps per CTA at trace + launch_index * stride
@@ -305,6 +306,7 @@ int matvec_tune(const char* key, int value) {
     if (k == "q4k_unit" && (value == 0 || value == 1 || value == 2 || value == 4)) return g_q4k_unit = value, QMM_OK;
     if (k == "rb_max" && (value == 1 || value == 2 || value == 4)) return g_rb_max = value, QMM_OK;
     if (k == "probe" && value >= 0 && value <= 1) return g_probe = value, QMM_OK;
+    if (k == "ctas_per_sm" && value >= 1 && value <= 2) return g_ctas_per_sm = value, QMM_OK;
     if (k == "mma_min_m") return mma_set_min_m(value);
     return QMM_ERR_UNSUPPORTED;
 }
@@ -379,7 +381,7 @@ int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, lo
     p.trace = g_trace ? g_trace + (size_t)(g_trace_count++) * g_trace_stride : nullptr;
     if (p.row_bytes > STAGE_MAX_BYTES) return QMM_ERR_UNSUPPORTED;
     const int nw = g_consumer_warps;
-    const int sms = sm_count();
+    const int sms = sm_count() * g_ctas_per_sm;
     const int rows_per_cta = (n + sms - 1) / sms;
     p.partial_off = (int)((sizeof(MatvecSmemHeader) + 127) & ~size_t(127));
     constexpr size_t SMEM_LIMIT = 200 * 1024;

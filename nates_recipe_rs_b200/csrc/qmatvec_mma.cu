@@ -39,10 +39,10 @@ struct MmaParams {
     int nst;           // ring stages
     int stage_bytes;   // 16 * pitch
     int tiles_total;   // ceil(n / 16)
-    int part_off, yacc_off, ring_off, xstage_off;
+    int part_off, yacc_off, ring_off, xstage_off, xdh_off;
     int opw, opw_p;    // outputs of a tile folded per warp, and the next power of two (<= 32)
     int pstride;       // floats between the partial tiles of two warps
-    unsigned long long* trace;  // optional (tuning aid): per stage and warp of CTA 0, four SM-clock stamps
+    unsigned long long* trace;  // optional (tuning aid): 4 global-timer stamps per CTA
 };
 
 constexpr int MMA_MAX_STAGES = 8;
@@ -169,9 +169,9 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
     const int rows_cta = min(p.n, t_end * 16) - row0;
     const int n_it = p.n_chunks * tiles;
 
-    // tuning aid: wall-clock stamps of CTA 0 (entry, predecessor done, activations in registers, exit)
-    unsigned long long* trg = (p.trace && blockIdx.x == 0 && threadIdx.x == 0) ? p.trace + (size_t)63 * p.cw * 8 : nullptr;
-    if (trg) trg[0] = globaltimer_ns(), trg[5] = clock64();
+    // tuning aid: wall-clock stamps of every CTA (entry, predecessor done, activations in registers, exit)
+    unsigned long long* trg = (p.trace && threadIdx.x == 0) ? p.trace + (size_t)blockIdx.x * 4 : nullptr;
+    if (trg) trg[0] = globaltimer_ns();
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.nst; ++s) mbar_init(full_s + 8 * s, 1);
         for (int s = 0; s < PART_DEPTH; ++s) mbar_init(pfull_s + 8 * s, p.cw);
@@ -219,13 +219,11 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
     const int o_row = ((my_o & 31) >> 2) + 8 * ((my_o >> 6) & 1);
     const int o_bt = 8 * (my_o >> 7) + 2 * (my_o & 3) + ((my_o >> 5) & 1);
     const uint32_t pstride_b = (uint32_t)p.pstride * 4u;
-    unsigned long long* trw = nullptr;
     auto fold = [&](int pbuf, uint32_t ppar, int c, int ti, int cols) {
         if (!mbar_wait_bounded(pfull_s + 8 * pbuf, ppar, cta_abort)) {
             give_up(DEV_TIMEOUT_EMPTY);
             return false;
         }
-        if (trw) trw[4] = clock64();
         // all loads first (up to four partial tiles per lane, and the running sum), then the additions
         const uint32_t src = part_s + ((uint32_t)(pbuf * p.cw + sub) * p.pstride + my_o) * 4u;
         const uint32_t ya = yacc_s + (uint32_t)(ti * OUTS + my_o) * 4u;
@@ -269,7 +267,9 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
     if (warp < p.k_blocks) stage_x(warp, 0);
 
     uint32_t xb0[NT][8], xb1[NT][8];  // B fragments: sub-block j, activation row 8t+q, elements 8pq.. and 8pq+4..
-    uint32_t xdh[NT][8];              // NT == 2: fp16 scales of activation rows 8t+2pq (low half) and 8t+2pq+1
+    // NT == 2: the fp16 scales of activation rows 8t+2pq (low half) and 8t+2pq+1 depend on pq only; they wait in
+    // shared memory ([t][j][pq] words per warp) instead of 16 registers per lane
+    const uint32_t xdh_s = smem_u32(smem + p.xdh_off) + (uint32_t)warp * (2 * 8 * 4 * 4) + (uint32_t)pq * 4;
     uint64_t xdf[NT][8];              // NT == 1: the same scales as a pair of floats
     uint32_t xsf[NT];                 // f16x2: Q8_1 sums of sub-blocks 2pq, 2pq+1 of activation row 8t+q
     const uint64_t minus_magic = pack_f2(-12582912.f, -12582912.f);
@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
                     if constexpr (NT == 1) {
                         xdf[t][j] = pack_f2(f16_bits_to_f32(da), f16_bits_to_f32(db));
                     } else {
-                        xdh[t][j] = da | (db << 16);
+                        if (q == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(xdh_s + (uint32_t)(t * 8 + j) * 16), "r"(da | (db << 16)) : "memory");
                     }
                 }
                 uint32_t s = 0;
@@ -325,19 +325,14 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
             }
         }
         if (c + 1 < p.n_chunks && col + p.cw < p.k_blocks) stage_x(col + p.cw, 0);
-        if (trg && c == 0) trg[2] = globaltimer_ns(), trg[6] = clock64();
+        if (trg && c == 0) trg[2] = globaltimer_ns();
 
         for (int ti = 0; ti < tiles; ++ti) {
-            const long long t_top = p.trace ? clock64() : 0;
             bool ok = !dead;  // after a timeout only the arrivals remain
             if (ok && !mbar_wait_bounded(full_s + 8 * slot, full_par, cta_abort)) {
                 give_up(DEV_TIMEOUT_FULL);
                 ok = false, dead = true;
             }
-            const bool tr = p.trace && blockIdx.x == 0 && lane == 0;
-            unsigned long long* trp = p.trace + ((size_t)it * p.cw + warp) * 8;
-            if (tr) trp[0] = clock64(), trp[5] = t_top;
-            trw = tr ? trp : nullptr;
             if (ok && active) {
                 const uint32_t r0 = ring_s + (uint32_t)slot * p.stage_bytes + my_row_off;
                 const uint32_t r1 = r0 + 8u * p.pitch;
@@ -378,7 +373,8 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
                                 if constexpr (NT == 1) {
                                     dab = xdf[t][j];
                                 } else {
-                                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xdh[t][j]));
+                                    const uint32_t hh = lds_u32(xdh_s + (uint32_t)(t * 8 + j) * 16);
+                                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hh));
                                     dab = pack_f2(f.x, f.y);
                                 }
                                 // sum * scale as exact floats: integer multiply-add onto 1.5 * 2^23, then subtract it
@@ -444,7 +440,8 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
                                 if constexpr (NT == 1) {
                                     dab = xdf[t][j];
                                 } else {
-                                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xdh[t][j]));
+                                    const uint32_t hh = lds_u32(xdh_s + (uint32_t)(t * 8 + j) * 16);
+                                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hh));
                                     dab = pack_f2(f.x, f.y);
                                 }
                                 const uint64_t f01 = add_f2(pack_b64((uint32_t)d[0], (uint32_t)d[1]), minus_magic);
@@ -471,9 +468,7 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
             // stage `it`.  A warp thus runs at most one stage ahead of the slowest one, and when it writes
             // partial tile it % 3 every warp has made its arrival for stage it-2, i.e. finished folding
             // stage it-3, the previous user of that tile.
-            if (tr) trp[1] = clock64();
             if (it > 0 && !dead && !fold(prev_pbuf, prev_ppar, prev_c, prev_ti, prev_cols)) dead = true;
-            if (tr) trp[2] = clock64();
             __syncwarp();
             // Once the arrivals of a stage are complete nobody reads its weights any more.  The warp that
             // arrives last sees the phase complete at once and refills the ring slot; if two warps see it,
@@ -485,7 +480,6 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
                 if (it + p.nst < n_it && !dead && mbar_test_wait(bar, ppar)) refill = atomicCAS(&hdr->refill_next, it, it + 1) == it;
             }
             if (refill) issue(it + p.nst);
-            if (tr) trp[3] = clock64();
             prev_pbuf = pbuf, prev_ppar = ppar, prev_c = c, prev_ti = ti, prev_cols = cols;
             ++it;
             if (++slot == p.nst) slot = 0, full_par ^= 1;
@@ -493,7 +487,7 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
         }
     }
     if (n_it > 0 && !dead) (void)fold(prev_pbuf, prev_ppar, prev_c, prev_ti, prev_cols);
-    if (trg) trg[3] = globaltimer_ns(), trg[7] = clock64();
+    if (trg) trg[3] = globaltimer_ns();
     __syncthreads();  // every warp is here (timed-out waits only skip work), so refill_next is final
     if (warp == 0 && lane == 0 && *cta_abort) {
         // wait (bounded) for copies still in flight before the CTA's shared memory is released
@@ -623,7 +617,8 @@ int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y
     p.pstride = outs + (p.opw_p < 32 ? p.opw_p : 0);
     const size_t part_bytes = (size_t)PART_DEPTH * cw * p.pstride * sizeof(float);
     p.xstage_off = (int)(p.part_off + part_bytes);  // 8 rows x 288 bytes per warp
-    p.yacc_off = p.xstage_off + cw * 8 * 8 * Q8_1_BYTES;
+    p.xdh_off = p.xstage_off + cw * 8 * 8 * Q8_1_BYTES;  // 256 bytes per warp
+    p.yacc_off = p.xdh_off + cw * 256;
     const size_t yacc_bytes = p.n_chunks > 1 ? (size_t)tiles_max * 128 * nt * sizeof(float) : 0;
     p.ring_off = (int)((p.yacc_off + yacc_bytes + 127) & ~size_t(127));
     if ((size_t)p.ring_off + 128 + 2 * (size_t)p.stage_bytes > SMEM_LIMIT) return QMM_ERR_UNSUPPORTED;
