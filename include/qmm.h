@@ -76,7 +76,10 @@ int qmm_set_overlap(int on);
  * "consumer_warps" (1..24), "q4k_unit" (0 = automatic, 1, 2, 4: 32-byte groups of a
  * Q4_K super-block per lane), "rb_max" (1, 2, 4: rows reduced together per warp), "probe" (0/1: 1 = the
  * matvec streams and synchronises but skips its arithmetic), "gemm_probe" (0/1/2: the GEMM skips its unpack
- * arithmetic / its tensor-core instructions).  Probe modes produce wrong results by design.  Not thread-safe against concurrent launches. */
+ * arithmetic / its tensor-core instructions), "mma_min_m" (0..16: fewest activation rows that take the
+ * tensor-core matvec where type and shape allow it; 0 = never; default 3), "ctas_per_sm" (1, 2: persistent
+ * CTAs per SM of the dp4a matvec; 2 needs "ring_bytes" and "consumer_warps" small enough to fit twice).
+ * Probe modes produce wrong results by design.  Not thread-safe against concurrent launches. */
 int qmm_tune(const char* key, int value);
 /* Tuning aid: while buf is non-NULL, matvec launch number i (counted from this call) stores four
  * global-timer stamps per CTA (start, dependency released, first stage landed, end) as 64-bit
@@ -109,7 +112,10 @@ int launch_dequantize_q6_k_bf16(const void* w, void* out, long n_elems, void* st
  * launch_gemm_bt_f64 (gpu-core/src/kernels/gemm_f64.hip:14-54; Rust
  * gpu_gemm_bt_f64_into, gpu-core/src/infer_ops.rs:224-240):
  *   y(m,n) = xq(m,k) . w(n,k)^T,  xq = Q8_1 blocks from launch_quantize_q8_1.
- * m >= 1 (small batches; weights are streamed once per 4 activation rows).
+ * m >= 1.  One or two activation rows: integer dot products (dp4a), the weights stream once per
+ * launch.  Three rows and more, Q4_K and Q6_K: int8 tensor cores (mma.sync), the weights stream once
+ * per 16 activation rows; that kernel needs w and xq on 16-byte boundaries and k a multiple of 512
+ * (Q4_K) or 2048 (Q6_K); other cases take the dp4a kernel, which streams the weights once per 4 rows.
  * k: whole blocks, at most 131072, and one packed row must fit a 48 KiB stage
  * (QMM_ERR_UNSUPPORTED otherwise).  Bit-identical across reruns (no atomics). */
 int launch_qmatvec_q8_0(const void* w, const void* xq, float* y, int m, int n, int k, void* stream);

@@ -47,6 +47,9 @@ struct MmaParams {
 
 constexpr int MMA_MAX_STAGES = 8;
 constexpr int MMA_MAX_CW = 16;
+#ifndef MMA_WAIT_SLEEP_NS
+#define MMA_WAIT_SLEEP_NS 100
+#endif
 
 struct __align__(16) MmaSmemHeader {
     uint64_t full[MMA_MAX_STAGES];
@@ -146,6 +149,22 @@ __device__ __forceinline__ float lds_f32(uint32_t a) {
 __device__ __forceinline__ void sts_f32(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory"); }
 __device__ __forceinline__ uint32_t byte_n(uint32_t v, int n) { return __byte_perm(v, 0, 0x4440 + n); }
 
+// Bounded wait of this kernel: a warp whose barrier is not ready sleeps between polls, leaving the issue
+// slots to the warps that have work (every warp waits twice per stage here).
+__device__ __forceinline__ bool mma_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i) {
+            __nanosleep(MMA_WAIT_SLEEP_NS);
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (*cta_abort) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+    }
+}
+
 constexpr int PART_DEPTH = 3;  // partial-sum tiles in flight (see the ordering argument in the kernel)
 
 // TYPE: Q4_K or Q6_K weights.  NT: activation rows in tiles of eight (1: m <= 8, 2: m <= 16)
@@ -220,7 +239,7 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
     const int o_bt = 8 * (my_o >> 7) + 2 * (my_o & 3) + ((my_o >> 5) & 1);
     const uint32_t pstride_b = (uint32_t)p.pstride * 4u;
     auto fold = [&](int pbuf, uint32_t ppar, int c, int ti, int cols) {
-        if (!mbar_wait_bounded(pfull_s + 8 * pbuf, ppar, cta_abort)) {
+        if (!mma_wait(pfull_s + 8 * pbuf, ppar, cta_abort)) {
             give_up(DEV_TIMEOUT_EMPTY);
             return false;
         }
@@ -266,7 +285,7 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
     if (trg) trg[1] = globaltimer_ns();
     if (warp < p.k_blocks) stage_x(warp, 0);
 
-    uint32_t xb0[NT][8], xb1[NT][8];  // B fragments: sub-block j, activation row 8t+q, elements 8pq.. and 8pq+4..
+    uint2 xb[NT][8];                  // B fragments: sub-block j, activation row 8t+q, elements 8pq.. (x) and 8pq+4.. (y)
     // NT == 2: the fp16 scales of activation rows 8t+2pq (low half) and 8t+2pq+1 depend on pq only; they wait in
     // shared memory ([t][j][pq] words per warp) instead of 16 registers per lane
     const uint32_t xdh_s = smem_u32(smem + p.xdh_off) + (uint32_t)warp * (2 * 8 * 4 * 4) + (uint32_t)pq * 4;
@@ -310,7 +329,7 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
                     }
                     if (ba < p.m) da = lds_u16(ra + j * Q8_1_BYTES);
                     if (ba + 1 < p.m) db = lds_u16(ra + X_COL_BYTES + j * Q8_1_BYTES);
-                    xb0[t][j] = w0, xb1[t][j] = w1;
+                    xb[t][j] = make_uint2(w0, w1);
                     if constexpr (NT == 1) {
                         xdf[t][j] = pack_f2(f16_bits_to_f32(da), f16_bits_to_f32(db));
                     } else {
@@ -329,7 +348,7 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
 
         for (int ti = 0; ti < tiles; ++ti) {
             bool ok = !dead;  // after a timeout only the arrivals remain
-            if (ok && !mbar_wait_bounded(full_s + 8 * slot, full_par, cta_abort)) {
+            if (ok && !mma_wait(full_s + 8 * slot, full_par, cta_abort)) {
                 give_up(DEV_TIMEOUT_FULL);
                 ok = false, dead = true;
             }
@@ -368,7 +387,7 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
     #pragma unroll
                             for (int t = 0; t < NT; ++t) {
                                 int d[4];
-                                mma_u8s8_k32(d, a0, a1, a2, a3, xb0[t][j], xb1[t][j]);
+                                mma_u8s8_k32(d, a0, a1, a2, a3, xb[t][j].x, xb[t][j].y);
                                 uint64_t dab;
                                 if constexpr (NT == 1) {
                                     dab = xdf[t][j];
@@ -432,7 +451,7 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
                             const uint64_t S0 = add_f2(pack_b64(v0, v0), minus_bias), S1 = add_f2(pack_b64(v1, v1), minus_bias);
 #pragma unroll
                             for (int t = 0; t < NT; ++t) {
-                                const uint32_t xw = s ? xb1[t][j] : xb0[t][j];
+                                const uint32_t xw = s ? xb[t][j].y : xb[t][j].x;
                                 int d1[4], d[4];
                                 mma_s8s8_k16(d1, 0xE0E0E0E0u, 0xE0E0E0E0u, xw, 0x4B400000);
                                 mma_u8s8_k16(d, qa0, qa1, xw, d1);
