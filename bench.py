@@ -328,6 +328,35 @@ def run_ours(args):
     achieved = q4_algo / (q4_us * 1e-6) / 1e9
 
     note("FFN legs done")
+    batched = None
+    if world == 1:
+        # ---- the same three FFN shapes at the decode batch sizes of the configs: time per launch over the
+        # same rotation of weights (1-2 rows: dp4a kernel; 3 and more: tensor-core kernel, 16 rows per pass)
+        batched = []
+        with torch.cuda.stream(stream):
+            for m in (1, 8, 16, 32):
+                xm = ops.gpu_quantize_q8_1(torch.randn(m, HID, device=dev))
+                hm = ops.gpu_quantize_q8_1(torch.randn(m, FFN, device=dev))
+                yg, yd = torch.empty(m, FFN, device=dev), torch.empty(m, HID, device=dev)
+                for label, qt, key, xin, yout, n_, k_, nbytes in (("gate_q4_k", Q4_K, "gate", xm, yg, FFN, HID, q4_bytes),
+                                                                  ("down_q4_k", Q4_K, "down4", hm, yd, HID, FFN, q4_bytes),
+                                                                  ("down_q6_k", Q6_K, "down6", hm, yd, HID, FFN, q6_bytes)):
+                    def body():
+                        for lw in layers:
+                            ops.gpu_qmatvec_into(qt, lw[key], xin, yout, m, n_, k_)
+                    g = make_graph(body)
+                    for _ in range(3):
+                        g.replay()
+                    b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    b0.record(stream)
+                    for _ in range(10):
+                        g.replay()
+                    b1.record(stream)
+                    stream.synchronize()
+                    us = b0.elapsed_time(b1) * 1e3 / (10 * LAYERS)
+                    batched.append({"shape": label, "rows": m, "us_per_launch": us, "weight_GBps": nbytes / us / 1e3})
+                    del g
+        check_status()
     decode = None if args.no_decode else run_decode(world, rank, dev, args.quick_decode)
     if rank == 0:
         cpu, _ = cpu_time_sample() if world == 1 else (None, None)
@@ -350,6 +379,8 @@ def run_ours(args):
         }
         if cpu:
             out["cpu_baseline"] = cpu
+        if batched is not None:
+            out["batched_matvec"] = batched
         if decode is not None:
             out["decode"] = decode
         print(json.dumps(out), flush=True)
@@ -378,62 +409,64 @@ def run_decode(world, rank, dev, quick):
     import torch
     import torch.distributed as dist
     from nates_recipe_rs_b200 import decoder as dec, quant_ops as ops
-    cases = [("8b", 1), ("8b", 16), ("70b", 1), ("70b", 8)]
+    cases = [("8b", (1, 16)), ("70b", (1, 8, 32))]
     if quick:
-        cases = [("8b", 1)]
+        cases = [("8b", (1,))]
     out = []
-    for name, batch in cases:
+    for name, batches in cases:
         make = dec.config_8b if name == "8b" else dec.config_70b
-        cfg = make(max_batch=batch, tp_rank=rank, tp_size=world)
+        cfg = make(max_batch=max(batches), tp_rank=rank, tp_size=world)
         if cfg.n_kv_heads % world != 0:
             continue
-        note(f"decode {name} batch {batch}: building")
+        note(f"decode {name}: building (cache for batch {max(batches)})")
         try:
             d = dec.Decoder(cfg)
         except Exception as e:  # e.g. not enough memory for the 70B stack on this GPU
-            out.append({"stack": name, "batch": batch, "error": f"{type(e).__name__}: {e}"[:120]})
+            out.append({"stack": name, "batch": max(batches), "error": f"{type(e).__name__}: {e}"[:120]})
             continue
         d.fill_cache(3)
         steps_per_graph = 8
         pos0 = cfg.ctx_len - steps_per_graph - 1
-        stream = torch.cuda.Stream(device=dev)
-        with torch.cuda.stream(stream):
-            d.tokens.fill_(11)
-
-            def body():
-                for i in range(steps_per_graph):
-                    d.step(batch, pos0 + i)
-                    d.tokens.copy_(d.next_tokens)
-            note("decode: eager steps")
-            body()
-            stream.synchronize()
-            if world > 1:
-                dist.barrier()
-            note("decode: capture")
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                body()
-            note("decode: first replay")
-            graph.replay()
-            stream.synchronize()
-            if world > 1:
-                dist.barrier()
-            note("decode: timed replays")
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            reps = 4
-            e0.record(stream)
-            for _ in range(reps):
-                graph.replay()
-            e1.record(stream)
-            stream.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) * 1e-3 / (reps * steps_per_graph)], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        sec = float(t.item())
-        ops.check_launch()
         wb = d.weight_bytes * world
-        out.append({"stack": name, "batch": batch, "context": cfg.ctx_len, "ms_per_step": sec * 1e3, "tok_s": batch / sec,
-                    "weight_GB_per_token": wb / 1e9, "weight_GBps": wb / sec / 1e9, "tp": world})
+        for batch in batches:
+            stream = torch.cuda.Stream(device=dev)
+            with torch.cuda.stream(stream):
+                d.tokens.fill_(11)
+
+                def body():
+                    for i in range(steps_per_graph):
+                        d.step(batch, pos0 + i)
+                        d.tokens.copy_(d.next_tokens)
+                note(f"decode {name} batch {batch}: eager steps")
+                body()
+                stream.synchronize()
+                if world > 1:
+                    dist.barrier()
+                note("decode: capture")
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    body()
+                note("decode: first replay")
+                graph.replay()
+                stream.synchronize()
+                if world > 1:
+                    dist.barrier()
+                note("decode: timed replays")
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 4 if batch < 32 else 2
+                e0.record(stream)
+                for _ in range(reps):
+                    graph.replay()
+                e1.record(stream)
+                stream.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) * 1e-3 / (reps * steps_per_graph)], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sec = float(t.item())
+            ops.check_launch()
+            out.append({"stack": name, "batch": batch, "context": cfg.ctx_len, "ms_per_step": sec * 1e3, "tok_s": batch / sec,
+                        "weight_GB_per_token": wb / 1e9, "weight_GBps": wb / sec / 1e9, "tp": world})
+            del graph
         d.close()
         del d
         torch.cuda.empty_cache()
