@@ -24,12 +24,14 @@ def main():
     base = dict(n_layers=3, hidden=512, n_q_heads=8, n_kv_heads=8, head_dim=64, ffn=2048, vocab=4096, ctx_len=40,
                 rope_theta=10000.0, rms_eps=1e-6, act=dec.ACT_GELU_TANH, type_attn_qk=Q4_K, type_attn_v=Q6_K, type_attn_o=Q4_K,
                 type_ffn_gate_up=Q4_K, type_ffn_down=Q6_K, type_head=Q6_K, max_batch=2, seed=4242)
+    if "wide" in sys.argv[1:]:  # five sequences, 2048-wide layers: the projections take the tensor-core matvec
+        base.update(n_layers=2, hidden=2048, n_q_heads=16, head_dim=128, ffn=8192, max_batch=5)
     if (base["n_q_heads"] * base["head_dim"]) % (256 * world) or base["ffn"] % (256 * world) or base["n_kv_heads"] % world:
         raise SystemExit(f"tp_check supports world sizes dividing 2 (got {world})" if world > 2 else "bad world size")
     tp = dec.Decoder(dec.DecoderConfig(tp_rank=rank, tp_size=world, **base))
     ref = dec.Decoder(dec.DecoderConfig(tp_rank=0, tp_size=1, **base)) if rank == 0 else None
     B, V = base["max_batch"], base["vocab"]
-    toks = torch.tensor([17, 3001], dtype=torch.int32, device="cuda")
+    toks = torch.tensor([17, 3001, 5, 4000, 999][:B], dtype=torch.int32, device="cuda")
     ok = True
     for pos in range(5):
         lg = torch.empty(B, V // world, device="cuda")

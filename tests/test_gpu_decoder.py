@@ -90,16 +90,21 @@ def test_model_bytes_are_the_seeded_quantized_normal(dec):
     d.close()
 
 
-@pytest.mark.parametrize("act", ["gelu", "silu"])
-def test_decode_steps_match_reference(dec, act):
-    d = dec.Decoder(tiny_cfg(dec, act=dec.ACT_GELU_TANH if act == "gelu" else dec.ACT_SILU))
+@pytest.mark.parametrize("act,wide", [("gelu", False), ("silu", False), ("gelu", True), ("silu", True)])
+def test_decode_steps_match_reference(dec, act, wide):
+    """wide: five sequences and 2048-wide layers, so that every projection of the engine takes the
+    tensor-core matvec (Q4_K and Q6_K, one and two K chunks); otherwise the dp4a kernel."""
+    kw = dict(act=dec.ACT_GELU_TANH if act == "gelu" else dec.ACT_SILU)
+    if wide:
+        kw.update(n_layers=1, hidden=2048, n_q_heads=16, n_kv_heads=4, head_dim=128, ffn=4096, vocab=2048, max_batch=5)
+    d = dec.Decoder(tiny_cfg(dec, **kw))
     c = d.cfg
     ref = RefModel(d, dec)
     from nates_recipe_rs_b200 import quant_ops as ops
     B = c.max_batch
-    toks = np.array([5, 700, 123], dtype=np.int32)
+    toks = np.array([5, 700, 123, 1999, 42][:B], dtype=np.int32)
     logits = torch.empty(B, c.vocab, device="cuda")
-    for pos in range(6):
+    for pos in range(3 if wide else 6):
         d.tokens.copy_(torch.from_numpy(toks))
         d.step(B, pos, logits)
         ops.check_launch()
