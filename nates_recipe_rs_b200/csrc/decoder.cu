@@ -172,13 +172,19 @@ static int create(const qmm_decoder_config* cfg, Decoder** out) {
         TRY(init_gamma(d, L.attn_norm, H, tensor_seed(d, l, QMM_T_ATTN_NORM), s));
         TRY(init_gamma(d, L.ffn_norm, H, tensor_seed(d, l, QMM_T_FFN_NORM), s));
         // [q heads | k heads] of this rank: rows of the full Wq then rows of the full Wk
+        // (with V right behind them when it has the same type: one projection launch instead of two)
         const size_t qk_b = (size_t)d->qk_rows * type_row_bytes(c.type_attn_qk, H);
-        TRY(dev_alloc(d, &L.wqk, qk_b));
+        const size_t v_b = (size_t)d->v_rows * type_row_bytes(c.type_attn_v, H);
+        const bool qkv_fused = c.type_attn_v == c.type_attn_qk;
+        TRY(dev_alloc(d, &L.wqk, qk_b + (qkv_fused ? v_b : 0)));
         TRY(init_matrix(d, L.wqk, c.type_attn_qk, (long)d->nq * hd, H, (long)r * d->nq * hd, 0, H, tensor_seed(d, l, QMM_T_WQ), tmp, tmp_elems, s));
         TRY(init_matrix(d, L.wqk + (size_t)d->nq * hd * type_row_bytes(c.type_attn_qk, H), c.type_attn_qk, (long)d->nkv * hd, H,
                         (long)r * d->nkv * hd, 0, H, tensor_seed(d, l, QMM_T_WK), tmp, tmp_elems, s));
-        const size_t v_b = (size_t)d->v_rows * type_row_bytes(c.type_attn_v, H);
-        TRY(dev_alloc(d, &L.wv, v_b));
+        if (qkv_fused) {
+            L.wv = L.wqk + qk_b;
+        } else {
+            TRY(dev_alloc(d, &L.wv, v_b));
+        }
         TRY(init_matrix(d, L.wv, c.type_attn_v, d->v_rows, H, (long)r * d->v_rows, 0, H, tensor_seed(d, l, QMM_T_WV), tmp, tmp_elems, s));
         const size_t o_b = (size_t)H * type_row_bytes(c.type_attn_o, ao);
         TRY(dev_alloc(d, &L.wo, o_b));
@@ -326,8 +332,12 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
     for (int l = 0; l < c.n_layers; ++l) {
         const LayerWeights& L = d->layers[l];
         TRY(add_norm(d, l == 0 ? -1 : 1, L.attn_norm, batch, s));
-        TRY(qmatvec_launch_strided(c.type_attn_qk, L.wqk, d->xq_h, d->qkv, d->qkv_cols, batch, d->qk_rows, H, s));
-        TRY(qmatvec_launch_strided(c.type_attn_v, L.wv, d->xq_h, d->qkv + d->qk_rows, d->qkv_cols, batch, d->v_rows, H, s));
+        if (c.type_attn_v == c.type_attn_qk) {  // V's rows follow K's in memory: one launch
+            TRY(qmatvec_launch_strided(c.type_attn_qk, L.wqk, d->xq_h, d->qkv, d->qkv_cols, batch, d->qk_rows + d->v_rows, H, s));
+        } else {
+            TRY(qmatvec_launch_strided(c.type_attn_qk, L.wqk, d->xq_h, d->qkv, d->qkv_cols, batch, d->qk_rows, H, s));
+            TRY(qmatvec_launch_strided(c.type_attn_v, L.wv, d->xq_h, d->qkv + d->qk_rows, d->qkv_cols, batch, d->v_rows, H, s));
+        }
         __half* kc = d->kcache + (size_t)l * cache_layer;
         __half* vc = d->vcache + (size_t)l * cache_layer;
         TRY(launch_pdl(rope_kv_append_kernel, dim3(8, batch), dim3(256), 0, s, d->qkv, kc, vc, d->nq, d->nkv, hd, pos, c.ctx_len, c.rope_theta));

@@ -47,6 +47,7 @@ struct MatvecParams {
     int pstage;       // floats per partial-sum stage: rows_stage * kw * M
     int partial_off;  // byte offset of the partial-sum area in dynamic shared memory
     int ring_off;     // byte offset of the ring
+    int rows_q, rows_r;  // n / grid and n % grid
     int probe;        // 0 = normal; 1 = stream only: every wait and arrival happens, the arithmetic is skipped
     unsigned long long* trace;  // optional (tuning aid): 4 global-timer stamps per CTA
 };
@@ -98,9 +99,10 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
     const int n_consumers = p.kw * p.rg;
 
     // contiguous row range of this CTA
-    const long row_begin = (long)blockIdx.x * p.n / gridDim.x;
-    const long row_end = (long)(blockIdx.x + 1) * p.n / gridDim.x;
-    const int n_rows = (int)(row_end - row_begin);
+    // (n / grid rows each, the first n % grid CTAs one more: no division on the device)
+    const int bx = (int)blockIdx.x;
+    const long row_begin = (long)bx * p.rows_q + min(bx, p.rows_r);
+    const int n_rows = p.rows_q + (bx < p.rows_r ? 1 : 0);
     const int n_it = (n_rows + p.rows_stage - 1) / p.rows_stage;
     const uintptr_t w_begin = reinterpret_cast<uintptr_t>(p.w) + (size_t)row_begin * p.row_bytes;
     const uint32_t stage_bytes = (uint32_t)p.rows_stage * p.row_bytes;
@@ -134,9 +136,11 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
             for (; issued < n_it && issued < p.nst; ++issued) issue(issued);
         pdl_wait_prior_grids();  // y may still be read by the preceding kernel
         bool ok = true;
+        // ring slot, its phase and the partial-sum slot of stage `it`, kept incrementally (no divisions)
+        int slot = 0, pslot = 0;
+        uint32_t phase = 0;
         for (int it = 0; it < n_it; ++it) {
-            const int slot = it % p.nst;
-            ok = mbar_wait_bounded(smem_u32(&hdr->empty[slot]), (it / p.nst) & 1, cta_abort);
+            ok = mbar_wait_bounded(smem_u32(&hdr->empty[slot]), phase, cta_abort);
             if (!ok) {
                 if (lane == 0 && !*cta_abort) {
                     atomicExch(&g_device_status, DEV_TIMEOUT_EMPTY);
@@ -149,7 +153,7 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
                 issued = it + p.nst + 1;
             }
             const int nr = min(p.rows_stage, n_rows - it * p.rows_stage);
-            const float* ps = partial + (size_t)(it % (2 * p.nst)) * p.pstage;
+            const float* ps = partial + (size_t)pslot * p.pstage;
             float* yrow = p.y + row_begin + (long)it * p.rows_stage;
             for (int idx = lane; idx < nr * M; idx += 32) {  // idx = r*M + mi
                 const int r = idx / M, mi = idx - r * M;
@@ -158,6 +162,8 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
                 for (int q = 0; q < p.kw; ++q) acc += src[q * M];
                 if (mi < p.m) yrow[(size_t)mi * p.y_stride + r] = acc;
             }
+            if (++slot == p.nst) slot = 0, phase ^= 1;
+            if (++pslot == 2 * p.nst) pslot = 0;
         }
         issued = __shfl_sync(0xffffffffu, issued, 0);
         if (p.trace && lane == 0) p.trace[blockIdx.x * 4 + 3] = globaltimer_ns();
@@ -180,6 +186,7 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
     const int kwi = warp % p.kw, rgi = warp / p.kw;
     typename F::XRegs x[M][P];
     int unit[P];
+    uint32_t unit_off[P];  // byte offset of the unit's block within a row
     pdl_wait_prior_grids();  // activations come from the preceding kernel
     if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 4 + 1] = globaltimer_ns();
 #pragma unroll
@@ -187,6 +194,7 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
         const int u = (pp * p.kw + kwi) * 32 + lane;
         // lanes past the end of the row re-read unit 0 against zero activations
         unit[pp] = u < p.units ? u : 0;
+        unit_off[pp] = F::unit_offset(unit[pp]);
 #pragma unroll
         for (int mi = 0; mi < M; ++mi) {
             if (u < p.units && mi < p.m)
@@ -200,6 +208,7 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
     const int my_val = lane / LANES_PER_VALUE, my_j = my_val / M, my_mi = my_val - my_j * M;
     const bool writer = (lane % LANES_PER_VALUE) == 0;
     const uint32_t w_begin_lo = (uint32_t)(w_begin & 15);
+    const uint32_t ring_s = smem_u32(ring);
     const uint32_t my_ps = ((uint32_t)my_j * p.kw + kwi) * M + my_mi;
     const uint32_t batch_bytes = (uint32_t)RB * p.row_bytes;
     const uint32_t batch_ps = (uint32_t)RB * p.kw * M;
@@ -207,8 +216,11 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
     // batches are numbered over the CTA's whole row range; batch g belongs to row group g % rg
     int next_b = rgi;                   // this warp's next batch, relative to the current stage
 
+    // ring slot, its phase and the partial-sum slot of stage `it`, kept incrementally (no divisions)
+    int slot = 0, pslot = 0;
+    uint32_t phase = 0;
+    uint32_t head = w_begin_lo;  // low four address bits of the stage's first byte
     for (int it = 0; it < n_it; ++it) {
-        const int slot = it % p.nst;
         const int nr = min(p.rows_stage, n_rows - it * p.rows_stage);
         const int nb = (nr + RB - 1) / RB;
         // Every warp passes every stage but only waits for the data of stages it has work in, so
@@ -216,7 +228,7 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
         // warps have released the previous use: that keeps its arrival in the right phase, makes
         // the parity test on the data barrier below unambiguous (the barrier cannot still be one
         // phase behind), and means no copy can still be in flight when the CTA exits.
-        if (it >= p.nst && !mbar_wait_bounded(smem_u32(&hdr->empty[slot]), ((it / p.nst) - 1) & 1, cta_abort)) {
+        if (it >= p.nst && !mbar_wait_bounded(smem_u32(&hdr->empty[slot]), phase ^ 1, cta_abort)) {
             if (lane == 0 && !*cta_abort) {
                 atomicExch(&g_device_status, DEV_TIMEOUT_EMPTY);
                 *cta_abort = 1;
@@ -224,7 +236,7 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
             return;
         }
         if (next_b < nb) {
-            if (!mbar_wait_bounded(smem_u32(&hdr->full[slot]), (it / p.nst) & 1, cta_abort)) {
+            if (!mbar_wait_bounded(smem_u32(&hdr->full[slot]), phase, cta_abort)) {
                 if (lane == 0 && !*cta_abort) {
                     atomicExch(&g_device_status, DEV_TIMEOUT_FULL);
                     *cta_abort = 1;
@@ -232,24 +244,23 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
                 return;
             }
             if (p.trace && threadIdx.x == 0 && it == 0) p.trace[blockIdx.x * 4 + 2] = globaltimer_ns();
-            const uint32_t head = (w_begin_lo + (uint32_t)it * stage_bytes) & 15u;
-            const uint8_t* base = ring + (uint32_t)slot * p.slot_bytes + head;
-            float* ps = partial + (uint32_t)(it % (2 * p.nst)) * p.pstage + my_ps;
+            const uint32_t base = ring_s + (uint32_t)slot * p.slot_bytes + head;
+            float* ps = partial + (uint32_t)pslot * p.pstage + my_ps;
             // Whole batches only: rows past nr (last stage of the CTA) hold stale bytes of an
             // earlier stage; their sums land in partial entries that nobody reads.
             if (p.probe == 0) {
                 for (; next_b < nb; next_b += p.rg) {
-                    const uint8_t* row0 = base + (uint32_t)next_b * batch_bytes;
+                    const uint32_t row0 = base + (uint32_t)next_b * batch_bytes;
                     float acc[V];
 #pragma unroll
                     for (int v = 0; v < V; ++v) acc[v] = 0.f;
 #pragma unroll
                     for (int j = 0; j < RB; ++j) {
-                        const uint8_t* row = row0 + (uint32_t)j * p.row_bytes;
+                        const uint32_t row = row0 + (uint32_t)j * p.row_bytes;
 #pragma unroll
                         for (int pp = 0; pp < P; ++pp) {
                             typename F::WRegs wr;
-                            F::load_w(row, unit[pp], wr);
+                            F::load_w_s(row, unit_off[pp], unit[pp], wr);
 #pragma unroll
                             for (int mi = 0; mi < M; ++mi) acc[j * M + mi] += F::dot(wr, unit[pp], x[mi][pp], nullptr);
                         }
@@ -264,6 +275,9 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
         next_b -= bps;  // renumber relative to the next stage (only the last stage is short)
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&hdr->empty[slot]));
+        if (++slot == p.nst) slot = 0, phase ^= 1;
+        if (++pslot == 2 * p.nst) pslot = 0;
+        head = (head + stage_bytes) & 15u;
     }
 }
 
@@ -436,6 +450,7 @@ int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, lo
         const int threads = (p.kw * p.rg + 1) * 32;
         int grid = (n + p.rows_stage - 1) / p.rows_stage;
         if (grid > sms) grid = sms;
+        p.rows_q = n / grid, p.rows_r = n % grid;
         p.pstage = p.rows_stage * p.kw * mt;
         // stages: as many as the ring budget allows, fewer if the partial sums (two per stage) crowd them out
         const size_t per_stage = (size_t)p.slot_bytes + 2 * (size_t)p.pstage * sizeof(float);

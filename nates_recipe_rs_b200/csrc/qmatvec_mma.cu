@@ -39,6 +39,7 @@ struct MmaParams {
     int nst;           // ring stages
     int stage_bytes;   // 16 * pitch
     int tiles_total;   // ceil(n / 16)
+    int tiles_q, tiles_r;  // tiles_total / grid and tiles_total % grid
     int part_off, yacc_off, ring_off, xstage_off, xdh_off;
     int opw, opw_p;    // outputs of a tile folded per warp, and the next power of two (<= 32)
     int pstride;       // floats between the partial tiles of two warps
@@ -181,9 +182,11 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
     const uint32_t full_s = smem_u32(&hdr->full[0]), pfull_s = smem_u32(&hdr->pfull[0]);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t_begin = (int)((long)blockIdx.x * p.tiles_total / gridDim.x);
-    const int t_end = (int)((long)(blockIdx.x + 1) * p.tiles_total / gridDim.x);
-    const int tiles = t_end - t_begin;
+    // tiles_q tiles each, the first tiles_r CTAs one more (no division on the device)
+    const int bx = (int)blockIdx.x;
+    const int t_begin = bx * p.tiles_q + min(bx, p.tiles_r);
+    const int tiles = p.tiles_q + (bx < p.tiles_r ? 1 : 0);
+    const int t_end = t_begin + tiles;
     const int row0 = t_begin * 16;
     const int rows_cta = min(p.n, t_end * 16) - row0;
     const int n_it = p.n_chunks * tiles;
@@ -626,6 +629,7 @@ int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y
     const int sms = sm_count();
     const int grid = p.tiles_total < sms ? p.tiles_total : sms;
     const int tiles_max = (p.tiles_total + grid - 1) / grid;
+    p.tiles_q = p.tiles_total / grid, p.tiles_r = p.tiles_total % grid;
     constexpr size_t SMEM_LIMIT = 220 * 1024;
     p.part_off = 256;
     const int outs = 128 * nt;

@@ -41,6 +41,35 @@ __device__ __forceinline__ uint32_t ld_u16(const uint8_t* p) {
     return *reinterpret_cast<const uint16_t*>(p);
 }
 
+// The same by 32-bit shared-memory address (the matvec's inner loop: no 64-bit address arithmetic)
+__device__ __forceinline__ uint32_t sld_u32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 sld_v4(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t sld_u16(uint32_t a) {
+    uint32_t v;
+    asm volatile("{ .reg .b16 h; ld.shared.u16 h, [%1]; cvt.u32.u16 %0, h; }" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void sld_words4_align2(uint32_t a, uint32_t (&o)[4]) {
+    const uint32_t q = a & ~3u, sh = (a & 2u) * 8u;
+    const uint32_t w0 = sld_u32(q), w1 = sld_u32(q + 4), w2 = sld_u32(q + 8), w3 = sld_u32(q + 12), w4 = sld_u32(q + 16);
+    o[0] = __funnelshift_r(w0, w1, sh);
+    o[1] = __funnelshift_r(w1, w2, sh);
+    o[2] = __funnelshift_r(w2, w3, sh);
+    o[3] = __funnelshift_r(w3, w4, sh);
+}
+__device__ __forceinline__ uint32_t sld_u32_align2(uint32_t a) {
+    const uint32_t q = a & ~3u;
+    return __funnelshift_r(sld_u32(q), sld_u32(q + 4), (a & 2u) * 8u);
+}
+
 // Q8_1 accessors (row pointer 4-byte aligned)
 __device__ __forceinline__ int q81_word(const uint8_t* xq, int blk, int w) {
     return *reinterpret_cast<const int*>(xq + (size_t)blk * Q8_1_BYTES + 4 + 4 * w);
@@ -104,6 +133,16 @@ struct Fmt<QMM_TYPE_Q4_K, UW> {
         const uint4* q = reinterpret_cast<const uint4*>(blk + 16 + 32 * UW * (u % UNITS_PER_BLOCK));
 #pragma unroll
         for (int i = 0; i < 2 * UW; ++i) wr.q[i] = q[i];
+    }
+    // byte offset of the unit's super-block within a row (loop invariant for a lane)
+    __device__ static __forceinline__ uint32_t unit_offset(int u) { return (uint32_t)(u / UNITS_PER_BLOCK) * Q4_K_BYTES; }
+    // the same fetch from shared memory: row_s = shared address of the row, blk_off = unit_offset(u)
+    __device__ static __forceinline__ void load_w_s(uint32_t row_s, uint32_t blk_off, int u, WRegs& wr) {
+        const uint32_t blk = row_s + blk_off;
+        wr.hdr = sld_v4(blk);
+        const uint32_t q = blk + 16 + 32 * UW * (u % UNITS_PER_BLOCK);
+#pragma unroll
+        for (int i = 0; i < 2 * UW; ++i) wr.q[i] = sld_v4(q + 16 * i);
     }
     __device__ static __forceinline__ float dot(const WRegs& wr, int u, const XRegs& x, int* sums) {
         // integer sums of the 2*UW sub-blocks
@@ -204,6 +243,17 @@ struct Fmt<QMM_TYPE_Q6_K, UW> {
         wr.sc[1] = lds_u32_align2(blk + 196 + 8 * h);
         wr.d = ld_u16(blk + 208);
     }
+    __device__ static __forceinline__ uint32_t unit_offset(int u) { return (uint32_t)(u >> 2) * Q6_K_BYTES; }
+    __device__ static __forceinline__ void load_w_s(uint32_t row_s, uint32_t blk_off, int u, WRegs& wr) {
+        const uint32_t blk = row_s + blk_off;
+        const int h = (u >> 1) & 1, l0 = 16 * (u & 1);
+        sld_words4_align2(blk + 64 * h + l0, wr.a);
+        sld_words4_align2(blk + 64 * h + 32 + l0, wr.b);
+        sld_words4_align2(blk + 128 + 32 * h + l0, wr.h);
+        wr.sc[0] = sld_u32_align2(blk + 192 + 8 * h);
+        wr.sc[1] = sld_u32_align2(blk + 196 + 8 * h);
+        wr.d = sld_u16(blk + 208);
+    }
     __device__ static __forceinline__ float dot(const WRegs& wr, int u, const XRegs& x, int* sums) {
         int s[4] = {x.xb[0], x.xb[1], x.xb[2], x.xb[3]};
 #pragma unroll
@@ -266,6 +316,16 @@ struct Fmt<QMM_TYPE_Q8_0, UW> {
         uint32_t lo[4], hi[4];
         ld_words4_align2(blk + 2, lo);
         ld_words4_align2(blk + 18, hi);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) wr.q[w] = lo[w], wr.q[4 + w] = hi[w];
+    }
+    __device__ static __forceinline__ uint32_t unit_offset(int u) { return (uint32_t)u * Q8_0_BYTES; }
+    __device__ static __forceinline__ void load_w_s(uint32_t row_s, uint32_t blk_off, int, WRegs& wr) {
+        const uint32_t blk = row_s + blk_off;
+        wr.d = sld_u16(blk);
+        uint32_t lo[4], hi[4];
+        sld_words4_align2(blk + 2, lo);
+        sld_words4_align2(blk + 18, hi);
 #pragma unroll
         for (int w = 0; w < 4; ++w) wr.q[w] = lo[w], wr.q[4 + w] = hi[w];
     }
