@@ -371,7 +371,7 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "kernel": "qmatvec_kernel<Q4_K> (gate, up, down at batch 1)", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "us_per_launch": q4_us,
                          "algorithmic_bytes_per_launch": q4_algo,
-                         "traffic": 33061376.0, "traffic_note": "dram read+write per launch from ncu (profiles/)"},
+                         "traffic": 33059584.0, "traffic_note": "dram read+write per launch from ncu (profiles/)"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": (HID + FFN) * 4, "d2h_bytes_per_step": 2 * HID * 4,
                     "note": "activations from pinned host memory and projections back to it every step; weights resident in HBM"},
             "gpu_launches": launches_per_step[0] * args.steps,
