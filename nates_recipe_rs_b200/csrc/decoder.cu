@@ -13,6 +13,8 @@
 namespace qmm {
 
 int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, cudaStream_t stream);
+int qmatvec_launch_limited(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
+                           cudaStream_t stream);
 int quantize_weights_launch(int type, const float* w, void* out, long rows, int k, cudaStream_t stream);
 
 constexpr int ARGMAX_PARTS = 256;
@@ -49,6 +51,11 @@ struct Decoder {
     int handshake_index = 0;                   // handshake number within the step being launched
     int attn_splits = 1, attn_chunk = 0;
     std::vector<void*> allocs;
+    // second stream for the V projection when its type differs from Q|K's (it then runs beside the Q|K
+    // projection on its own share of the SMs instead of after it)
+    cudaStream_t side = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+    int sms = 0;
     long weight_bytes_per_token = 0;
 };
 
@@ -126,6 +133,9 @@ static void destroy(Decoder* d) {
     for (size_t r = 0; r < d->peer_xchg.size(); ++r)
         if (d->peer_xchg[r] && d->peer_xchg[r] != d->xchg) cudaIpcCloseMemHandle(d->peer_xchg[r]);
     for (void* p : d->allocs) cudaFree(p);
+    if (d->fork) cudaEventDestroy(d->fork);
+    if (d->join) cudaEventDestroy(d->join);
+    if (d->side) cudaStreamDestroy(d->side);
     delete d;
 }
 
@@ -159,6 +169,13 @@ static int create(const qmm_decoder_config* cfg, Decoder** out) {
             return st;        \
         }                     \
     } while (0)
+    d->sms = sm_count();
+    if (cudaStreamCreateWithFlags(&d->side, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&d->fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&d->join, cudaEventDisableTiming) != cudaSuccess) {
+        destroy(d);
+        return cuda_fail(cudaGetLastError());
+    }
     const long tmp_elems = 32l << 20;  // 128 MB of f32 staging for initialisation
     float* tmp = nullptr;
     TRY(dev_alloc(d, &tmp, tmp_elems * sizeof(float)));
@@ -335,8 +352,17 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
         if (c.type_attn_v == c.type_attn_qk) {  // V's rows follow K's in memory: one launch
             TRY(qmatvec_launch_strided(c.type_attn_qk, L.wqk, d->xq_h, d->qkv, d->qkv_cols, batch, d->qk_rows + d->v_rows, H, s));
         } else {
-            TRY(qmatvec_launch_strided(c.type_attn_qk, L.wqk, d->xq_h, d->qkv, d->qkv_cols, batch, d->qk_rows, H, s));
-            TRY(qmatvec_launch_strided(c.type_attn_v, L.wv, d->xq_h, d->qkv + d->qk_rows, d->qkv_cols, batch, d->v_rows, H, s));
+            // two kernels side by side: the SMs are shared in proportion to the weight bytes
+            const double qk_b = (double)d->qk_rows * type_row_bytes(c.type_attn_qk, H), v_b = (double)d->v_rows * type_row_bytes(c.type_attn_v, H);
+            int v_ctas = (int)(d->sms * v_b / (qk_b + v_b) + 0.5);
+            if (v_ctas < 1) v_ctas = 1;
+            if (v_ctas > d->sms - 1) v_ctas = d->sms - 1;
+            QMM_CUDA_TRY(cudaEventRecord(d->fork, s));  // after the norm that produced the activations
+            QMM_CUDA_TRY(cudaStreamWaitEvent(d->side, d->fork, 0));
+            TRY(qmatvec_launch_limited(c.type_attn_qk, L.wqk, d->xq_h, d->qkv, d->qkv_cols, batch, d->qk_rows, H, d->sms - v_ctas, s));
+            TRY(qmatvec_launch_limited(c.type_attn_v, L.wv, d->xq_h, d->qkv + d->qk_rows, d->qkv_cols, batch, d->v_rows, H, v_ctas, d->side));
+            QMM_CUDA_TRY(cudaEventRecord(d->join, d->side));
+            QMM_CUDA_TRY(cudaStreamWaitEvent(s, d->join, 0));
         }
         __half* kc = d->kcache + (size_t)l * cache_layer;
         __half* vc = d->vcache + (size_t)l * cache_layer;

@@ -309,7 +309,7 @@ void matvec_set_trace(unsigned long long* buf, int stride_words) { g_trace = buf
 void gemm_set_probe(int v);
 int mma_set_min_m(int v);
 int mma_min_m();
-int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k,
+int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                        unsigned long long* trace, cudaStream_t stream);
 int matvec_tune(const char* key, int value) {
     const std::string k(key ? key : "");
@@ -370,12 +370,21 @@ static int launch_p(const MatvecParams& p, int passes, int grid, int threads, si
 }
 
 int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, cudaStream_t stream);
+int qmatvec_launch_limited(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
+                           cudaStream_t stream);
 int qmatvec_launch(int type, const void* w, const void* xq, float* y, int m, int n, int k, cudaStream_t stream) {
     return qmatvec_launch_strided(type, w, xq, y, n, m, n, k, stream);
 }
 
 // y_stride: floats between consecutive output rows (lets several projections write slices of one row)
 int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, cudaStream_t stream) {
+    return qmatvec_launch_limited(type, w, xq, y, y_stride, m, n, k, 0, stream);
+}
+
+// cta_limit > 0: use at most that many CTAs (SMs), so that two independent projections launched on
+// two streams share the GPU side by side instead of one after the other
+int qmatvec_launch_limited(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
+                           cudaStream_t stream) {
     if (!w || !xq || !y) return QMM_ERR_NULL;
     if (y_stride < n) return QMM_ERR_SHAPE;
     int block_elems, block_bytes, unit_elems, w_align;
@@ -395,7 +404,8 @@ int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, lo
     p.trace = g_trace ? g_trace + (size_t)(g_trace_count++) * g_trace_stride : nullptr;
     if (p.row_bytes > STAGE_MAX_BYTES) return QMM_ERR_UNSUPPORTED;
     const int nw = g_consumer_warps;
-    const int sms = sm_count() * g_ctas_per_sm;
+    int sms = sm_count() * g_ctas_per_sm;
+    if (cta_limit > 0 && cta_limit < sms) sms = cta_limit;
     const int rows_per_cta = (n + sms - 1) / sms;
     p.partial_off = (int)((sizeof(MatvecSmemHeader) + 127) & ~size_t(127));
     constexpr size_t SMEM_LIMIT = 200 * 1024;
@@ -407,7 +417,7 @@ int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, lo
         while (m - m_done >= mma_min_m()) {
             const int mg = m - m_done < 16 ? m - m_done : 16;
             const int st = qmatvec_mma_launch(type, w, static_cast<const uint8_t*>(xq) + (size_t)m_done * p.xq_row_bytes,
-                                              y + (size_t)m_done * y_stride, y_stride, mg, n, k, p.trace, stream);
+                                              y + (size_t)m_done * y_stride, y_stride, mg, n, k, cta_limit, p.trace, stream);
             if (st == QMM_ERR_UNSUPPORTED) break;
             if (st) return st;
             m_done += mg;

@@ -561,7 +561,7 @@ static int mma_launch_inst(const CUtensorMap& wmap, const MmaParams& p, int grid
 
 // Returns QMM_ERR_UNSUPPORTED (nothing launched) when the type or shape does not fit this kernel; the
 // caller then uses the dp4a kernel.  m <= 16.
-int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k,
+int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                        unsigned long long* trace, cudaStream_t stream) {
     if ((type != QMM_TYPE_Q4_K && type != QMM_TYPE_Q6_K) || m < 1 || m > 16 || k % QKK != 0) return QMM_ERR_UNSUPPORTED;
     // 16-byte asynchronous copies of the activations, tensor copies of the weights
@@ -626,7 +626,8 @@ int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y
             return cuda_fail(cudaErrorInvalidValue);
     }
     p.tiles_total = (n + 15) / 16;
-    const int sms = sm_count();
+    int sms = sm_count();
+    if (cta_limit > 0 && cta_limit < sms) sms = cta_limit;
     const int grid = p.tiles_total < sms ? p.tiles_total : sms;
     const int tiles_max = (p.tiles_total + grid - 1) / grid;
     p.tiles_q = p.tiles_total / grid, p.tiles_r = p.tiles_total % grid;
