@@ -26,9 +26,21 @@ static int attn_run(const float* qkv, const void* kc, const void* vc, float* scr
         QMM_CUDA_TRY(cudaFuncSetAttribute(attn_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
-    attn_decode_split_kernel<<<dim3(nkv, batch, splits), ATTN_THREADS, smem, s>>>(qkv, static_cast<const __half*>(kc),
-                                                                                   static_cast<const __half*>(vc), scratch, nqh, nkv, hd,
-                                                                                   len, ctx_cap, splits);
+    if (batch >= ATTN_TC_MIN_BATCH) {
+        // several sequences: scores and outputs on the f16 tensor cores (q and the probabilities rounded to f16)
+        static size_t configured_tc[64] = {};
+        const size_t smem_tc = attn_tc_smem_bytes(hd);
+        if (dev < 0 || dev >= 64 || smem_tc > configured_tc[dev]) {
+            QMM_CUDA_TRY(cudaFuncSetAttribute(attn_decode_split_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_tc));
+            if (dev >= 0 && dev < 64) configured_tc[dev] = smem_tc;
+        }
+        attn_decode_split_tc_kernel<<<dim3(nkv, batch, splits), ATTN_THREADS, smem_tc, s>>>(
+            qkv, static_cast<const __half*>(kc), static_cast<const __half*>(vc), scratch, nqh, nkv, hd, len, ctx_cap, splits);
+    } else {
+        attn_decode_split_kernel<<<dim3(nkv, batch, splits), ATTN_THREADS, smem, s>>>(qkv, static_cast<const __half*>(kc),
+                                                                                       static_cast<const __half*>(vc), scratch, nqh, nkv, hd,
+                                                                                       len, ctx_cap, splits);
+    }
     QMM_CUDA_TRY(cudaGetLastError());
     // the merge always produces Q8_1 blocks; a caller that only wants f32 gets them in a throw-away tail of the scratch
     uint8_t* q8 = static_cast<uint8_t*>(out_q8);

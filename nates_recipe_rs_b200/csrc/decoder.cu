@@ -367,8 +367,13 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
         __half* kc = d->kcache + (size_t)l * cache_layer;
         __half* vc = d->vcache + (size_t)l * cache_layer;
         TRY(launch_pdl(rope_kv_append_kernel, dim3(8, batch), dim3(256), 0, s, d->qkv, kc, vc, d->nq, d->nkv, hd, pos, c.ctx_len, c.rope_theta));
-        TRY(launch_pdl(attn_decode_split_kernel, dim3(d->nkv, batch, splits), dim3(ATTN_THREADS), attn_smem, s, (const float*)d->qkv,
-                       (const __half*)kc, (const __half*)vc, d->attn_scratch, d->nq, d->nkv, hd, len, c.ctx_len, splits));
+        if (batch >= ATTN_TC_MIN_BATCH && hd % 32 == 0) {
+            TRY(launch_pdl(attn_decode_split_tc_kernel, dim3(d->nkv, batch, splits), dim3(ATTN_THREADS), attn_tc_smem_bytes(hd), s,
+                           (const float*)d->qkv, (const __half*)kc, (const __half*)vc, d->attn_scratch, d->nq, d->nkv, hd, len, c.ctx_len, splits));
+        } else {
+            TRY(launch_pdl(attn_decode_split_kernel, dim3(d->nkv, batch, splits), dim3(ATTN_THREADS), attn_smem, s, (const float*)d->qkv,
+                           (const __half*)kc, (const __half*)vc, d->attn_scratch, d->nq, d->nkv, hd, len, c.ctx_len, splits));
+        }
         TRY(launch_pdl(attn_combine_q8_kernel, dim3(d->nq, batch), dim3(hd < 128 ? hd : 128), 0, s, (const float*)d->attn_scratch, d->xq_attn,
                        (float*)nullptr, d->nq, hd, splits));
         TRY(qmatvec_launch_strided(c.type_attn_o, L.wo, d->xq_attn, d->part[0], H, batch, H, ao, s));
@@ -419,7 +424,9 @@ int qmm_decoder_create(const qmm_decoder_config* cfg, void** handle) {
         destroy(d);
         return QMM_ERR_UNSUPPORTED;
     }
-    if (cudaFuncSetAttribute(attn_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem) != cudaSuccess) {
+    if (cudaFuncSetAttribute(attn_decode_split_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)attn_tc_smem_bytes(cfg->head_dim)) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem) != cudaSuccess) {
         destroy(d);
         return cuda_fail(cudaGetLastError());
     }

@@ -358,6 +358,134 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_decode_split_kernel(const f
     }
 }
 
+// The same split attention on the f16 tensor cores, for batches of several sequences, where the scalar
+// kernel above is bound by its own arithmetic (2.2 TB/s of K and V at batch 16): scores S = Q K^T and
+// outputs O = P V as mma.sync.m16n8k16 (f16 operands, f32 accumulation).  The group's query heads (<= 8)
+// are the rows 0..7 of the 16-row A operand (rows 8..15 stay zero), q (scaled) and the probabilities
+// are rounded to f16 - the only numerical difference to the scalar kernel, about 1e-3 relative.  K rows
+// are B fragments as they lie in shared memory, V rows go through ldmatrix.trans.  Same scratch layout
+// and merge kernel as above.  hd a multiple of 32.
+__device__ __forceinline__ void mma_f16_k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// from this many sequences on the tensor-core form is used (below it the scalar kernel is not the bottleneck
+// and keeps f32 q and probabilities)
+constexpr int ATTN_TC_MIN_BATCH = 4;
+__host__ __device__ inline size_t attn_tc_smem_bytes(int hd) {
+    return (size_t)(2 * ATTN_CHUNK * (hd + 8) + 8 * (hd + 8) + 8 * (ATTN_CHUNK + 8)) * sizeof(__half) + (size_t)(8 * ATTN_CHUNK + 16) * sizeof(float);
+}
+__global__ void __launch_bounds__(ATTN_THREADS) attn_decode_split_tc_kernel(const float* __restrict__ qkv, const __half* __restrict__ kcache,
+                                                                           const __half* __restrict__ vcache, float* __restrict__ scratch,
+                                                                           int nqh, int nkv, int hd, int len, int ctx_cap, int splits) {
+    extern __shared__ __align__(16) uint8_t att_raw[];
+    // layout (halves unless noted): K rows 64 x (hd+8) | V rows 64 x (hd+8) | Q 8 x (hd+8) | P 8 x 72 |
+    //                               S/P floats 8 x 64 | stats 2 x 8 floats
+    const int pitch = hd + 8;
+    constexpr int PPITCH = ATTN_CHUNK + 8;
+    __half* ks = reinterpret_cast<__half*>(att_raw);
+    __half* vs = ks + ATTN_CHUNK * pitch;
+    __half* qh = vs + ATTN_CHUNK * pitch;
+    __half* ph = qh + 8 * pitch;
+    float* ps = reinterpret_cast<float*>(ph + 8 * PPITCH);
+    float* stat = ps + 8 * ATTN_CHUNK;
+    const int group = nqh / nkv;
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    const int kvh = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
+    const int t0 = sp * ATTN_CHUNK, nt = max(min(len - t0, ATTN_CHUNK), 0);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = lane >> 2, pq = lane & 3;
+    const float scale = rsqrtf((float)hd);
+    const float* qrow = qkv + (size_t)b * (nqh + 2 * nkv) * hd + (size_t)kvh * group * hd;
+    const int pieces = hd / 8;
+    const size_t row_stride = (size_t)nkv * hd;
+    const __half* kbase = kcache + (((size_t)b * ctx_cap + t0) * nkv + kvh) * hd;
+    const __half* vbase = vcache + (((size_t)b * ctx_cap + t0) * nkv + kvh) * hd;
+    // stage K and V (rows past the end of the context as zeros: they meet zero probabilities)
+    for (int i = tid; i < ATTN_CHUNK * pieces; i += ATTN_THREADS) {
+        const int t = i / pieces, c = i - t * pieces;
+        uint4 kk = make_uint4(0, 0, 0, 0), vv = kk;
+        if (t < nt) {
+            kk = *reinterpret_cast<const uint4*>(kbase + t * row_stride + 8 * c);
+            vv = *reinterpret_cast<const uint4*>(vbase + t * row_stride + 8 * c);
+        }
+        *reinterpret_cast<uint4*>(ks + t * pitch + 8 * c) = kk;
+        *reinterpret_cast<uint4*>(vs + t * pitch + 8 * c) = vv;
+    }
+    for (int i = tid; i < 8 * hd; i += ATTN_THREADS) {
+        const int g = i / hd, d = i - g * hd;
+        qh[g * pitch + d] = __float2half_rn(g < group ? qrow[i] * scale : 0.f);
+    }
+    __syncthreads();
+    // scores: warp w owns positions 16w .. 16w+15 (two n-tiles), k runs over the head dimension
+    {
+        float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+        const __half* qa = qh + q * pitch + 2 * pq;
+        const __half* kb0 = ks + (16 * warp + q) * pitch + 2 * pq;
+        const __half* kb1 = kb0 + 8 * pitch;
+        for (int kk = 0; kk < hd; kk += 16) {
+            const uint32_t a0 = *reinterpret_cast<const uint32_t*>(qa + kk), a2 = *reinterpret_cast<const uint32_t*>(qa + kk + 8);
+            mma_f16_k16(c0, a0, 0u, a2, 0u, *reinterpret_cast<const uint32_t*>(kb0 + kk), *reinterpret_cast<const uint32_t*>(kb0 + kk + 8));
+            mma_f16_k16(c1, a0, 0u, a2, 0u, *reinterpret_cast<const uint32_t*>(kb1 + kk), *reinterpret_cast<const uint32_t*>(kb1 + kk + 8));
+        }
+        // c[0], c[1]: head q, positions 16w + 8n + 2pq, +1
+        if (q < group) {
+            const int p0 = 16 * warp + 2 * pq;
+            ps[q * ATTN_CHUNK + p0] = p0 < nt ? c0[0] : -INFINITY;
+            ps[q * ATTN_CHUNK + p0 + 1] = p0 + 1 < nt ? c0[1] : -INFINITY;
+            ps[q * ATTN_CHUNK + p0 + 8] = p0 + 8 < nt ? c1[0] : -INFINITY;
+            ps[q * ATTN_CHUNK + p0 + 9] = p0 + 9 < nt ? c1[1] : -INFINITY;
+        }
+    }
+    __syncthreads();
+    // per head: max, exponentials, sum (as in the scalar kernel), the probabilities also as f16 A operand
+    for (int head = warp; head < 8; head += ATTN_THREADS / 32) {
+        float a = 0.f, c = 0.f;
+        if (head < group) {
+            a = ps[head * ATTN_CHUNK + lane], c = ps[head * ATTN_CHUNK + 32 + lane];
+            float m = fmaxf(a, c);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            a = (lane < nt) ? __expf(a - m) : 0.f;
+            c = (32 + lane < nt) ? __expf(c - m) : 0.f;
+            const float sum = warp_sum(a + c);
+            if (lane == 0) stat[2 * head] = m, stat[2 * head + 1] = sum;
+        }
+        ph[head * PPITCH + lane] = __float2half_rn(a);
+        ph[head * PPITCH + 32 + lane] = __float2half_rn(c);
+    }
+    __syncthreads();
+    // outputs: warp w owns head dimensions w*hd/4 .. (w+1)*hd/4 - 1 in n-tiles of eight, k runs over the positions
+    {
+        const int nw = hd / 4;  // dimensions per warp
+        const __half* pa = ph + q * PPITCH + 2 * pq;
+        uint32_t a0[4], a2[4];
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) a0[k4] = *reinterpret_cast<const uint32_t*>(pa + 16 * k4), a2[k4] = *reinterpret_cast<const uint32_t*>(pa + 16 * k4 + 8);
+        for (int n0 = warp * nw; n0 < (warp + 1) * nw; n0 += 8) {
+            float o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+                // two 8x8 blocks of V (positions 16*k4 + 0..7 and + 8..15, dimensions n0..n0+7), transposed on load
+                const uint32_t addr = smem_u32(vs + (16 * k4 + (lane & 15)) * pitch + n0);
+                uint32_t b0, b1;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+                mma_f16_k16(o, a0[k4], 0u, a2[k4], 0u, b0, b1);
+            }
+            if (q < group) {
+                float* dst = scratch + (((size_t)b * nqh + kvh * group + q) * splits + sp) * (hd + 2);
+                dst[2 + n0 + 2 * pq] = o[0];
+                dst[3 + n0 + 2 * pq] = o[1];
+            }
+        }
+        if (tid < group) {
+            float* dst = scratch + (((size_t)b * nqh + kvh * group + tid) * splits + sp) * (hd + 2);
+            dst[0] = stat[2 * tid], dst[1] = stat[2 * tid + 1];
+        }
+    }
+}
+
 // Merge of the context splits + Q8_1 of the attention output (the activations of the O projection).
 // One CTA per (query head, batch): the split weights are computed once into shared memory, then
 // every thread merges its output element with independent loads.

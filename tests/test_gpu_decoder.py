@@ -134,9 +134,13 @@ def test_step_rejects_bad_arguments(dec):
     d.close()
 
 
-@pytest.mark.parametrize("batch,nqh,nkv,hd,length", [(1, 4, 2, 64, 1), (2, 8, 2, 128, 70), (3, 32, 8, 128, 300), (1, 8, 8, 32, 129)])
+@pytest.mark.parametrize("batch,nqh,nkv,hd,length", [(1, 4, 2, 64, 1), (2, 8, 2, 128, 70), (3, 32, 8, 128, 300), (1, 8, 8, 32, 129),
+                                                     (4, 8, 2, 128, 70), (5, 32, 8, 128, 300), (4, 8, 8, 64, 129), (6, 64, 8, 128, 1),
+                                                     (4, 16, 4, 96, 200)])
 def test_attention_entry_matches_oracle(dec, batch, nqh, nkv, hd, length):
-    """launch_attn_decode through the C ABI against the oracle's straight-loop attention."""
+    """launch_attn_decode through the C ABI against the oracle's straight-loop attention.  From four
+    sequences on the library computes scores and outputs on the f16 tensor cores with q and the
+    probabilities rounded to f16 (2^-11 relative each), hence the wider bound there."""
     from nates_recipe_rs_b200._lib import check, lib
     L = lib()
     cap = length + 5
@@ -154,7 +158,8 @@ def test_attention_entry_matches_oracle(dec, batch, nqh, nkv, hd, length):
     got = out.cpu().numpy()
     for b in range(batch):
         want = oracle.attn_decode(qkv[b, :nqh * hd].reshape(nqh, hd), kc[b], vc[b], nqh, nkv, hd, length).reshape(-1)
-        assert np.abs(got[b] - want).max() <= 1e-4 + 1e-3 * np.abs(want).max()
+        rel = 1e-3 if batch < 4 else 4e-3
+        assert np.abs(got[b] - want).max() <= 1e-4 + rel * np.abs(want).max()
     # the Q8_1 output is the library's own quantization of the f32 output
     from nates_recipe_rs_b200 import quant_ops as ops
     assert torch.equal(q8, ops.gpu_quantize_q8_1(out))
