@@ -206,6 +206,12 @@ __global__ void rope_kv_append_kernel(float* __restrict__ qkv, __half* __restric
 constexpr int ATTN_THREADS = 128;
 constexpr int ATTN_MAX_GROUP = 8;
 constexpr int ATTN_CHUNK = 64;
+// 16-byte asynchronous copy global -> shared (no register in between, so a thread keeps all its copies
+// of a chunk in flight at once); `valid` false writes zeros instead
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(valid ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory"); }
 __global__ void __launch_bounds__(ATTN_THREADS) attn_decode_split_kernel(const float* __restrict__ qkv, const __half* __restrict__ kcache,
                                                                         const __half* __restrict__ vcache, float* __restrict__ scratch,
                                                                         int nqh, int nkv, int hd, int len, int ctx_cap, int splits) {
@@ -231,15 +237,15 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_decode_split_kernel(const f
     const size_t row_stride = (size_t)nkv * hd;  // halves between consecutive positions
     const __half* kbase = kcache + (((size_t)b * ctx_cap + t0) * nkv + kvh) * hd;
     const __half* vbase = vcache + (((size_t)b * ctx_cap + t0) * nkv + kvh) * hd;
-    for (int i = tid; i < nt * pieces; i += ATTN_THREADS) {
+    // (V rows past the end of the context are multiplied by zero probabilities below: zeros, so that they are finite)
+    for (int i = tid; i < ATTN_CHUNK * pieces; i += ATTN_THREADS) {
         const int t = i / pieces, c = i - t * pieces;
-        *reinterpret_cast<uint4*>(ks + t * kpitch + 8 * c) = *reinterpret_cast<const uint4*>(kbase + t * row_stride + 8 * c);
-        *reinterpret_cast<uint4*>(vs + t * hd + 8 * c) = *reinterpret_cast<const uint4*>(vbase + t * row_stride + 8 * c);
+        const bool in = t < nt;
+        if (in) cp_async16(ks + t * kpitch + 8 * c, kbase + t * row_stride + 8 * c, true);
+        cp_async16(vs + t * hd + 8 * c, in ? vbase + t * row_stride + 8 * c : vbase, in);
     }
-    // V rows past the end of the context are multiplied by zero probabilities below: make them finite
-    for (int i = nt * pieces + tid; i < ATTN_CHUNK * pieces; i += ATTN_THREADS)
-        *reinterpret_cast<uint4*>(vs + (i / pieces) * hd + 8 * (i % pieces)) = make_uint4(0, 0, 0, 0);
     for (int i = tid; i < group * hd; i += ATTN_THREADS) qs[i] = qrow[i] * scale;
+    cp_async_wait_all();
     __syncthreads();
     // scores: thread = (position t, head parity): heads g = par, par+2, ...; eight elements per step, the
     // K row as one 16-byte load, q as 16-byte broadcast loads
@@ -405,18 +411,15 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_decode_split_tc_kernel(cons
     // stage K and V (rows past the end of the context as zeros: they meet zero probabilities)
     for (int i = tid; i < ATTN_CHUNK * pieces; i += ATTN_THREADS) {
         const int t = i / pieces, c = i - t * pieces;
-        uint4 kk = make_uint4(0, 0, 0, 0), vv = kk;
-        if (t < nt) {
-            kk = *reinterpret_cast<const uint4*>(kbase + t * row_stride + 8 * c);
-            vv = *reinterpret_cast<const uint4*>(vbase + t * row_stride + 8 * c);
-        }
-        *reinterpret_cast<uint4*>(ks + t * pitch + 8 * c) = kk;
-        *reinterpret_cast<uint4*>(vs + t * pitch + 8 * c) = vv;
+        const bool in = t < nt;
+        cp_async16(ks + t * pitch + 8 * c, in ? kbase + t * row_stride + 8 * c : kbase, in);
+        cp_async16(vs + t * pitch + 8 * c, in ? vbase + t * row_stride + 8 * c : vbase, in);
     }
     for (int i = tid; i < 8 * hd; i += ATTN_THREADS) {
         const int g = i / hd, d = i - g * hd;
         qh[g * pitch + d] = __float2half_rn(g < group ? qrow[i] * scale : 0.f);
     }
+    cp_async_wait_all();
     __syncthreads();
     // scores: warp w owns positions 16w .. 16w+15 (two n-tiles), k runs over the head dimension
     {
