@@ -110,6 +110,13 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_q8_kernel(float* __restrict_
     __shared__ float red[32];
     __shared__ int peers_ok;
     pdl_release_dependents();
+    // gamma is model data: fetched before the wait for the preceding kernel
+    float gm[NORM_MAX_PER_THREAD];
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_PER_THREAD; ++i) {
+        const int e = i * blockDim.x + threadIdx.x;
+        gm[i] = e < hidden ? gamma[e] : 0.f;
+    }
     pdl_wait_prior_grids();
     const int b = blockIdx.x, lane = threadIdx.x & 31;
     if (n_parts > 1) {
@@ -158,7 +165,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_q8_kernel(float* __restrict_
 #pragma unroll
     for (int i = 0; i < NORM_MAX_PER_THREAD; ++i) {
         const int e = i * blockDim.x + threadIdx.x;  // a warp covers 32 consecutive elements = one block
-        if (e < hidden) warp_store_q8_1(v[i] * inv * gamma[e], qrow + (size_t)(e >> 5) * Q8_1_BYTES, lane);
+        if (e < hidden) warp_store_q8_1(v[i] * inv * gm[i], qrow + (size_t)(e >> 5) * Q8_1_BYTES, lane);
     }
 }
 
