@@ -174,17 +174,52 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_q8_kernel(float* __restrict_
 __global__ void rope_kv_append_kernel(float* __restrict__ qkv, __half* __restrict__ kcache, __half* __restrict__ vcache, int nqh, int nkv,
                                       int hd, int pos, int ctx_cap, float theta) {
     pdl_release_dependents();
-    pdl_wait_prior_grids();
     const int b = blockIdx.y;
     const int half = hd / 2;
     const int pairs = (nqh + nkv) * half;
+    const int first = blockIdx.x * blockDim.x + threadIdx.x, step = gridDim.x * blockDim.x;
+    // the angles depend on nothing the preceding kernel writes: sines and cosines of this thread's first
+    // pairs are ready before the wait for it
+    constexpr int PRE = 4;
+    float psn[PRE], pcs[PRE];
+#pragma unroll
+    for (int u = 0; u < PRE; ++u) {
+        const int idx = first + u * step;
+        psn[u] = 0.f, pcs[u] = 1.f;
+        if (idx < pairs) {
+            const int i = idx % half;
+            sincosf((float)pos * powf(theta, -2.0f * (float)i / (float)hd), &psn[u], &pcs[u]);
+        }
+    }
+    pdl_wait_prior_grids();
     float* row = qkv + (size_t)b * (nqh + 2 * nkv) * hd;
-    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < pairs + nkv * hd; idx += gridDim.x * blockDim.x) {
+#pragma unroll
+    for (int u = 0; u < PRE; ++u) {
+        const int idx = first + u * step;
         if (idx < pairs) {
             const int head = idx / half, i = idx - head * half;
-            const float freq = powf(theta, -2.0f * (float)i / (float)hd);
+            const float sn = psn[u], cs = pcs[u];
+            float* h = row + (size_t)head * hd;
+            const float a = h[i], c = h[i + half];
+            const float ra = a * cs - c * sn, rc = a * sn + c * cs;
+            if (head < nqh) {
+                h[i] = ra;
+                h[i + half] = rc;
+            } else {
+                __half* dst = kcache + (((size_t)b * ctx_cap + pos) * nkv + (head - nqh)) * hd;
+                dst[i] = __float2half_rn(ra);
+                dst[i + half] = __float2half_rn(rc);
+            }
+        } else if (idx < pairs + nkv * hd) {
+            const int j = idx - pairs;  // element of v
+            vcache[((size_t)b * ctx_cap + pos) * nkv * hd + j] = __float2half_rn(row[(size_t)(nqh + nkv) * hd + j]);
+        }
+    }
+    for (int idx = first + PRE * step; idx < pairs + nkv * hd; idx += step) {  // wider stacks than the grid covers in PRE rounds
+        if (idx < pairs) {
+            const int head = idx / half, i = idx - head * half;
             float sn, cs;
-            sincosf((float)pos * freq, &sn, &cs);
+            sincosf((float)pos * powf(theta, -2.0f * (float)i / (float)hd), &sn, &cs);
             float* h = row + (size_t)head * hd;
             const float a = h[i], c = h[i + half];
             const float ra = a * cs - c * sn, rc = a * sn + c * cs;
@@ -197,7 +232,7 @@ __global__ void rope_kv_append_kernel(float* __restrict__ qkv, __half* __restric
                 dst[i + half] = __float2half_rn(rc);
             }
         } else {
-            const int j = idx - pairs;  // element of v
+            const int j = idx - pairs;
             vcache[((size_t)b * ctx_cap + pos) * nkv * hd + j] = __float2half_rn(row[(size_t)(nqh + nkv) * hd + j]);
         }
     }
@@ -508,8 +543,13 @@ __global__ void attn_combine_q8_kernel(const float* __restrict__ scratch, uint8_
     pdl_wait_prior_grids();
     const int head = blockIdx.x, b = blockIdx.y, lane = threadIdx.x & 31;
     const float* src = scratch + ((size_t)b * nqh + head) * splits * (hd + 2);
+    // maxima and sums of all splits in one round of loads (the sums wait in wgt[])
     float m = -INFINITY;
-    for (int s = threadIdx.x; s < splits; s += blockDim.x) m = fmaxf(m, src[(size_t)s * (hd + 2)]);
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+        const float2 ml = *reinterpret_cast<const float2*>(src + (size_t)s * (hd + 2));
+        wgt[s] = ml.y;
+        m = fmaxf(m, ml.x);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if (lane == 0) red[threadIdx.x >> 5] = m;
@@ -519,7 +559,7 @@ __global__ void attn_combine_q8_kernel(const float* __restrict__ scratch, uint8_
     __syncthreads();
     float den = 0.f;
     for (int s = threadIdx.x; s < splits; s += blockDim.x) {
-        const float l = src[(size_t)s * (hd + 2) + 1];
+        const float l = wgt[s];
         const float w = l > 0.f ? __expf(src[(size_t)s * (hd + 2)] - m) : 0.f;
         wgt[s] = w;
         den += w * l;
