@@ -78,7 +78,9 @@ int qmm_set_overlap(int on);
  * matvec streams and synchronises but skips its arithmetic), "gemm_probe" (0/1/2: the GEMM skips its unpack
  * arithmetic / its tensor-core instructions), "mma_min_m" (0..16: fewest activation rows that take the
  * tensor-core matvec where type and shape allow it; 0 = never; default 3), "ctas_per_sm" (1, 2: persistent
- * CTAs per SM of the dp4a matvec; 2 needs "ring_bytes" and "consumer_warps" small enough to fit twice).
+ * CTAs per SM of the dp4a matvec; 2 needs "ring_bytes" and "consumer_warps" small enough to fit twice),
+ * "attn_tc_min_batch" (fewest sequences from which the decode attention runs on the f16 tensor cores;
+ * 0 = never; default 4).
  * Probe modes produce wrong results by design.  Not thread-safe against concurrent launches. */
 int qmm_tune(const char* key, int value);
 /* Tuning aid: while buf is non-NULL, matvec launch number i (counted from this call) stores four

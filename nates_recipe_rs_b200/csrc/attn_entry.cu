@@ -26,7 +26,7 @@ static int attn_run(const float* qkv, const void* kc, const void* vc, float* scr
         QMM_CUDA_TRY(cudaFuncSetAttribute(attn_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
-    if (batch >= ATTN_TC_MIN_BATCH) {
+    if (attn_use_tc(batch, hd)) {
         // several sequences: scores and outputs on the f16 tensor cores (q and the probabilities rounded to f16)
         static size_t configured_tc[64] = {};
         const size_t smem_tc = attn_tc_smem_bytes(hd);

@@ -367,7 +367,7 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
         __half* kc = d->kcache + (size_t)l * cache_layer;
         __half* vc = d->vcache + (size_t)l * cache_layer;
         TRY(launch_pdl(rope_kv_append_kernel, dim3(8, batch), dim3(256), 0, s, d->qkv, kc, vc, d->nq, d->nkv, hd, pos, c.ctx_len, c.rope_theta));
-        if (batch >= ATTN_TC_MIN_BATCH && hd % 32 == 0) {
+        if (attn_use_tc(batch, hd)) {
             TRY(launch_pdl(attn_decode_split_tc_kernel, dim3(d->nkv, batch, splits), dim3(ATTN_THREADS), attn_tc_smem_bytes(hd), s,
                            (const float*)d->qkv, (const __half*)kc, (const __half*)vc, d->attn_scratch, d->nq, d->nkv, hd, len, c.ctx_len, splits));
         } else {

@@ -420,7 +420,13 @@ __device__ __forceinline__ void mma_f16_k16(float (&d)[4], uint32_t a0, uint32_t
 }
 // from this many sequences on the tensor-core form is used (below it the scalar kernel is not the bottleneck
 // and keeps f32 q and probabilities)
-constexpr int ATTN_TC_MIN_BATCH = 4;
+static int g_attn_tc_min_batch = 4;  // tunable "attn_tc_min_batch"; 0: never
+int attn_set_tc_min_batch(int v) {
+    if (v < 0 || v > 1 << 20) return QMM_ERR_UNSUPPORTED;
+    g_attn_tc_min_batch = v;
+    return QMM_OK;
+}
+inline bool attn_use_tc(int batch, int hd) { return g_attn_tc_min_batch > 0 && batch >= g_attn_tc_min_batch && hd % 32 == 0; }
 __host__ __device__ inline size_t attn_tc_smem_bytes(int hd) {
     return (size_t)(2 * ATTN_CHUNK * (hd + 8) + 8 * (hd + 8) + 8 * (ATTN_CHUNK + 8)) * sizeof(__half) + (size_t)(8 * ATTN_CHUNK + 16) * sizeof(float);
 }

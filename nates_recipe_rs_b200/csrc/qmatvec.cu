@@ -309,6 +309,7 @@ static int g_trace_stride = 0, g_trace_count = 0;
 void matvec_set_trace(unsigned long long* buf, int stride_words) { g_trace = buf; g_trace_stride = stride_words; g_trace_count = 0; }
 void gemm_set_probe(int v);
 int mma_set_min_m(int v);
+int attn_set_tc_min_batch(int v);
 int mma_min_m();
 int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                        unsigned long long* trace, cudaStream_t stream);
@@ -323,6 +324,7 @@ int matvec_tune(const char* key, int value) {
     if (k == "probe" && value >= 0 && value <= 1) return g_probe = value, QMM_OK;
     if (k == "ctas_per_sm" && value >= 1 && value <= 2) return g_ctas_per_sm = value, QMM_OK;
     if (k == "mma_min_m") return mma_set_min_m(value);
+    if (k == "attn_tc_min_batch") return attn_set_tc_min_batch(value);
     return QMM_ERR_UNSUPPORTED;
 }
 

@@ -20,6 +20,10 @@ from ._lib import Q4_K, Q6_K
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    for kv in os.environ.get("QMM_TUNE", "").split(","):  # e.g. QMM_TUNE=attn_tc_min_batch=0,mma_min_m=0
+        if kv:
+            from ._lib import check, lib
+            check(lib().qmm_tune(kv.split("=")[0].encode(), int(kv.split("=")[1])), "qmm_tune")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     base = dict(n_layers=3, hidden=512, n_q_heads=8, n_kv_heads=8, head_dim=64, ffn=2048, vocab=4096, ctx_len=40,
                 rope_theta=10000.0, rms_eps=1e-6, act=dec.ACT_GELU_TANH, type_attn_qk=Q4_K, type_attn_v=Q6_K, type_attn_o=Q4_K,
