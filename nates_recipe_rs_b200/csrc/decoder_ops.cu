@@ -193,12 +193,10 @@ __global__ void rope_kv_append_kernel(float* __restrict__ qkv, __half* __restric
     }
     pdl_wait_prior_grids();
     float* row = qkv + (size_t)b * (nqh + 2 * nkv) * hd;
-#pragma unroll
-    for (int u = 0; u < PRE; ++u) {
-        const int idx = first + u * step;
+    // item idx: a rotation pair of a q or k head (idx < pairs), else one element of v
+    auto item = [&](int idx, float sn, float cs) {
         if (idx < pairs) {
             const int head = idx / half, i = idx - head * half;
-            const float sn = psn[u], cs = pcs[u];
             float* h = row + (size_t)head * hd;
             const float a = h[i], c = h[i + half];
             const float ra = a * cs - c * sn, rc = a * sn + c * cs;
@@ -211,30 +209,16 @@ __global__ void rope_kv_append_kernel(float* __restrict__ qkv, __half* __restric
                 dst[i + half] = __float2half_rn(rc);
             }
         } else if (idx < pairs + nkv * hd) {
-            const int j = idx - pairs;  // element of v
-            vcache[((size_t)b * ctx_cap + pos) * nkv * hd + j] = __float2half_rn(row[(size_t)(nqh + nkv) * hd + j]);
-        }
-    }
-    for (int idx = first + PRE * step; idx < pairs + nkv * hd; idx += step) {  // wider stacks than the grid covers in PRE rounds
-        if (idx < pairs) {
-            const int head = idx / half, i = idx - head * half;
-            float sn, cs;
-            sincosf((float)pos * powf(theta, -2.0f * (float)i / (float)hd), &sn, &cs);
-            float* h = row + (size_t)head * hd;
-            const float a = h[i], c = h[i + half];
-            const float ra = a * cs - c * sn, rc = a * sn + c * cs;
-            if (head < nqh) {
-                h[i] = ra;
-                h[i + half] = rc;
-            } else {
-                __half* dst = kcache + (((size_t)b * ctx_cap + pos) * nkv + (head - nqh)) * hd;
-                dst[i] = __float2half_rn(ra);
-                dst[i + half] = __float2half_rn(rc);
-            }
-        } else {
             const int j = idx - pairs;
             vcache[((size_t)b * ctx_cap + pos) * nkv * hd + j] = __float2half_rn(row[(size_t)(nqh + nkv) * hd + j]);
         }
+    };
+#pragma unroll
+    for (int u = 0; u < PRE; ++u) item(first + u * step, psn[u], pcs[u]);
+    for (int idx = first + PRE * step; idx < pairs + nkv * hd; idx += step) {  // wider stacks than the grid covers in PRE rounds
+        float sn = 0.f, cs = 1.f;
+        if (idx < pairs) sincosf((float)pos * powf(theta, -2.0f * (float)(idx % half) / (float)hd), &sn, &cs);
+        item(idx, sn, cs);
     }
 }
 
