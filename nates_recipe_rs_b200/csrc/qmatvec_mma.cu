@@ -130,6 +130,13 @@ __device__ __forceinline__ uint2 lds_v2(uint32_t a) {
     asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
     return v;
 }
+// the same with a compile-time byte offset folded into the instruction
+template <int OFF>
+__device__ __forceinline__ uint2 lds_v2_at(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(a), "n"(OFF));
+    return v;
+}
 __device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
@@ -360,6 +367,7 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
                 const uint32_t r1 = r0 + 8u * p.pitch;
                 const uint32_t mp = part_s + (uint32_t)pbuf * part_buf_b + my_part_off;
                 if constexpr (TYPE == QMM_TYPE_Q4_K) {
+                    const uint32_t q0 = r0 + 8 * pq, q1 = r1 + 8 * pq;  // this lane's 8 bytes of every 32-byte group
                     const uint4 h0 = lds_v4(r0), h1 = lds_v4(r1);
                     // 6-bit codes, one per byte: A = sub-blocks 0..3, B = 4..7
                     const uint32_t scA0 = h0.y & 0x3F3F3F3Fu, scB0 = (h0.w & 0x0F0F0F0Fu) | ((h0.y >> 2) & 0x30303030u);
@@ -378,8 +386,8 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
                     }
     #pragma unroll
                     for (int g = 0; g < 4; ++g) {
-                        const uint2 w0 = lds_v2(r0 + 16 + 32 * g + 8 * pq);
-                        const uint2 w1 = lds_v2(r1 + 16 + 32 * g + 8 * pq);
+                        const uint2 w0 = g == 0 ? lds_v2_at<16>(q0) : g == 1 ? lds_v2_at<48>(q0) : g == 2 ? lds_v2_at<80>(q0) : lds_v2_at<112>(q0);
+                        const uint2 w1 = g == 0 ? lds_v2_at<16>(q1) : g == 1 ? lds_v2_at<48>(q1) : g == 2 ? lds_v2_at<80>(q1) : lds_v2_at<112>(q1);
     #pragma unroll
                         for (int hi = 0; hi < 2; ++hi) {
                             const int j = 2 * g + hi;
