@@ -148,6 +148,15 @@ __device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
     return v;
 }
 // two 16-bit loads (addresses a and a+8) packed into one word: bytes a, a+1, a+8, a+9
+template <int OFF>
+__device__ __forceinline__ uint32_t lds_u16_at(uint32_t a) {
+    uint32_t v;
+    asm volatile("{ .reg .b16 h; ld.shared.u16 h, [%1+%2]; cvt.u32.u16 %0, h; }" : "=r"(v) : "r"(a), "n"(OFF));
+    return v;
+}
+// bytes a+OFF, a+OFF+1, a+OFF+8, a+OFF+9 in one word
+template <int OFF>
+__device__ __forceinline__ uint32_t lds_h2_at(uint32_t a) { return __byte_perm(lds_u16_at<OFF>(a), lds_u16_at<OFF + 8>(a), 0x5410); }
 __device__ __forceinline__ uint32_t lds_h2(uint32_t a) { return __byte_perm(lds_u16(a), lds_u16(a + 8), 0x5410); }
 __device__ __forceinline__ float lds_f32(uint32_t a) {
     float v;
@@ -433,21 +442,33 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
                     // a first mma of the constant -32 against the same activations, which also plants the
                     // float magic 1.5 * 2^23 in the accumulator, so the result is the exact sum as a float.
                     uint32_t sw0[4], sw1[4];  // the sixteen scales of both rows, biased to unsigned
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        sw0[i] = __byte_perm(lds_u16(r0 + 192 + 4 * i), lds_u16(r0 + 194 + 4 * i), 0x5410) ^ 0x80808080u;
-                        sw1[i] = __byte_perm(lds_u16(r1 + 192 + 4 * i), lds_u16(r1 + 194 + 4 * i), 0x5410) ^ 0x80808080u;
-                    }
+#define QMM_Q6_SCALES(I)                                                                                                  \
+    sw0[I] = __byte_perm(lds_u16_at<192 + 4 * I>(r0), lds_u16_at<194 + 4 * I>(r0), 0x5410) ^ 0x80808080u,                \
+    sw1[I] = __byte_perm(lds_u16_at<192 + 4 * I>(r1), lds_u16_at<194 + 4 * I>(r1), 0x5410) ^ 0x80808080u
+                    QMM_Q6_SCALES(0);
+                    QMM_Q6_SCALES(1);
+                    QMM_Q6_SCALES(2);
+                    QMM_Q6_SCALES(3);
+#undef QMM_Q6_SCALES
                     const uint64_t minus_bias = pack_f2(-(12582912.f + 128.f), -(12582912.f + 128.f));
                     uint64_t acc01[NT], acc23[NT];
 #pragma unroll
                     for (int t = 0; t < NT; ++t) acc01[t] = 0, acc23[t] = 0;
+                    const uint32_t q0 = r0 + 2 * pq, q1 = r1 + 2 * pq;  // this lane's two bytes of every 8-byte piece
 #pragma unroll
                     for (int hs = 0; hs < 4; ++hs) {
                         const int h = hs >> 1, s = hs & 1;
-                        const uint32_t oa = 64 * h + 16 * s + 2 * pq, oh = 128 + 32 * h + 16 * s + 2 * pq;
-                        const uint32_t A0 = lds_h2(r0 + oa), B0 = lds_h2(r0 + oa + 32), H0 = lds_h2(r0 + oh);
-                        const uint32_t A1 = lds_h2(r1 + oa), B1 = lds_h2(r1 + oa + 32), H1 = lds_h2(r1 + oh);
+                        uint32_t A0, B0, H0, A1, B1, H1;
+                        // ql at 64h + 16s (+32), qh at 128 + 32h + 16s; the offsets are instruction immediates
+#define QMM_Q6_LOAD(HS)                                                                                                  \
+    A0 = lds_h2_at<64 * (HS >> 1) + 16 * (HS & 1)>(q0), B0 = lds_h2_at<64 * (HS >> 1) + 16 * (HS & 1) + 32>(q0),         \
+    H0 = lds_h2_at<128 + 32 * (HS >> 1) + 16 * (HS & 1)>(q0), A1 = lds_h2_at<64 * (HS >> 1) + 16 * (HS & 1)>(q1),        \
+    B1 = lds_h2_at<64 * (HS >> 1) + 16 * (HS & 1) + 32>(q1), H1 = lds_h2_at<128 + 32 * (HS >> 1) + 16 * (HS & 1)>(q1)
+                        if (hs == 0) QMM_Q6_LOAD(0);
+                        else if (hs == 1) QMM_Q6_LOAD(1);
+                        else if (hs == 2) QMM_Q6_LOAD(2);
+                        else QMM_Q6_LOAD(3);
+#undef QMM_Q6_LOAD
 #pragma unroll
                         for (int t4 = 0; t4 < 4; ++t4) {
                             const uint32_t s0 = (t4 & 1) ? B0 : A0, s1 = (t4 & 1) ? B1 : A1;
@@ -481,7 +502,7 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
                             }
                         }
                     }
-                    const float d0 = f16_bits_to_f32(lds_u16(r0 + 208)), d1f = f16_bits_to_f32(lds_u16(r1 + 208));
+                    const float d0 = f16_bits_to_f32(lds_u16_at<208>(r0)), d1f = f16_bits_to_f32(lds_u16_at<208>(r1));
 #pragma unroll
                     for (int t = 0; t < NT; ++t) {
                         float a, b, e, f;
