@@ -172,6 +172,38 @@ def test_small_batch_tensor_core_kernel_matches_dp4a_kernel(ops, qtype, m, n, k)
     assert_close(y_mma.cpu().numpy(), y_dp4a.cpu().numpy())
 
 
+# per-rank projection shapes of the 8B- and 70B-class stacks under tensor parallelism 4 and 8
+TP_SHARD_SHAPES = [
+    (oracle.Q4_K, 1280, 4096), (oracle.Q6_K, 256, 4096), (oracle.Q4_K, 4096, 1024), (oracle.Q4_K, 7168, 4096), (oracle.Q6_K, 4096, 3584),
+    (oracle.Q4_K, 640, 4096), (oracle.Q6_K, 128, 4096), (oracle.Q4_K, 4096, 512), (oracle.Q4_K, 3584, 4096), (oracle.Q6_K, 4096, 1792),
+    (oracle.Q4_K, 2560, 8192), (oracle.Q4_K, 8192, 2048), (oracle.Q4_K, 8192, 7168), (oracle.Q4_K, 8192, 1024), (oracle.Q4_K, 8192, 3584),
+    (oracle.Q6_K, 16032, 8192),
+]
+
+
+@pytest.mark.parametrize("qtype,n,k", TP_SHARD_SHAPES)
+def test_tensor_parallel_shard_shapes_both_kernels(ops, qtype, n, k):
+    """Decode batch sizes 1, 8, 16 and 32 on every shard shape: the launcher's own choice of kernel
+    against the dp4a kernel alone, every output written (NaN sentinel)."""
+    from nates_recipe_rs_b200 import _lib
+    L = _lib.lib()
+    gen = torch.Generator(device="cuda").manual_seed(n + k)
+    w = ops.gpu_quantize_weights(qtype, torch.randn(n, k, device="cuda", generator=gen) * 0.02)
+    try:
+        for m in (1, 8, 16, 32):
+            xq = ops.gpu_quantize_q8_1(torch.randn(m, k, device="cuda", generator=gen))
+            _lib.check(L.qmm_tune(b"mma_min_m", 0), "tune")
+            y_dp4a = ops.gpu_qmatvec(qtype, w, xq, m, n, k)
+            _lib.check(L.qmm_tune(b"mma_min_m", 3), "tune")
+            y = torch.full((m, n), float("nan"), device="cuda")
+            ops.gpu_qmatvec_into(qtype, w, xq, y, m, n, k)
+            ops.check_launch()
+            assert not torch.isnan(y).any()
+            assert_close(y.cpu().numpy(), y_dp4a.cpu().numpy(), f"m={m}")
+    finally:
+        _lib.check(L.qmm_tune(b"mma_min_m", 3), "tune")
+
+
 @pytest.mark.parametrize("qtype", TYPES)
 @pytest.mark.parametrize("m", [2, 8, 16])
 def test_matvec_random_byte_weights(ops, qtype, m):
