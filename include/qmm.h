@@ -125,6 +125,32 @@ int launch_qmatvec_q4_k(const void* w, const void* xq, float* y, int m, int n, i
 int launch_qmatvec_q6_k(const void* w, const void* xq, float* y, int m, int n, int k, void* stream);
 int launch_qmatvec(int type, const void* w, const void* xq, float* y, int m, int n, int k, void* stream);
 
+/* ---- several independent decode projections in ONE launch.  The upstream issues the projections
+ * that share an input one launch after the other (q, k, v: examples/gemma4.rs:653-667; gate and up:
+ * :675-678; the chosen experts: :726-742) through gpu_gemm_bt_f64_into (gpu-core/src/infer_ops.rs:
+ * 224-240); here a list of such jobs is walked by persistent CTAs that keep the weight stream running
+ * from one matrix into the next, so a 33 MB matrix costs its bytes and not a launch on top.
+ *   y_j(m, n_j) = xq_j(m, k_j) . w_j(n_j, k_j)^T   for every job j, all with the same m.
+ * Jobs must be independent of each other's outputs (they run overlapped).  `jobs` is a HOST array,
+ * read during the call.  y_stride: floats between the output rows of two activation rows (0 = n).
+ * select (optional, device): the job's matrix is w + select[0] * select_stride_bytes, read on the
+ * device when the kernel runs (an expert chosen by a router kernel earlier in the stream);
+ * select_stride_bytes must be a multiple of 16.
+ * The persistent kernel takes m <= 2, xq on a 16-byte boundary and K up to 64 * 32 * 16 elements
+ * (Q8_0: half of that); any other list without selectors runs as one launch_qmatvec per job, with
+ * selectors it is rejected with QMM_ERR_UNSUPPORTED.  Bit-identical across reruns. */
+typedef struct {
+    int type;                 /* QMM_TYPE_Q8_0 / Q4_K / Q6_K */
+    int n, k;
+    const void* w;            /* packed (n, k) rows */
+    const void* xq;           /* Q8_1 (m, k) */
+    float* y;                 /* (m, n) */
+    long y_stride;
+    const int* select;
+    long select_stride_bytes;
+} qmm_matvec_job;
+int launch_qmatvec_batch(const qmm_matvec_job* jobs, int n_jobs, int m, void* stream);
+
 /* ---- dequant-GEMM for prefill on the tcgen05 tensor cores.  Same operator shape as
  * launch_gemm_bt_f64 (gpu-core/src/kernels/gemm_f64.hip:48-54; gpu-core/src/infer_ops.rs:224-240) with
  * m in the hundreds:  y(m,n) = bf16( sum_k x(m,k) * bf16(w(n,k)) ), x and y bf16 row-major, w Q4_K

@@ -56,7 +56,14 @@ int qmm_decoder_read_tensor(void* handle, int layer, int which, void* host_dst, 
 int qmm_decoder_fill_cache(void* handle, unsigned long long seed, void* stream);
 
 /* Tensor-parallel wiring.  Each rank exports the handle of its exchange area (64 bytes, a
- * cudaIpcMemHandle_t), the host program gathers them, and every rank imports its peers'. */
+ * cudaIpcMemHandle_t), the host program gathers them, and every rank imports its peers'.
+ * Rules for a tensor-parallel host:
+ *   - all ranks pass a host-side barrier after qmm_decoder_tp_ready and before the first step, and
+ *     enter every step within the wait bound (about two seconds of SM clock) of each other: a rank
+ *     that waits longer for a peer gives up, leaves its activations unwritten for that step and
+ *     stores -1 in next_tokens;
+ *   - after a step (or a batch of steps) call qmm_device_status before trusting next_tokens: a
+ *     non-zero status (5 = a peer did not arrive) means the step's results are not valid. */
 int qmm_decoder_ipc_export(void* handle, void* out_handle_64_bytes);
 int qmm_decoder_ipc_import(void* handle, int peer_rank, const void* handle_64_bytes);
 int qmm_decoder_tp_ready(void* handle); /* call once after all imports (uploads the pointer tables) */

@@ -13,6 +13,12 @@ TYPE_NAMES = {Q8_0: "q8_0", Q8_1: "q8_1", Q4_K: "q4_k", Q6_K: "q6_k"}
 
 vp, i32, i64 = C.c_void_p, C.c_int, C.c_long
 
+class MatvecJob(C.Structure):
+    """qmm_matvec_job of include/qmm.h."""
+    _fields_ = [("type", C.c_int), ("n", C.c_int), ("k", C.c_int), ("w", C.c_void_p), ("xq", C.c_void_p), ("y", C.c_void_p),
+                ("y_stride", C.c_long), ("select", C.c_void_p), ("select_stride_bytes", C.c_long)]
+
+
 # name -> (restype, argtypes); must list every symbol include/qmm.h declares
 SIGNATURES = {
     "qmm_status_string": (C.c_char_p, [i32]),
@@ -36,6 +42,7 @@ SIGNATURES = {
     "launch_qmatvec_q4_k": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "launch_qmatvec_q6_k": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "launch_qmatvec": (i32, [i32, vp, vp, vp, i32, i32, i32, vp]),
+    "launch_qmatvec_batch": (i32, [C.POINTER(MatvecJob), i32, i32, vp]),
     "launch_qgemm_q4_k_bf16": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "launch_qgemm_q4_k_bf16_f32acc": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "qmm_attn_decode_scratch_bytes": (i64, [i32, i32, i32, i32]),

@@ -30,6 +30,8 @@ int dequantize_f32_launch(int type, const void* w, float* out, long n_elems, cud
 int dequantize_bf16_launch(int type, const void* w, void* out, long n_elems, cudaStream_t stream);
 int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, int n, int k, cudaStream_t stream);
 int matvec_tune(const char* key, int value);
+int jobs_tune(const char* key, int value);
+int qmatvec_jobs_launch(const qmm_matvec_job* jobs, int n_jobs, int m, cudaStream_t stream);
 void matvec_set_trace(unsigned long long* buf, int stride_words);
 
 }  // namespace qmm
@@ -86,7 +88,10 @@ int qmm_set_overlap(int on) {
     return prev;
 }
 
-int qmm_tune(const char* key, int value) { return matvec_tune(key, value); }
+int qmm_tune(const char* key, int value) {
+    const int st = matvec_tune(key, value);
+    return st == QMM_ERR_UNSUPPORTED ? jobs_tune(key, value) : st;
+}
 int qmm_trace(void* buf, int stride_words) { matvec_set_trace(static_cast<unsigned long long*>(buf), stride_words); return QMM_OK; }
 
 int launch_quantize_q8_1(const float* x, void* xq, int m, int k, void* stream) {
@@ -115,6 +120,10 @@ int launch_qmatvec(int type, const void* w, const void* xq, float* y, int m, int
 int launch_qmatvec_q8_0(const void* w, const void* xq, float* y, int m, int n, int k, void* s) { return qmatvec_launch(QMM_TYPE_Q8_0, w, xq, y, m, n, k, as_stream(s)); }
 int launch_qmatvec_q4_k(const void* w, const void* xq, float* y, int m, int n, int k, void* s) { return qmatvec_launch(QMM_TYPE_Q4_K, w, xq, y, m, n, k, as_stream(s)); }
 int launch_qmatvec_q6_k(const void* w, const void* xq, float* y, int m, int n, int k, void* s) { return qmatvec_launch(QMM_TYPE_Q6_K, w, xq, y, m, n, k, as_stream(s)); }
+
+int launch_qmatvec_batch(const qmm_matvec_job* jobs, int n_jobs, int m, void* stream) {
+    return qmatvec_jobs_launch(jobs, n_jobs, m, as_stream(stream));
+}
 
 int launch_qgemm_q4_k_bf16(const void* w, const void* x, void* y, int m, int n, int k, void* stream) {
     if (!y) return QMM_ERR_NULL;

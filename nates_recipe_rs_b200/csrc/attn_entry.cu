@@ -1,5 +1,6 @@
 // Stand-alone entry points for the decode attention (the engine calls the same kernels directly).
 #include "qmm_formats.cuh"
+#include <mutex>
 
 namespace qmm {
 
@@ -19,21 +20,11 @@ static int attn_check(const float* qkv, const void* kc, const void* vc, const vo
 
 static int attn_run(const float* qkv, const void* kc, const void* vc, float* scratch, float* out_f32, void* out_q8, int batch, int nqh, int nkv,
                     int hd, int len, int ctx_cap, int splits, size_t smem, cudaStream_t s) {
-    static size_t configured[64] = {};
-    int dev = 0;
-    QMM_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || smem > configured[dev]) {
-        QMM_CUDA_TRY(cudaFuncSetAttribute(attn_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        if (dev >= 0 && dev < 64) configured[dev] = smem;
-    }
+    if (int st = attn_opt_in_smem(false, smem)) return st;
     if (attn_use_tc(batch, hd)) {
         // several sequences: scores and outputs on the f16 tensor cores (q and the probabilities rounded to f16)
-        static size_t configured_tc[64] = {};
         const size_t smem_tc = attn_tc_smem_bytes(hd);
-        if (dev < 0 || dev >= 64 || smem_tc > configured_tc[dev]) {
-            QMM_CUDA_TRY(cudaFuncSetAttribute(attn_decode_split_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_tc));
-            if (dev >= 0 && dev < 64) configured_tc[dev] = smem_tc;
-        }
+        if (int st = attn_opt_in_smem(true, smem_tc)) return st;
         attn_decode_split_tc_kernel<<<dim3(nkv, batch, splits), ATTN_THREADS, smem_tc, s>>>(
             qkv, static_cast<const __half*>(kc), static_cast<const __half*>(vc), scratch, nqh, nkv, hd, len, ctx_cap, splits);
     } else {
@@ -70,9 +61,11 @@ static __device__ __align__(256) float g_attn_static_scratch[ATTN_STATIC_FLOATS]
 // current, and remembered.
 static int attn_static_scratch_ptr(float** out) {
     static float* cached[64] = {};
+    static std::mutex guard;  // first calls from several host threads
     int dev = 0;
     QMM_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return QMM_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(guard);
     if (!cached[dev]) {
         float* p = nullptr;
         QMM_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_attn_static_scratch));

@@ -7,6 +7,7 @@
 // residual-add + RMSNorm + Q8_1 kernel, which reads the peers' partial buffers directly.
 #include "qmm_formats.cuh"
 #include "../../include/qmm_decoder.h"
+#include <algorithm>
 #include <vector>
 #include <cstring>
 
@@ -90,6 +91,8 @@ __global__ void f32_to_f16_kernel(const float* in, __half* out, long n) {
     if (i < n) out[i] = __float2half_rn(in[i]);
 }
 
+static inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? QMM_OK : cuda_fail(e); }
+
 template <typename T>
 static int dev_alloc(Decoder* d, T** p, size_t bytes) {
     void* q = nullptr;
@@ -144,7 +147,7 @@ static int create(const qmm_decoder_config* cfg, Decoder** out) {
     if (c.n_layers <= 0 || c.hidden <= 0 || c.head_dim <= 0 || c.n_q_heads <= 0 || c.n_kv_heads <= 0 || c.ffn <= 0 || c.vocab <= 0 ||
         c.ctx_len <= 0 || c.max_batch <= 0 || c.tp_size <= 0 || c.tp_rank < 0 || c.tp_rank >= c.tp_size)
         return QMM_ERR_SHAPE;
-    if (c.hidden % 256 || c.head_dim % 8 || c.head_dim > 256 || (c.n_q_heads * c.head_dim) % (256 * c.tp_size) || c.ffn % (256 * c.tp_size) ||
+    if (c.hidden % 256 || c.head_dim % 32 || c.head_dim > 256 || (c.n_q_heads * c.head_dim) % (256 * c.tp_size) || c.ffn % (256 * c.tp_size) ||
         c.n_q_heads % c.n_kv_heads || c.n_kv_heads % c.tp_size || c.vocab % c.tp_size || c.hidden > NORM_MAX_PER_THREAD * 1024 ||
         c.n_q_heads / c.n_kv_heads > ATTN_MAX_GROUP || c.tp_size > QMM_DECODER_MAX_TP)
         return QMM_ERR_UNSUPPORTED;
@@ -233,8 +236,8 @@ static int create(const qmm_decoder_config* cfg, Decoder** out) {
     const size_t cache_elems = (size_t)c.n_layers * B * c.ctx_len * d->nkv * hd;
     TRY(dev_alloc(d, &d->kcache, cache_elems * sizeof(__half)));
     TRY(dev_alloc(d, &d->vcache, cache_elems * sizeof(__half)));
-    QMM_CUDA_TRY(cudaMemsetAsync(d->kcache, 0, cache_elems * sizeof(__half), s));
-    QMM_CUDA_TRY(cudaMemsetAsync(d->vcache, 0, cache_elems * sizeof(__half), s));
+    TRY(cuda_status(cudaMemsetAsync(d->kcache, 0, cache_elems * sizeof(__half), s)));
+    TRY(cuda_status(cudaMemsetAsync(d->vcache, 0, cache_elems * sizeof(__half), s)));
 
     TRY(dev_alloc(d, &d->x, (size_t)B * H * sizeof(float)));
     TRY(dev_alloc(d, &d->qkv, (size_t)B * d->qkv_cols * sizeof(float)));
@@ -258,7 +261,7 @@ static int create(const qmm_decoder_config* cfg, Decoder** out) {
     d->cand_bytes = (((size_t)B * sizeof(Candidate)) + 255) & ~size_t(255);
     d->xchg_bytes = 2 * d->part_bytes + d->cand_bytes + 256 * 2;
     TRY(dev_alloc(d, &d->xchg, d->xchg_bytes));
-    QMM_CUDA_TRY(cudaMemsetAsync(d->xchg, 0, d->xchg_bytes, s));
+    TRY(cuda_status(cudaMemsetAsync(d->xchg, 0, d->xchg_bytes, s)));
     d->part[0] = reinterpret_cast<float*>(d->xchg);
     d->part[1] = reinterpret_cast<float*>(d->xchg + d->part_bytes);
     d->flags = reinterpret_cast<unsigned*>(d->xchg + 2 * d->part_bytes + d->cand_bytes);
@@ -268,8 +271,11 @@ static int create(const qmm_decoder_config* cfg, Decoder** out) {
     TRY(dev_alloc(d, &d->argmax_cand, (size_t)B * ARGMAX_PARTS * sizeof(Candidate)));
     TRY(dev_alloc(d, &d->peer_flags_dev, QMM_DECODER_MAX_TP * sizeof(unsigned*)));
     TRY(dev_alloc(d, &d->step_counter, 256));
-    QMM_CUDA_TRY(cudaMemsetAsync(d->step_counter, 0, 256, s));
-    QMM_CUDA_TRY(cudaStreamSynchronize(s));
+    TRY(cuda_status(cudaMemsetAsync(d->step_counter, 0, 256, s)));
+    TRY(cuda_status(cudaStreamSynchronize(s)));
+    // the staging buffer of the initialisation is not needed again
+    d->allocs.erase(std::find(d->allocs.begin(), d->allocs.end(), static_cast<void*>(tmp)));
+    TRY(cuda_status(cudaFree(tmp)));
 #undef TRY
     *out = d;
     return QMM_OK;
@@ -293,11 +299,12 @@ static int launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem
 }
 
 static int norm_threads(int hidden) {
-    // whole warps of valid elements in every pass (hidden is a multiple of 256): 1024 threads when they
-    // divide the row, else the largest multiple of 256 that does
-    for (int t = 1024; t >= 256; t -= 256)
-        if (hidden % t == 0 && hidden <= NORM_MAX_PER_THREAD * t) return t;
-    return 256;
+    // The fewest passes of at most 1024 threads that cover the row, then the smallest whole number of warps
+    // per pass that still covers it (hidden is a multiple of 256, so every warp is either all inside the
+    // row or all outside it, whatever the block size).
+    const int passes = (hidden + 1023) / 1024;
+    const int per_pass = (hidden + passes - 1) / passes;
+    return (per_pass + 31) & ~31;
 }
 
 // residual add of the partial outputs in buffer `which` (or none), RMSNorm with gamma, Q8_1 into xq_h
@@ -424,11 +431,9 @@ int qmm_decoder_create(const qmm_decoder_config* cfg, void** handle) {
         destroy(d);
         return QMM_ERR_UNSUPPORTED;
     }
-    if (cudaFuncSetAttribute(attn_decode_split_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)attn_tc_smem_bytes(cfg->head_dim)) != cudaSuccess ||
-        cudaFuncSetAttribute(attn_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem) != cudaSuccess) {
+    if (attn_opt_in_smem(true, attn_tc_smem_bytes(cfg->head_dim)) != QMM_OK || attn_opt_in_smem(false, attn_smem) != QMM_OK) {
         destroy(d);
-        return cuda_fail(cudaGetLastError());
+        return QMM_ERR_CUDA;
     }
     // single GPU: the pointer tables hold only this rank's buffers
     if (cfg->tp_size == 1) {

@@ -521,6 +521,23 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_decode_split_tc_kernel(cons
     }
 }
 
+// Opt-in to more than 48 KiB of dynamic shared memory for the two split kernels.  cudaFuncSetAttribute
+// REPLACES the limit, so every caller (the stand-alone entry points and every decoder) goes through this
+// one per-device high-water mark and the limit is only ever raised.
+inline int attn_opt_in_smem(bool tensor_core, size_t bytes) {
+    static size_t high[2][64] = {};
+    int dev = 0;
+    QMM_CUDA_TRY(cudaGetDevice(&dev));
+    const bool track = dev >= 0 && dev < 64;
+    if (track && bytes <= high[tensor_core ? 1 : 0][dev]) return QMM_OK;
+    if (tensor_core)
+        QMM_CUDA_TRY(cudaFuncSetAttribute(attn_decode_split_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    else
+        QMM_CUDA_TRY(cudaFuncSetAttribute(attn_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    if (track) high[tensor_core ? 1 : 0][dev] = bytes;
+    return QMM_OK;
+}
+
 // Merge of the context splits + Q8_1 of the attention output (the activations of the O projection).
 // One CTA per (query head, batch): the split weights are computed once into shared memory, then
 // every thread merges its output element with independent loads.
@@ -670,7 +687,11 @@ __global__ void tp_pick_token_kernel(const float* __restrict__ best_val, int* __
         __threadfence_system();
     }
     __syncthreads();
-    if (!peers_ok || (int)threadIdx.x >= batch) return;
+    if ((int)threadIdx.x >= batch) return;
+    if (!peers_ok) {  // a peer never arrived: make the failure visible in the result as well as in the status word
+        tokens_io[threadIdx.x] = -1;
+        return;
+    }
     float bv = -INFINITY;
     int bi = 0x7fffffff;
     for (int r = 0; r < n_ranks; ++r) {

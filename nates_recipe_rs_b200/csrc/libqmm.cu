@@ -3,6 +3,7 @@
 #include "api.cu"
 #include "quantize.cu"
 #include "qmatvec.cu"
+#include "qmatvec_jobs.cu"
 #include "qgemm.cu"
 #include "qmatvec_mma.cu"
 #include "decoder_ops.cu"

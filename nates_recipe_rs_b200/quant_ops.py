@@ -23,6 +23,7 @@ __all__ = [
     "Q8_0", "Q8_1", "Q4_K", "Q6_K", "row_bytes", "check_launch",
     "gpu_quantize_q8_1_into", "gpu_quantize_q8_1", "gpu_quantize_weights_into", "gpu_quantize_weights",
     "gpu_dequantize_into", "gpu_dequantize", "gpu_qmatvec_into", "gpu_qmatvec", "gpu_qblock_dots",
+    "MatvecJobs", "gpu_qmatvec_batch_into",
     "gpu_qgemm_q4_k_bf16_into", "gpu_qgemm_q4_k_bf16",
     "gpu_qlinear",
 ]
@@ -125,6 +126,36 @@ def gpu_qmatvec(qtype, w, xq, m, n, k):
     out = torch.empty((m, n), dtype=torch.float32, device=w.device)
     gpu_qmatvec_into(qtype, w, xq, out, m, n, k)
     return out
+
+
+class MatvecJobs:
+    """A host-side list of independent projections for gpu_qmatvec_batch_into (one launch for all).
+    Holds references to the tensors so the device pointers stay valid while the list is in use."""
+
+    def __init__(self):
+        self._jobs, self._keep = [], []
+
+    def add(self, qtype, w, xq, out, n, k, y_stride=0, select=None, select_stride_bytes=0):
+        """out(m,n) = xq(m,k) . w(n,k)^T, as gpu_qmatvec_into; `select` (int32 device tensor) makes the
+        matrix w + select[0] * select_stride_bytes, resolved on the device when the kernel runs."""
+        self._jobs.append(_lib.MatvecJob(qtype, n, k, _ptr(w), _ptr(xq), _ptr(out), y_stride,
+                                         _ptr(select) if select is not None else None, select_stride_bytes))
+        self._keep.append((w, xq, out, select))
+        return self
+
+    def __len__(self):
+        return len(self._jobs)
+
+    def array(self):
+        return (_lib.MatvecJob * len(self._jobs))(*self._jobs)
+
+
+def gpu_qmatvec_batch_into(jobs, m):
+    """Every job of `jobs` (MatvecJobs) in one launch: persistent CTAs walk from one matrix into the
+    next.  The upstream issues such projections as consecutive gpu_gemm_bt_f64_into calls on one
+    input (examples/gemma4.rs:653-667, 675-678, 726-742)."""
+    arr = jobs.array()
+    check(lib().launch_qmatvec_batch(arr, len(jobs), m, _stream()), "launch_qmatvec_batch")
 
 
 def gpu_qblock_dots(qtype, w, xq, n, k):

@@ -1,0 +1,154 @@
+"""The job-list matvec (launch_qmatvec_batch: several projections in one persistent launch) against
+the CPU oracle and against the single-matrix launcher, through the C ABI.  Needs a B200.
+
+Bars as for the single matvec: fp32 outputs within 1e-3 relative / 1e-4 absolute of the oracle;
+bit-identical across reruns."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL, ABS_TOL = 1e-3, 1e-4
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device")
+    from nates_recipe_rs_b200 import quant_ops
+    return quant_ops
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def assert_close(got, want, what=""):
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    bound = ABS_TOL + REL_TOL * np.abs(want.astype(np.float64))
+    bad = err > bound
+    assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} outside tolerance, max err {err.max():.3e}"
+
+
+def make_job(qtype, n, k, m, seed):
+    w = oracle.quantize(qtype, oracle.fill_normal(n * k, seed, 0.02).reshape(n, k))
+    x = oracle.fill_normal(m * k, seed + 1000, 1.0).reshape(m, k)
+    xq = oracle.quantize(oracle.Q8_1, x)
+    return w, xq, oracle.matvec(qtype, w, xq, k)
+
+
+def run_list(ops, specs, m, seed=1):
+    """specs: [(qtype, n, k)]; returns (got list, want list)."""
+    jobs = ops.MatvecJobs()
+    outs, wants = [], []
+    for i, (qtype, n, k) in enumerate(specs):
+        w, xq, want = make_job(qtype, n, k, m, seed + 17 * i)
+        y = torch.full((m, n), float("nan"), device="cuda")
+        jobs.add(qtype, dev(w), dev(xq), y, n, k)
+        outs.append(y)
+        wants.append(want)
+    ops.gpu_qmatvec_batch_into(jobs, m)
+    torch.cuda.synchronize()
+    ops.check_launch()
+    return [y.cpu().numpy() for y in outs], wants
+
+
+Q8, Q4, Q6 = oracle.Q8_0, oracle.Q4_K, oracle.Q6_K
+
+LISTS = [
+    # one job; fewer rows than CTAs; a row count that is no multiple of anything
+    [(Q4, 1, 256)], [(Q4, 37, 512)], [(Q6, 150, 1024)], [(Q8, 149, 256)],
+    # mixed types and K in one list, short and long jobs alternating (stages of different jobs share the ring)
+    [(Q4, 300, 1024), (Q6, 7, 2048), (Q8, 513, 4096), (Q4, 1000, 4096), (Q6, 257, 4096)],
+    # the FFN shapes of the decode benchmark at reduced width, then a Q8_0 K that is 2-byte aligned only
+    [(Q4, 1792, 4096), (Q4, 1792, 4096), (Q4, 512, 14336), (Q6, 512, 14336)],
+    [(Q8, 333, 4224), (Q6, 91, 14336), (Q4, 40, 28672)],
+    # many tiny jobs: activations of the next job land while the current one has a single stage
+    [(Q4, 5 + 3 * i, 256 * (1 + i % 3)) for i in range(12)],
+]
+
+
+@pytest.mark.parametrize("m", [1, 2])
+@pytest.mark.parametrize("specs", LISTS, ids=[f"list{i}" for i in range(len(LISTS))])
+def test_job_list_matches_oracle(ops, specs, m):
+    got, want = run_list(ops, specs, m)
+    for i, (g, w) in enumerate(zip(got, want)):
+        assert not np.isnan(g).any(), f"job {i}: rows left unwritten"
+        assert_close(g, w, f"job {i} {specs[i]}")
+
+
+def test_job_list_longer_than_one_launch_and_rerun_bit_identical(ops):
+    specs = [((Q4, Q6, Q8)[i % 3], 64 + i, 512) for i in range(45)]   # more than the 40 jobs one launch takes
+    a, want = run_list(ops, specs, 1, seed=5)
+    b, _ = run_list(ops, specs, 1, seed=5)
+    for i in range(len(specs)):
+        assert_close(a[i], want[i], f"job {i}")
+        assert np.array_equal(a[i].view(np.uint32), b[i].view(np.uint32)), f"job {i}: rerun differs"
+
+
+def test_job_list_equals_single_launches_on_ffn_shapes(ops):
+    """Full-size FFN shapes of the decode benchmark: same arithmetic and fold order as the single-matrix
+    kernel, so the outputs are equal bit for bit when both use the same K split."""
+    m = 1
+    specs = [(Q4, 14336, 4096), (Q4, 14336, 4096), (Q4, 4096, 14336), (Q6, 4096, 14336)]
+    jobs = ops.MatvecJobs()
+    pairs = []
+    for i, (qtype, n, k) in enumerate(specs):
+        g = torch.Generator(device="cuda").manual_seed(40 + i)
+        w = ops.gpu_quantize_weights(qtype, torch.randn(n, k, device="cuda", generator=g) * 0.02)
+        xq = ops.gpu_quantize_q8_1(torch.randn(m, k, device="cuda", generator=g))
+        y = torch.zeros(m, n, device="cuda")
+        jobs.add(qtype, w, xq, y, n, k)
+        pairs.append((qtype, w, xq, y, n, k))
+    ops.gpu_qmatvec_batch_into(jobs, m)
+    for qtype, w, xq, y, n, k in pairs:
+        ref = ops.gpu_qmatvec(qtype, w, xq, m, n, k)
+        assert torch.allclose(y, ref, rtol=REL_TOL, atol=ABS_TOL), (qtype, n, k, float((y - ref).abs().max()))
+    # a row sample against the oracle
+    qtype, w, xq, y, n, k = pairs[3]
+    rows = np.arange(0, n, 97)
+    wn = w.cpu().numpy().reshape(n, -1)[rows]
+    want = oracle.matvec(qtype, wn, xq.cpu().numpy(), k)
+    assert_close(y.cpu().numpy()[:, rows], want, "Q6_K down rows")
+    ops.check_launch()
+
+
+def test_job_list_device_side_selector(ops):
+    """A job whose matrix is chosen on the device: w + select[0] * stride (an expert picked by a router)."""
+    m, n, k, experts = 1, 200, 1024, 5
+    rb = oracle.row_bytes(Q4, k)
+    bank = [oracle.quantize(Q4, oracle.fill_normal(n * k, 300 + e, 0.02).reshape(n, k)) for e in range(experts)]
+    bank_d = dev(np.stack(bank))
+    x = oracle.fill_normal(k, 9, 1.0)
+    xq = oracle.quantize(oracle.Q8_1, x)
+    xq_d = dev(xq)
+    picks = [3, 0, 4]
+    sel = [torch.tensor([e], dtype=torch.int32, device="cuda") for e in picks]
+    outs = [torch.zeros(m, n, device="cuda") for _ in picks]
+    jobs = ops.MatvecJobs()
+    for s, y in zip(sel, outs):
+        jobs.add(Q4, bank_d, xq_d, y, n, k, select=s, select_stride_bytes=n * rb)
+    ops.gpu_qmatvec_batch_into(jobs, m)
+    torch.cuda.synchronize()
+    for e, y in zip(picks, outs):
+        assert_close(y.cpu().numpy(), oracle.matvec(Q4, bank[e], xq, k), f"expert {e}")
+    ops.check_launch()
+
+
+def test_job_list_falls_back_and_rejects(ops):
+    from nates_recipe_rs_b200._lib import lib, MatvecJob
+    # m = 5 is outside the persistent kernel: the launcher runs one launch per job, same results
+    got, want = run_list(ops, [(Q4, 130, 4096), (Q6, 70, 2048)], 5)
+    for g, w in zip(got, want):
+        assert_close(g, w, "fallback")
+    L = lib()
+    assert L.launch_qmatvec_batch(None, 1, 1, None) == -1
+    j = (MatvecJob * 1)(MatvecJob(Q4, 8, 100, 16, 16, 16, 0, None, 0))
+    assert L.launch_qmatvec_batch(j, 1, 1, None) == -2
+    j = (MatvecJob * 1)(MatvecJob(99, 8, 256, 16, 16, 16, 0, None, 0))
+    assert L.launch_qmatvec_batch(j, 1, 1, None) == -5
+    j = (MatvecJob * 1)(MatvecJob(Q4, 8, 256, 16, 16, 16, 0, 16, 24))   # selector stride not a multiple of 16
+    assert L.launch_qmatvec_batch(j, 1, 1, None) == -4
