@@ -9,14 +9,26 @@ LAYERS distinct sets of weights (so the working set is far larger than L2):
                         -> up    Q4_K 4096->14336
     h(14336) f32 -> Q8_1 -> down Q4_K 14336->4096
                          -> down Q6_K 14336->4096
-One step = one pass over all LAYERS sets (LAYERS * 6 kernel launches), replayed
-as one CUDA graph.  value = packed weight bytes streamed per second, whole job.
-With N > 1 every rank owns the same amount of work (weak scaling): the FFN is N
-times wider, gate/up are split by output rows, down by input columns, and the
-N partial down outputs are summed with one NCCL allreduce per down projection.
+One pass = all LAYERS sets: 2*LAYERS activation-quantize launches and ONE job-list launch
+(launch_qmatvec_batch) that walks the 4*LAYERS projections with persistent CTAs, captured as
+one CUDA graph.  One step = PASSES graph replays (so that the timed region is long enough to
+be insensitive to scheduler noise).  value = packed weight bytes streamed per second, whole job.
+With N > 1 every rank owns the same amount of work (weak scaling): the FFN is N times wider,
+gate/up are split by output rows, down by input columns, and the N partial down outputs of a
+pass are summed across the ranks.
+
+Further sections of the JSON line: the same shapes as single launches and at the decode batch
+sizes, the Q8_0 matvec of configs[0], the Q4_K prefill GEMM of configs[2], decode tok/s of the
+two stacks of configs[3] and [4], and (N > 1) a tensor-parallel parity check of the engine.
 
 `--impl reference` times the CPU restatement of the same path (oracle/, the only
 CPU implementation there is: the upstream has none) on the host cores.
+
+`--case ...` runs one small case and exits (for profiler captures; see profiles/):
+    --case matvec:<q8_0|q4_k|q6_k>:<n>:<k>:<m>[:launches]    single-matrix launches over rotating weights
+    --case jobs:<q4k|ffn>[:launches]                          one job-list launch (24 Q4_K / 32 FFN jobs)
+    --case gemm:<n>:<k>:<m>[:launches]                        Q4_K x bf16 prefill GEMM
+    --case decode:<8b|70b>:<batch>[:steps[:layers]]           eager decode steps of a (cut) stack
 """
 import argparse
 import json
@@ -34,6 +46,7 @@ LAYERS = 8
 SEED = 0x5EED
 METRIC = "ffn_decode_matvec_weight_bandwidth"
 UNIT = "GB/s"
+WORKLOAD = "ffn_decode_q4k_q6k"
 
 
 def layer_weight_bytes():
@@ -43,12 +56,24 @@ def layer_weight_bytes():
     return 3 * q4 + q6, q4, q6
 
 
-def measured_peak():
+def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    return 6650.0, "fallback (6.65 TB/s)"
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, 1590.0, "fallback (6.65 TB/s, 1.59 PFLOP/s)"
+
+
+def profile_traffic(name):
+    """DRAM bytes per launch of the dominant kernel, from the committed ncu summary (profiles/<name>.json)."""
+    path = os.path.join(ROOT, "profiles", name)
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["dram_bytes_read"]) + float(d["dram_bytes_write"]), f"profiles/{name}"
+    except (OSError, KeyError, ValueError):
+        return None, "no ncu summary committed for this launch"
 
 
 class ClockSampler:
@@ -92,12 +117,18 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def note(msg):
+    """Progress line on stderr (QMM_BENCH_VERBOSE=1): where a multi-rank run is, should it stall."""
+    if os.environ.get("QMM_BENCH_VERBOSE"):
+        print(f"[bench rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
+
 # ------------------------------------------------------------------------- CPU arm
 def cpu_time_sample(budget_s=12.0):
     """Times the oracle on one layer set (gate, up, down Q4_K, down Q6_K; activation
-    quantization included) repeatedly for about budget_s seconds."""
-    import numpy as np
+    quantization included) repeatedly for about budget_s seconds, on every host core."""
     import oracle
+    oracle.set_num_threads(os.cpu_count() or 1)  # a launcher may have exported OMP_NUM_THREADS=1
     total, q4, q6 = layer_weight_bytes()
     gate = oracle.quantize(oracle.Q4_K, oracle.fill_normal(FFN * HID, SEED, 0.02).reshape(FFN, HID))
     down4 = oracle.quantize(oracle.Q4_K, oracle.fill_normal(FFN * HID, SEED + 2, 0.02).reshape(HID, FFN))
@@ -144,20 +175,59 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 dot / f32 accumulate", "data": "synthetic (seeded closed-form normal, quantized on the host)",
-        "config": {"workload": "ffn_decode_q4k_q6k", "hidden": HID, "ffn": FFN, "batch": 1,
+        "config": {"workload": WORKLOAD, "hidden": HID, "ffn": FFN, "batch": 1,
                    "note": "CPU restatement of the path (oracle/): the upstream has no implementation of these block "
-                           "formats; each step is a ~2 s sample of one layer set"},
+                           "formats; each step is a ~2 s sample of one layer set on all host cores"},
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
 # ------------------------------------------------------------------------- GPU arm
+class Timer:
+    """CUDA-event timing of graph replays on one stream."""
+
+    def __init__(self, torch, stream):
+        self.torch, self.stream = torch, stream
+
+    def graph(self, body):
+        torch = self.torch
+        with torch.cuda.stream(self.stream):
+            body()
+            self.stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=self.stream):
+                body()
+        return g
+
+    def us(self, body, reps=10, warm=3):
+        """Mean microseconds of one replay of `body` captured as a graph."""
+        torch = self.torch
+        g = self.graph(body)
+        with torch.cuda.stream(self.stream):
+            for _ in range(warm):
+                g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(self.stream)
+            for _ in range(reps):
+                g.replay()
+            e1.record(self.stream)
+            self.stream.synchronize()
+        del g
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def gen_weights(torch, ops, dev, rows, cols, seed, qtype):
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    return ops.gpu_quantize_weights(qtype, torch.randn(rows, cols, device=dev, generator=g) * 0.02)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
     from nates_recipe_rs_b200 import quant_ops as ops
-    from nates_recipe_rs_b200._lib import Q4_K, Q6_K, Q8_1, lib
+    from nates_recipe_rs_b200._lib import Q4_K, Q6_K, Q8_0, Q8_1, lib
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -168,79 +238,87 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    L = lib()
+    lib()
     total_layer, q4_bytes, q6_bytes = layer_weight_bytes()
+    hbm_peak, tensor_peak, peak_src = measured_peaks()
+    passes = max(1, args.passes)
+
+    # ---- tensor-parallel parity first: a run that computes the wrong thing is not timed
+    tp_par = None
+    if world > 1:
+        from nates_recipe_rs_b200.tp_parity import tp_parity
+        note("tensor-parallel parity")
+        checks = []
+        for wide in (False, True):
+            try:
+                checks.append(tp_parity(wide=wide))
+            except ValueError as e:   # the check model does not divide by this world size
+                checks.append({"n": world, "wide": wide, "skipped": str(e), "ok": True})
+        tp_par = {"n": world, "max_logit_diff": max(c.get("max_logit_diff", 0.0) for c in checks),
+                  "tokens_agree": all(c.get("tokens_agree", True) for c in checks), "ok": all(c["ok"] for c in checks),
+                  "checks": checks}
+        if not tp_par["ok"]:
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "error": "tensor-parallel parity failed", "tp_parity": tp_par}), flush=True)
+            dist.barrier()
+            os._exit(3)
 
     # ---- synthetic model: LAYERS sets of FFN weights, generated and quantized on the device
-    def gen(rows, cols, seed, qtype):
-        g = torch.Generator(device=dev)
-        g.manual_seed(seed)
-        w = torch.randn(rows, cols, device=dev, generator=g) * 0.02
-        return ops.gpu_quantize_weights(qtype, w)
-
     layers = []
     for li in range(LAYERS):
         s = SEED + 100 * li + 7919 * rank
-        layers.append({"gate": gen(FFN, HID, s, Q4_K), "up": gen(FFN, HID, s + 1, Q4_K),
-                       "down4": gen(HID, FFN, s + 2, Q4_K), "down6": gen(HID, FFN, s + 3, Q6_K)})
+        layers.append({"gate": gen_weights(torch, ops, dev, FFN, HID, s, Q4_K), "up": gen_weights(torch, ops, dev, FFN, HID, s + 1, Q4_K),
+                       "down4": gen_weights(torch, ops, dev, HID, FFN, s + 2, Q4_K),
+                       "down6": gen_weights(torch, ops, dev, HID, FFN, s + 3, Q6_K)})
     g = torch.Generator(device=dev)
     g.manual_seed(SEED + 5)
     x = torch.randn(1, HID, device=dev, generator=g)
     h = torch.randn(1, FFN, device=dev, generator=g)
-    xq = torch.empty(ops.row_bytes(Q8_1, HID), dtype=torch.uint8, device=dev)
-    hq = torch.empty(ops.row_bytes(Q8_1, FFN), dtype=torch.uint8, device=dev)
-    y_gate = torch.empty(1, FFN, device=dev)
-    y_up = torch.empty(1, FFN, device=dev)
-    y_d4 = torch.empty(1, HID, device=dev)
-    y_d6 = torch.empty(1, HID, device=dev)
-    launches_per_step = [0]
+    xq = [torch.empty(ops.row_bytes(Q8_1, HID), dtype=torch.uint8, device=dev) for _ in range(LAYERS)]
+    hq = [torch.empty(ops.row_bytes(Q8_1, FFN), dtype=torch.uint8, device=dev) for _ in range(LAYERS)]
+    y_gate = torch.empty(LAYERS, FFN, device=dev)
+    y_up = torch.empty(LAYERS, FFN, device=dev)
+    y_down = torch.empty(LAYERS, 2, HID, device=dev)   # [layer][Q4_K, Q6_K]: the partial sums of this rank when N > 1
 
-    def step_body(count=False):
-        n = 0
-        for lw in layers:
-            ops.gpu_quantize_q8_1_into(x, xq, 1, HID)
-            ops.gpu_qmatvec_into(Q4_K, lw["gate"], xq, y_gate, 1, FFN, HID)
-            ops.gpu_qmatvec_into(Q4_K, lw["up"], xq, y_up, 1, FFN, HID)
-            ops.gpu_quantize_q8_1_into(h, hq, 1, FFN)
-            ops.gpu_qmatvec_into(Q4_K, lw["down4"], hq, y_d4, 1, HID, FFN)
-            if world > 1:
-                dist.all_reduce(y_d4)
-            ops.gpu_qmatvec_into(Q6_K, lw["down6"], hq, y_d6, 1, HID, FFN)
-            if world > 1:
-                dist.all_reduce(y_d6)
-            n += 6
-        if count:
-            launches_per_step[0] = n
+    ffn_jobs = ops.MatvecJobs()
+    q4_jobs = ops.MatvecJobs()
+    for li, lw in enumerate(layers):
+        for jobs in (ffn_jobs, q4_jobs):
+            jobs.add(Q4_K, lw["gate"], xq[li], y_gate[li], FFN, HID)
+            jobs.add(Q4_K, lw["up"], xq[li], y_up[li], FFN, HID)
+            jobs.add(Q4_K, lw["down4"], hq[li], y_down[li, 0], HID, FFN)
+        ffn_jobs.add(Q6_K, lw["down6"], hq[li], y_down[li, 1], HID, FFN)
+    launches_per_pass = 2 * LAYERS + 1
+
+    def pass_body():
+        for li in range(LAYERS):
+            ops.gpu_quantize_q8_1_into(x, xq[li], 1, HID)
+            ops.gpu_quantize_q8_1_into(h, hq[li], 1, FFN)
+        ops.gpu_qmatvec_batch_into(ffn_jobs, 1)
+        if world > 1:
+            dist.all_reduce(y_down)   # the 2*LAYERS partial down outputs of the pass in one exchange
 
     stream = torch.cuda.Stream(device=dev)
-
-    def make_graph(body):
-        with torch.cuda.stream(stream):
-            body()
-            stream.synchronize()
-            gr = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gr, stream=stream):
-                body()
-        return gr
-
-    note("model built; first eager step")
-    step_body(count=True)
-    torch.cuda.synchronize()
-    note("capturing the step graph")
+    timer = Timer(torch, stream)
+    note("model built; capturing the pass graph")
     use_graph = True
     try:
-        graph = make_graph(step_body)
+        graph = timer.graph(pass_body)
     except Exception as e:  # NCCL capture refused: fall back to eager launches of the same kernels
         use_graph = False
         graph = None
         if rank == 0:
             print(f"# graph capture unavailable ({type(e).__name__}); timing eager launches", file=sys.stderr)
 
-    def run_step():
+    def run_pass():
         if use_graph:
             graph.replay()
         else:
-            step_body()
+            pass_body()
+
+    def run_step():
+        for _ in range(passes):
+            run_pass()
 
     def barrier():
         if world > 1:
@@ -249,7 +327,7 @@ def run_ours(args):
 
     note(f"graph={use_graph}; warm-up")
     with torch.cuda.stream(stream):
-        sampler = ClockSampler(local) if rank == 0 else None  # spans warm-up, the timed steps and the two legs below
+        sampler = ClockSampler(local) if rank == 0 else None  # spans warm-up, the timed steps and the legs below
         for _ in range(max(args.warmup, 3)):
             run_step()
         barrier()
@@ -261,102 +339,65 @@ def run_ours(args):
         e1.record(stream)
         barrier()
         elapsed_ms = e0.elapsed_time(e1)
-        # keep the same load running for ~1.5 s so the clock sampler (20 ms period, slow to start) sees it
+        # keep the same load running for ~1 s more so the clock sampler (20 ms period, slow to start) sees it
         t_soak = time.perf_counter()
-        while time.perf_counter() - t_soak < 1.5:
-            for _ in range(20):
-                run_step()
+        while time.perf_counter() - t_soak < 1.0:
+            run_step()
             stream.synchronize()
-        note("timed steps done; Q4_K-only graph")
 
-        # ---- dominant kernel alone: the Q4_K matvec launches of the same step, same rotation of weights
-        def q4_body():
-            for lw in layers:
-                ops.gpu_qmatvec_into(Q4_K, lw["gate"], xq, y_gate, 1, FFN, HID)
-                ops.gpu_qmatvec_into(Q4_K, lw["up"], xq, y_up, 1, FFN, HID)
-                ops.gpu_qmatvec_into(Q4_K, lw["down4"], hq, y_d4, 1, HID, FFN)
-        q4_graph = make_graph(q4_body)
-        for _ in range(3):
-            q4_graph.replay()
-        torch.cuda.synchronize()
-        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = max(args.steps, 10)
-        k0.record(stream)
-        for _ in range(reps):
-            q4_graph.replay()
-        k1.record(stream)
-        torch.cuda.synchronize()
-        q4_launch_s = k0.elapsed_time(k1) * 1e-3 / (reps * 3 * LAYERS)
+        # ---- dominant kernel alone: one job-list launch over the 3*LAYERS Q4_K projections of the pass
+        note("timed steps done; Q4_K job list alone")
+        q4_list_us = timer.us(lambda: ops.gpu_qmatvec_batch_into(q4_jobs, 1), reps=max(args.steps, 20))
+        ffn_list_us = timer.us(lambda: ops.gpu_qmatvec_batch_into(ffn_jobs, 1), reps=max(args.steps, 20))
 
         # ---- end to end through the C ABI with host buffers: activations come from pinned host
-        # memory and the projections go back to it every step; the weights stay resident in HBM
+        # memory and the projections go back to it every pass; the weights stay resident in HBM
         note("end-to-end leg")
         hx = torch.randn(1, HID).pin_memory()
         hh = torch.randn(1, FFN).pin_memory()
         hy = torch.empty(2, HID).pin_memory()
 
-        def e2e_step():
+        def e2e_pass():
             x.copy_(hx, non_blocking=True)
             h.copy_(hh, non_blocking=True)
-            run_step()
-            hy[0].copy_(y_d4[0], non_blocking=True)
-            hy[1].copy_(y_d6[0], non_blocking=True)
+            run_pass()
+            hy.copy_(y_down[LAYERS - 1], non_blocking=True)
             stream.synchronize()
         for _ in range(3):
-            e2e_step()
+            e2e_pass()
         barrier()
         t0 = time.perf_counter()
-        for _ in range(args.steps):
-            e2e_step()
+        for _ in range(args.steps * passes):
+            e2e_pass()
         barrier()
         e2e_s = time.perf_counter() - t0
         clocks = sampler.stop() if sampler else None
 
-    t = torch.tensor([elapsed_ms, e2e_s * 1e3, q4_launch_s * 1e6], device=dev, dtype=torch.float64)
+    t = torch.tensor([elapsed_ms, e2e_s * 1e3, q4_list_us, ffn_list_us], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms, q4_us = [float(v) for v in t.tolist()]
-    check_status = ops.check_launch  # raises if any kernel abandoned a bounded wait
-    check_status()
+    elapsed_ms, e2e_ms, q4_list_us, ffn_list_us = [float(v) for v in t.tolist()]
+    ops.check_launch()  # raises if any kernel abandoned a bounded wait
 
-    step_bytes = total_layer * LAYERS * world
-    value = step_bytes * args.steps / (elapsed_ms * 1e-3) / 1e9
-    e2e_value = step_bytes * args.steps / (e2e_ms * 1e-3) / 1e9
-    peak, peak_src = measured_peak()
-    # algorithmic bytes of one Q4_K launch: packed weights + Q8_1 activations + f32 outputs
-    q4_algo = q4_bytes + (HID // 32 * 36 * 2 + FFN // 32 * 36) / 3 + (FFN * 4 * 2 + HID * 4) / 3
-    achieved = q4_algo / (q4_us * 1e-6) / 1e9
+    pass_bytes = total_layer * LAYERS * world
+    n_pass = args.steps * passes
+    value = pass_bytes * n_pass / (elapsed_ms * 1e-3) / 1e9
+    e2e_value = pass_bytes * n_pass / (e2e_ms * 1e-3) / 1e9
+    # algorithmic bytes of the Q4_K job-list launch: packed weights + Q8_1 activations + f32 outputs of its 3*LAYERS jobs
+    q4_algo = LAYERS * (3 * q4_bytes + (2 * HID + FFN) // 32 * 36 + (2 * FFN + HID) * 4)
+    achieved = q4_algo / (q4_list_us * 1e-6) / 1e9
+    ffn_algo = q4_algo + LAYERS * (q6_bytes + FFN // 32 * 36 + HID * 4)
+    traffic, traffic_src = profile_traffic("qmatvec_jobs_q4k_ffn.json")
 
     note("FFN legs done")
-    batched = None
+    sections = {}
     if world == 1:
-        # ---- the same three FFN shapes at the decode batch sizes of the configs: time per launch over the
-        # same rotation of weights (1-2 rows: dp4a kernel; 3 and more: tensor-core kernel, 16 rows per pass)
-        batched = []
         with torch.cuda.stream(stream):
-            for m in (1, 8, 16, 32):
-                xm = ops.gpu_quantize_q8_1(torch.randn(m, HID, device=dev))
-                hm = ops.gpu_quantize_q8_1(torch.randn(m, FFN, device=dev))
-                yg, yd = torch.empty(m, FFN, device=dev), torch.empty(m, HID, device=dev)
-                for label, qt, key, xin, yout, n_, k_, nbytes in (("gate_q4_k", Q4_K, "gate", xm, yg, FFN, HID, q4_bytes),
-                                                                  ("down_q4_k", Q4_K, "down4", hm, yd, HID, FFN, q4_bytes),
-                                                                  ("down_q6_k", Q6_K, "down6", hm, yd, HID, FFN, q6_bytes)):
-                    def body():
-                        for lw in layers:
-                            ops.gpu_qmatvec_into(qt, lw[key], xin, yout, m, n_, k_)
-                    g = make_graph(body)
-                    for _ in range(3):
-                        g.replay()
-                    b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    b0.record(stream)
-                    for _ in range(10):
-                        g.replay()
-                    b1.record(stream)
-                    stream.synchronize()
-                    us = b0.elapsed_time(b1) * 1e3 / (10 * LAYERS)
-                    batched.append({"shape": label, "rows": m, "us_per_launch": us, "weight_GBps": nbytes / us / 1e3})
-                    del g
-        check_status()
+            sections["matvec_shapes"] = shapes_section(torch, ops, timer, dev, layers, hbm_peak)
+            sections["q8_0_matvec"] = q8_0_section(torch, ops, timer, dev, hbm_peak)
+            sections["batched_matvec"] = batched_section(torch, ops, timer, dev, layers, q4_bytes, q6_bytes)
+            sections["prefill_gemm"] = gemm_section(torch, ops, timer, dev, layers, tensor_peak)
+        ops.check_launch()
     decode = None if args.no_decode else run_decode(world, rank, dev, args.quick_decode)
     if rank == 0:
         cpu, _ = cpu_time_sample() if world == 1 else (None, None)
@@ -364,31 +405,38 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int8 dot (dp4a) / f32 accumulate", "data": "synthetic (seeded normal weights sigma 0.02, quantized on the device)",
-            "config": {"workload": "ffn_decode_q4k_q6k", "hidden": HID, "ffn": FFN, "batch": 1, "layers_per_step": LAYERS,
-                       "bytes_per_step": step_bytes, "l2": "inputs larger than L2: each step streams %d MB of distinct weights" % (step_bytes // world // 10**6),
-                       "launch": "cuda graph replay" if use_graph else "eager",
-                       "parallelism": "single GPU" if world == 1 else f"tp{world}: gate/up split by rows, down by columns + NCCL allreduce"},
-            "roofline": {"bound": "hbm", "kernel": "qmatvec_kernel<Q4_K> (gate, up, down at batch 1)", "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "us_per_launch": q4_us,
-                         "algorithmic_bytes_per_launch": q4_algo,
-                         "traffic": 33059584.0, "traffic_note": "dram read+write per launch from ncu (profiles/)"},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": (HID + FFN) * 4, "d2h_bytes_per_step": 2 * HID * 4,
-                    "note": "activations from pinned host memory and projections back to it every step; weights resident in HBM"},
-            "gpu_launches": launches_per_step[0] * args.steps,
+            "config": {"workload": WORKLOAD, "hidden": HID, "ffn": FFN, "batch": 1, "layers_per_pass": LAYERS,
+                       "passes_per_step": passes, "bytes_per_pass": pass_bytes, "ms_per_pass": elapsed_ms / n_pass,
+                       "l2": "inputs larger than L2: each pass streams %d MB of distinct weights per GPU" % (pass_bytes // world // 10**6),
+                       "launch": ("cuda graph replay" if use_graph else "eager") +
+                                 f": per pass {2 * LAYERS} activation-quantize launches + 1 job-list launch of {4 * LAYERS} projections",
+                       "parallelism": "single GPU" if world == 1 else
+                                      f"tp{world}: gate/up split by rows, down by columns, one NCCL allreduce of the pass's partial down outputs"},
+            "roofline": {"bound": "hbm", "kernel": f"qmatvec_jobs_kernel<1>: one launch = the {3 * LAYERS} Q4_K projections (gate, up, down) of a pass",
+                         "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src,
+                         "us_per_launch": q4_list_us, "us_per_projection": q4_list_us / (3 * LAYERS),
+                         "algorithmic_bytes_per_launch": q4_algo, "traffic": traffic, "traffic_source": traffic_src,
+                         "whole_pass_list": {"jobs": 4 * LAYERS, "us_per_launch": ffn_list_us, "GBps": ffn_algo / ffn_list_us / 1e3,
+                                             "frac": ffn_algo / ffn_list_us / 1e3 / hbm_peak}},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": (HID + FFN) * 4 * passes, "d2h_bytes_per_step": 2 * HID * 4 * passes,
+                    "note": "every pass: activations from pinned host memory, the pass, the last layer's projections back to the host, "
+                            "stream synchronize; weights resident in HBM"},
+            "gpu_launches": launches_per_pass * n_pass,
             "clocks": clocks,
         }
         if cpu:
             out["cpu_baseline"] = cpu
-        if batched is not None:
-            out["batched_matvec"] = batched
+        out.update(sections)
         if decode is not None:
             out["decode"] = decode
+        if tp_par is not None:
+            out["tp_parity"] = tp_par
         print(json.dumps(out), flush=True)
     if world > 1:
         # The NCCL communicator is referenced by the captured graphs: release them first, and do not let
         # a slow teardown outlive the measurement (the line above is already printed).
         import threading
-        graph = q4_graph = None
+        graph = None
         torch.cuda.synchronize()
         dist.barrier()
         threading.Timer(20.0, lambda: os._exit(0)).start()
@@ -396,10 +444,94 @@ def run_ours(args):
         os._exit(0)
 
 
-def note(msg):
-    """Progress line on stderr (QMM_BENCH_VERBOSE=1): where a multi-rank run is, should it stall."""
-    if os.environ.get("QMM_BENCH_VERBOSE"):
-        print(f"[bench rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+def shapes_section(torch, ops, timer, dev, layers, hbm_peak):
+    """The three FFN shapes one at a time over the same rotation of weights: as single launches of the
+    one-matrix kernel and as one job list of LAYERS jobs (time per projection)."""
+    from nates_recipe_rs_b200._lib import Q4_K, Q6_K
+    _, q4, q6 = layer_weight_bytes()
+    xq = ops.gpu_quantize_q8_1(torch.randn(1, HID, device=dev))
+    hq = ops.gpu_quantize_q8_1(torch.randn(1, FFN, device=dev))
+    yg, yd = torch.empty(1, FFN, device=dev), torch.empty(1, HID, device=dev)
+    out = []
+    for label, qt, key, xin, y, n, k, nbytes in (("gate_q4_k", Q4_K, "gate", xq, yg, FFN, HID, q4), ("down_q4_k", Q4_K, "down4", hq, yd, HID, FFN, q4),
+                                                  ("down_q6_k", Q6_K, "down6", hq, yd, HID, FFN, q6)):
+        def single():
+            for lw in layers:
+                ops.gpu_qmatvec_into(qt, lw[key], xin, y, 1, n, k)
+        jobs = ops.MatvecJobs()
+        for lw in layers:
+            jobs.add(qt, lw[key], xin, y, n, k)
+        us_single = timer.us(single) / LAYERS
+        us_list = timer.us(lambda: ops.gpu_qmatvec_batch_into(jobs, 1)) / LAYERS
+        algo = nbytes + k // 32 * 36 + n * 4
+        out.append({"shape": label, "n": n, "k": k, "algorithmic_bytes": algo,
+                    "single_launch_us": us_single, "single_launch_frac": algo / us_single / 1e3 / hbm_peak,
+                    "job_list_us_per_projection": us_list, "job_list_frac": algo / us_list / 1e3 / hbm_peak,
+                    "note": f"job list of {LAYERS} such projections; its launch overhead is shared by only {LAYERS} jobs"})
+    return out
+
+
+def q8_0_section(torch, ops, timer, dev, hbm_peak):
+    """BASELINE configs[0]: Q8_0 4096 x 4096 at batch 1, over 16 distinct matrices (285 MB > L2)."""
+    from nates_recipe_rs_b200._lib import Q8_0
+    n = k = 4096
+    copies = 16
+    ws = [gen_weights(torch, ops, dev, n, k, SEED + 900 + i, Q8_0) for i in range(copies)]
+    xq = ops.gpu_quantize_q8_1(torch.randn(1, k, device=dev))
+    y = torch.empty(copies, n, device=dev)
+    nbytes = n * k // 32 * 34
+    algo = nbytes + k // 32 * 36 + n * 4
+
+    def single():
+        for i, w in enumerate(ws):
+            ops.gpu_qmatvec_into(Q8_0, w, xq, y[i], 1, n, k)
+    jobs = ops.MatvecJobs()
+    for i, w in enumerate(ws):
+        jobs.add(Q8_0, w, xq, y[i], n, k)
+    us_single = timer.us(single) / copies
+    us_list = timer.us(lambda: ops.gpu_qmatvec_batch_into(jobs, 1)) / copies
+    return {"shape": "q8_0 4096x4096 batch 1", "weight_bytes": nbytes, "algorithmic_bytes": algo, "copies": copies, "bound": "hbm", "peak": hbm_peak,
+            "single_launch_us": us_single, "single_launch_GBps": algo / us_single / 1e3, "single_launch_frac": algo / us_single / 1e3 / hbm_peak,
+            "job_list_us_per_projection": us_list, "job_list_GBps": algo / us_list / 1e3, "job_list_frac": algo / us_list / 1e3 / hbm_peak}
+
+
+def batched_section(torch, ops, timer, dev, layers, q4_bytes, q6_bytes):
+    """The three FFN shapes at the decode batch sizes of the configs: time per launch over the rotation of
+    weights (1-2 rows: dp4a kernel; 3 and more: tensor-core kernel)."""
+    from nates_recipe_rs_b200._lib import Q4_K, Q6_K
+    out = []
+    for m in (1, 8, 16, 32):
+        xm = ops.gpu_quantize_q8_1(torch.randn(m, HID, device=dev))
+        hm = ops.gpu_quantize_q8_1(torch.randn(m, FFN, device=dev))
+        yg, yd = torch.empty(m, FFN, device=dev), torch.empty(m, HID, device=dev)
+        for label, qt, key, xin, yout, n_, k_, nbytes in (("gate_q4_k", Q4_K, "gate", xm, yg, FFN, HID, q4_bytes),
+                                                          ("down_q4_k", Q4_K, "down4", hm, yd, HID, FFN, q4_bytes),
+                                                          ("down_q6_k", Q6_K, "down6", hm, yd, HID, FFN, q6_bytes)):
+            def body():
+                for lw in layers:
+                    ops.gpu_qmatvec_into(qt, lw[key], xin, yout, m, n_, k_)
+            us = timer.us(body) / LAYERS
+            out.append({"shape": label, "rows": m, "us_per_launch": us, "weight_GBps": nbytes / us / 1e3})
+    return out
+
+
+def gemm_section(torch, ops, timer, dev, layers, tensor_peak):
+    """BASELINE configs[2]: Q4_K dequant-GEMM, X bf16 (M, 4096), M = 512 and 2048, N = 4096 and 14336."""
+    out = []
+    k = HID
+    for m in (512, 2048):
+        xb = torch.randn(m, k, device=dev).to(torch.bfloat16)
+        for n in (4096, 14336):
+            y = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+
+            def body():
+                for lw in layers:   # rotating weights (the first n rows of each gate matrix)
+                    ops.gpu_qgemm_q4_k_bf16_into(lw["gate"], xb, y, m, n, k)
+            us = timer.us(body, reps=5) / LAYERS
+            flops = 2.0 * m * n * k
+            out.append({"m": m, "n": n, "k": k, "us_per_launch": us, "flops": flops, "TFLOPs": flops / us / 1e6,
+                        "bound": "tensor", "peak": tensor_peak, "frac": flops / us / 1e6 / tensor_peak})
+    return out
 
 
 def run_decode(world, rank, dev, quick):
@@ -473,16 +605,94 @@ def run_decode(world, rank, dev, quick):
     return out
 
 
+# ------------------------------------------------------------------------- profiler cases
+def run_case(spec):
+    """One small case for a profiler capture (see the module docstring); weights rotate over about 300 MB."""
+    import torch
+    from nates_recipe_rs_b200 import _lib, quant_ops as ops
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    L = _lib.lib()
+    for kv in os.environ.get("QMM_TUNE", "").split(","):   # tuning overrides, e.g. QMM_TUNE=jobs_warps=12
+        if kv:
+            key, val = kv.split("=")
+            _lib.check(L.qmm_tune(key.encode(), int(val)), f"qmm_tune({key})")
+    parts = spec.split(":")
+    kind = parts[0]
+    names = {"q8_0": _lib.Q8_0, "q4_k": _lib.Q4_K, "q6_k": _lib.Q6_K}
+    if kind in ("matvec", "gemm"):
+        if kind == "matvec":
+            qt, n, k, m = names[parts[1]], int(parts[2]), int(parts[3]), int(parts[4])
+            reps = int(parts[5]) if len(parts) > 5 else 4
+        else:
+            qt, n, k, m = _lib.Q4_K, int(parts[1]), int(parts[2]), int(parts[3])
+            reps = int(parts[4]) if len(parts) > 4 else 4
+        rb = ops.row_bytes(qt, k)
+        ncopy = max(2, int(300e6 // (n * rb)) + 1)
+        ws = [gen_weights(torch, ops, dev, n, k, i, qt) for i in range(ncopy)]
+        if kind == "gemm":
+            xb = torch.randn(m, k, device=dev).to(torch.bfloat16)
+            y = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+            torch.cuda.synchronize()
+            for i in range(reps):
+                ops.gpu_qgemm_q4_k_bf16_into(ws[i % ncopy], xb, y, m, n, k)
+        else:
+            xq = ops.gpu_quantize_q8_1(torch.randn(m, k, device=dev))
+            y = torch.empty(m, n, device=dev)
+            torch.cuda.synchronize()
+            for i in range(reps):
+                ops.gpu_qmatvec_into(qt, ws[i % ncopy], xq, y, m, n, k)
+    elif kind == "jobs":
+        which = parts[1] if len(parts) > 1 else "q4k"
+        reps = int(parts[2]) if len(parts) > 2 else 3
+        xq = ops.gpu_quantize_q8_1(torch.randn(1, HID, device=dev))
+        hq = ops.gpu_quantize_q8_1(torch.randn(1, FFN, device=dev))
+        yg, yd = torch.empty(2, LAYERS, FFN, device=dev), torch.empty(2, LAYERS, HID, device=dev)
+        jobs = ops.MatvecJobs()
+        for li in range(LAYERS):
+            jobs.add(_lib.Q4_K, gen_weights(torch, ops, dev, FFN, HID, 4 * li, _lib.Q4_K), xq, yg[0, li], FFN, HID)
+            jobs.add(_lib.Q4_K, gen_weights(torch, ops, dev, FFN, HID, 4 * li + 1, _lib.Q4_K), xq, yg[1, li], FFN, HID)
+            jobs.add(_lib.Q4_K, gen_weights(torch, ops, dev, HID, FFN, 4 * li + 2, _lib.Q4_K), hq, yd[0, li], HID, FFN)
+            if which == "ffn":
+                jobs.add(_lib.Q6_K, gen_weights(torch, ops, dev, HID, FFN, 4 * li + 3, _lib.Q6_K), hq, yd[1, li], HID, FFN)
+        torch.cuda.synchronize()
+        for _ in range(reps):
+            ops.gpu_qmatvec_batch_into(jobs, 1)
+    elif kind == "decode":
+        from nates_recipe_rs_b200 import decoder as dec
+        name, batch = parts[1], int(parts[2])
+        steps = int(parts[3]) if len(parts) > 3 else 3
+        cfg = (dec.config_8b if name == "8b" else dec.config_70b)(max_batch=batch)
+        if len(parts) > 4:
+            cfg.n_layers = int(parts[4])
+        d = dec.Decoder(cfg)
+        d.fill_cache(3)
+        d.tokens.fill_(11)
+        pos0 = cfg.ctx_len - steps - 1
+        for i in range(steps):   # eager launches, so that a launch list attributes the step to its kernels
+            d.step(batch, pos0 + i)
+            d.tokens.copy_(d.next_tokens)
+    else:
+        raise SystemExit(f"unknown --case {spec!r}")
+    torch.cuda.synchronize()
+    ops.check_launch()
+    print("case done:", spec)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--passes", type=int, default=50, help="graph replays (passes over all layer sets) per step")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the decode tok/s section")
     ap.add_argument("--quick-decode", action="store_true", help="decode section: 8B batch 1 only")
+    ap.add_argument("--case", default=None, help="run one small case for a profiler capture and exit")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args.case)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

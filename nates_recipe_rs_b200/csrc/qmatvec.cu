@@ -223,26 +223,18 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
     for (int it = 0; it < n_it; ++it) {
         const int nr = min(p.rows_stage, n_rows - it * p.rows_stage);
         const int nb = (nr + RB - 1) / RB;
-        // Every warp passes every stage but only waits for the data of stages it has work in, so
-        // it can run ahead of the copies.  Before touching this use of the slot it waits until all
-        // warps have released the previous use: that keeps its arrival in the right phase, makes
-        // the parity test on the data barrier below unambiguous (the barrier cannot still be one
-        // phase behind), and means no copy can still be in flight when the CTA exits.
-        if (it >= p.nst && !mbar_wait_bounded(smem_u32(&hdr->empty[slot]), phase ^ 1, cta_abort)) {
+        // Every warp waits for every stage's data, with or without work in it.  The copy of this use of the
+        // slot is only issued after all warps released the previous use, so once the data is seen this
+        // warp's arrival below lands in the right phase, the parity test cannot be a phase off, and no
+        // copy can still be in flight when the CTA exits.
+        if (!mbar_wait_bounded(smem_u32(&hdr->full[slot]), phase, cta_abort)) {
             if (lane == 0 && !*cta_abort) {
-                atomicExch(&g_device_status, DEV_TIMEOUT_EMPTY);
+                atomicExch(&g_device_status, DEV_TIMEOUT_FULL);
                 *cta_abort = 1;
             }
             return;
         }
         if (next_b < nb) {
-            if (!mbar_wait_bounded(smem_u32(&hdr->full[slot]), phase, cta_abort)) {
-                if (lane == 0 && !*cta_abort) {
-                    atomicExch(&g_device_status, DEV_TIMEOUT_FULL);
-                    *cta_abort = 1;
-                }
-                return;
-            }
             if (p.trace && threadIdx.x == 0 && it == 0) p.trace[blockIdx.x * 4 + 2] = globaltimer_ns();
             const uint32_t base = ring_s + (uint32_t)slot * p.slot_bytes + head;
             float* ps = partial + (uint32_t)pslot * p.pstage + my_ps;

@@ -119,15 +119,15 @@ __device__ __noinline__ ConsumerState consume_job(const JobArgs a, JobsSmemHeade
     const int unit = have ? u_raw : 0;  // lanes past the end of the row re-read unit 0 against zero activations
     const uint32_t unit_off = F::unit_offset(unit);
     typename F::XRegs x[M];
-    if (active) {
-        if (!mbar_wait_bounded(smem_u32(&hdr->xfull), a.x_parity, cta_abort)) {
-            if (lane == 0 && !*cta_abort) {
-                atomicExch(&g_device_status, DEV_TIMEOUT_FULL);
-                *cta_abort = 1;
-            }
-            st.ok = 0;
-            return st;
+    // Every warp waits for every job's activations, also one without a share in this job: a warp that
+    // skipped a phase of this barrier could not tell the next phase from the one before it.
+    if (!mbar_wait_bounded(smem_u32(&hdr->xfull), a.x_parity, cta_abort)) {
+        if (lane == 0 && !*cta_abort) {
+            atomicExch(&g_device_status, DEV_TIMEOUT_FULL);
+            *cta_abort = 1;
         }
+        st.ok = 0;
+        return st;
     }
 #pragma unroll
     for (int mi = 0; mi < M; ++mi) {
@@ -386,7 +386,7 @@ __global__ void __launch_bounds__((JOBS_MAX_WARPS + 1) * 32, 1) qmatvec_jobs_ker
 // ------------------------------------------------------------------- host side
 int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, cudaStream_t stream);
 
-static int g_jobs_warps = 16;
+static int g_jobs_warps = 14;
 static int g_jobs_ring = 150 * 1024;
 static int g_jobs_stage = 48 * 1024;
 static int g_jobs_rotate = 1;

@@ -56,6 +56,7 @@ def lib():
         L.qo_f32_to_bf16.argtypes = [f32]
         L.qo_f32_to_bf16.restype = C.c_uint16
         L.qo_num_threads.restype = i32
+        L.qo_set_num_threads.argtypes = [i32]
         _lib = L
     return _lib
 
@@ -76,6 +77,11 @@ def row_bytes(qtype, k):
 
 def num_threads():
     return lib().qo_num_threads()
+
+
+def set_num_threads(n):
+    """OpenMP threads of the C oracle (overrides an inherited OMP_NUM_THREADS)."""
+    lib().qo_set_num_threads(int(n))
 
 
 def fill_normal(n, seed, sigma, first_index=0):

@@ -14,6 +14,12 @@
 #include <omp.h>
 #endif
 
+/* The benchmark's CPU legs set the thread count themselves: a launcher may have exported
+ * OMP_NUM_THREADS=1 for its children. */
+void qo_set_num_threads(int n) {
+    if (n > 0) omp_set_num_threads(n);
+}
+
 int qo_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

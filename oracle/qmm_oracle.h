@@ -96,6 +96,7 @@ void qo_attn_decode(const float* q, const uint16_t* kc, const uint16_t* vc, floa
                     long nqh, long nkv, long hd, long len);
 
 int qo_num_threads(void);
+void qo_set_num_threads(int n);
 
 #ifdef __cplusplus
 }

@@ -80,6 +80,22 @@ def test_job_list_matches_oracle(ops, specs, m):
         assert_close(g, w, f"job {i} {specs[i]}")
 
 
+@pytest.mark.parametrize("warps", [8, 12, 16, 21, 24])
+def test_job_list_other_warp_counts(ops, warps):
+    """The split of a CTA's warps into K slices and row groups differs per job and with the warp count
+    (tunable "jobs_warps"); warps without a share in a job still take part in every hand-over."""
+    from nates_recipe_rs_b200._lib import check, lib
+    check(lib().qmm_tune(b"jobs_warps", warps), "qmm_tune")
+    try:
+        for specs in (LISTS[4], LISTS[6], LISTS[7]):
+            for rep in range(3):   # timing-dependent faults would differ between repetitions
+                got, want = run_list(ops, specs, 1, seed=11 + rep)
+                for i, (g, w) in enumerate(zip(got, want)):
+                    assert_close(g, w, f"warps {warps} rep {rep} job {i} {specs[i]}")
+    finally:
+        check(lib().qmm_tune(b"jobs_warps", 14), "qmm_tune")
+
+
 def test_job_list_longer_than_one_launch_and_rerun_bit_identical(ops):
     specs = [((Q4, Q6, Q8)[i % 3], 64 + i, 512) for i in range(45)]   # more than the 40 jobs one launch takes
     a, want = run_list(ops, specs, 1, seed=5)
