@@ -188,6 +188,40 @@ int launch_attn_decode(const float* qkv, const void* kcache, const void* vcache,
 int launch_attn_decode_static(const float* qkv, const void* kcache, const void* vcache, float* out_f32, void* out_q8, int batch,
                               int n_q_heads, int n_kv_heads, int head_dim, int len, int ctx_cap, void* stream);
 
+/* ---- the small per-layer operators of the decode stack, fp32 with Q8_1 outputs so that the next
+ * projection finds its activations ready.  act: 0 = tanh-GELU, 1 = SiLU.
+ *
+ * launch_add_rmsnorm_q8_1: counterpart of launch_normx_rmsnorm (gpu-core/src/kernels/normx.hip:135-159;
+ *   Rust gpu_rmsnorm_f64_into, gpu-core/src/infer_ops.rs:117-139) fused with the residual add before it
+ *   (add_kernel, gpu-core/src/kernels/elementwise.hip:13) and the quantization after it:
+ *   x(rows,cols) += add (when add != NULL; x is updated in place), then
+ *   xq = Q8_1( x / sqrt(mean(x^2) + eps) * gamma ); gamma == NULL is the scale-less variant; out_f32
+ *   (optional) receives the normalised values before quantization.  cols a multiple of 32, at most 8192.
+ * launch_rope_kv_append: counterpart of launch_rope_partial with rotary_dim == head_dim
+ *   (gpu-core/src/kernels/f64_infer.hip:107-132; Rust gpu_rope_partial, infer_ops.rs:61-83) for one new
+ *   token per sequence at position pos: rotates the q heads of qkv (batch, (n_q + 2 n_kv) * head_dim) in
+ *   place (NeoX rotate-half) and appends the rotated k and the v heads to the fp16 caches
+ *   (batch, ctx_cap, n_kv_heads, head_dim) at pos.
+ * launch_glu_act_q8_1: counterpart of launch_glu_gelu (gpu-core/src/kernels/f64_infer.hip:150-166; Rust
+ *   gpu_glu_gelu_into, infer_ops.rs:206-222): gate_up (rows, 2*half) = [gate | up] per row ->
+ *   xq = Q8_1( act(gate) * up ) (rows, half); out_f32 optional.  half a multiple of 32.
+ * launch_embed_rows: x[b] = decoded row tokens[b] of a packed (vocab, hidden) table (the upstream example
+ *   gathers its bf16 embedding rows on the host: examples/gemma4.rs:951-958); tokens are clamped to the table.
+ * launch_argmax_rows: index (lowest on ties) and value of the largest logit of every row (the upstream
+ *   example picks the next token on the host: examples/gemma4.rs:1021-1046; greedy here).  scratch:
+ *   qmm_argmax_scratch_bytes(batch) bytes of caller-owned device memory, 8-byte aligned.
+ * launch_scale_f32: x *= scalar, counterpart of launch_scale_f64 (gpu-core/src/kernels/gemm_f64.hip:57-65;
+ *   Rust gpu_scale_f64_inplace, infer_ops.rs:242-248). */
+int launch_add_rmsnorm_q8_1(float* x, const float* add, const float* gamma, void* xq, float* out_f32, int rows, int cols, float eps,
+                            void* stream);
+int launch_rope_kv_append(float* qkv, void* kcache, void* vcache, int batch, int n_q_heads, int n_kv_heads, int head_dim, int pos,
+                          int ctx_cap, float theta, void* stream);
+int launch_glu_act_q8_1(const float* gate_up, void* xq, float* out_f32, int rows, int half, int act, void* stream);
+int launch_embed_rows(int type, const void* table, const int* tokens, float* x, int batch, int hidden, int vocab, void* stream);
+long qmm_argmax_scratch_bytes(int batch);
+int launch_argmax_rows(const float* logits, void* scratch, int* out_index, float* out_value, int batch, int vocab, void* stream);
+int launch_scale_f32(float* x, float scalar, long n, void* stream);
+
 /* ---- per-block integer dot sums (parity instrumentation; same device code as
  * the matvec).  One Q8_1 row xq (k); out int32 (n, k/32) for Q8_0 and Q4_K,
  * (n, k/16) for Q6_K. */

@@ -49,6 +49,13 @@ SIGNATURES = {
     "launch_attn_decode": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
     "launch_attn_decode_static": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
     "launch_qblock_dots": (i32, [i32, vp, vp, vp, i32, i32, vp]),
+    "launch_add_rmsnorm_q8_1": (i32, [vp, vp, vp, vp, vp, i32, i32, C.c_float, vp]),
+    "launch_rope_kv_append": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, vp]),
+    "launch_glu_act_q8_1": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "launch_embed_rows": (i32, [i32, vp, vp, vp, i32, i32, i32, vp]),
+    "qmm_argmax_scratch_bytes": (i64, [i32]),
+    "launch_argmax_rows": (i32, [vp, vp, vp, vp, i32, i32, vp]),
+    "launch_scale_f32": (i32, [vp, C.c_float, i64, vp]),
 }
 
 _lib = None

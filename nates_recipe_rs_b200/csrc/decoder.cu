@@ -327,7 +327,7 @@ static int add_norm(Decoder* d, int which, const float* gamma, int batch, cudaSt
         }
     }
     return launch_pdl(add_rmsnorm_q8_kernel, dim3(batch), dim3(norm_threads(d->c.hidden)), 0, s, d->x, parts, n_parts, (long)d->c.hidden,
-                      gamma, d->xq_h, d->c.hidden, d->c.rms_eps, sync);
+                      gamma, d->xq_h, d->c.hidden, d->c.rms_eps, sync, (float*)nullptr);
 }
 
 static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tokens, float* logits_out, float* best_out, cudaStream_t s) {
@@ -386,7 +386,7 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
         TRY(qmatvec_launch_strided(c.type_attn_o, L.wo, d->xq_attn, d->part[0], H, batch, H, ao, s));
         TRY(add_norm(d, 0, L.ffn_norm, batch, s));
         TRY(qmatvec_launch_strided(c.type_ffn_gate_up, L.wgu, d->xq_h, d->gu, 2 * d->ffn_l, batch, 2 * d->ffn_l, H, s));
-        TRY(launch_pdl(act_mul_q8_kernel, dim3((d->ffn_l / 32 + 3) / 4, batch), dim3(128), 0, s, (const float*)d->gu, d->xq_ffn, d->ffn_l, c.act));
+        TRY(launch_pdl(act_mul_q8_kernel, dim3((d->ffn_l / 32 + 3) / 4, batch), dim3(128), 0, s, (const float*)d->gu, d->xq_ffn, d->ffn_l, c.act, (float*)nullptr));
         TRY(qmatvec_launch_strided(c.type_ffn_down, L.wdown, d->xq_ffn, d->part[1], H, batch, H, d->ffn_l, s));
     }
     TRY(add_norm(d, 1, d->final_norm, batch, s));

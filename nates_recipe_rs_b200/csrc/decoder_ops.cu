@@ -106,7 +106,8 @@ struct TpSync {
 };
 constexpr int QMM_TP_SLOTS = 8;
 __global__ void __launch_bounds__(1024) add_rmsnorm_q8_kernel(float* __restrict__ x, const PartPtrs parts, int n_parts, long part_stride,
-                                      const float* __restrict__ gamma, uint8_t* __restrict__ xq, int hidden, float eps, TpSync tp) {
+                                      const float* __restrict__ gamma, uint8_t* __restrict__ xq, int hidden, float eps, TpSync tp,
+                                      float* __restrict__ out_f32) {
     __shared__ float red[32];
     __shared__ int peers_ok;
     pdl_release_dependents();
@@ -115,7 +116,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_q8_kernel(float* __restrict_
 #pragma unroll
     for (int i = 0; i < NORM_MAX_PER_THREAD; ++i) {
         const int e = i * blockDim.x + threadIdx.x;
-        gm[i] = e < hidden ? gamma[e] : 0.f;
+        gm[i] = e < hidden ? (gamma ? gamma[e] : 1.f) : 0.f;  // no gamma: the scale-less variant
     }
     pdl_wait_prior_grids();
     const int b = blockIdx.x, lane = threadIdx.x & 31;
@@ -165,7 +166,11 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_q8_kernel(float* __restrict_
 #pragma unroll
     for (int i = 0; i < NORM_MAX_PER_THREAD; ++i) {
         const int e = i * blockDim.x + threadIdx.x;  // a warp covers 32 consecutive elements = one block
-        if (e < hidden) warp_store_q8_1(v[i] * inv * gm[i], qrow + (size_t)(e >> 5) * Q8_1_BYTES, lane);
+        if (e < hidden) {
+            const float nv = v[i] * inv * gm[i];
+            if (out_f32) out_f32[(size_t)b * hidden + e] = nv;
+            warp_store_q8_1(nv, qrow + (size_t)(e >> 5) * Q8_1_BYTES, lane);
+        }
     }
 }
 
@@ -589,7 +594,7 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
 }
 
 // gated activation on the fused [gate | up] projection output + Q8_1: act(gate) * up -> xq (ffn per row)
-__global__ void act_mul_q8_kernel(const float* __restrict__ gate_up, uint8_t* __restrict__ xq, int ffn, int act) {
+__global__ void act_mul_q8_kernel(const float* __restrict__ gate_up, uint8_t* __restrict__ xq, int ffn, int act, float* __restrict__ out_f32) {
     pdl_release_dependents();
     pdl_wait_prior_grids();
     const int b = blockIdx.y, lane = threadIdx.x & 31;
@@ -598,6 +603,7 @@ __global__ void act_mul_q8_kernel(const float* __restrict__ gate_up, uint8_t* __
     const float* row = gate_up + (size_t)b * 2 * ffn;
     const float g = row[blk * 32 + lane], u = row[ffn + blk * 32 + lane];
     const float a = act == 0 ? gelu_tanh_f(g) : g / (1.0f + __expf(-g));
+    if (out_f32) out_f32[(size_t)b * ffn + blk * 32 + lane] = a * u;
     warp_store_q8_1(a * u, xq + ((size_t)b * (ffn / 32) + blk) * Q8_1_BYTES, lane);
 }
 

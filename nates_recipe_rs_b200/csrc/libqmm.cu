@@ -8,4 +8,5 @@
 #include "qmatvec_mma.cu"
 #include "decoder_ops.cu"
 #include "attn_entry.cu"
+#include "ops_entry.cu"
 #include "decoder.cu"

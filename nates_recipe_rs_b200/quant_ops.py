@@ -26,6 +26,8 @@ __all__ = [
     "MatvecJobs", "gpu_qmatvec_batch_into",
     "gpu_qgemm_q4_k_bf16_into", "gpu_qgemm_q4_k_bf16",
     "gpu_qlinear",
+    "gpu_rmsnorm_q8_1_into", "gpu_rope_kv_append", "gpu_glu_act_q8_1_into", "gpu_embed_rows_into", "gpu_argmax_rows",
+    "gpu_scale_f32_inplace",
 ]
 
 
@@ -192,3 +194,56 @@ def gpu_qlinear(qtype, w, x, n, k):
     x = x.contiguous()
     m = 1 if x.dim() == 1 else x.shape[0]
     return gpu_qmatvec(qtype, w, gpu_quantize_q8_1(x.reshape(m, k)), m, n, k)
+
+
+# ---- the small per-layer operators -----------------------------------------------------
+def _opt(t):
+    return _ptr(t) if t is not None else None
+
+
+def gpu_rmsnorm_q8_1_into(x, gamma, xq, rows, cols, eps, add=None, out_f32=None):
+    """x (rows, cols) f32 [+= add, in place] -> xq = Q8_1(rmsnorm(x) * gamma); the upstream's
+    gpu_rmsnorm_f64_into (gpu-core/src/infer_ops.rs:117-139) fused with the residual add before it and
+    the activation quantization after it.  gamma None: the scale-less variant; out_f32 (optional)
+    receives the normalised values."""
+    _need(x, rows * cols * 4, "x")
+    _need(xq, rows * row_bytes(Q8_1, cols), "xq")
+    check(lib().launch_add_rmsnorm_q8_1(_ptr(x), _opt(add), _opt(gamma), _ptr(xq), _opt(out_f32), rows, cols, eps, _stream()),
+          "launch_add_rmsnorm_q8_1")
+
+
+def gpu_rope_kv_append(qkv, kcache, vcache, batch, n_q_heads, n_kv_heads, head_dim, pos, ctx_cap, theta):
+    """NeoX rotary embedding of the q heads in place and append of the rotated k and the v heads to the fp16
+    caches at `pos`: the upstream's gpu_rope_partial (gpu-core/src/infer_ops.rs:61-83) with rotary_dim ==
+    head_dim, for one new token per sequence."""
+    check(lib().launch_rope_kv_append(_ptr(qkv), _ptr(kcache), _ptr(vcache), batch, n_q_heads, n_kv_heads, head_dim, pos, ctx_cap, theta,
+                                      _stream()), "launch_rope_kv_append")
+
+
+def gpu_glu_act_q8_1_into(gate_up, xq, rows, half, act, out_f32=None):
+    """gate_up (rows, 2*half) = [gate | up] -> xq = Q8_1(act(gate) * up): the upstream's gpu_glu_gelu_into
+    (gpu-core/src/infer_ops.rs:206-222) with the quantization fused; act 0 = tanh-GELU, 1 = SiLU."""
+    _need(gate_up, rows * 2 * half * 4, "gate_up")
+    _need(xq, rows * row_bytes(Q8_1, half), "xq")
+    check(lib().launch_glu_act_q8_1(_ptr(gate_up), _ptr(xq), _opt(out_f32), rows, half, act, _stream()), "launch_glu_act_q8_1")
+
+
+def gpu_embed_rows_into(qtype, table, tokens, x, batch, hidden, vocab):
+    """x[b] = decoded row tokens[b] of the packed (vocab, hidden) table."""
+    _need(x, batch * hidden * 4, "x")
+    check(lib().launch_embed_rows(qtype, _ptr(table), _ptr(tokens), _ptr(x), batch, hidden, vocab, _stream()), "launch_embed_rows")
+
+
+def gpu_argmax_rows(logits):
+    """(index int32, value f32) of the largest entry of every row; the lowest index wins ties.  Allocates."""
+    batch, vocab = logits.shape
+    scratch = torch.empty(lib().qmm_argmax_scratch_bytes(batch), dtype=torch.uint8, device=logits.device)
+    idx = torch.empty(batch, dtype=torch.int32, device=logits.device)
+    val = torch.empty(batch, dtype=torch.float32, device=logits.device)
+    check(lib().launch_argmax_rows(_ptr(logits), _ptr(scratch), _ptr(idx), _ptr(val), batch, vocab, _stream()), "launch_argmax_rows")
+    return idx, val
+
+
+def gpu_scale_f32_inplace(x, scalar):
+    """x *= scalar: the upstream's gpu_scale_f64_inplace (gpu-core/src/infer_ops.rs:242-248)."""
+    check(lib().launch_scale_f32(_ptr(x), scalar, x.numel(), _stream()), "launch_scale_f32")
