@@ -71,22 +71,18 @@ long qmm_row_bytes(int type, long k);
  * activations or outputs.  Returns the previous setting. */
 int qmm_set_overlap(int on);
 
-/* Tuning hook for the matvec launcher (benchmark sweeps; the defaults are the tuned
- * values): "stage_bytes" (1024..49152), "ring_bytes" (8192..194560),
- * "consumer_warps" (1..24), "q4k_unit" (0 = automatic, 1, 2, 4: 32-byte groups of a
- * Q4_K super-block per lane), "rb_max" (1, 2, 4: rows reduced together per warp), "probe" (0/1: 1 = the
- * matvec streams and synchronises but skips its arithmetic), "gemm_probe" (0/1/2: the GEMM skips its unpack
- * arithmetic / its tensor-core instructions), "mma_min_m" (0..16: fewest activation rows that take the
- * tensor-core matvec where type and shape allow it; 0 = never; default 3), "ctas_per_sm" (1, 2: persistent
- * CTAs per SM of the dp4a matvec; 2 needs "ring_bytes" and "consumer_warps" small enough to fit twice),
- * "attn_tc_min_batch" (fewest sequences from which the decode attention runs on the f16 tensor cores;
- * 0 = never; default 4).
- * Probe modes produce wrong results by design.  Not thread-safe against concurrent launches. */
+/* Tuning hook for the launchers (benchmark sweeps; the defaults are the tuned values):
+ * "stage_bytes" (1024..49152), "ring_bytes" (8192..194560), "consumer_warps" (1..24), "q4k_unit" (0 = automatic,
+ * 1, 2, 4: 32-byte groups of a Q4_K super-block per lane), "rb_max" (1, 2, 4: rows reduced together per warp),
+ * "ctas_per_sm" (1, 2: persistent CTAs per SM of the single-matrix dp4a matvec; 2 needs "ring_bytes" and
+ * "consumer_warps" small enough to fit twice), "mma_min_m" (0..16: fewest activation rows that take the
+ * tensor-core matvec where type and shape allow it; 0 = never; default 3), "attn_tc_min_batch" (fewest
+ * sequences from which the decode attention runs on the f16 tensor cores; 0 = never; default 4), and for the
+ * job-list matvec "jobs_warps" (1..24), "jobs_ring_bytes", "jobs_stage_bytes", "jobs_rotate" (0/1).
+ * Every setting computes the same results.  Not thread-safe against concurrent launches.
+ * (A library built with -DQMM_TUNING also has instrumentation that is not part of this interface:
+ * stream-only probe modes and a per-CTA time-stamp trace, declared in csrc/qmm_tuning.h.) */
 int qmm_tune(const char* key, int value);
-/* Tuning aid: while buf is non-NULL, matvec launch number i (counted from this call) stores four
- * global-timer stamps per CTA (start, dependency released, first stage landed, end) as 64-bit
- * words at buf + i*stride_words.  buf = NULL switches it off. */
-int qmm_trace(void* buf, int stride_words);
 
 /* ---- activations -> Q8_1.  No upstream counterpart (its quantizers are affine
  * per-tensor: gpu-core/src/kernels/quantizedx.hip:12-33); rounding follows its

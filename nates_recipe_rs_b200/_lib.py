@@ -27,7 +27,6 @@ SIGNATURES = {
     "qmm_row_bytes": (i64, [i32, i64]),
     "qmm_set_overlap": (i32, [i32]),
     "qmm_tune": (i32, [C.c_char_p, i32]),
-    "qmm_trace": (i32, [vp, i32]),
     "launch_quantize_q8_1": (i32, [vp, vp, i32, i32, vp]),
     "launch_quantize_q8_0": (i32, [vp, vp, i64, i32, vp]),
     "launch_quantize_q4_k": (i32, [vp, vp, i64, i32, vp]),

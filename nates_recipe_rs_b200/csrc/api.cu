@@ -1,6 +1,9 @@
 // extern "C" surface of libqmm (declared in include/qmm.h) and the few pieces of
 // host state shared by the launchers.
 #include "qmm_common.cuh"
+#ifdef QMM_TUNING
+#include "qmm_tuning.h"
+#endif
 
 namespace qmm {
 
@@ -92,7 +95,9 @@ int qmm_tune(const char* key, int value) {
     const int st = matvec_tune(key, value);
     return st == QMM_ERR_UNSUPPORTED ? jobs_tune(key, value) : st;
 }
+#ifdef QMM_TUNING
 int qmm_trace(void* buf, int stride_words) { matvec_set_trace(static_cast<unsigned long long*>(buf), stride_words); return QMM_OK; }
+#endif
 
 int launch_quantize_q8_1(const float* x, void* xq, int m, int k, void* stream) {
     return quantize_q8_1_launch(x, xq, m, k, as_stream(stream));

@@ -307,13 +307,15 @@ int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y
                        unsigned long long* trace, cudaStream_t stream);
 int matvec_tune(const char* key, int value) {
     const std::string k(key ? key : "");
+#ifdef QMM_TUNING  // wrong results by design: development builds only
     if (k == "gemm_probe" && value >= 0 && value <= 2) return gemm_set_probe(value), QMM_OK;
+    if (k == "probe" && value >= 0 && value <= 1) return g_probe = value, QMM_OK;
+#endif
     if (k == "stage_bytes" && value >= 1024 && value <= STAGE_MAX_BYTES) return g_stage_target = value, QMM_OK;
     if (k == "ring_bytes" && value >= 8 * 1024 && value <= 190 * 1024) return g_ring_budget = value, QMM_OK;
     if (k == "consumer_warps" && value >= 1 && value <= MAX_CONSUMER_WARPS) return g_consumer_warps = value, g_consumer_warps_set = true, QMM_OK;
     if (k == "q4k_unit" && (value == 0 || value == 1 || value == 2 || value == 4)) return g_q4k_unit = value, QMM_OK;
     if (k == "rb_max" && (value == 1 || value == 2 || value == 4)) return g_rb_max = value, QMM_OK;
-    if (k == "probe" && value >= 0 && value <= 1) return g_probe = value, QMM_OK;
     if (k == "ctas_per_sm" && value >= 1 && value <= 2) return g_ctas_per_sm = value, QMM_OK;
     if (k == "mma_min_m") return mma_set_min_m(value);
     if (k == "attn_tc_min_batch") return attn_set_tc_min_batch(value);
