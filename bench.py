@@ -280,23 +280,36 @@ def run_ours(args):
     y_up = torch.empty(LAYERS, FFN, device=dev)
     y_down = torch.empty(LAYERS, 2, HID, device=dev)   # [layer][Q4_K, Q6_K]: the partial sums of this rank when N > 1
 
-    ffn_jobs = ops.MatvecJobs()
+    ffn_jobs = ops.MatvecJobs()    # the pass; N > 1: the down projections are summed over the ranks inside the launch
+    nccl_jobs = ops.MatvecJobs()   # N > 1, second number: the same pass with the sum done by one NCCL allreduce
     q4_jobs = ops.MatvecJobs()
     for li, lw in enumerate(layers):
-        for jobs in (ffn_jobs, q4_jobs):
+        for jobs in (ffn_jobs, nccl_jobs, q4_jobs):
+            summed = world > 1 and jobs is ffn_jobs
             jobs.add(Q4_K, lw["gate"], xq[li], y_gate[li], FFN, HID)
             jobs.add(Q4_K, lw["up"], xq[li], y_up[li], FFN, HID)
-            jobs.add(Q4_K, lw["down4"], hq[li], y_down[li, 0], HID, FFN)
-        ffn_jobs.add(Q6_K, lw["down6"], hq[li], y_down[li, 1], HID, FFN)
-    launches_per_pass = 2 * LAYERS + 1
+            jobs.add(Q4_K, lw["down4"], hq[li], y_down[li, 0], HID, FFN, tp_sum=summed)
+        ffn_jobs.add(Q6_K, lw["down6"], hq[li], y_down[li, 1], HID, FFN, tp_sum=world > 1)
+        nccl_jobs.add(Q6_K, lw["down6"], hq[li], y_down[li, 1], HID, FFN)
+    comm = ops.TpComm(2 * LAYERS * HID) if world > 1 else None
+    launches_per_pass = 2 * LAYERS + (2 if world > 1 else 1)
 
-    def pass_body():
+    def quantize_all():
         for li in range(LAYERS):
             ops.gpu_quantize_q8_1_into(x, xq[li], 1, HID)
             ops.gpu_quantize_q8_1_into(h, hq[li], 1, FFN)
-        ops.gpu_qmatvec_batch_into(ffn_jobs, 1)
-        if world > 1:
-            dist.all_reduce(y_down)   # the 2*LAYERS partial down outputs of the pass in one exchange
+
+    def pass_body():
+        quantize_all()
+        if world > 1:   # partial down outputs pushed into every rank's exchange area by the matvec kernel, then summed
+            ops.gpu_qmatvec_batch_tp_into(comm, ffn_jobs, 1)
+        else:
+            ops.gpu_qmatvec_batch_into(ffn_jobs, 1)
+
+    def nccl_pass_body():
+        quantize_all()
+        ops.gpu_qmatvec_batch_into(nccl_jobs, 1)
+        dist.all_reduce(y_down)   # the 2*LAYERS partial down outputs of the pass in one allreduce
 
     stream = torch.cuda.Stream(device=dev)
     timer = Timer(torch, stream)
@@ -348,7 +361,20 @@ def run_ours(args):
         # ---- dominant kernel alone: one job-list launch over the 3*LAYERS Q4_K projections of the pass
         note("timed steps done; Q4_K job list alone")
         q4_list_us = timer.us(lambda: ops.gpu_qmatvec_batch_into(q4_jobs, 1), reps=max(args.steps, 20))
-        ffn_list_us = timer.us(lambda: ops.gpu_qmatvec_batch_into(ffn_jobs, 1), reps=max(args.steps, 20))
+        ffn_list_us = timer.us(lambda: ops.gpu_qmatvec_batch_into(nccl_jobs, 1), reps=max(args.steps, 20))
+        nccl_pass_us = None
+        if world > 1:
+            # check the fused sum against NCCL on the same partial outputs, then time the NCCL form of the pass
+            pass_body()
+            fused = y_down.clone()
+            nccl_pass_body()
+            stream.synchronize()
+            sum_diff = float((fused - y_down).abs().max() / y_down.abs().max())
+            try:
+                barrier()
+                nccl_pass_us = timer.us(nccl_pass_body, reps=50)
+            except Exception:
+                nccl_pass_us = None
 
         # ---- end to end through the C ABI with host buffers: activations come from pinned host
         # memory and the projections go back to it every pass; the weights stay resident in HBM
@@ -373,10 +399,10 @@ def run_ours(args):
         e2e_s = time.perf_counter() - t0
         clocks = sampler.stop() if sampler else None
 
-    t = torch.tensor([elapsed_ms, e2e_s * 1e3, q4_list_us, ffn_list_us], device=dev, dtype=torch.float64)
+    t = torch.tensor([elapsed_ms, e2e_s * 1e3, q4_list_us, ffn_list_us, nccl_pass_us or 0.0], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms, q4_list_us, ffn_list_us = [float(v) for v in t.tolist()]
+    elapsed_ms, e2e_ms, q4_list_us, ffn_list_us, nccl_pass_us = [float(v) for v in t.tolist()]
     ops.check_launch()  # raises if any kernel abandoned a bounded wait
 
     pass_bytes = total_layer * LAYERS * world
@@ -411,7 +437,8 @@ def run_ours(args):
                        "launch": ("cuda graph replay" if use_graph else "eager") +
                                  f": per pass {2 * LAYERS} activation-quantize launches + 1 job-list launch of {4 * LAYERS} projections",
                        "parallelism": "single GPU" if world == 1 else
-                                      f"tp{world}: gate/up split by rows, down by columns, one NCCL allreduce of the pass's partial down outputs"},
+                                      f"tp{world}: gate/up split by rows, down by columns; the matvec kernel stores the partial down outputs "
+                                      f"into every rank's exchange area (NVLink peer stores) and one small kernel per pass adds them"},
             "roofline": {"bound": "hbm", "kernel": f"qmatvec_jobs_kernel<1>: one launch = the {3 * LAYERS} Q4_K projections (gate, up, down) of a pass",
                          "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src,
                          "us_per_launch": q4_list_us, "us_per_projection": q4_list_us / (3 * LAYERS),
@@ -431,6 +458,9 @@ def run_ours(args):
             out["decode"] = decode
         if tp_par is not None:
             out["tp_parity"] = tp_par
+            out["tp_exchange"] = {"fused_vs_nccl_max_rel_diff": sum_diff, "fused_pass_us": elapsed_ms * 1e3 / n_pass,
+                                  "nccl_allreduce_pass_us": nccl_pass_us or None,
+                                  "note": "the same pass with the sum of the partial down outputs done by one NCCL allreduce"}
         print(json.dumps(out), flush=True)
     if world > 1:
         # The NCCL communicator is referenced by the captured graphs: release them first, and do not let
@@ -439,6 +469,7 @@ def run_ours(args):
         graph = None
         torch.cuda.synchronize()
         dist.barrier()
+        comm.close()
         threading.Timer(20.0, lambda: os._exit(0)).start()
         dist.destroy_process_group()
         os._exit(0)

@@ -144,8 +144,36 @@ typedef struct {
     long y_stride;
     const int* select;
     long select_stride_bytes;
+    int tp_sum;               /* launch_qmatvec_batch_tp only: sum this job's outputs over the ranks */
 } qmm_matvec_job;
 int launch_qmatvec_batch(const qmm_matvec_job* jobs, int n_jobs, int m, void* stream);
+
+/* ---- tensor parallelism over the GPUs of one box: row-parallel projections with the sum over the ranks
+ * fused in.  The upstream runs every projection of a layer on one device (examples/gemma4.rs:653-679); when
+ * a layer is partitioned, O and down are split by input columns in whole blocks (rank r holds columns
+ * [r*k_local, (r+1)*k_local) of the full matrix as its own (n, k_local) matrix and the matching slice of the
+ * activations) and their partial outputs must be added.  One process per GPU; no collective library: the
+ * matvec kernel of every rank stores its outputs straight into exchange areas that all ranks have mapped
+ * (cudaIpc), each value with the sequence number of the exchange in the same 64-bit word, and a small
+ * kernel adds the ranks' values in rank order, so every rank ends with bit-identical sums.
+ *   qmm_tp_comm_create   on every rank, with that rank's device current.  capacity_floats: the most values
+ *                        (m * n, or the total of a job list's summed jobs) one exchange carries.
+ *   qmm_tp_comm_export   64 bytes (a cudaIpcMemHandle_t) to hand to the other ranks by any host channel
+ *   qmm_tp_comm_import   once per peer with that peer's 64 bytes;  qmm_tp_comm_ready after the last import
+ *   launch_qmatvec_tp    y(m,n) = sum over ranks of xq_r(m,k_local) . w_r(n,k_local)^T on every rank.
+ *                        Collective: every rank calls it, in the same order as its peers and within the
+ *                        wait bound (about two seconds of SM clock) of them; a rank whose peer does not
+ *                        arrive leaves y unwritten and raises the device status (qmm_device_status = 5).
+ *   launch_qmatvec_batch_tp  a job list (launch_qmatvec_batch) in which the jobs with tp_sum != 0 are
+ *                        summed over the ranks as above and the others are local.
+ * All ranks must pass a host-side barrier between qmm_tp_comm_ready and the first launch. */
+int qmm_tp_comm_create(int rank, int world, long capacity_floats, void** comm);
+int qmm_tp_comm_destroy(void* comm);
+int qmm_tp_comm_export(void* comm, void* out_handle_64_bytes);
+int qmm_tp_comm_import(void* comm, int peer_rank, const void* handle_64_bytes);
+int qmm_tp_comm_ready(void* comm);
+int launch_qmatvec_tp(void* comm, int type, const void* w, const void* xq, float* y, int m, int n, int k, void* stream);
+int launch_qmatvec_batch_tp(void* comm, const qmm_matvec_job* jobs, int n_jobs, int m, void* stream);
 
 /* ---- dequant-GEMM for prefill on the tcgen05 tensor cores.  Same operator shape as
  * launch_gemm_bt_f64 (gpu-core/src/kernels/gemm_f64.hip:48-54; gpu-core/src/infer_ops.rs:224-240) with

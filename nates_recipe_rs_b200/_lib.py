@@ -16,7 +16,7 @@ vp, i32, i64 = C.c_void_p, C.c_int, C.c_long
 class MatvecJob(C.Structure):
     """qmm_matvec_job of include/qmm.h."""
     _fields_ = [("type", C.c_int), ("n", C.c_int), ("k", C.c_int), ("w", C.c_void_p), ("xq", C.c_void_p), ("y", C.c_void_p),
-                ("y_stride", C.c_long), ("select", C.c_void_p), ("select_stride_bytes", C.c_long)]
+                ("y_stride", C.c_long), ("select", C.c_void_p), ("select_stride_bytes", C.c_long), ("tp_sum", C.c_int)]
 
 
 # name -> (restype, argtypes); must list every symbol include/qmm.h declares
@@ -42,6 +42,13 @@ SIGNATURES = {
     "launch_qmatvec_q6_k": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "launch_qmatvec": (i32, [i32, vp, vp, vp, i32, i32, i32, vp]),
     "launch_qmatvec_batch": (i32, [C.POINTER(MatvecJob), i32, i32, vp]),
+    "qmm_tp_comm_create": (i32, [i32, i32, i64, C.POINTER(vp)]),
+    "qmm_tp_comm_destroy": (i32, [vp]),
+    "qmm_tp_comm_export": (i32, [vp, vp]),
+    "qmm_tp_comm_import": (i32, [vp, i32, vp]),
+    "qmm_tp_comm_ready": (i32, [vp]),
+    "launch_qmatvec_tp": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, vp]),
+    "launch_qmatvec_batch_tp": (i32, [vp, C.POINTER(MatvecJob), i32, i32, vp]),
     "launch_qgemm_q4_k_bf16": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "launch_qgemm_q4_k_bf16_f32acc": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "qmm_attn_decode_scratch_bytes": (i64, [i32, i32, i32, i32]),

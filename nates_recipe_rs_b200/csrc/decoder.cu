@@ -17,6 +17,8 @@ int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, lo
 int qmatvec_launch_limited(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                            cudaStream_t stream);
 int quantize_weights_launch(int type, const float* w, void* out, long rows, int k, cudaStream_t stream);
+int qmatvec_launch_push(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
+                        const TpPush* push, cudaStream_t stream);
 
 constexpr int ARGMAX_PARTS = 256;
 
@@ -38,18 +40,11 @@ struct Decoder {
     // activations (allocated once)
     float *x = nullptr, *qkv = nullptr, *gu = nullptr, *logits = nullptr, *attn_scratch = nullptr, *best_val = nullptr;
     uint8_t *xq_h = nullptr, *xq_attn = nullptr, *xq_ffn = nullptr;
-    // tensor-parallel exchange area (one IPC-able allocation): partial outputs A (after O), B (after down), flags
-    uint8_t* xchg = nullptr;
-    size_t xchg_bytes = 0, part_bytes = 0, cand_bytes = 0;
-    Candidate** cand_dev = nullptr;            // device array of tp_size pointers to the ranks' candidate areas
+    // projection outputs that the next residual + norm kernel adds: [0] after O, [1] after down.  With tensor
+    // parallelism the matvec kernels store them into every rank's exchange area (comm) instead.
     float* part[2] = {nullptr, nullptr};
-    unsigned* flags = nullptr;                 // [2][tp_size] arrival counters written by the peers
-    std::vector<uint8_t*> peer_xchg;           // mapped peers (own entry = xchg)
-    PartPtrs parts_host[2] = {};               // the ranks' partial buffers A and B (own included)
+    TpComm* comm = nullptr;                    // tensor parallel only
     Candidate* argmax_cand = nullptr;          // argmax stage-one candidates: max_batch x ARGMAX_PARTS
-    unsigned** peer_flags_dev = nullptr;       // device array of tp_size pointers to the peers' flag areas
-    unsigned* step_counter = nullptr;          // device word: decode steps so far
-    int handshake_index = 0;                   // handshake number within the step being launched
     int attn_splits = 1, attn_chunk = 0;
     std::vector<void*> allocs;
     // second stream for the V projection when its type differs from Q|K's (it then runs beside the Q|K
@@ -133,8 +128,7 @@ static int init_gamma(Decoder* d, float* g, int n, uint64_t seed, cudaStream_t s
 
 static void destroy(Decoder* d) {
     if (!d) return;
-    for (size_t r = 0; r < d->peer_xchg.size(); ++r)
-        if (d->peer_xchg[r] && d->peer_xchg[r] != d->xchg) cudaIpcCloseMemHandle(d->peer_xchg[r]);
+    tp_comm_destroy(d->comm);
     for (void* p : d->allocs) cudaFree(p);
     if (d->fork) cudaEventDestroy(d->fork);
     if (d->join) cudaEventDestroy(d->join);
@@ -256,22 +250,14 @@ static int create(const qmm_decoder_config* cfg, Decoder** out) {
     }
     TRY(dev_alloc(d, &d->attn_scratch, (size_t)B * d->nq * d->attn_splits * (hd + 2) * sizeof(float)));
 
-    // exchange area: [part A][part B][token candidates][flags], 256-aligned pieces
-    d->part_bytes = (((size_t)B * H * sizeof(float)) + 255) & ~size_t(255);
-    d->cand_bytes = (((size_t)B * sizeof(Candidate)) + 255) & ~size_t(255);
-    d->xchg_bytes = 2 * d->part_bytes + d->cand_bytes + 256 * 2;
-    TRY(dev_alloc(d, &d->xchg, d->xchg_bytes));
-    TRY(cuda_status(cudaMemsetAsync(d->xchg, 0, d->xchg_bytes, s)));
-    d->part[0] = reinterpret_cast<float*>(d->xchg);
-    d->part[1] = reinterpret_cast<float*>(d->xchg + d->part_bytes);
-    d->flags = reinterpret_cast<unsigned*>(d->xchg + 2 * d->part_bytes + d->cand_bytes);
-    TRY(dev_alloc(d, &d->cand_dev, QMM_DECODER_MAX_TP * sizeof(Candidate*)));
-    d->peer_xchg.assign(c.tp_size, nullptr);
-    d->peer_xchg[r] = d->xchg;
+    TRY(dev_alloc(d, &d->part[0], (size_t)B * H * sizeof(float)));
+    TRY(dev_alloc(d, &d->part[1], (size_t)B * H * sizeof(float)));
     TRY(dev_alloc(d, &d->argmax_cand, (size_t)B * ARGMAX_PARTS * sizeof(Candidate)));
-    TRY(dev_alloc(d, &d->peer_flags_dev, QMM_DECODER_MAX_TP * sizeof(unsigned*)));
-    TRY(dev_alloc(d, &d->step_counter, 256));
-    TRY(cuda_status(cudaMemsetAsync(d->step_counter, 0, 256, s)));
+    if (c.tp_size > 1) {
+        // one exchange carries a (batch, hidden) partial output, or two words per sequence for the token pick
+        const long cap = (long)B * H > 2l * B ? (long)B * H : 2l * B;
+        TRY(tp_comm_create(c.tp_rank, c.tp_size, cap, &d->comm));
+    }
     TRY(cuda_status(cudaStreamSynchronize(s)));
     // the staging buffer of the initialisation is not needed again
     d->allocs.erase(std::find(d->allocs.begin(), d->allocs.end(), static_cast<void*>(tmp)));
@@ -307,27 +293,30 @@ static int norm_threads(int hidden) {
     return (per_pass + 31) & ~31;
 }
 
-// residual add of the partial outputs in buffer `which` (or none), RMSNorm with gamma, Q8_1 into xq_h
+// residual add of the projection output `which` (or none: -1), RMSNorm with gamma, Q8_1 into xq_h
 static int add_norm(Decoder* d, int which, const float* gamma, int batch, cudaStream_t s) {
-    const int tp = d->c.tp_size;
-    TpSync sync = {};
-    int n_parts = 0;
     PartPtrs parts = {};
+    TpRecv rcv = {};
+    int n_parts = 0;
     if (which >= 0) {
-        n_parts = tp;
-        parts = d->parts_host[which];
-        if (tp > 1) {
-            sync.peer_flags = d->peer_flags_dev;
-            sync.my_flags = d->flags;
-            sync.rank = d->c.tp_rank;
-            sync.which = which;
-            sync.step_counter = d->step_counter;
-            sync.per_step = 2 * d->c.n_layers + 2;
-            sync.index = d->handshake_index++;
+        if (d->comm) {
+            rcv = tp_comm_recv(d->comm);
+        } else {
+            n_parts = 1;
+            parts.p[0] = d->part[which];
         }
     }
     return launch_pdl(add_rmsnorm_q8_kernel, dim3(batch), dim3(norm_threads(d->c.hidden)), 0, s, d->x, parts, n_parts, (long)d->c.hidden,
-                      gamma, d->xq_h, d->c.hidden, d->c.rms_eps, sync, (float*)nullptr);
+                      gamma, d->xq_h, d->c.hidden, d->c.rms_eps, rcv, (float*)nullptr);
+}
+
+// row-parallel projection (O, down): the output goes to part[which], or with tensor parallelism into every
+// rank's exchange area, where the next add_norm finds the partial outputs of all ranks
+static int row_parallel(Decoder* d, int type, const uint8_t* w, const uint8_t* xq, int which, int batch, int k, cudaStream_t s) {
+    const int H = d->c.hidden;
+    if (!d->comm) return qmatvec_launch_strided(type, w, xq, d->part[which], H, batch, H, k, s);
+    const TpPush push = tp_comm_push(d->comm, 0);
+    return qmatvec_launch_push(type, w, xq, d->part[which], H, batch, H, k, 0, &push, s);
 }
 
 static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tokens, float* logits_out, float* best_out, cudaStream_t s) {
@@ -340,13 +329,12 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
     do {       \
         if ((st = (e)) != 0) return st; \
     } while (0)
-    d->handshake_index = 0;
     {   // embedding
         const int rb = type_row_bytes(c.type_head, H);
         const dim3 grid((H + 255) / 256, batch);
-        if (c.type_head == QMM_TYPE_Q6_K) TRY(launch_pdl(embed_rows_kernel<QMM_TYPE_Q6_K>, grid, dim3(256), 0, s, d->embed, tokens, d->x, H, rb, c.vocab, d->step_counter));
-        else if (c.type_head == QMM_TYPE_Q4_K) TRY(launch_pdl(embed_rows_kernel<QMM_TYPE_Q4_K>, grid, dim3(256), 0, s, d->embed, tokens, d->x, H, rb, c.vocab, d->step_counter));
-        else TRY(launch_pdl(embed_rows_kernel<QMM_TYPE_Q8_0>, grid, dim3(256), 0, s, d->embed, tokens, d->x, H, rb, c.vocab, d->step_counter));
+        if (c.type_head == QMM_TYPE_Q6_K) TRY(launch_pdl(embed_rows_kernel<QMM_TYPE_Q6_K>, grid, dim3(256), 0, s, d->embed, tokens, d->x, H, rb, c.vocab, (unsigned*)nullptr));
+        else if (c.type_head == QMM_TYPE_Q4_K) TRY(launch_pdl(embed_rows_kernel<QMM_TYPE_Q4_K>, grid, dim3(256), 0, s, d->embed, tokens, d->x, H, rb, c.vocab, (unsigned*)nullptr));
+        else TRY(launch_pdl(embed_rows_kernel<QMM_TYPE_Q8_0>, grid, dim3(256), 0, s, d->embed, tokens, d->x, H, rb, c.vocab, (unsigned*)nullptr));
     }
     const size_t cache_layer = (size_t)c.max_batch * c.ctx_len * d->nkv * hd;
     const int len = pos + 1;
@@ -383,11 +371,11 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
         }
         TRY(launch_pdl(attn_combine_q8_kernel, dim3(d->nq, batch), dim3(hd < 128 ? hd : 128), 0, s, (const float*)d->attn_scratch, d->xq_attn,
                        (float*)nullptr, d->nq, hd, splits));
-        TRY(qmatvec_launch_strided(c.type_attn_o, L.wo, d->xq_attn, d->part[0], H, batch, H, ao, s));
+        TRY(row_parallel(d, c.type_attn_o, L.wo, d->xq_attn, 0, batch, ao, s));
         TRY(add_norm(d, 0, L.ffn_norm, batch, s));
         TRY(qmatvec_launch_strided(c.type_ffn_gate_up, L.wgu, d->xq_h, d->gu, 2 * d->ffn_l, batch, 2 * d->ffn_l, H, s));
         TRY(launch_pdl(act_mul_q8_kernel, dim3((d->ffn_l / 32 + 3) / 4, batch), dim3(128), 0, s, (const float*)d->gu, d->xq_ffn, d->ffn_l, c.act, (float*)nullptr));
-        TRY(qmatvec_launch_strided(c.type_ffn_down, L.wdown, d->xq_ffn, d->part[1], H, batch, H, d->ffn_l, s));
+        TRY(row_parallel(d, c.type_ffn_down, L.wdown, d->xq_ffn, 1, batch, d->ffn_l, s));
     }
     TRY(add_norm(d, 1, d->final_norm, batch, s));
     float* lg = logits_out ? logits_out : d->logits;
@@ -396,17 +384,9 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
     TRY(launch_pdl(argmax_partial_kernel, dim3(ARGMAX_PARTS, batch), dim3(256), 0, s, (const float*)lg, d->argmax_cand, d->vocab_l));
     TRY(launch_pdl(argmax_final_kernel, dim3(batch), dim3(256), 0, s, (const Candidate*)d->argmax_cand, ARGMAX_PARTS, next_tokens,
                    c.tp_rank * d->vocab_l, bv));
-    if (c.tp_size > 1) {
-        TpSync sync = {};
-        sync.peer_flags = d->peer_flags_dev;
-        sync.my_flags = d->flags;
-        sync.rank = c.tp_rank;
-        sync.which = 2;
-        sync.step_counter = d->step_counter;
-        sync.per_step = 2 * c.n_layers + 2;
-        sync.index = d->handshake_index++;
+    if (d->comm) {
         TRY(launch_pdl(tp_pick_token_kernel, dim3(1), dim3(batch < 32 ? 32 : ((batch + 31) & ~31)), 0, s, (const float*)bv, next_tokens,
-                       (Candidate* const*)d->cand_dev, c.tp_size, batch, sync));
+                       tp_comm_push(d->comm, 0), tp_comm_recv(d->comm), batch));
     }
 #undef TRY
     return QMM_OK;
@@ -434,14 +414,6 @@ int qmm_decoder_create(const qmm_decoder_config* cfg, void** handle) {
     if (attn_opt_in_smem(true, attn_tc_smem_bytes(cfg->head_dim)) != QMM_OK || attn_opt_in_smem(false, attn_smem) != QMM_OK) {
         destroy(d);
         return QMM_ERR_CUDA;
-    }
-    // single GPU: the pointer tables hold only this rank's buffers
-    if (cfg->tp_size == 1) {
-        const int rc = qmm_decoder_tp_ready(d);
-        if (rc) {
-            destroy(d);
-            return rc;
-        }
     }
     *handle = d;
     return QMM_OK;
@@ -522,45 +494,22 @@ int qmm_decoder_fill_cache(void* handle, unsigned long long seed, void* stream) 
 
 int qmm_decoder_ipc_export(void* handle, void* out_handle_64_bytes) {
     if (!handle || !out_handle_64_bytes) return QMM_ERR_NULL;
-    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
-    cudaIpcMemHandle_t h;
-    QMM_CUDA_TRY(cudaIpcGetMemHandle(&h, static_cast<Decoder*>(handle)->xchg));
-    std::memcpy(out_handle_64_bytes, &h, 64);
-    return QMM_OK;
+    Decoder* d = static_cast<Decoder*>(handle);
+    if (!d->comm) return QMM_ERR_UNSUPPORTED;  // single GPU: nothing to exchange
+    return tp_comm_export(d->comm, out_handle_64_bytes);
 }
 
 int qmm_decoder_ipc_import(void* handle, int peer_rank, const void* handle_64_bytes) {
     if (!handle || !handle_64_bytes) return QMM_ERR_NULL;
     Decoder* d = static_cast<Decoder*>(handle);
-    if (peer_rank < 0 || peer_rank >= d->c.tp_size) return QMM_ERR_SHAPE;
-    if (peer_rank == d->c.tp_rank) return QMM_OK;
-    cudaIpcMemHandle_t h;
-    std::memcpy(&h, handle_64_bytes, 64);
-    void* p = nullptr;
-    QMM_CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
-    d->peer_xchg[peer_rank] = static_cast<uint8_t*>(p);
-    return QMM_OK;
+    if (!d->comm) return QMM_ERR_UNSUPPORTED;
+    return tp_comm_import(d->comm, peer_rank, handle_64_bytes);
 }
 
 int qmm_decoder_tp_ready(void* handle) {
     if (!handle) return QMM_ERR_NULL;
     Decoder* d = static_cast<Decoder*>(handle);
-    const int tp = d->c.tp_size;
-    const float* pa[QMM_DECODER_MAX_TP] = {};
-    const float* pb[QMM_DECODER_MAX_TP] = {};
-    unsigned* pf[QMM_DECODER_MAX_TP] = {};
-    Candidate* pc[QMM_DECODER_MAX_TP] = {};
-    for (int r = 0; r < tp; ++r) {
-        if (!d->peer_xchg[r]) return QMM_ERR_NULL;  // a peer has not been imported
-        pa[r] = reinterpret_cast<const float*>(d->peer_xchg[r]);
-        pb[r] = reinterpret_cast<const float*>(d->peer_xchg[r] + d->part_bytes);
-        pf[r] = reinterpret_cast<unsigned*>(d->peer_xchg[r] + 2 * d->part_bytes + d->cand_bytes);
-        pc[r] = reinterpret_cast<Candidate*>(d->peer_xchg[r] + 2 * d->part_bytes);
-    }
-    QMM_CUDA_TRY(cudaMemcpy(d->cand_dev, pc, sizeof(pc), cudaMemcpyHostToDevice));
-    for (int r = 0; r < QMM_DECODER_MAX_TP; ++r) d->parts_host[0].p[r] = pa[r], d->parts_host[1].p[r] = pb[r];
-    QMM_CUDA_TRY(cudaMemcpy(d->peer_flags_dev, pf, sizeof(pf), cudaMemcpyHostToDevice));
-    return QMM_OK;
+    return d->comm ? tp_comm_ready(d->comm) : QMM_OK;
 }
 
 int qmm_decoder_step(void* handle, const int* tokens, int batch, int pos, int* next_tokens, float* logits, float* best, void* stream) {

@@ -83,33 +83,24 @@ __device__ __forceinline__ void warp_store_q8_1(float v, uint8_t* blk, int lane)
 }
 
 // Residual update + RMSNorm + Q8_1 in one pass over a row, fused with the tensor-parallel sum:
-//   x += sum_{r < n_parts} part[r]          (n_parts = 0: no update.  The parts are the partial outputs of
-//                                            the preceding row-parallel projection, one per rank; the
-//                                            peers' buffers are read in place over NVLink)
+//   x += part                               (single GPU: the output of the preceding projection, n_parts = 1)
+//   x += sum_{r < tp} part_r                (tensor parallel: the partial outputs of the preceding row-parallel
+//                                            projection, which every rank's matvec kernel stored into this
+//                                            rank's exchange area, one 64-bit word {value, sequence number}
+//                                            per output; the words are polled here, in local memory, with a
+//                                            bound, and added in rank order - see TpPush / TpRecv)
 //   xq = Q8_1( x * rsqrt(mean(x^2) + eps) * gamma )
-// Handshake when n_parts > 1: CTA 0 publishes this rank's arrival number `seq` in every peer's flag
-// area (after a system-scope fence: its own partial was written by the preceding kernel), then every
-// CTA waits, with a bound, until all peers have published `seq` here.  Two partial buffers alternate
-// (after O, after down), so a buffer is rewritten only after a later handshake has shown that every
-// peer finished reading it.
-// One CTA per activation row, one element per thread per pass (hidden <= 8 * blockDim.x).
+// One CTA per activation row, one element per thread per pass (hidden <= 8 * blockDim.x).  The last CTA
+// to finish advances the exchange counter.
 constexpr int NORM_MAX_PER_THREAD = 8;
 struct PartPtrs {
-    const float* p[8];  // the ranks' partial-output buffers (own included), passed by value: no pointer chase
+    const float* p[8];  // single GPU: p[0] = the projection output to add (or none)
 };
-struct TpSync {
-    unsigned* const* peer_flags;  // [n_parts] flag areas of all ranks (own included), each [3][QMM_TP_SLOTS]
-    unsigned* my_flags;
-    const unsigned* step_counter;  // device word, incremented once per decode step (graph replays included)
-    int rank, which;
-    int index, per_step;           // handshake number within a step, handshakes per step
-};
-constexpr int QMM_TP_SLOTS = 8;
 __global__ void __launch_bounds__(1024) add_rmsnorm_q8_kernel(float* __restrict__ x, const PartPtrs parts, int n_parts, long part_stride,
-                                      const float* __restrict__ gamma, uint8_t* __restrict__ xq, int hidden, float eps, TpSync tp,
+                                      const float* __restrict__ gamma, uint8_t* __restrict__ xq, int hidden, float eps, const TpRecv rcv,
                                       float* __restrict__ out_f32) {
     __shared__ float red[32];
-    __shared__ int peers_ok;
+    __shared__ int give_up;
     pdl_release_dependents();
     // gamma is model data: fetched before the wait for the preceding kernel
     float gm[NORM_MAX_PER_THREAD];
@@ -118,31 +109,12 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_q8_kernel(float* __restrict_
         const int e = i * blockDim.x + threadIdx.x;
         gm[i] = e < hidden ? (gamma ? gamma[e] : 1.f) : 0.f;  // no gamma: the scale-less variant
     }
+    if (threadIdx.x == 0) give_up = 0;
+    __syncthreads();
     pdl_wait_prior_grids();
     const int b = blockIdx.x, lane = threadIdx.x & 31;
-    if (n_parts > 1) {
-        const unsigned seq = *tp.step_counter * (unsigned)tp.per_step + (unsigned)tp.index;
-        if (threadIdx.x == 0) peers_ok = 1;
-        __syncthreads();
-        if (b == 0 && threadIdx.x < n_parts && (int)threadIdx.x != tp.rank) {
-            __threadfence_system();
-            *reinterpret_cast<volatile unsigned*>(tp.peer_flags[threadIdx.x] + tp.which * QMM_TP_SLOTS + tp.rank) = seq;
-        }
-        if (threadIdx.x < n_parts && (int)threadIdx.x != tp.rank) {
-            const volatile unsigned* f = tp.my_flags + tp.which * QMM_TP_SLOTS + threadIdx.x;
-            const long long t0 = clock64();
-            while ((int)(*f - seq) < 0) {
-                if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                    atomicExch(&g_device_status, DEV_TIMEOUT_PEER);
-                    peers_ok = 0;
-                    break;
-                }
-            }
-            __threadfence_system();
-        }
-        __syncthreads();
-        if (!peers_ok) return;
-    }
+    const bool exchange = rcv.tp > 1;
+    const unsigned seq = exchange ? tp_next_seq(rcv.counter) : 0u;
     float* xr = x + (size_t)b * hidden;
     float v[NORM_MAX_PER_THREAD];
     float ss = 0.f;
@@ -152,21 +124,32 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_q8_kernel(float* __restrict_
         v[i] = 0.f;
         if (e < hidden) {
             float t = xr[e];
-#pragma unroll
-            for (int r = 0; r < 8; ++r)
-                if (r < n_parts) t += __ldcv(parts.p[r] + (size_t)b * part_stride + e);  // never from a stale cache line
-            if (n_parts > 0) xr[e] = t;
+            if (exchange) {
+                for (int r = 0; r < rcv.tp; ++r) {  // rank order: the same sum on every rank
+                    float pv = 0.f;
+                    if (!tp_poll_word(rcv, seq, r, (long)b * part_stride + e, pv, &give_up)) break;
+                    t += pv;
+                }
+            } else if (n_parts > 0) {
+                t += parts.p[0][(size_t)b * part_stride + e];
+            }
             v[i] = t;
             ss += t * t;
         }
     }
-    ss = block_sum(ss, red);
+    ss = block_sum(ss, red);  // (two block-wide barriers: every thread is past its polls after them)
+    if (exchange && threadIdx.x == 0) {
+        if (give_up) atomicExch(&g_device_status, DEV_TIMEOUT_PEER);
+        tp_consumer_done(rcv, seq, gridDim.x);
+    }
+    if (give_up) return;  // a peer never arrived: leave x and xq as they were
     const float inv = rsqrtf(ss / (float)hidden + eps);
     uint8_t* qrow = xq + (size_t)b * (hidden / 32) * Q8_1_BYTES;
 #pragma unroll
     for (int i = 0; i < NORM_MAX_PER_THREAD; ++i) {
         const int e = i * blockDim.x + threadIdx.x;  // a warp covers 32 consecutive elements = one block
         if (e < hidden) {
+            if (exchange || n_parts > 0) xr[e] = v[i];
             const float nv = v[i] * inv * gm[i];
             if (out_f32) out_f32[(size_t)b * hidden + e] = nv;
             warp_store_q8_1(nv, qrow + (size_t)(e >> 5) * Q8_1_BYTES, lane);
@@ -660,53 +643,38 @@ __global__ void argmax_final_kernel(const Candidate* __restrict__ cand, int part
     }
 }
 
-// Tensor-parallel greedy pick: every rank has the argmax of its vocabulary slice (global index and
-// value) in cand[rank]; after the same bounded handshake as the residual kernel each rank reads all
-// candidates and keeps the best (lowest index on ties), so all ranks continue with the same token.
-// cand areas: per rank `max_batch` pairs {float value, int index}.  One CTA, one thread per row.
-__global__ void tp_pick_token_kernel(const float* __restrict__ best_val, int* __restrict__ tokens_io, Candidate* const* __restrict__ cand,
-                                     int n_ranks, int batch, TpSync tp) {
-    __shared__ int peers_ok;
+// Tensor-parallel greedy pick: every rank has the argmax of its vocabulary slice (global index and value);
+// it pushes both as two exchange words per sequence into every rank's area, then reads all ranks' pairs
+// from its own area (bounded polls) and keeps the best (lowest index on ties), so all ranks continue with
+// the same token.  One CTA, one thread per sequence.  A rank whose peer never arrives stores -1.
+__global__ void tp_pick_token_kernel(const float* __restrict__ best_val, int* __restrict__ tokens_io, const TpPush push, const TpRecv rcv,
+                                     int batch) {
+    __shared__ int give_up;
     pdl_release_dependents();
+    if (threadIdx.x == 0) give_up = 0;
+    __syncthreads();
     pdl_wait_prior_grids();
-    const unsigned seq = *tp.step_counter * (unsigned)tp.per_step + (unsigned)tp.index;
-    if (threadIdx.x == 0) peers_ok = 1;
-    if ((int)threadIdx.x < batch) {
-        Candidate c;
-        c.value = best_val[threadIdx.x];
-        c.index = tokens_io[threadIdx.x];
-        cand[tp.rank][threadIdx.x] = c;
-    }
-    __syncthreads();
-    if ((int)threadIdx.x < n_ranks && (int)threadIdx.x != tp.rank) {
-        __threadfence_system();
-        *reinterpret_cast<volatile unsigned*>(tp.peer_flags[threadIdx.x] + tp.which * QMM_TP_SLOTS + tp.rank) = seq;
-        const volatile unsigned* f = tp.my_flags + tp.which * QMM_TP_SLOTS + threadIdx.x;
-        const long long t0 = clock64();
-        while ((int)(*f - seq) < 0) {
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                atomicExch(&g_device_status, DEV_TIMEOUT_PEER);
-                peers_ok = 0;
-                break;
-            }
-        }
-        __threadfence_system();
-    }
-    __syncthreads();
-    if ((int)threadIdx.x >= batch) return;
-    if (!peers_ok) {  // a peer never arrived: make the failure visible in the result as well as in the status word
-        tokens_io[threadIdx.x] = -1;
-        return;
-    }
+    const unsigned seq = tp_next_seq(rcv.counter);
+    const int b = threadIdx.x;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int r = 0; r < n_ranks; ++r) {
-        const volatile Candidate* c = cand[r] + threadIdx.x;
-        const float v = c->value;
-        const int i = c->index;
-        if (v > bv || (v == bv && i < bi)) bv = v, bi = i;
+    bool ok = true;
+    if (b < batch) {
+        tp_push_word(push, seq, 2l * b, best_val[b]);
+        tp_push_word(push, seq, 2l * b + 1, __int_as_float(tokens_io[b]));
+        for (int r = 0; r < rcv.tp && ok; ++r) {
+            float v = 0.f, fi = 0.f;
+            ok = tp_poll_word(rcv, seq, r, 2l * b, v, &give_up) && tp_poll_word(rcv, seq, r, 2l * b + 1, fi, &give_up);
+            const int i = __float_as_int(fi);
+            if (ok && (v > bv || (v == bv && i < bi))) bv = v, bi = i;
+        }
     }
-    tokens_io[threadIdx.x] = bi;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (give_up) atomicExch(&g_device_status, DEV_TIMEOUT_PEER);
+        tp_consumer_done(rcv, seq, 1u);
+    }
+    if (b < batch) tokens_io[b] = ok ? bi : -1;
 }
 
 }  // namespace qmm

@@ -7,6 +7,7 @@
 #include "qgemm.cu"
 #include "qmatvec_mma.cu"
 #include "decoder_ops.cu"
+#include "tp_comm.cu"
 #include "attn_entry.cu"
 #include "ops_entry.cu"
 #include "decoder.cu"

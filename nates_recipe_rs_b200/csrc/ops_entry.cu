@@ -37,7 +37,7 @@ int launch_add_rmsnorm_q8_1(float* x, const float* add, const float* gamma, void
     if (reinterpret_cast<uintptr_t>(xq) % 4 != 0) return QMM_ERR_ALIGN;
     PartPtrs parts = {};
     parts.p[0] = add;
-    TpSync none = {};
+    TpRecv none = {};
     add_rmsnorm_q8_kernel<<<rows, ops_norm_threads(cols), 0, as_stream(stream)>>>(x, parts, add ? 1 : 0, (long)cols, gamma,
                                                                                     static_cast<uint8_t*>(xq), cols, eps, none, out_f32);
     QMM_CUDA_TRY(cudaGetLastError());

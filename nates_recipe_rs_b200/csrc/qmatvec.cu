@@ -50,6 +50,7 @@ struct MatvecParams {
     int rows_q, rows_r;  // n / grid and n % grid
     int probe;        // 0 = normal; 1 = stream only: every wait and arrival happens, the arithmetic is skipped
     unsigned long long* trace;  // optional (tuning aid): 4 global-timer stamps per CTA
+    TpPush push;      // tensor parallel: the outputs go to every rank's exchange area instead of y
 };
 
 constexpr int MAX_STAGES = 8;
@@ -135,6 +136,7 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
         if (lane == 0)
             for (; issued < n_it && issued < p.nst; ++issued) issue(issued);
         pdl_wait_prior_grids();  // y may still be read by the preceding kernel
+        const unsigned seq = p.push.tp > 0 ? tp_next_seq(p.push.counter) : 0u;
         bool ok = true;
         // ring slot, its phase and the partial-sum slot of stage `it`, kept incrementally (no divisions)
         int slot = 0, pslot = 0;
@@ -154,13 +156,13 @@ __global__ void __launch_bounds__((MAX_CONSUMER_WARPS + 1) * 32, 1) qmatvec_kern
             }
             const int nr = min(p.rows_stage, n_rows - it * p.rows_stage);
             const float* ps = partial + (size_t)pslot * p.pstage;
-            float* yrow = p.y + row_begin + (long)it * p.rows_stage;
+            const long yrow = row_begin + (long)it * p.rows_stage;
             for (int idx = lane; idx < nr * M; idx += 32) {  // idx = r*M + mi
                 const int r = idx / M, mi = idx - r * M;
                 const float* src = ps + (size_t)r * p.kw * M + mi;
                 float acc = 0.f;
                 for (int q = 0; q < p.kw; ++q) acc += src[q * M];
-                if (mi < p.m) yrow[(size_t)mi * p.y_stride + r] = acc;
+                if (mi < p.m) tp_store_out(p.push, seq, p.y, p.y_stride, mi, yrow + r, acc);
             }
             if (++slot == p.nst) slot = 0, phase ^= 1;
             if (++pslot == 2 * p.nst) pslot = 0;
@@ -304,7 +306,7 @@ int mma_set_min_m(int v);
 int attn_set_tc_min_batch(int v);
 int mma_min_m();
 int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
-                       unsigned long long* trace, cudaStream_t stream);
+                       unsigned long long* trace, const TpPush* push, cudaStream_t stream);
 int matvec_tune(const char* key, int value) {
     const std::string k(key ? key : "");
 #ifdef QMM_TUNING  // wrong results by design: development builds only
@@ -369,6 +371,8 @@ static int launch_p(const MatvecParams& p, int passes, int grid, int threads, si
 int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, cudaStream_t stream);
 int qmatvec_launch_limited(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                            cudaStream_t stream);
+int qmatvec_launch_push(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
+                        const TpPush* push, cudaStream_t stream);
 int qmatvec_launch(int type, const void* w, const void* xq, float* y, int m, int n, int k, cudaStream_t stream) {
     return qmatvec_launch_strided(type, w, xq, y, n, m, n, k, stream);
 }
@@ -382,6 +386,13 @@ int qmatvec_launch_strided(int type, const void* w, const void* xq, float* y, lo
 // two streams share the GPU side by side instead of one after the other
 int qmatvec_launch_limited(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                            cudaStream_t stream) {
+    return qmatvec_launch_push(type, w, xq, y, y_stride, m, n, k, cta_limit, nullptr, stream);
+}
+
+// push != nullptr (tensor parallel): output (mi, row) goes to slot push->word0 + mi * y_stride + row of every
+// rank's exchange area instead of y (y must still be a valid pointer; it is not written)
+int qmatvec_launch_push(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
+                        const TpPush* push, cudaStream_t stream) {
     if (!w || !xq || !y) return QMM_ERR_NULL;
     if (y_stride < n) return QMM_ERR_SHAPE;
     int block_elems, block_bytes, unit_elems, w_align;
@@ -419,8 +430,10 @@ int qmatvec_launch_limited(int type, const void* w, const void* xq, float* y, lo
     if (mma_min_m() > 0 && !g_probe) {
         while (m - m_done >= mma_min_m()) {
             const int mg = m - m_done < 16 ? m - m_done : 16;
+            TpPush sub = {};
+            if (push) sub = *push, sub.word0 += (long)m_done * y_stride;
             const int st = qmatvec_mma_launch(type, w, static_cast<const uint8_t*>(xq) + (size_t)m_done * p.xq_row_bytes,
-                                              y + (size_t)m_done * y_stride, y_stride, mg, n, k, cta_limit, p.trace, stream);
+                                              y + (size_t)m_done * y_stride, y_stride, mg, n, k, cta_limit, p.trace, push ? &sub : nullptr, stream);
             if (st == QMM_ERR_UNSUPPORTED) break;
             if (st) return st;
             m_done += mg;
@@ -434,6 +447,8 @@ int qmatvec_launch_limited(int type, const void* w, const void* xq, float* y, lo
         p.xq = static_cast<const uint8_t*>(xq) + (size_t)m0 * p.xq_row_bytes;
         p.y = y + (size_t)m0 * y_stride;
         p.y_stride = y_stride;
+        p.push = TpPush{};
+        if (push) p.push = *push, p.push.word0 += (long)m0 * y_stride;
 
         // Q4_K unit width: one 32-byte group per lane measured fastest on every decode shape (wider units
         // decode the packed scales less often but cost registers and occupancy); "q4k_unit" overrides.

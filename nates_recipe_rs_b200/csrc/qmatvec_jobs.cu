@@ -24,7 +24,7 @@
 
 namespace qmm {
 
-constexpr int JOBS_MAX = 40;           // jobs per launch (the descriptor array travels as kernel parameter)
+constexpr int JOBS_MAX = 36;           // jobs per launch (the descriptor array travels as kernel parameter)
 constexpr int JOBS_MAX_STAGES = 8;
 constexpr int JOBS_MAX_WARPS = 24;     // consumer warps
 
@@ -41,6 +41,7 @@ struct JobDesc {
     int kw, rg, rb;       // warps along K, row groups, rows reduced together
     int rows_q, rows_r;   // n / grid, n % grid
     int rot;              // rotation of the CTA -> row-range assignment (0 <= rot < grid)
+    long push_word;       // tensor parallel: slot index of this job's y[0][0] in the exchange areas, or -1: plain stores to y
 };
 
 struct JobList {
@@ -49,6 +50,7 @@ struct JobList {
     int nst, slot_bytes, pstage_max;
     int x_off, partial_off, ring_off;
     int n_consumers, any_sel;
+    TpPush push;          // used by the jobs with push_word >= 0
 };
 static_assert(sizeof(JobList) <= 4096, "the job list travels as a kernel parameter");
 
@@ -279,6 +281,7 @@ __global__ void __launch_bounds__((JOBS_MAX_WARPS + 1) * 32, 1) qmatvec_jobs_ker
             advance(is);
         }
         if (!L.any_sel) pdl_wait_prior_grids();  // activations come from the preceding kernel, y may still be read by it
+        const unsigned push_seq = L.push.tp > 0 ? tp_next_seq(L.push.counter) : 0u;
         int x_issued = 0;  // activation copies issued
         if (fo.j < L.n_jobs) {
             if (lane == 0) issue_x(fo.j);
@@ -315,14 +318,21 @@ __global__ void __launch_bounds__((JOBS_MAX_WARPS + 1) * 32, 1) qmatvec_jobs_ker
             // fold the K-split partial sums of this stage in a fixed order
             const int nr = min(J.rows_stage, fo.n_rows - fo.it * J.rows_stage);
             const float* ps = partial + (size_t)pslot * L.pstage_max;
-            float* yrow = J.y + fo.row_begin + (long)fo.it * J.rows_stage;
+            const long yrow = fo.row_begin + (long)fo.it * J.rows_stage;
             const int kwj = J.kw, ysj = J.y_stride, mj = L.m;
+            float* const yj = J.y;
+            const long pw = J.push_word;
             for (int idx = lane; idx < nr * M; idx += 32) {  // idx = r*M + mi
                 const int r = idx / M, mi = idx - r * M;
                 const float* src = ps + (size_t)r * kwj * M + mi;
                 float acc = 0.f;
                 for (int q = 0; q < kwj; ++q) acc += src[q * M];
-                if (mi < mj) yrow[(size_t)mi * ysj + r] = acc;
+                if (mi < mj) {
+                    if (pw >= 0)
+                        tp_push_word(L.push, push_seq, pw + (long)mi * ysj + yrow + r, acc);
+                    else
+                        yj[(size_t)mi * ysj + yrow + r] = acc;
+                }
             }
             advance(fo);
             if (++slot == L.nst) slot = 0, phase ^= 1;
@@ -435,7 +445,15 @@ static int job_geometry(int type, int& block_elems, int& block_bytes, int& w_ali
 // Validates the jobs, then launches them in groups of up to JOBS_MAX.  Shapes the persistent kernel does
 // not take (see the head of this file) run as one single-matrix launch per job instead; a job with a
 // device-side selector has no such fallback and is rejected with QMM_ERR_UNSUPPORTED.
+int qmatvec_jobs_launch_push(const qmm_matvec_job* jobs, int n_jobs, int m, const TpPush* push, const long* push_words, cudaStream_t stream);
 int qmatvec_jobs_launch(const qmm_matvec_job* jobs, int n_jobs, int m, cudaStream_t stream) {
+    return qmatvec_jobs_launch_push(jobs, n_jobs, m, nullptr, nullptr, stream);
+}
+
+// push / push_words (tensor parallel, both or neither): job i with push_words[i] >= 0 sends its outputs to slot
+// push_words[i] + mi * y_stride + row of every rank's exchange area instead of storing them to its y.  Such a
+// list has no per-job fallback: QMM_ERR_UNSUPPORTED when it does not fit the persistent kernel.
+int qmatvec_jobs_launch_push(const qmm_matvec_job* jobs, int n_jobs, int m, const TpPush* push, const long* push_words, cudaStream_t stream) {
     if (!jobs) return QMM_ERR_NULL;
     if (n_jobs <= 0 || m <= 0) return QMM_ERR_SHAPE;
     const int sms = sm_count();
@@ -464,7 +482,7 @@ int qmatvec_jobs_launch(const qmm_matvec_job* jobs, int n_jobs, int m, cudaStrea
             fits = false;
     }
     if (!fits) {
-        if (any_sel) return QMM_ERR_UNSUPPORTED;
+        if (any_sel || push) return QMM_ERR_UNSUPPORTED;
         for (int i = 0; i < n_jobs; ++i) {
             const qmm_matvec_job& q = jobs[i];
             if (int st = qmatvec_launch_strided(q.type, q.w, q.xq, q.y, q.y_stride ? q.y_stride : q.n, m, q.n, q.k, stream)) return st;
@@ -479,6 +497,7 @@ int qmatvec_jobs_launch(const qmm_matvec_job* jobs, int n_jobs, int m, cudaStrea
         L.m = m;
         L.n_consumers = nw;
         L.any_sel = 0;
+        if (push) L.push = *push;
         int slot_max = 0, pstage_max = 0, x_max = 0;
         for (int i = 0; i < nj; ++i) {
             const qmm_matvec_job& q = jobs[j0 + i];
@@ -508,6 +527,7 @@ int qmatvec_jobs_launch(const qmm_matvec_job* jobs, int n_jobs, int m, cudaStrea
             J.rows_stage = rb * batches;
             J.rows_q = q.n / sms, J.rows_r = q.n % sms;
             J.rot = g_jobs_rotate ? (int)(((long)(j0 + i) * 61) % sms) : 0;
+            J.push_word = (push && push_words) ? push_words[j0 + i] : -1;
             const int slot = (J.rows_stage * J.row_bytes + 32 + 127) & ~127;
             const int pst = J.rows_stage * J.kw * mt;
             const int xb = (m * J.xq_row_bytes + 127) & ~127;

@@ -44,6 +44,7 @@ struct MmaParams {
     int opw, opw_p;    // outputs of a tile folded per warp, and the next power of two (<= 32)
     int pstride;       // floats between the partial tiles of two warps
     unsigned long long* trace;  // optional (tuning aid): 4 global-timer stamps per CTA
+    TpPush push;       // tensor parallel: the outputs go to every rank's exchange area instead of y
 };
 
 constexpr int MMA_MAX_STAGES = 8;
@@ -257,6 +258,7 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
     const int o_row = ((my_o & 31) >> 2) + 8 * ((my_o >> 6) & 1);
     const int o_bt = 8 * (my_o >> 7) + 2 * (my_o & 3) + ((my_o >> 5) & 1);
     const uint32_t pstride_b = (uint32_t)p.pstride * 4u;
+    unsigned push_seq = 0u;  // read after the wait for the preceding kernel, below
     auto fold = [&](int pbuf, uint32_t ppar, int c, int ti, int cols) {
         if (!mma_wait(pfull_s + 8 * pbuf, ppar, cta_abort)) {
             give_up(DEV_TIMEOUT_EMPTY);
@@ -277,7 +279,7 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
             if (c + 1 < p.n_chunks) sts_f32(ya, sum);
             if (c + 1 == p.n_chunks) {
                 const int row = ti * 16 + o_row;
-                if (row < rows_cta && o_bt < p.m) p.y[(size_t)o_bt * p.y_stride + row0 + row] = sum;
+                if (row < rows_cta && o_bt < p.m) tp_store_out(p.push, push_seq, p.y, p.y_stride, o_bt, (long)row0 + row, sum);
             }
         }
         return true;
@@ -285,6 +287,7 @@ __global__ void __launch_bounds__(MMA_MAX_CW * 32, 1) qmv_mma_kernel(const __gri
 
     const int q = lane >> 2, pq = lane & 3;
     pdl_wait_prior_grids();  // activations come from the preceding kernel, y may still be read by it
+    if (p.push.tp > 0) push_seq = tp_next_seq(p.push.counter);
 
     // Activations of a warp's column reach its registers through a private staging area: eight rows x
     // 288 bytes fetched with 16-byte asynchronous copies (whole lines, a fraction of the requests that
@@ -591,7 +594,7 @@ static int mma_launch_inst(const CUtensorMap& wmap, const MmaParams& p, int grid
 // Returns QMM_ERR_UNSUPPORTED (nothing launched) when the type or shape does not fit this kernel; the
 // caller then uses the dp4a kernel.  m <= 16.
 int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
-                       unsigned long long* trace, cudaStream_t stream) {
+                       unsigned long long* trace, const TpPush* push, cudaStream_t stream) {
     if ((type != QMM_TYPE_Q4_K && type != QMM_TYPE_Q6_K) || m < 1 || m > 16 || k % QKK != 0) return QMM_ERR_UNSUPPORTED;
     // 16-byte asynchronous copies of the activations, tensor copies of the weights
     if (reinterpret_cast<uintptr_t>(xq) % 16 != 0 || reinterpret_cast<uintptr_t>(w) % 16 != 0) return QMM_ERR_UNSUPPORTED;
@@ -605,6 +608,7 @@ int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y
     p.m = m;
     p.n = n;
     p.trace = trace;
+    if (push) p.push = *push;
     p.k_blocks = k / QKK;
     p.row_bytes = p.k_blocks * block_bytes;
     p.xq_row_bytes = k / QK8 * Q8_1_BYTES;

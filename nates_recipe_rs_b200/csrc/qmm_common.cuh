@@ -148,5 +148,79 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// ---- tensor-parallel exchange: a sum of partial outputs over the ranks of one box, pushed ----
+// Every rank owns an exchange area that all its peers have mapped (cudaIpc): two alternating buffers,
+// each with one slot array per source rank.  A partial output travels as ONE 64-bit word per value,
+// {float bits, sequence number of the exchange}, stored straight into every rank's area (the own one
+// included) by the kernel that produced it; the consumer polls its LOCAL area until the word carries the
+// expected sequence number, so there is no separate flag, no fence and no remote read on the critical path.
+// The sequence number of the next exchange is (completed exchanges + 1), kept in device memory and advanced
+// by the last CTA of the consuming kernel, so graph replays stay in step; the buffer is (sequence & 1).  A
+// buffer is rewritten two exchanges later, which a rank can only reach after every peer has finished
+// reading it (a peer's words of the exchange in between are stored after its own read completed).
+constexpr int QMM_TP_MAX = 8;
+struct TpPush {                          // by value in the matvec kernels' parameters; tp == 0: plain stores to y
+    unsigned long long* dst[QMM_TP_MAX];  // dst[r]: this rank's slot array in rank r's area (buffer 0)
+    const unsigned* counter;              // exchanges completed on this rank
+    long buf_words;                       // words from buffer 0 to buffer 1
+    long word0;                           // slot index of y[0][0]; y[mi][row] goes to word0 + mi * y_stride + row
+    int tp;
+};
+struct TpRecv {                          // the consuming side
+    const unsigned long long* base;       // own area, buffer 0, source rank 0
+    unsigned* counter;                    // exchanges completed (advanced by the last CTA of the consumer)
+    unsigned* ticket;                     // CTAs of the consumer that have finished
+    long buf_words, src_words;            // words between the buffers, and between the slot arrays of two source ranks
+    int tp;
+};
+__device__ __forceinline__ unsigned ld_volatile_u32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ unsigned tp_next_seq(const unsigned* counter) { return ld_volatile_u32(counter) + 1u; }
+__device__ __forceinline__ void tp_push_word(const TpPush& s, unsigned seq, long word, float v) {
+    const unsigned long long bits = ((unsigned long long)seq << 32) | (unsigned long long)__float_as_uint(v);
+    const long off = ((seq & 1u) ? s.buf_words : 0) + word;
+#pragma unroll
+    for (int r = 0; r < QMM_TP_MAX; ++r)
+        if (r < s.tp) asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(s.dst[r] + off), "l"(bits) : "memory");
+}
+// one output of a matvec: an ordinary store, or the push to every rank
+__device__ __forceinline__ void tp_store_out(const TpPush& s, unsigned seq, float* y, long y_stride, int mi, long row, float v) {
+    if (s.tp > 0)
+        tp_push_word(s, seq, s.word0 + (long)mi * y_stride + row, v);
+    else
+        y[(size_t)mi * y_stride + row] = v;
+}
+// Polls the word of source rank r (bounded): true and the value once it carries `seq`.
+__device__ __forceinline__ bool tp_poll_word(const TpRecv& rcv, unsigned seq, int r, long word, float& v, volatile int* give_up) {
+    const unsigned long long* p = rcv.base + ((seq & 1u) ? rcv.buf_words : 0) + (long)r * rcv.src_words + word;
+    unsigned long long bits;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(bits) : "l"(p) : "memory");
+    if ((unsigned)(bits >> 32) != seq) {
+        const long long t0 = clock64();
+        for (;;) {
+            asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(bits) : "l"(p) : "memory");
+            if ((unsigned)(bits >> 32) == seq) break;
+            if (*give_up || clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *give_up = 1;
+                return false;
+            }
+        }
+    }
+    v = __uint_as_float((unsigned)bits);
+    return true;
+}
+// End of the consuming kernel (one thread per CTA, after the CTA's last read): the last CTA advances the counter.
+__device__ __forceinline__ void tp_consumer_done(const TpRecv& rcv, unsigned seq, unsigned n_ctas) {
+    __threadfence();
+    if (atomicAdd(rcv.ticket, 1u) == n_ctas - 1u) {
+        *rcv.ticket = 0u;
+        __threadfence();
+        *reinterpret_cast<volatile unsigned*>(rcv.counter) = seq;
+    }
+}
+
 #endif  // __CUDACC__
 }  // namespace qmm

@@ -23,7 +23,7 @@ __all__ = [
     "Q8_0", "Q8_1", "Q4_K", "Q6_K", "row_bytes", "check_launch",
     "gpu_quantize_q8_1_into", "gpu_quantize_q8_1", "gpu_quantize_weights_into", "gpu_quantize_weights",
     "gpu_dequantize_into", "gpu_dequantize", "gpu_qmatvec_into", "gpu_qmatvec", "gpu_qblock_dots",
-    "MatvecJobs", "gpu_qmatvec_batch_into",
+    "MatvecJobs", "gpu_qmatvec_batch_into", "TpComm", "gpu_qmatvec_tp_into", "gpu_qmatvec_batch_tp_into",
     "gpu_qgemm_q4_k_bf16_into", "gpu_qgemm_q4_k_bf16",
     "gpu_qlinear",
     "gpu_rmsnorm_q8_1_into", "gpu_rope_kv_append", "gpu_glu_act_q8_1_into", "gpu_embed_rows_into", "gpu_argmax_rows",
@@ -137,11 +137,12 @@ class MatvecJobs:
     def __init__(self):
         self._jobs, self._keep = [], []
 
-    def add(self, qtype, w, xq, out, n, k, y_stride=0, select=None, select_stride_bytes=0):
+    def add(self, qtype, w, xq, out, n, k, y_stride=0, select=None, select_stride_bytes=0, tp_sum=False):
         """out(m,n) = xq(m,k) . w(n,k)^T, as gpu_qmatvec_into; `select` (int32 device tensor) makes the
-        matrix w + select[0] * select_stride_bytes, resolved on the device when the kernel runs."""
+        matrix w + select[0] * select_stride_bytes, resolved on the device when the kernel runs; tp_sum
+        (gpu_qmatvec_batch_tp_into only): the outputs are summed over the tensor-parallel ranks."""
         self._jobs.append(_lib.MatvecJob(qtype, n, k, _ptr(w), _ptr(xq), _ptr(out), y_stride,
-                                         _ptr(select) if select is not None else None, select_stride_bytes))
+                                         _ptr(select) if select is not None else None, select_stride_bytes, 1 if tp_sum else 0))
         self._keep.append((w, xq, out, select))
         return self
 
@@ -158,6 +159,53 @@ def gpu_qmatvec_batch_into(jobs, m):
     input (examples/gemma4.rs:653-667, 675-678, 726-742)."""
     arr = jobs.array()
     check(lib().launch_qmatvec_batch(arr, len(jobs), m, _stream()), "launch_qmatvec_batch")
+
+
+class TpComm:
+    """One rank's end of the tensor-parallel sum (qmm_tp_comm_* of include/qmm.h).  The 64-byte handles of
+    the ranks' exchange areas travel through torch.distributed (any host channel would do)."""
+
+    def __init__(self, capacity_floats, group=None):
+        import ctypes as C
+        import torch.distributed as dist
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.h = C.c_void_p()
+        check(lib().qmm_tp_comm_create(self.rank, self.world, capacity_floats, C.byref(self.h)), "qmm_tp_comm_create")
+        buf = C.create_string_buffer(64)
+        check(lib().qmm_tp_comm_export(self.h, buf), "qmm_tp_comm_export")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(buf.raw), group=group)
+        for r, hb in enumerate(handles):
+            if r != self.rank:
+                check(lib().qmm_tp_comm_import(self.h, r, C.create_string_buffer(hb, 64)), "qmm_tp_comm_import")
+        check(lib().qmm_tp_comm_ready(self.h), "qmm_tp_comm_ready")
+        dist.barrier(group=group)
+
+    def close(self):
+        if self.h:
+            lib().qmm_tp_comm_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def gpu_qmatvec_tp_into(comm, qtype, w, xq, out, m, n, k):
+    """Row-parallel projection: this rank's (n, k) column shard against its slice of the activations;
+    out(m,n) receives the sum over the ranks (bit-identical on all of them).  Collective."""
+    _need(w, n * row_bytes(qtype, k), "w")
+    _need(xq, m * row_bytes(Q8_1, k), "xq")
+    _need(out, m * n * 4, "out")
+    check(lib().launch_qmatvec_tp(comm.h, qtype, _ptr(w), _ptr(xq), _ptr(out), m, n, k, _stream()), "launch_qmatvec_tp")
+
+
+def gpu_qmatvec_batch_tp_into(comm, jobs, m):
+    """A job list in which the jobs added with tp_sum=True are summed over the ranks.  Collective."""
+    arr = jobs.array()
+    check(lib().launch_qmatvec_batch_tp(comm.h, arr, len(jobs), m, _stream()), "launch_qmatvec_batch_tp")
 
 
 def gpu_qblock_dots(qtype, w, xq, n, k):

@@ -75,3 +75,74 @@ def tp_parity(wide=False, steps=5, verbose=False):
     worst, scale_at_worst, agree = float(res[0]), float(res[1]), bool(res[2] > 0.5)
     return {"n": world, "wide": bool(wide), "max_logit_diff": worst, "logit_scale": scale_at_worst, "tokens_agree": agree,
             "ok": bool(agree and worst <= LOGIT_TOL * scale_at_worst)}
+
+
+def tp_matvec_parity(verbose=False):
+    """The row-parallel projections with the fused sum (launch_qmatvec_tp, launch_qmatvec_batch_tp) against
+    the same shards computed one by one on rank 0 and added in rank order: bit-identical, and the same bits on
+    every rank.  Returns {"n", "cases", "ok"}."""
+    from ._lib import Q8_0
+    rank, world = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    n_max, m_max = 4096, 16
+    comm = ops.TpComm(4 * m_max * n_max)
+    ok, cases = True, 0
+
+    def shard(qt, n, kl, r, seed):
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed * 131 + r)
+        w = ops.gpu_quantize_weights(qt, torch.randn(n, kl, device=dev, generator=g) * 0.02)
+        xq = ops.gpu_quantize_q8_1(torch.randn(m_max, kl, device=dev, generator=g))
+        return w, xq
+
+    def reference(qt, n, kl, m, seed):
+        """Sum over ranks of the single-GPU result of every shard, in rank order (computed on this rank)."""
+        acc = torch.zeros(m, n, device=dev)
+        for r in range(world):
+            w, xq = shard(qt, n, kl, r, seed)
+            acc += ops.gpu_qmatvec(qt, w, xq, m, n, kl)
+        return acc
+
+    def same_everywhere(y):
+        ys = [torch.empty_like(y) for _ in range(world)]
+        dist.all_gather(ys, y.contiguous())
+        return all(torch.equal(ys[0], t) for t in ys)
+
+    for seed, (qt, n, kl, m) in enumerate([(Q4_K, 4096, 1792, 1), (Q6_K, 4096, 1792, 1), (Q4_K, 512, 3584, 2), (Q8_0, 300, 512, 1),
+                                           (Q4_K, 4096, 2048, 5), (Q6_K, 2048, 2048, 16), (Q6_K, 1000, 1792, 9), (Q4_K, 37, 256, 3)]):
+        w, xq = shard(qt, n, kl, rank, seed)
+        for rep in range(2):   # two exchanges in a row use the two alternating buffers
+            y = torch.full((m, n), float("nan"), device=dev)
+            ops.gpu_qmatvec_tp_into(comm, qt, w, xq, y, m, n, kl)
+            torch.cuda.synchronize()
+            ops.check_launch()
+            want = reference(qt, n, kl, m, seed)
+            good = torch.equal(y, want) and same_everywhere(y)
+            if verbose and rank == 0:
+                print(f"launch_qmatvec_tp type {qt} n {n} k_local {kl} m {m} rep {rep}: {'ok' if good else 'MISMATCH'} "
+                      f"(max diff {float((y - want).abs().max()):.3e})")
+            ok, cases = ok and good, cases + 1
+    # a job list: two local projections and three summed ones of different shapes
+    for m in (1, 2, 5):
+        specs = [(Q4_K, 1024, 1024, False), (Q4_K, 2048, 1792, True), (Q6_K, 512, 1792, True), (Q8_0, 256, 512, False), (Q4_K, 4096, 512, True)]
+        jobs = ops.MatvecJobs()
+        outs, wants = [], []
+        for i, (qt, n, kl, summed) in enumerate(specs):
+            w, xq = shard(qt, n, kl, rank, 100 + i)
+            y = torch.full((m, n), float("nan"), device=dev)
+            jobs.add(qt, w, xq, y, n, kl, tp_sum=summed)
+            outs.append(y)
+            wants.append(reference(qt, n, kl, m, 100 + i) if summed else ops.gpu_qmatvec(qt, w, xq, m, n, kl))
+        ops.gpu_qmatvec_batch_tp_into(comm, jobs, m)
+        torch.cuda.synchronize()
+        ops.check_launch()
+        for i, (y, want) in enumerate(zip(outs, wants)):
+            good = torch.equal(y, want) and (not specs[i][3] or same_everywhere(y))
+            if verbose and rank == 0:
+                print(f"launch_qmatvec_batch_tp m {m} job {i} {specs[i]}: {'ok' if good else 'MISMATCH'}")
+            ok, cases = ok and good, cases + 1
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    comm.close()
+    dist.barrier()
+    return {"n": world, "cases": cases, "ok": bool(int(flag.item()))}

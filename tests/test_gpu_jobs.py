@@ -162,9 +162,50 @@ def test_job_list_falls_back_and_rejects(ops):
         assert_close(g, w, "fallback")
     L = lib()
     assert L.launch_qmatvec_batch(None, 1, 1, None) == -1
-    j = (MatvecJob * 1)(MatvecJob(Q4, 8, 100, 16, 16, 16, 0, None, 0))
+    j = (MatvecJob * 1)(MatvecJob(Q4, 8, 100, 16, 16, 16, 0, None, 0, 0))
     assert L.launch_qmatvec_batch(j, 1, 1, None) == -2
-    j = (MatvecJob * 1)(MatvecJob(99, 8, 256, 16, 16, 16, 0, None, 0))
+    j = (MatvecJob * 1)(MatvecJob(99, 8, 256, 16, 16, 16, 0, None, 0, 0))
     assert L.launch_qmatvec_batch(j, 1, 1, None) == -5
-    j = (MatvecJob * 1)(MatvecJob(Q4, 8, 256, 16, 16, 16, 0, 16, 24))   # selector stride not a multiple of 16
+    j = (MatvecJob * 1)(MatvecJob(Q4, 8, 256, 16, 16, 16, 0, 16, 24, 0))   # selector stride not a multiple of 16
     assert L.launch_qmatvec_batch(j, 1, 1, None) == -4
+
+
+def test_tp_exchange_with_one_rank_equals_plain_launches(ops):
+    """The tensor-parallel entry points with a world of one rank: the outputs travel through the exchange
+    area (push, poll, sum of one term) and must equal the plain launchers bit for bit, exchange after
+    exchange (the two buffers alternate; the sequence counter advances on the device)."""
+    import ctypes as C
+    from nates_recipe_rs_b200._lib import check, lib
+    L = lib()
+    comm = C.c_void_p()
+    check(L.qmm_tp_comm_create(0, 1, 16 * 4096, C.byref(comm)), "qmm_tp_comm_create")
+    stream = torch.cuda.current_stream().cuda_stream
+    try:
+        for rep, (qtype, n, k, m) in enumerate([(Q4, 4096, 1024, 1), (Q6, 1000, 2048, 2), (Q4, 4096, 2048, 16), (Q8, 333, 512, 3), (Q6, 512, 4096, 7)]):
+            g = torch.Generator(device="cuda").manual_seed(70 + rep)
+            w = ops.gpu_quantize_weights(qtype, torch.randn(n, k, device="cuda", generator=g) * 0.02)
+            xq = ops.gpu_quantize_q8_1(torch.randn(m, k, device="cuda", generator=g))
+            y = torch.full((m, n), float("nan"), device="cuda")
+            check(L.launch_qmatvec_tp(comm, qtype, w.data_ptr(), xq.data_ptr(), y.data_ptr(), m, n, k, stream), "launch_qmatvec_tp")
+            assert torch.equal(y, ops.gpu_qmatvec(qtype, w, xq, m, n, k)), (rep, qtype, n, k, m)
+        # a job list with summed and local jobs
+        jobs = ops.MatvecJobs()
+        pairs = []
+        for i, (qtype, n, k, summed) in enumerate([(Q4, 1024, 1024, False), (Q4, 2048, 1792, True), (Q6, 512, 1792, True), (Q4, 4096, 512, True)]):
+            g = torch.Generator(device="cuda").manual_seed(90 + i)
+            w = ops.gpu_quantize_weights(qtype, torch.randn(n, k, device="cuda", generator=g) * 0.02)
+            xq = ops.gpu_quantize_q8_1(torch.randn(1, k, device="cuda", generator=g))
+            y = torch.full((1, n), float("nan"), device="cuda")
+            jobs.add(qtype, w, xq, y, n, k, tp_sum=summed)
+            pairs.append((qtype, w, xq, y, n, k))
+        arr = jobs.array()
+        for _ in range(3):
+            check(L.launch_qmatvec_batch_tp(comm, arr, len(jobs), 1, stream), "launch_qmatvec_batch_tp")
+        for qtype, w, xq, y, n, k in pairs:
+            assert torch.allclose(y, ops.gpu_qmatvec(qtype, w, xq, 1, n, k), rtol=REL_TOL, atol=ABS_TOL)
+        ops.check_launch()
+        # too large for the exchange area
+        big = torch.zeros(8, device="cuda")
+        assert L.launch_qmatvec_tp(comm, Q4, big.data_ptr(), big.data_ptr(), big.data_ptr(), 32, 4096, 256, stream) == -7
+    finally:
+        check(L.qmm_tp_comm_destroy(comm), "qmm_tp_comm_destroy")
