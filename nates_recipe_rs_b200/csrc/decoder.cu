@@ -284,15 +284,6 @@ static int launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem
     return QMM_OK;
 }
 
-static int norm_threads(int hidden) {
-    // The fewest passes of at most 1024 threads that cover the row, then the smallest whole number of warps
-    // per pass that still covers it (hidden is a multiple of 256, so every warp is either all inside the
-    // row or all outside it, whatever the block size).
-    const int passes = (hidden + 1023) / 1024;
-    const int per_pass = (hidden + passes - 1) / passes;
-    return (per_pass + 31) & ~31;
-}
-
 // residual add of the projection output `which` (or none: -1), RMSNorm with gamma, Q8_1 into xq_h
 static int add_norm(Decoder* d, int which, const float* gamma, int batch, cudaStream_t s) {
     PartPtrs parts = {};
@@ -306,8 +297,7 @@ static int add_norm(Decoder* d, int which, const float* gamma, int batch, cudaSt
             parts.p[0] = d->part[which];
         }
     }
-    return launch_pdl(add_rmsnorm_q8_kernel, dim3(batch), dim3(norm_threads(d->c.hidden)), 0, s, d->x, parts, n_parts, (long)d->c.hidden,
-                      gamma, d->xq_h, d->c.hidden, d->c.rms_eps, rcv, (float*)nullptr);
+    return add_rmsnorm_launch(d->x, parts, n_parts, (long)d->c.hidden, gamma, d->xq_h, d->c.hidden, d->c.rms_eps, rcv, nullptr, batch, true, s);
 }
 
 // row-parallel projection (O, down): the output goes to part[which], or with tensor parallelism into every

@@ -8,8 +8,10 @@
 // in fp32 with fp16 KV, as the decode configurations ask.  All of them take part in
 // programmatic dependent launch so the following matvec can prefetch its weights.
 #include "qmm_formats.cuh"
+#include <cooperative_groups.h>
 
 namespace qmm {
+namespace cg = cooperative_groups;
 
 __device__ __forceinline__ uint64_t mix64(uint64_t z) {
     z += 0x9E3779B97F4A7C15ull;
@@ -155,6 +157,150 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_q8_kernel(float* __restrict_
             warp_store_q8_1(nv, qrow + (size_t)(e >> 5) * Q8_1_BYTES, lane);
         }
     }
+}
+
+// The same operator with the row split over a cluster of NORM_CLUSTER CTAs (hidden a multiple of 256, at most
+// 8192): each CTA owns hidden / NORM_CLUSTER consecutive elements, the partial sums of squares meet through
+// distributed shared memory in a fixed order.  A row of 8192 values handled by one CTA is bound by that
+// CTA's memory latency (and, tensor parallel, by one SM polling 8 x 8192 exchange words); eight CTAs of 256
+// threads keep all their loads in flight at once: every thread first issues the exchange-word loads of all
+// its elements and ranks, then checks the sequence numbers and re-polls only what had not arrived.
+constexpr int NORM_CLUSTER = 8;
+constexpr int NORM_CL_THREADS = 256;
+constexpr int NORM_CL_PER_THREAD = 4;   // slice <= 1024 elements
+__global__ void __launch_bounds__(NORM_CL_THREADS) add_rmsnorm_q8_cluster_kernel(float* __restrict__ x, const PartPtrs parts, int n_parts,
+                                                                                long part_stride, const float* __restrict__ gamma,
+                                                                                uint8_t* __restrict__ xq, int hidden, float eps, const TpRecv rcv,
+                                                                                float* __restrict__ out_f32) {
+    __shared__ float red[32];
+    __shared__ float cl_ss;     // this CTA's sum of squares, read by the other CTAs of the cluster
+    __shared__ int cl_bad;      // this CTA gave up on a peer
+    __shared__ int give_up;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int cl = (int)cluster.num_blocks(), cr = (int)cluster.block_rank();
+    pdl_release_dependents();
+    const int slice = hidden / cl, e0 = cr * slice;
+    const int b = blockIdx.y, lane = threadIdx.x & 31;
+    float gm[NORM_CL_PER_THREAD];
+#pragma unroll
+    for (int i = 0; i < NORM_CL_PER_THREAD; ++i) {
+        const int o = i * NORM_CL_THREADS + threadIdx.x;
+        gm[i] = o < slice ? (gamma ? gamma[e0 + o] : 1.f) : 0.f;
+    }
+    if (threadIdx.x == 0) give_up = 0;
+    __syncthreads();
+    pdl_wait_prior_grids();
+    const bool exchange = rcv.tp > 1;
+    const unsigned seq = exchange ? tp_next_seq(rcv.counter) : 0u;
+    float* xr = x + (size_t)b * hidden;
+    float v[NORM_CL_PER_THREAD];
+    if (exchange) {
+        const unsigned long long* p0 = rcv.base + ((seq & 1u) ? rcv.buf_words : 0) + (long)b * part_stride + e0 + threadIdx.x;
+        unsigned long long w[NORM_CL_PER_THREAD][QMM_TP_MAX];
+#pragma unroll
+        for (int i = 0; i < NORM_CL_PER_THREAD; ++i)
+#pragma unroll
+            for (int r = 0; r < QMM_TP_MAX; ++r)
+                if (r < rcv.tp && i * NORM_CL_THREADS + (int)threadIdx.x < slice)
+                    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w[i][r]) : "l"(p0 + (long)r * rcv.src_words + i * NORM_CL_THREADS) : "memory");
+#pragma unroll
+        for (int i = 0; i < NORM_CL_PER_THREAD; ++i) {
+            const int o = i * NORM_CL_THREADS + threadIdx.x;
+            v[i] = 0.f;
+            if (o < slice) {
+                float t = xr[e0 + o];
+#pragma unroll
+                for (int r = 0; r < QMM_TP_MAX; ++r)  // rank order: the same sum on every rank
+                    if (r < rcv.tp) {
+                        float pv = __uint_as_float((unsigned)w[i][r]);
+                        if ((unsigned)(w[i][r] >> 32) != seq && !tp_poll_word(rcv, seq, r, (long)b * part_stride + e0 + o, pv, &give_up)) pv = 0.f;
+                        t += pv;
+                    }
+                v[i] = t;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NORM_CL_PER_THREAD; ++i) {
+            const int o = i * NORM_CL_THREADS + threadIdx.x;
+            v[i] = 0.f;
+            if (o < slice) {
+                float t = xr[e0 + o];
+                if (n_parts > 0) t += parts.p[0][(size_t)b * part_stride + e0 + o];
+                v[i] = t;
+            }
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_CL_PER_THREAD; ++i) ss += v[i] * v[i];
+    ss = block_sum(ss, red);
+    if (threadIdx.x == 0) {
+        cl_ss = ss;
+        cl_bad = give_up;
+    }
+    cluster.sync();
+    float total = 0.f;
+    int bad = 0;
+    for (int c = 0; c < cl; ++c) {  // fixed order
+        total += *cluster.map_shared_rank(&cl_ss, c);
+        bad |= *cluster.map_shared_rank(&cl_bad, c);
+    }
+    cluster.sync();  // nobody leaves while its shared memory may still be read
+    if (exchange && threadIdx.x == 0) {
+        if (give_up) atomicExch(&g_device_status, DEV_TIMEOUT_PEER);
+        tp_consumer_done(rcv, seq, gridDim.x * gridDim.y);
+    }
+    if (bad) return;  // a peer never arrived: the row keeps its old x and xq
+    const float inv = rsqrtf(total / (float)hidden + eps);
+    uint8_t* qrow = xq + (size_t)b * (hidden / 32) * Q8_1_BYTES;
+#pragma unroll
+    for (int i = 0; i < NORM_CL_PER_THREAD; ++i) {
+        const int o = i * NORM_CL_THREADS + threadIdx.x;  // a warp covers 32 consecutive elements = one block
+        if (o < slice) {
+            const int e = e0 + o;
+            if (exchange || n_parts > 0) xr[e] = v[i];
+            const float nv = v[i] * inv * gm[i];
+            if (out_f32) out_f32[(size_t)b * hidden + e] = nv;
+            warp_store_q8_1(nv, qrow + (size_t)(e >> 5) * Q8_1_BYTES, lane);
+        }
+    }
+}
+
+// Launches the residual + norm + Q8_1 operator: the cluster form when the row splits evenly, else one CTA per row.
+inline int add_rmsnorm_launch(float* x, const PartPtrs& parts, int n_parts, long part_stride, const float* gamma, uint8_t* xq, int hidden,
+                              float eps, const TpRecv& rcv, float* out_f32, int rows, bool pdl, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (pdl && overlap_enabled()) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    const bool clustered = hidden % (NORM_CLUSTER * 32) == 0 && hidden / NORM_CLUSTER <= NORM_CL_THREADS * NORM_CL_PER_THREAD;
+    if (clustered) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = NORM_CLUSTER;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+        cfg.gridDim = dim3(NORM_CLUSTER, rows);
+        cfg.blockDim = dim3(NORM_CL_THREADS);
+        cfg.attrs = attr;
+        cfg.numAttrs = na;
+        QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, add_rmsnorm_q8_cluster_kernel, x, parts, n_parts, part_stride, gamma, xq, hidden, eps, rcv, out_f32));
+        return QMM_OK;
+    }
+    const int passes = (hidden + 1023) / 1024;
+    const int threads = (((hidden + passes - 1) / passes) + 31) & ~31;
+    cfg.gridDim = dim3(rows);
+    cfg.blockDim = dim3(threads);
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, add_rmsnorm_q8_kernel, x, parts, n_parts, part_stride, gamma, xq, hidden, eps, rcv, out_f32));
+    return QMM_OK;
 }
 
 // NeoX rotary embedding of q (in place, fp32) and k, then k and v appended to the fp16 cache at `pos`.

@@ -10,12 +10,6 @@
 
 namespace qmm {
 
-static int ops_norm_threads(int cols) {
-    const int passes = (cols + 1023) / 1024;
-    const int per_pass = (cols + passes - 1) / passes;
-    return (per_pass + 31) & ~31;
-}
-
 __global__ void scale_f32_kernel(float* __restrict__ x, float scalar, long n) {
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) x[i] = __fmul_rn(x[i], scalar);
@@ -38,10 +32,8 @@ int launch_add_rmsnorm_q8_1(float* x, const float* add, const float* gamma, void
     PartPtrs parts = {};
     parts.p[0] = add;
     TpRecv none = {};
-    add_rmsnorm_q8_kernel<<<rows, ops_norm_threads(cols), 0, as_stream(stream)>>>(x, parts, add ? 1 : 0, (long)cols, gamma,
-                                                                                    static_cast<uint8_t*>(xq), cols, eps, none, out_f32);
-    QMM_CUDA_TRY(cudaGetLastError());
-    return QMM_OK;
+    return add_rmsnorm_launch(x, parts, add ? 1 : 0, (long)cols, gamma, static_cast<uint8_t*>(xq), cols, eps, none, out_f32, rows, false,
+                              as_stream(stream));
 }
 
 int launch_rope_kv_append(float* qkv, void* kcache, void* vcache, int batch, int n_q_heads, int n_kv_heads, int head_dim, int pos,
