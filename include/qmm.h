@@ -56,6 +56,8 @@ extern "C" {
 #define QMM_ERR_TYPE (-5)        /* unknown type tag                                   */
 #define QMM_ERR_CUDA (-6)        /* the CUDA runtime refused the launch (see qmm_last_cuda_error) */
 #define QMM_ERR_SCRATCH (-7)     /* request exceeds a fixed scratch capacity           */
+#define QMM_ERR_IO (-8)          /* a file could not be opened, read or written        */
+#define QMM_ERR_FORMAT (-9)      /* a file is not what it claims to be (bad magic, truncated, missing tensor) */
 
 const char* qmm_status_string(int status);
 /* cudaError_t of the most recent failed runtime call made by this library on this thread */

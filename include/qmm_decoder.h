@@ -10,6 +10,7 @@
 #ifndef QMM_DECODER_H
 #define QMM_DECODER_H
 #include "qmm.h"
+#include "qmm_gguf.h"
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -45,6 +46,16 @@ typedef struct {
 /* Builds the model on the current device: allocates and fills weights (seeded closed-form normal,
  * sigma 0.02, quantized on the device), KV cache (fp16, zeroed) and every activation buffer. */
 int qmm_decoder_create(const qmm_decoder_config* cfg, void** handle);
+/* The same engine with its weights read from a GGUF file (include/qmm_gguf.h): hyper-parameters from the
+ * "<architecture>." metadata keys of the format's naming convention, matrices from blk.<i>.attn_q /
+ * attn_k / attn_v / attn_output / ffn_gate / ffn_up / ffn_down .weight, token_embd.weight, output.weight
+ * (absent: tied to token_embd) and the f32 norm gains; every rank reads only its shard (row ranges of the
+ * column-parallel matrices, whole-block column ranges of O and down).  ctx_len 0 = the file's context
+ * length.  One block type per role across the layers.  This is the place where the upstream would plug a
+ * quantized dense into its forward (recipe-infer/src/forward.rs:372-384). */
+int qmm_decoder_create_from_gguf(const char* path, int max_batch, int ctx_len, int tp_rank, int tp_size, void** handle);
+/* Writes the model of a single-GPU decoder as a GGUF file (architecture NULL = "llama"). */
+int qmm_decoder_export_gguf(void* handle, const char* path, const char* architecture);
 int qmm_decoder_destroy(void* handle);
 /* packed weight bytes this rank streams per decoded token (all layers + head) */
 long qmm_decoder_weight_bytes(void* handle);

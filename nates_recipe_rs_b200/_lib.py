@@ -19,6 +19,12 @@ class MatvecJob(C.Structure):
                 ("y_stride", C.c_long), ("select", C.c_void_p), ("select_stride_bytes", C.c_long), ("tp_sum", C.c_int)]
 
 
+class GgufTensorInfo(C.Structure):
+    """qmm_gguf_tensor of include/qmm_gguf.h."""
+    _fields_ = [("name", C.c_char * 128), ("type", C.c_int), ("n_dims", C.c_int), ("dims", C.c_long * 4), ("file_offset", C.c_long),
+                ("bytes", C.c_long)]
+
+
 # name -> (restype, argtypes); must list every symbol include/qmm.h declares
 SIGNATURES = {
     "qmm_status_string": (C.c_char_p, [i32]),
@@ -62,6 +68,22 @@ SIGNATURES = {
     "qmm_argmax_scratch_bytes": (i64, [i32]),
     "launch_argmax_rows": (i32, [vp, vp, vp, vp, i32, i32, vp]),
     "launch_scale_f32": (i32, [vp, C.c_float, i64, vp]),
+    "qmm_gguf_open": (i32, [C.c_char_p, C.POINTER(vp)]),
+    "qmm_gguf_close": (i32, [vp]),
+    "qmm_gguf_tensor_count": (i64, [vp]),
+    "qmm_gguf_find": (i64, [vp, C.c_char_p]),
+    "qmm_gguf_tensor_info": (i32, [vp, i64, C.POINTER(GgufTensorInfo)]),
+    "qmm_gguf_read_tensor": (i32, [vp, i64, vp, i64]),
+    "qmm_gguf_upload_tensor": (i32, [vp, i64, vp, i64, vp]),
+    "qmm_gguf_meta_u64": (i32, [vp, C.c_char_p, C.POINTER(C.c_ulonglong)]),
+    "qmm_gguf_meta_f64": (i32, [vp, C.c_char_p, C.POINTER(C.c_double)]),
+    "qmm_gguf_meta_str": (i64, [vp, C.c_char_p, C.c_char_p, i64]),
+    "qmm_gguf_writer_create": (i32, [C.c_char_p, C.POINTER(vp)]),
+    "qmm_gguf_writer_meta_u32": (i32, [vp, C.c_char_p, C.c_uint]),
+    "qmm_gguf_writer_meta_f32": (i32, [vp, C.c_char_p, C.c_float]),
+    "qmm_gguf_writer_meta_str": (i32, [vp, C.c_char_p, C.c_char_p]),
+    "qmm_gguf_writer_add_tensor": (i32, [vp, C.c_char_p, i32, i32, C.POINTER(C.c_long), vp, i64]),
+    "qmm_gguf_writer_finish": (i32, [vp]),
 }
 
 _lib = None

@@ -53,6 +53,8 @@ const char* qmm_status_string(int status) {
     case QMM_ERR_TYPE: return "unknown block type";
     case QMM_ERR_CUDA: return "CUDA runtime error (see qmm_last_cuda_error)";
     case QMM_ERR_SCRATCH: return "request exceeds the fixed scratch capacity";
+    case QMM_ERR_IO: return "file could not be opened, read or written";
+    case QMM_ERR_FORMAT: return "file format error (bad magic, truncated, or a tensor is missing or of another type)";
     }
     return "unknown status";
 }

@@ -8,6 +8,7 @@
 #include "qmm_formats.cuh"
 #include "../../include/qmm_decoder.h"
 #include <algorithm>
+#include <string>
 #include <vector>
 #include <cstring>
 
@@ -126,6 +127,80 @@ static int init_gamma(Decoder* d, float* g, int n, uint64_t seed, cudaStream_t s
     return QMM_OK;
 }
 
+// Where a decoder's weights come from: a seeded closed-form model quantized on the device, or a GGUF file.
+// matrix(): the packed (rows, k) shard made of rows [row0, row0 + rows) and columns [col0, col0 + k) of the full
+// (., k_full) tensor `which` of `layer`; vector(): an f32 norm gain of n values.
+struct WeightSource {
+    virtual ~WeightSource() {}
+    virtual int matrix(Decoder* d, uint8_t* dst, int type, int layer, int which, long rows, int k, long row0, int col0, int k_full,
+                       cudaStream_t s) = 0;
+    virtual int vector(Decoder* d, float* dst, int layer, int which, int n, cudaStream_t s) = 0;
+};
+
+struct SeededSource : WeightSource {
+    float* tmp = nullptr;  // f32 staging on the device, owned by the decoder's allocation list until create() frees it
+    long tmp_elems = 0;
+    int matrix(Decoder* d, uint8_t* dst, int type, int layer, int which, long rows, int k, long row0, int col0, int k_full,
+               cudaStream_t s) override {
+        // the head and the embedding of a tied model are the same tensor
+        const int seed_which = which == QMM_T_EMBED ? QMM_T_HEAD : which;
+        return init_matrix(d, dst, type, rows, k, row0, col0, k_full, tensor_seed(d, layer, seed_which), tmp, tmp_elems, s);
+    }
+    int vector(Decoder* d, float* dst, int layer, int which, int n, cudaStream_t s) override {
+        return init_gamma(d, dst, n, tensor_seed(d, layer, which), s);
+    }
+};
+
+int gguf_upload_rows(GgufFile* f, long index, uint64_t row0, uint64_t rows, uint64_t col_off, uint64_t width, void* device_dst,
+                     cudaStream_t stream);
+
+// GGUF tensor names of a Llama/Gemma-style decoder (the naming convention of the format's reference tools)
+static std::string gguf_tensor_name(int layer, int which) {
+    const char* base = nullptr;
+    switch (which) {
+    case QMM_T_ATTN_NORM: base = "attn_norm"; break;
+    case QMM_T_WQ: base = "attn_q"; break;
+    case QMM_T_WK: base = "attn_k"; break;
+    case QMM_T_WV: base = "attn_v"; break;
+    case QMM_T_WO: base = "attn_output"; break;
+    case QMM_T_FFN_NORM: base = "ffn_norm"; break;
+    case QMM_T_WGATE: base = "ffn_gate"; break;
+    case QMM_T_WUP: base = "ffn_up"; break;
+    case QMM_T_WDOWN: base = "ffn_down"; break;
+    case QMM_T_FINAL_NORM: return "output_norm.weight";
+    case QMM_T_HEAD: return "output.weight";
+    case QMM_T_EMBED: return "token_embd.weight";
+    }
+    return "blk." + std::to_string(layer) + "." + (base ? base : "?") + ".weight";
+}
+
+struct GgufSource : WeightSource {
+    GgufFile* f = nullptr;
+    long find(int layer, int which) const {
+        auto it = f->by_name.find(gguf_tensor_name(layer, which));
+        if (it == f->by_name.end() && which == QMM_T_HEAD) it = f->by_name.find(gguf_tensor_name(layer, QMM_T_EMBED));  // tied
+        return it == f->by_name.end() ? -1 : it->second;
+    }
+    int matrix(Decoder*, uint8_t* dst, int type, int layer, int which, long rows, int k, long row0, int col0, int k_full,
+               cudaStream_t s) override {
+        const long idx = find(layer, which);
+        if (idx < 0) return QMM_ERR_FORMAT;
+        const GgufTensor& t = f->tensors[idx];
+        if ((int)t.type != type || t.n_dims != 2 || (long)t.dims[0] != k_full || (long)t.dims[1] < row0 + rows) return QMM_ERR_FORMAT;
+        const int be = type == QMM_TYPE_Q8_0 ? 32 : 256;
+        if (col0 % be != 0 || k % be != 0) return QMM_ERR_SHAPE;
+        const uint64_t bb = (uint64_t)type_row_bytes(type, be);
+        return gguf_upload_rows(f, idx, (uint64_t)row0, (uint64_t)rows, (uint64_t)(col0 / be) * bb, (uint64_t)(k / be) * bb, dst, s);
+    }
+    int vector(Decoder*, float* dst, int layer, int which, int n, cudaStream_t s) override {
+        auto it = f->by_name.find(gguf_tensor_name(layer, which));
+        if (it == f->by_name.end()) return QMM_ERR_FORMAT;
+        const GgufTensor& t = f->tensors[it->second];
+        if (t.type != 0 || (long)t.dims[0] != n || t.bytes != (uint64_t)n * 4) return QMM_ERR_FORMAT;
+        return gguf_upload_rows(f, it->second, 0, 1, 0, (uint64_t)n * 4, dst, s);
+    }
+};
+
 static void destroy(Decoder* d) {
     if (!d) return;
     tp_comm_destroy(d->comm);
@@ -136,7 +211,7 @@ static void destroy(Decoder* d) {
     delete d;
 }
 
-static int create(const qmm_decoder_config* cfg, Decoder** out) {
+static int create(const qmm_decoder_config* cfg, WeightSource* src, Decoder** out) {
     const qmm_decoder_config& c = *cfg;
     if (c.n_layers <= 0 || c.hidden <= 0 || c.head_dim <= 0 || c.n_q_heads <= 0 || c.n_kv_heads <= 0 || c.ffn <= 0 || c.vocab <= 0 ||
         c.ctx_len <= 0 || c.max_batch <= 0 || c.tp_size <= 0 || c.tp_rank < 0 || c.tp_rank >= c.tp_size)
@@ -173,9 +248,12 @@ static int create(const qmm_decoder_config* cfg, Decoder** out) {
         destroy(d);
         return cuda_fail(cudaGetLastError());
     }
-    const long tmp_elems = 32l << 20;  // 128 MB of f32 staging for initialisation
     float* tmp = nullptr;
-    TRY(dev_alloc(d, &tmp, tmp_elems * sizeof(float)));
+    if (SeededSource* seeded = dynamic_cast<SeededSource*>(src)) {
+        seeded->tmp_elems = 32l << 20;  // 128 MB of f32 staging for initialisation
+        TRY(dev_alloc(d, &tmp, seeded->tmp_elems * sizeof(float)));
+        seeded->tmp = tmp;
+    }
     const int r = c.tp_rank;
     d->layers.resize(c.n_layers);
     long per_token = 0;
@@ -183,47 +261,49 @@ static int create(const qmm_decoder_config* cfg, Decoder** out) {
         LayerWeights& L = d->layers[l];
         TRY(dev_alloc(d, &L.attn_norm, H * sizeof(float)));
         TRY(dev_alloc(d, &L.ffn_norm, H * sizeof(float)));
-        TRY(init_gamma(d, L.attn_norm, H, tensor_seed(d, l, QMM_T_ATTN_NORM), s));
-        TRY(init_gamma(d, L.ffn_norm, H, tensor_seed(d, l, QMM_T_FFN_NORM), s));
+        TRY(src->vector(d, L.attn_norm, l, QMM_T_ATTN_NORM, H, s));
+        TRY(src->vector(d, L.ffn_norm, l, QMM_T_FFN_NORM, H, s));
         // [q heads | k heads] of this rank: rows of the full Wq then rows of the full Wk
         // (with V right behind them when it has the same type: one projection launch instead of two)
         const size_t qk_b = (size_t)d->qk_rows * type_row_bytes(c.type_attn_qk, H);
         const size_t v_b = (size_t)d->v_rows * type_row_bytes(c.type_attn_v, H);
         const bool qkv_fused = c.type_attn_v == c.type_attn_qk;
         TRY(dev_alloc(d, &L.wqk, qk_b + (qkv_fused ? v_b : 0)));
-        TRY(init_matrix(d, L.wqk, c.type_attn_qk, (long)d->nq * hd, H, (long)r * d->nq * hd, 0, H, tensor_seed(d, l, QMM_T_WQ), tmp, tmp_elems, s));
-        TRY(init_matrix(d, L.wqk + (size_t)d->nq * hd * type_row_bytes(c.type_attn_qk, H), c.type_attn_qk, (long)d->nkv * hd, H,
-                        (long)r * d->nkv * hd, 0, H, tensor_seed(d, l, QMM_T_WK), tmp, tmp_elems, s));
+        TRY(src->matrix(d, L.wqk, c.type_attn_qk, l, QMM_T_WQ, (long)d->nq * hd, H, (long)r * d->nq * hd, 0, H, s));
+        TRY(src->matrix(d, L.wqk + (size_t)d->nq * hd * type_row_bytes(c.type_attn_qk, H), c.type_attn_qk, l, QMM_T_WK, (long)d->nkv * hd, H,
+                        (long)r * d->nkv * hd, 0, H, s));
         if (qkv_fused) {
             L.wv = L.wqk + qk_b;
         } else {
             TRY(dev_alloc(d, &L.wv, v_b));
         }
-        TRY(init_matrix(d, L.wv, c.type_attn_v, d->v_rows, H, (long)r * d->v_rows, 0, H, tensor_seed(d, l, QMM_T_WV), tmp, tmp_elems, s));
+        TRY(src->matrix(d, L.wv, c.type_attn_v, l, QMM_T_WV, d->v_rows, H, (long)r * d->v_rows, 0, H, s));
         const size_t o_b = (size_t)H * type_row_bytes(c.type_attn_o, ao);
         TRY(dev_alloc(d, &L.wo, o_b));
-        TRY(init_matrix(d, L.wo, c.type_attn_o, H, ao, 0, r * ao, c.n_q_heads * hd, tensor_seed(d, l, QMM_T_WO), tmp, tmp_elems, s));
+        TRY(src->matrix(d, L.wo, c.type_attn_o, l, QMM_T_WO, H, ao, 0, r * ao, c.n_q_heads * hd, s));
         const size_t gu_b = (size_t)2 * d->ffn_l * type_row_bytes(c.type_ffn_gate_up, H);
         TRY(dev_alloc(d, &L.wgu, gu_b));
-        TRY(init_matrix(d, L.wgu, c.type_ffn_gate_up, d->ffn_l, H, (long)r * d->ffn_l, 0, H, tensor_seed(d, l, QMM_T_WGATE), tmp, tmp_elems, s));
-        TRY(init_matrix(d, L.wgu + (size_t)d->ffn_l * type_row_bytes(c.type_ffn_gate_up, H), c.type_ffn_gate_up, d->ffn_l, H,
-                        (long)r * d->ffn_l, 0, H, tensor_seed(d, l, QMM_T_WUP), tmp, tmp_elems, s));
+        TRY(src->matrix(d, L.wgu, c.type_ffn_gate_up, l, QMM_T_WGATE, d->ffn_l, H, (long)r * d->ffn_l, 0, H, s));
+        TRY(src->matrix(d, L.wgu + (size_t)d->ffn_l * type_row_bytes(c.type_ffn_gate_up, H), c.type_ffn_gate_up, l, QMM_T_WUP, d->ffn_l, H,
+                        (long)r * d->ffn_l, 0, H, s));
         const size_t dn_b = (size_t)H * type_row_bytes(c.type_ffn_down, d->ffn_l);
         TRY(dev_alloc(d, &L.wdown, dn_b));
-        TRY(init_matrix(d, L.wdown, c.type_ffn_down, H, d->ffn_l, 0, r * d->ffn_l, c.ffn, tensor_seed(d, l, QMM_T_WDOWN), tmp, tmp_elems, s));
+        TRY(src->matrix(d, L.wdown, c.type_ffn_down, l, QMM_T_WDOWN, H, d->ffn_l, 0, r * d->ffn_l, c.ffn, s));
         per_token += (long)(qk_b + v_b + o_b + gu_b + dn_b);
     }
     TRY(dev_alloc(d, &d->final_norm, H * sizeof(float)));
-    TRY(init_gamma(d, d->final_norm, H, tensor_seed(d, -1, QMM_T_FINAL_NORM), s));
+    TRY(src->vector(d, d->final_norm, -1, QMM_T_FINAL_NORM, H, s));
     const size_t head_b = (size_t)d->vocab_l * type_row_bytes(c.type_head, H);
     TRY(dev_alloc(d, &d->head, head_b));
-    TRY(init_matrix(d, d->head, c.type_head, d->vocab_l, H, (long)r * d->vocab_l, 0, H, tensor_seed(d, -1, QMM_T_HEAD), tmp, tmp_elems, s));
+    TRY(src->matrix(d, d->head, c.type_head, -1, QMM_T_HEAD, d->vocab_l, H, (long)r * d->vocab_l, 0, H, s));
     per_token += (long)head_b;
-    if (c.tp_size == 1) {
+    GgufSource* from_file = dynamic_cast<GgufSource*>(src);
+    const bool tied = !from_file || from_file->f->by_name.find("output.weight") == from_file->f->by_name.end();
+    if (c.tp_size == 1 && tied) {
         d->embed = d->head;  // tied embedding
     } else {                 // every rank needs every row of the embedding
         TRY(dev_alloc(d, &d->embed, (size_t)c.vocab * type_row_bytes(c.type_head, H)));
-        TRY(init_matrix(d, d->embed, c.type_head, c.vocab, H, 0, 0, H, tensor_seed(d, -1, QMM_T_HEAD), tmp, tmp_elems, s));
+        TRY(src->matrix(d, d->embed, c.type_head, -1, QMM_T_EMBED, c.vocab, H, 0, 0, H, s));
     }
     d->weight_bytes_per_token = per_token;
 
@@ -259,9 +339,10 @@ static int create(const qmm_decoder_config* cfg, Decoder** out) {
         TRY(tp_comm_create(c.tp_rank, c.tp_size, cap, &d->comm));
     }
     TRY(cuda_status(cudaStreamSynchronize(s)));
-    // the staging buffer of the initialisation is not needed again
-    d->allocs.erase(std::find(d->allocs.begin(), d->allocs.end(), static_cast<void*>(tmp)));
-    TRY(cuda_status(cudaFree(tmp)));
+    if (tmp) {  // the staging buffer of the initialisation is not needed again
+        d->allocs.erase(std::find(d->allocs.begin(), d->allocs.end(), static_cast<void*>(tmp)));
+        TRY(cuda_status(cudaFree(tmp)));
+    }
 #undef TRY
     *out = d;
     return QMM_OK;
@@ -388,10 +469,133 @@ using namespace qmm;
 
 extern "C" {
 
+static int finish_create(const qmm_decoder_config* cfg, WeightSource* src, void** handle);
+
 int qmm_decoder_create(const qmm_decoder_config* cfg, void** handle) {
     if (!cfg || !handle) return QMM_ERR_NULL;
+    SeededSource src;
+    return finish_create(cfg, &src, handle);
+}
+
+// Reads the hyper-parameters of a Llama/Gemma-style decoder from the metadata of a GGUF file ("<arch>." keys of
+// the format's naming convention) and the block types from its tensors, then builds this rank's shard of it.
+int qmm_decoder_create_from_gguf(const char* path, int max_batch, int ctx_len, int tp_rank, int tp_size, void** handle) {
+    if (!path || !handle) return QMM_ERR_NULL;
+    void* fv = nullptr;
+    if (int st = qmm_gguf_open(path, &fv)) return st;
+    GgufFile* f = static_cast<GgufFile*>(fv);
+    auto u = [&](const std::string& key, unsigned long long dflt) {
+        auto it = f->meta.find(key);
+        return it == f->meta.end() ? dflt : (unsigned long long)it->second.u;
+    };
+    auto fl = [&](const std::string& key, double dflt) {
+        auto it = f->meta.find(key);
+        return it == f->meta.end() ? dflt : it->second.f;
+    };
+    auto type_of = [&](int layer, int which) -> int {
+        auto it = f->by_name.find(gguf_tensor_name(layer, which));
+        return it == f->by_name.end() ? -1 : (int)f->tensors[it->second].type;
+    };
+    std::string arch = "llama";
+    if (f->meta.count("general.architecture")) arch = f->meta["general.architecture"].s;
+    qmm_decoder_config c = {};
+    c.n_layers = (int)u(arch + ".block_count", 0);
+    c.hidden = (int)u(arch + ".embedding_length", 0);
+    c.ffn = (int)u(arch + ".feed_forward_length", 0);
+    c.n_q_heads = (int)u(arch + ".attention.head_count", 0);
+    c.n_kv_heads = (int)u(arch + ".attention.head_count_kv", c.n_q_heads);
+    c.head_dim = (int)u(arch + ".attention.key_length", c.n_q_heads ? c.hidden / c.n_q_heads : 0);
+    c.ctx_len = ctx_len > 0 ? ctx_len : (int)u(arch + ".context_length", 0);
+    c.rope_theta = (float)fl(arch + ".rope.freq_base", 10000.0);
+    c.rms_eps = (float)fl(arch + ".attention.layer_norm_rms_epsilon", 1e-6);
+    // gated GELU for the Gemma family, SiLU otherwise; "qmm.activation" (0 / 1) overrides
+    c.act = (int)u("qmm.activation", arch.find("gemma") != std::string::npos ? QMM_ACT_GELU_TANH : QMM_ACT_SILU);
+    c.max_batch = max_batch;
+    c.tp_rank = tp_rank, c.tp_size = tp_size;
+    c.type_attn_qk = type_of(0, QMM_T_WQ), c.type_attn_v = type_of(0, QMM_T_WV), c.type_attn_o = type_of(0, QMM_T_WO);
+    c.type_ffn_gate_up = type_of(0, QMM_T_WGATE), c.type_ffn_down = type_of(0, QMM_T_WDOWN);
+    const int t_embd = type_of(-1, QMM_T_EMBED), t_out = type_of(-1, QMM_T_HEAD);
+    c.type_head = t_out >= 0 ? t_out : t_embd;
+    int st = QMM_OK;
+    if (t_embd < 0 || c.type_attn_qk < 0 || c.type_attn_v < 0 || c.type_attn_o < 0 || c.type_ffn_gate_up < 0 || c.type_ffn_down < 0) st = QMM_ERR_FORMAT;
+    else if (t_embd != c.type_head) st = QMM_ERR_UNSUPPORTED;  // the engine decodes embedding rows with the head's block type
+    else if (type_of(0, QMM_T_WK) != c.type_attn_qk || type_of(0, QMM_T_WUP) != c.type_ffn_gate_up) st = QMM_ERR_UNSUPPORTED;
+    if (!st) {
+        // one block type per role across the layers (the engine keeps one kernel choice per role)
+        for (int l = 1; l < c.n_layers && !st; ++l)
+            if (type_of(l, QMM_T_WQ) != c.type_attn_qk || type_of(l, QMM_T_WK) != c.type_attn_qk || type_of(l, QMM_T_WV) != c.type_attn_v ||
+                type_of(l, QMM_T_WO) != c.type_attn_o || type_of(l, QMM_T_WGATE) != c.type_ffn_gate_up ||
+                type_of(l, QMM_T_WUP) != c.type_ffn_gate_up || type_of(l, QMM_T_WDOWN) != c.type_ffn_down)
+                st = QMM_ERR_UNSUPPORTED;
+        auto it = f->by_name.find("token_embd.weight");
+        c.vocab = (int)f->tensors[it->second].dims[1];
+    }
+    if (!st) {
+        GgufSource src;
+        src.f = f;
+        st = finish_create(&c, &src, handle);
+    }
+    qmm_gguf_close(f);
+    return st;
+}
+
+// Writes the model of a single-GPU decoder as a GGUF file (synthetic models for tests and examples).
+int qmm_decoder_export_gguf(void* handle, const char* path, const char* architecture) {
+    if (!handle || !path) return QMM_ERR_NULL;
+    Decoder* d = static_cast<Decoder*>(handle);
+    const qmm_decoder_config& c = d->c;
+    if (c.tp_size != 1) return QMM_ERR_UNSUPPORTED;
+    const std::string arch = architecture ? architecture : "llama";
+    void* w = nullptr;
+    if (int st = qmm_gguf_writer_create(path, &w)) return st;
+    qmm_gguf_writer_meta_str(w, "general.architecture", arch.c_str());
+    qmm_gguf_writer_meta_u32(w, (arch + ".block_count").c_str(), c.n_layers);
+    qmm_gguf_writer_meta_u32(w, (arch + ".embedding_length").c_str(), c.hidden);
+    qmm_gguf_writer_meta_u32(w, (arch + ".feed_forward_length").c_str(), c.ffn);
+    qmm_gguf_writer_meta_u32(w, (arch + ".attention.head_count").c_str(), c.n_q_heads);
+    qmm_gguf_writer_meta_u32(w, (arch + ".attention.head_count_kv").c_str(), c.n_kv_heads);
+    qmm_gguf_writer_meta_u32(w, (arch + ".attention.key_length").c_str(), c.head_dim);
+    qmm_gguf_writer_meta_u32(w, (arch + ".context_length").c_str(), c.ctx_len);
+    qmm_gguf_writer_meta_f32(w, (arch + ".rope.freq_base").c_str(), c.rope_theta);
+    qmm_gguf_writer_meta_f32(w, (arch + ".attention.layer_norm_rms_epsilon").c_str(), c.rms_eps);
+    qmm_gguf_writer_meta_u32(w, "qmm.activation", c.act);
+    const int H = c.hidden, hd = c.head_dim;
+    std::vector<uint8_t> host;
+    int st = cudaDeviceSynchronize() == cudaSuccess ? QMM_OK : QMM_ERR_CUDA;
+    auto add = [&](int layer, int which, int type, const void* dev, long rows, long k) {
+        if (st) return;
+        const long bytes = type == 0 ? rows * k * 4 : rows * (long)type_row_bytes(type, k);
+        host.resize((size_t)bytes);
+        if (cudaMemcpy(host.data(), dev, (size_t)bytes, cudaMemcpyDeviceToHost) != cudaSuccess) {
+            st = QMM_ERR_CUDA;
+            return;
+        }
+        const long dims[2] = {k, rows};
+        st = qmm_gguf_writer_add_tensor(w, gguf_tensor_name(layer, which).c_str(), type, rows > 1 || type != 0 ? 2 : 1, dims, host.data(), bytes);
+    };
+    add(-1, QMM_T_EMBED, c.type_head, d->embed, c.vocab, H);
+    for (int l = 0; l < c.n_layers; ++l) {
+        const LayerWeights& L = d->layers[l];
+        const size_t rbqk = type_row_bytes(c.type_attn_qk, H), rbgu = type_row_bytes(c.type_ffn_gate_up, H);
+        add(l, QMM_T_ATTN_NORM, 0, L.attn_norm, 1, H);
+        add(l, QMM_T_WQ, c.type_attn_qk, L.wqk, (long)c.n_q_heads * hd, H);
+        add(l, QMM_T_WK, c.type_attn_qk, L.wqk + (size_t)c.n_q_heads * hd * rbqk, (long)c.n_kv_heads * hd, H);
+        add(l, QMM_T_WV, c.type_attn_v, L.wv, (long)c.n_kv_heads * hd, H);
+        add(l, QMM_T_WO, c.type_attn_o, L.wo, H, (long)c.n_q_heads * hd);
+        add(l, QMM_T_FFN_NORM, 0, L.ffn_norm, 1, H);
+        add(l, QMM_T_WGATE, c.type_ffn_gate_up, L.wgu, c.ffn, H);
+        add(l, QMM_T_WUP, c.type_ffn_gate_up, L.wgu + (size_t)c.ffn * rbgu, c.ffn, H);
+        add(l, QMM_T_WDOWN, c.type_ffn_down, L.wdown, H, c.ffn);
+    }
+    add(-1, QMM_T_FINAL_NORM, 0, d->final_norm, 1, H);
+    if (d->embed != d->head) add(-1, QMM_T_HEAD, c.type_head, d->head, c.vocab, H);
+    const int fin = qmm_gguf_writer_finish(w);
+    return st ? st : fin;
+}
+
+static int finish_create(const qmm_decoder_config* cfg, WeightSource* src, void** handle) {
     Decoder* d = nullptr;
-    const int st = create(cfg, &d);
+    const int st = create(cfg, src, &d);
     if (st) return st;
     // attention kernel: opt in to the shared memory its largest context split needs
     const int group = d->nq / d->nkv;

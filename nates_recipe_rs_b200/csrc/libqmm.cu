@@ -10,4 +10,5 @@
 #include "tp_comm.cu"
 #include "attn_entry.cu"
 #include "ops_entry.cu"
+#include "gguf.cu"
 #include "decoder.cu"

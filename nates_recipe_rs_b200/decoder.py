@@ -57,16 +57,24 @@ def _bind():
         L.qmm_decoder_ipc_import.argtypes = [vp, i32, vp]
         L.qmm_decoder_tp_ready.argtypes = [vp]
         L.qmm_decoder_step.argtypes = [vp, vp, i32, i32, vp, vp, vp, vp]
+        L.qmm_decoder_create_from_gguf.argtypes = [C.c_char_p, i32, i32, i32, i32, C.POINTER(vp)]
+        L.qmm_decoder_export_gguf.argtypes = [vp, C.c_char_p, C.c_char_p]
         _bound = True
     return L
 
 
 class Decoder:
-    def __init__(self, cfg, group=None):
+    def __init__(self, cfg, group=None, gguf_path=None):
+        """cfg: a DecoderConfig (weights: the seeded model).  With gguf_path the weights and the shapes come
+        from that file; of cfg only max_batch, ctx_len (0 = the file's), tp_rank and tp_size are used."""
         self.L = _bind()
         self.cfg = cfg
         self.h = C.c_void_p()
-        check(self.L.qmm_decoder_create(C.byref(cfg), C.byref(self.h)), "qmm_decoder_create")
+        if gguf_path is None:
+            check(self.L.qmm_decoder_create(C.byref(cfg), C.byref(self.h)), "qmm_decoder_create")
+        else:
+            check(self.L.qmm_decoder_create_from_gguf(str(gguf_path).encode(), cfg.max_batch, cfg.ctx_len, cfg.tp_rank, cfg.tp_size,
+                                                      C.byref(self.h)), "qmm_decoder_create_from_gguf")
         dev = torch.device("cuda", torch.cuda.current_device())
         self.tokens = torch.zeros(cfg.max_batch, dtype=torch.int32, device=dev)
         self.next_tokens = torch.zeros(cfg.max_batch, dtype=torch.int32, device=dev)
@@ -99,6 +107,10 @@ class Decoder:
         out = np.empty(n.value, dtype=np.uint8)
         check(self.L.qmm_decoder_read_tensor(self.h, layer, which, out.ctypes.data_as(C.c_void_p), n.value), "qmm_decoder_read_tensor")
         return out
+
+    def export_gguf(self, path, architecture="llama"):
+        """Writes this (single-GPU) decoder's model as a GGUF file."""
+        check(self.L.qmm_decoder_export_gguf(self.h, str(path).encode(), architecture.encode()), "qmm_decoder_export_gguf")
 
     def fill_cache(self, seed=1):
         check(self.L.qmm_decoder_fill_cache(self.h, seed, torch.cuda.current_stream().cuda_stream), "qmm_decoder_fill_cache")

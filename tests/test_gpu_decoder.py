@@ -174,3 +174,70 @@ def test_attention_entry_matches_oracle(dec, batch, nqh, nkv, hd, length):
     # the Q8_1 output is the library's own quantization of the f32 output
     from nates_recipe_rs_b200 import quant_ops as ops
     assert torch.equal(q8, ops.gpu_quantize_q8_1(out))
+
+
+def test_gguf_round_trip_gives_the_same_decoder(dec, tmp_path):
+    """The seeded model written as a GGUF file and loaded back decodes bit-identically; a tensor-parallel
+    rank that loads its shard from the file holds the same bytes as the seeded shard."""
+    from nates_recipe_rs_b200 import gguf, quant_ops as ops
+    cfg = tiny_cfg(dec, n_layers=2, max_batch=2)
+    a = dec.Decoder(cfg)
+    path = tmp_path / "tiny.gguf"
+    a.export_gguf(path, "gemma")
+    with gguf.GgufFile(path) as f:
+        assert f.meta_int("gemma.block_count") == 2 and f.meta_int("gemma.embedding_length") == cfg.hidden
+        assert f.find("blk.1.ffn_down.weight") >= 0 and f.find("output.weight") == -1      # tied head
+        buf = torch.zeros(f.info(f.find("blk.0.attn_v.weight"))["bytes"], dtype=torch.uint8, device="cuda")
+        f.upload("blk.0.attn_v.weight", buf)
+        assert np.array_equal(buf.cpu().numpy(), a.tensor(0, dec.T_WV))
+    b = dec.Decoder(dec.DecoderConfig(max_batch=2, ctx_len=0, tp_rank=0, tp_size=1), gguf_path=path)
+    for which in (dec.T_ATTN_NORM, dec.T_WQK, dec.T_WV, dec.T_WO, dec.T_FFN_NORM, dec.T_WGU, dec.T_WDOWN):
+        assert np.array_equal(a.tensor(1, which), b.tensor(1, which)), which
+    assert np.array_equal(a.tensor(-1, dec.T_HEAD), b.tensor(-1, dec.T_HEAD))
+    toks = torch.tensor([5, 700], dtype=torch.int32, device="cuda")
+    la, lb = torch.empty(2, cfg.vocab, device="cuda"), torch.empty(2, cfg.vocab, device="cuda")
+    for pos in range(4):
+        for d, lg in ((a, la), (b, lb)):
+            d.tokens.copy_(toks)
+            d.step(2, pos, lg)
+        ops.check_launch()
+        assert torch.equal(la, lb), pos
+        assert torch.equal(a.next_tokens, b.next_tokens)
+        toks = a.next_tokens.clone()
+    a.close()
+    b.close()
+    # rank 1 of 2: row ranges of Q/K/V/gate/up/head, whole-block column ranges of O and down
+    kw = dict(n_layers=2, max_batch=2, tp_rank=1, tp_size=2, hidden=512, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn=1024)
+    full = dec.Decoder(tiny_cfg(dec, **{**kw, "tp_rank": 0, "tp_size": 1}))
+    full.export_gguf(path, "llama")
+    full.close()
+    seeded = dec.Decoder.__new__(dec.Decoder)      # shards without wiring peers: only the tensors are compared
+    loaded = dec.Decoder.__new__(dec.Decoder)
+    import ctypes as C
+    L = dec._bind()
+    from nates_recipe_rs_b200._lib import check
+    for obj, make in ((seeded, lambda h: L.qmm_decoder_create(C.byref(tiny_cfg(dec, **kw)), C.byref(h))),
+                      (loaded, lambda h: L.qmm_decoder_create_from_gguf(str(path).encode(), 2, 0, 1, 2, C.byref(h)))):
+        obj.L, obj.h, obj.cfg = L, C.c_void_p(), None
+        check(make(obj.h), "create shard")
+    for layer, which in [(0, dec.T_WQK), (0, dec.T_WV), (1, dec.T_WO), (1, dec.T_WGU), (0, dec.T_WDOWN), (-1, dec.T_HEAD), (-1, dec.T_EMBED),
+                         (1, dec.T_FFN_NORM), (-1, dec.T_FINAL_NORM)]:
+        assert np.array_equal(seeded.tensor(layer, which), loaded.tensor(layer, which)), (layer, which)
+    seeded.close()
+    loaded.close()
+
+
+def test_gguf_decoder_rejects_what_it_cannot_run(dec, tmp_path):
+    from nates_recipe_rs_b200 import gguf
+    from nates_recipe_rs_b200._lib import QmmError
+    path = tmp_path / "bad.gguf"
+    w = gguf.GgufWriter(path)
+    w.meta("general.architecture", "llama").meta("llama.block_count", 1).meta("llama.embedding_length", 256)
+    w.tensor("token_embd.weight", oracle.Q6_K, [256, 4], oracle.quantize(oracle.Q6_K, oracle.fill_normal(1024, 1, 0.02).reshape(4, 256)))
+    w.finish()
+    with pytest.raises(QmmError) as e:       # the layer tensors are missing
+        dec.Decoder(dec.DecoderConfig(max_batch=1, ctx_len=16, tp_rank=0, tp_size=1), gguf_path=path)
+    assert e.value.status == -9
+    with pytest.raises(QmmError) as e:
+        dec.Decoder(dec.DecoderConfig(max_batch=1, ctx_len=16, tp_rank=0, tp_size=1), gguf_path=tmp_path / "none.gguf")
+    assert e.value.status == -8
