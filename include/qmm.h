@@ -248,6 +248,30 @@ long qmm_argmax_scratch_bytes(int batch);
 int launch_argmax_rows(const float* logits, void* scratch, int* out_index, float* out_value, int batch, int vocab, void* stream);
 int launch_scale_f32(float* x, float scalar, long n, void* stream);
 
+/* ---- mixture-of-experts branch of a decode step, on the device.  The upstream example routes on the host:
+ * it downloads the activations, computes router logits, softmax and top-k per token in f64 loops, gathers the
+ * tokens of every chosen expert, uploads them and runs the experts one after the other
+ * (examples/gemma4.rs:684-742).  Here the choice never leaves the device.
+ * launch_moe_router_topk: per token p of x (m, hidden) f32:
+ *     r = x / sqrt(mean(x^2) + eps) * scale * gain          (gain NULL = 1; the upstream's rnp * 1/sqrt(NE) * gis)
+ *     prob = softmax(router_w (n_experts, hidden, f32) . r)
+ *     sel[p][0..top_k) = the top_k experts by probability, largest first, lowest index first on ties
+ *     weight[p][j] = prob[sel[p][j]] / sum_j prob[sel[p][j]]
+ *   probs (optional) receives all probabilities (m, n_experts).  n_experts <= 256, top_k <= 8.
+ * launch_moe_experts: for every (token, slot): gu = xq[token] . W_gu[sel]^T, ea = Q8_1(act(gate) * up),
+ *     dv = ea . W_dn[sel]^T;  out[token] = sum over slots of weight * expert_scale[sel] * dv (expert_scale NULL = 1).
+ *   The experts' matrices lie in two banks, matrix e at bank + e * stride_bytes (strides multiples of 16):
+ *   gate_up (2 * ffn_expert, hidden) rows [gate | up], down (hidden, ffn_expert).  xq: Q8_1 (m, hidden).
+ *   Each of the two projections is ONE job-list launch whose jobs read their expert index on the device.
+ *   scratch: qmm_moe_scratch_bytes(...) bytes of caller-owned device memory, 16-byte aligned.
+ *   Decode-sized m: an expert chosen by several tokens is streamed once per token. */
+int launch_moe_router_topk(const float* x, const float* gain, const float* router_w, int m, int hidden, int n_experts, int top_k, float scale,
+                           float eps, int* sel, float* weight, float* probs, void* stream);
+long qmm_moe_scratch_bytes(int m, int top_k, int hidden, int ffn_expert);
+int launch_moe_experts(int type_gu, const void* gate_up_bank, long gu_stride_bytes, int type_dn, const void* down_bank, long dn_stride_bytes,
+                       const void* xq, const int* sel, const float* weight, const float* expert_scale, float* out, void* scratch, int m,
+                       int top_k, int hidden, int ffn_expert, int act, void* stream);
+
 /* ---- per-block integer dot sums (parity instrumentation; same device code as
  * the matvec).  One Q8_1 row xq (k); out int32 (n, k/32) for Q8_0 and Q4_K,
  * (n, k/16) for Q6_K. */

@@ -27,7 +27,7 @@ __all__ = [
     "gpu_qgemm_q4_k_bf16_into", "gpu_qgemm_q4_k_bf16",
     "gpu_qlinear",
     "gpu_rmsnorm_q8_1_into", "gpu_rope_kv_append", "gpu_glu_act_q8_1_into", "gpu_embed_rows_into", "gpu_argmax_rows",
-    "gpu_scale_f32_inplace",
+    "gpu_scale_f32_inplace", "gpu_moe_router_topk", "gpu_moe_experts_into",
 ]
 
 
@@ -295,3 +295,33 @@ def gpu_argmax_rows(logits):
 def gpu_scale_f32_inplace(x, scalar):
     """x *= scalar: the upstream's gpu_scale_f64_inplace (gpu-core/src/infer_ops.rs:242-248)."""
     check(lib().launch_scale_f32(_ptr(x), scalar, x.numel(), _stream()), "launch_scale_f32")
+
+
+# ---- mixture of experts ---------------------------------------------------------------------
+def gpu_moe_router_topk(x, router_w, top_k, scale=1.0, eps=1e-6, gain=None, want_probs=False):
+    """Router of a mixture-of-experts layer, on the device (the upstream routes on the host:
+    examples/gemma4.rs:694-711): per row of x (m, hidden) the top_k experts of softmax(router_w . r),
+    r = rms_normalise(x) * scale * gain.  Returns (sel int32 (m, top_k), weight f32 (m, top_k)[, probs])."""
+    m, hidden = x.shape
+    n_experts = router_w.shape[0]
+    sel = torch.empty(m, top_k, dtype=torch.int32, device=x.device)
+    weight = torch.empty(m, top_k, dtype=torch.float32, device=x.device)
+    probs = torch.empty(m, n_experts, dtype=torch.float32, device=x.device) if want_probs else None
+    check(lib().launch_moe_router_topk(_ptr(x), _opt(gain), _ptr(router_w), m, hidden, n_experts, top_k, scale, eps, _ptr(sel), _ptr(weight),
+                                       _opt(probs), _stream()), "launch_moe_router_topk")
+    return (sel, weight, probs) if want_probs else (sel, weight)
+
+
+def gpu_moe_experts_into(type_gu, gate_up_bank, type_dn, down_bank, xq, sel, weight, out, hidden, ffn_expert, act, expert_scale=None):
+    """The chosen experts' gated FFN for every token and their weighted sum into out (m, hidden); the
+    banks hold n_experts matrices back to back (gate_up: (2*ffn_expert, hidden) each, down: (hidden,
+    ffn_expert) each).  The upstream runs the experts one by one from the host
+    (examples/gemma4.rs:713-737).  Allocates its scratch."""
+    m, top_k = sel.shape
+    gu_stride = 2 * ffn_expert * row_bytes(type_gu, hidden)
+    dn_stride = hidden * row_bytes(type_dn, ffn_expert)
+    scratch = torch.empty(lib().qmm_moe_scratch_bytes(m, top_k, hidden, ffn_expert), dtype=torch.uint8, device=out.device)
+    check(lib().launch_moe_experts(type_gu, _ptr(gate_up_bank), gu_stride, type_dn, _ptr(down_bank), dn_stride, _ptr(xq), _ptr(sel),
+                                   _ptr(weight), _opt(expert_scale), _ptr(out), _ptr(scratch), m, top_k, hidden, ffn_expert, act, _stream()),
+          "launch_moe_experts")
+    return scratch
