@@ -25,6 +25,12 @@ class GgufTensorInfo(C.Structure):
                 ("bytes", C.c_long)]
 
 
+class StoreStats(C.Structure):
+    """qmm_store_stats_t of include/qmm_store.h."""
+    _fields_ = [(n, C.c_long) for n in ("vram_bytes", "ram_bytes", "disk_bytes", "fetches_vram", "fetches_ram", "fetches_disk", "cache_hits",
+                                        "staged_bytes")]
+
+
 # name -> (restype, argtypes); must list every symbol include/qmm.h declares
 SIGNATURES = {
     "qmm_status_string": (C.c_char_p, [i32]),
@@ -71,6 +77,15 @@ SIGNATURES = {
     "launch_moe_router_topk": (i32, [vp, vp, vp, i32, i32, i32, i32, C.c_float, C.c_float, vp, vp, vp, vp]),
     "qmm_moe_scratch_bytes": (i64, [i32, i32, i32, i32]),
     "launch_moe_experts": (i32, [i32, vp, i64, i32, vp, i64, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
+    "qmm_store_create": (i32, [i64, i64, i64, i32, i64, C.POINTER(vp)]),
+    "qmm_store_destroy": (i32, [vp]),
+    "qmm_store_place_host": (i32, [vp, C.c_char_p, vp, i64]),
+    "qmm_store_place_file": (i32, [vp, C.c_char_p, C.c_char_p, i64, i64]),
+    "qmm_store_home": (i32, [vp, C.c_char_p]),
+    "qmm_store_stats": (i32, [vp, C.POINTER(StoreStats)]),
+    "qmm_store_fetch": (i32, [vp, C.c_char_p, vp, C.POINTER(vp)]),
+    "qmm_store_prefetch": (i32, [vp, C.c_char_p, vp]),
+    "qmm_store_fetch_cached": (i32, [vp, C.c_char_p, vp, C.POINTER(vp)]),
     "qmm_gguf_open": (i32, [C.c_char_p, C.POINTER(vp)]),
     "qmm_gguf_close": (i32, [vp]),
     "qmm_gguf_tensor_count": (i64, [vp]),
