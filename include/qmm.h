@@ -80,7 +80,9 @@ int qmm_set_overlap(int on);
  * "consumer_warps" small enough to fit twice), "mma_min_m" (0..16: fewest activation rows that take the
  * tensor-core matvec where type and shape allow it; 0 = never; default 3), "attn_tc_min_batch" (fewest
  * sequences from which the decode attention runs on the f16 tensor cores; 0 = never; default 4), and for the
- * job-list matvec "jobs_warps" (1..24), "jobs_ring_bytes", "jobs_stage_bytes", "jobs_rotate" (0/1).
+ * job-list matvec "jobs_warps" (1..24), "jobs_ring_bytes", "jobs_stage_bytes", "jobs_rotate" (0/1); "decoder_fuse"
+ * (0..3, decode engine at batch 1-2: default 0 = every operator its own launch, 1 = Q|K and V as one job list, 2 = also norms built inside the matvec
+ * launches, 3 = also the gated activation).
  * Every setting computes the same results.  Not thread-safe against concurrent launches.
  * (A library built with -DQMM_TUNING also has instrumentation that is not part of this interface:
  * stream-only probe modes and a per-CTA time-stamp trace, declared in csrc/qmm_tuning.h.) */
@@ -149,6 +151,21 @@ typedef struct {
     int tp_sum;               /* launch_qmatvec_batch_tp only: sum this job's outputs over the ranks */
 } qmm_matvec_job;
 int launch_qmatvec_batch(const qmm_matvec_job* jobs, int n_jobs, int m, void* stream);
+
+/* ---- a job list whose activations are built inside the launch (all jobs share them; the jobs' xq is ignored).
+ * launch_norm_qmatvec_batch: xq = Q8_1( rmsnorm(x_in + x_add) * gamma ) for the projections of a block:
+ *   the upstream's residual add (gpu-core/src/kernels/elementwise.hip:13), gpu_rmsnorm_f64_into
+ *   (gpu-core/src/infer_ops.rs:117-139) and the projections that follow (examples/gemma4.rs:646-667) as ONE
+ *   launch.  x_in (m, k) f32; x_add (m, k) or NULL; gamma (k) or NULL; x_out (m, k) or NULL receives
+ *   x_in + x_add and must be a buffer other than x_in.  Every job has K = jobs[0].k.
+ * launch_glu_qmatvec_batch: xq = Q8_1( act(gate) * up ) from gate_up (m, 2k) = [gate | up] per row
+ *   (gpu_glu_gelu_into, infer_ops.rs:206-222) for the projection(s) that consume it (:678); act 0 = tanh-GELU,
+ *   1 = SiLU.
+ * Both need the persistent kernel (m <= 2, K within its warps, at most 36 jobs); QMM_ERR_UNSUPPORTED otherwise,
+ * and the caller uses launch_add_rmsnorm_q8_1 / launch_glu_act_q8_1 followed by launch_qmatvec_batch. */
+int launch_norm_qmatvec_batch(const float* x_in, const float* x_add, const float* gamma, float* x_out, float eps, const qmm_matvec_job* jobs,
+                              int n_jobs, int m, void* stream);
+int launch_glu_qmatvec_batch(const float* gate_up, int act, const qmm_matvec_job* jobs, int n_jobs, int m, void* stream);
 
 /* ---- tensor parallelism over the GPUs of one box: row-parallel projections with the sum over the ranks
  * fused in.  The upstream runs every projection of a layer on one device (examples/gemma4.rs:653-679); when

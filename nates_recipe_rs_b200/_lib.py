@@ -61,6 +61,8 @@ SIGNATURES = {
     "qmm_tp_comm_ready": (i32, [vp]),
     "launch_qmatvec_tp": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, vp]),
     "launch_qmatvec_batch_tp": (i32, [vp, C.POINTER(MatvecJob), i32, i32, vp]),
+    "launch_norm_qmatvec_batch": (i32, [vp, vp, vp, vp, C.c_float, C.POINTER(MatvecJob), i32, i32, vp]),
+    "launch_glu_qmatvec_batch": (i32, [vp, i32, C.POINTER(MatvecJob), i32, i32, vp]),
     "launch_qgemm_q4_k_bf16": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "launch_qgemm_q4_k_bf16_f32acc": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "qmm_attn_decode_scratch_bytes": (i64, [i32, i32, i32, i32]),

@@ -35,6 +35,18 @@ int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, in
 int matvec_tune(const char* key, int value);
 int jobs_tune(const char* key, int value);
 int qmatvec_jobs_launch(const qmm_matvec_job* jobs, int n_jobs, int m, cudaStream_t stream);
+struct XBuild {  // qmatvec_jobs.cu
+    const float* x_in;
+    const float* x_add;
+    const float* gamma;
+    float* x_out;
+    float eps;
+    int act;
+    int k;
+};
+int qmatvec_jobs_launch_ex(const qmm_matvec_job* jobs, int n_jobs, int m, const TpPush* push, const long* push_words, int x_mode,
+                           const XBuild* xb, cudaStream_t stream);
+constexpr int JOBS_X_NORM = 1, JOBS_X_GLU = 2;
 void matvec_set_trace(unsigned long long* buf, int stride_words);
 
 }  // namespace qmm
@@ -130,6 +142,24 @@ int launch_qmatvec_q6_k(const void* w, const void* xq, float* y, int m, int n, i
 
 int launch_qmatvec_batch(const qmm_matvec_job* jobs, int n_jobs, int m, void* stream) {
     return qmatvec_jobs_launch(jobs, n_jobs, m, as_stream(stream));
+}
+
+int launch_norm_qmatvec_batch(const float* x_in, const float* x_add, const float* gamma, float* x_out, float eps, const qmm_matvec_job* jobs,
+                              int n_jobs, int m, void* stream) {
+    if (!x_in || !jobs) return QMM_ERR_NULL;
+    if (n_jobs <= 0 || m <= 0) return QMM_ERR_SHAPE;
+    if (x_out == x_in) return QMM_ERR_ALIGN;  // every CTA reads x_in while one of them writes x_out
+    XBuild xb = {};
+    xb.x_in = x_in, xb.x_add = x_add, xb.gamma = gamma, xb.x_out = x_out, xb.eps = eps, xb.k = jobs[0].k;
+    return qmatvec_jobs_launch_ex(jobs, n_jobs, m, nullptr, nullptr, JOBS_X_NORM, &xb, as_stream(stream));
+}
+int launch_glu_qmatvec_batch(const float* gate_up, int act, const qmm_matvec_job* jobs, int n_jobs, int m, void* stream) {
+    if (!gate_up || !jobs) return QMM_ERR_NULL;
+    if (n_jobs <= 0 || m <= 0) return QMM_ERR_SHAPE;
+    if (act != 0 && act != 1) return QMM_ERR_UNSUPPORTED;
+    XBuild xb = {};
+    xb.x_in = gate_up, xb.act = act, xb.k = jobs[0].k;
+    return qmatvec_jobs_launch_ex(jobs, n_jobs, m, nullptr, nullptr, JOBS_X_GLU, &xb, as_stream(stream));
 }
 
 int launch_qgemm_q4_k_bf16(const void* w, const void* x, void* y, int m, int n, int k, void* stream) {

@@ -20,6 +20,7 @@ int qmatvec_launch_limited(int type, const void* w, const void* xq, float* y, lo
 int quantize_weights_launch(int type, const float* w, void* out, long rows, int k, cudaStream_t stream);
 int qmatvec_launch_push(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                         const TpPush* push, cudaStream_t stream);
+int decoder_fusion();
 
 constexpr int ARGMAX_PARTS = 256;
 
@@ -39,7 +40,7 @@ struct Decoder {
     uint8_t *head = nullptr, *embed = nullptr;  // embed == head when tp_size == 1
     __half *kcache = nullptr, *vcache = nullptr;
     // activations (allocated once)
-    float *x = nullptr, *qkv = nullptr, *gu = nullptr, *logits = nullptr, *attn_scratch = nullptr, *best_val = nullptr;
+    float *x = nullptr, *x_alt = nullptr, *x_home = nullptr, *qkv = nullptr, *gu = nullptr, *logits = nullptr, *attn_scratch = nullptr, *best_val = nullptr;
     uint8_t *xq_h = nullptr, *xq_attn = nullptr, *xq_ffn = nullptr;
     // projection outputs that the next residual + norm kernel adds: [0] after O, [1] after down.  With tensor
     // parallelism the matvec kernels store them into every rank's exchange area (comm) instead.
@@ -314,6 +315,8 @@ static int create(const qmm_decoder_config* cfg, WeightSource* src, Decoder** ou
     TRY(cuda_status(cudaMemsetAsync(d->vcache, 0, cache_elems * sizeof(__half), s)));
 
     TRY(dev_alloc(d, &d->x, (size_t)B * H * sizeof(float)));
+    TRY(dev_alloc(d, &d->x_alt, (size_t)B * H * sizeof(float)));
+    d->x_home = d->x;
     TRY(dev_alloc(d, &d->qkv, (size_t)B * d->qkv_cols * sizeof(float)));
     TRY(dev_alloc(d, &d->gu, (size_t)B * 2 * d->ffn_l * sizeof(float)));
     TRY(dev_alloc(d, &d->logits, (size_t)B * d->vocab_l * sizeof(float)));
@@ -390,6 +393,30 @@ static int row_parallel(Decoder* d, int type, const uint8_t* w, const uint8_t* x
     return qmatvec_launch_push(type, w, xq, d->part[which], H, batch, H, k, 0, &push, s);
 }
 
+// Small batches on one GPU: the residual add + norm + quantization before a block's projections, and the
+// gated activation before the down projection, are built inside the job-list matvec launch that needs them
+// (JOBS_X_NORM / JOBS_X_GLU) instead of in launches of their own.  The residual alternates between two buffers:
+// every CTA reads the old one while CTA 0 writes the new one.  QMM_ERR_UNSUPPORTED: the caller takes the
+// separate kernels.
+static qmm_matvec_job make_job(int type, const uint8_t* w, float* y, int n, int k, long y_stride) {
+    qmm_matvec_job q = {};
+    q.type = type, q.n = n, q.k = k, q.w = w, q.y = y, q.y_stride = y_stride;
+    return q;
+}
+static int norm_proj(Decoder* d, int which, const float* gamma, const qmm_matvec_job* jobs, int n_jobs, int batch, cudaStream_t s) {
+    XBuild xb = {};
+    xb.x_in = d->x, xb.gamma = gamma, xb.eps = d->c.rms_eps, xb.k = d->c.hidden;
+    if (which >= 0) xb.x_add = d->part[which], xb.x_out = d->x_alt;
+    const int st = qmatvec_jobs_launch_ex(jobs, n_jobs, batch, nullptr, nullptr, JOBS_X_NORM, &xb, s);
+    if (st == QMM_OK && which >= 0) std::swap(d->x, d->x_alt);
+    return st;
+}
+static int glu_proj(Decoder* d, const qmm_matvec_job* job, int batch, cudaStream_t s) {
+    XBuild xb = {};
+    xb.x_in = d->gu, xb.act = d->c.act, xb.k = d->ffn_l;
+    return qmatvec_jobs_launch_ex(job, 1, batch, nullptr, nullptr, JOBS_X_GLU, &xb, s);
+}
+
 static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tokens, float* logits_out, float* best_out, cudaStream_t s) {
     const qmm_decoder_config& c = d->c;
     if (!tokens || !next_tokens) return QMM_ERR_NULL;
@@ -400,6 +427,11 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
     do {       \
         if ((st = (e)) != 0) return st; \
     } while (0)
+    const int fuse_level = batch <= 2 ? decoder_fusion() : 0;
+    const bool fuse = !d->comm && fuse_level >= 2;       // norms inside the matvec launches
+    const bool fuse_glu = !d->comm && fuse_level >= 3;   // gated activation inside the down launch
+    const bool qkv_list = fuse_level >= 1;               // Q|K and V of different types as one job list
+    if (d->x_home && d->x != d->x_home) std::swap(d->x, d->x_alt);  // every step starts in the same buffer
     {   // embedding
         const int rb = type_row_bytes(c.type_head, H);
         const dim3 grid((H + 255) / 256, batch);
@@ -414,9 +446,33 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
     const size_t attn_smem = (size_t)ATTN_CHUNK * (2 * hd + 8) * sizeof(__half) + (size_t)group * (hd + ATTN_CHUNK + 2) * sizeof(float);
     for (int l = 0; l < c.n_layers; ++l) {
         const LayerWeights& L = d->layers[l];
-        TRY(add_norm(d, l == 0 ? -1 : 1, L.attn_norm, batch, s));
-        if (c.type_attn_v == c.type_attn_qk) {  // V's rows follow K's in memory: one launch
+        bool qkv_done = false;
+        if (fuse) {  // norm + Q|K (+ V) in one launch
+            qmm_matvec_job jobs[2];
+            int nj = 1;
+            if (c.type_attn_v == c.type_attn_qk) {
+                jobs[0] = make_job(c.type_attn_qk, L.wqk, d->qkv, d->qk_rows + d->v_rows, H, d->qkv_cols);
+            } else {
+                jobs[0] = make_job(c.type_attn_qk, L.wqk, d->qkv, d->qk_rows, H, d->qkv_cols);
+                jobs[1] = make_job(c.type_attn_v, L.wv, d->qkv + d->qk_rows, d->v_rows, H, d->qkv_cols);
+                nj = 2;
+            }
+            st = norm_proj(d, l == 0 ? -1 : 1, L.attn_norm, jobs, nj, batch, s);
+            if (st != QMM_OK && st != QMM_ERR_UNSUPPORTED) return st;
+            qkv_done = st == QMM_OK;
+        }
+        if (!qkv_done) TRY(add_norm(d, l == 0 ? -1 : 1, L.attn_norm, batch, s));
+        if (qkv_done) {
+        } else if (c.type_attn_v == c.type_attn_qk) {  // V's rows follow K's in memory: one launch
             TRY(qmatvec_launch_strided(c.type_attn_qk, L.wqk, d->xq_h, d->qkv, d->qkv_cols, batch, d->qk_rows + d->v_rows, H, s));
+        } else if (qkv_list && [&]() {
+                       qmm_matvec_job jobs[2] = {make_job(c.type_attn_qk, L.wqk, d->qkv, d->qk_rows, H, d->qkv_cols),
+                                                 make_job(c.type_attn_v, L.wv, d->qkv + d->qk_rows, d->v_rows, H, d->qkv_cols)};
+                       jobs[0].xq = jobs[1].xq = d->xq_h;
+                       st = qmatvec_jobs_launch_ex(jobs, 2, batch, nullptr, nullptr, 0, nullptr, s);
+                       return st != QMM_ERR_UNSUPPORTED;
+                   }()) {
+            if (st) return st;  // one launch walked both matrices
         } else {
             // two kernels side by side: the SMs are shared in proportion to the weight bytes
             const double qk_b = (double)d->qk_rows * type_row_bytes(c.type_attn_qk, H), v_b = (double)d->v_rows * type_row_bytes(c.type_attn_v, H);
@@ -443,14 +499,38 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
         TRY(launch_pdl(attn_combine_q8_kernel, dim3(d->nq, batch), dim3(hd < 128 ? hd : 128), 0, s, (const float*)d->attn_scratch, d->xq_attn,
                        (float*)nullptr, d->nq, hd, splits));
         TRY(row_parallel(d, c.type_attn_o, L.wo, d->xq_attn, 0, batch, ao, s));
-        TRY(add_norm(d, 0, L.ffn_norm, batch, s));
-        TRY(qmatvec_launch_strided(c.type_ffn_gate_up, L.wgu, d->xq_h, d->gu, 2 * d->ffn_l, batch, 2 * d->ffn_l, H, s));
-        TRY(launch_pdl(act_mul_q8_kernel, dim3((d->ffn_l / 32 + 3) / 4, batch), dim3(128), 0, s, (const float*)d->gu, d->xq_ffn, d->ffn_l, c.act, (float*)nullptr));
-        TRY(row_parallel(d, c.type_ffn_down, L.wdown, d->xq_ffn, 1, batch, d->ffn_l, s));
+        st = QMM_ERR_UNSUPPORTED;
+        if (fuse) {  // norm + gate|up in one launch
+            const qmm_matvec_job gu = make_job(c.type_ffn_gate_up, L.wgu, d->gu, 2 * d->ffn_l, H, 2 * d->ffn_l);
+            st = norm_proj(d, 0, L.ffn_norm, &gu, 1, batch, s);
+            if (st != QMM_OK && st != QMM_ERR_UNSUPPORTED) return st;
+        }
+        if (st != QMM_OK) {
+            TRY(add_norm(d, 0, L.ffn_norm, batch, s));
+            TRY(qmatvec_launch_strided(c.type_ffn_gate_up, L.wgu, d->xq_h, d->gu, 2 * d->ffn_l, batch, 2 * d->ffn_l, H, s));
+        }
+        st = QMM_ERR_UNSUPPORTED;
+        if (fuse_glu) {  // gated activation + down in one launch
+            const qmm_matvec_job dn = make_job(c.type_ffn_down, L.wdown, d->part[1], H, d->ffn_l, H);
+            st = glu_proj(d, &dn, batch, s);
+            if (st != QMM_OK && st != QMM_ERR_UNSUPPORTED) return st;
+        }
+        if (st != QMM_OK) {
+            TRY(launch_pdl(act_mul_q8_kernel, dim3((d->ffn_l / 32 + 3) / 4, batch), dim3(128), 0, s, (const float*)d->gu, d->xq_ffn, d->ffn_l, c.act, (float*)nullptr));
+            TRY(row_parallel(d, c.type_ffn_down, L.wdown, d->xq_ffn, 1, batch, d->ffn_l, s));
+        }
     }
-    TRY(add_norm(d, 1, d->final_norm, batch, s));
     float* lg = logits_out ? logits_out : d->logits;
-    TRY(qmatvec_launch_strided(c.type_head, d->head, d->xq_h, lg, d->vocab_l, batch, d->vocab_l, H, s));
+    st = QMM_ERR_UNSUPPORTED;
+    if (fuse) {  // final norm + head in one launch
+        const qmm_matvec_job hj = make_job(c.type_head, d->head, lg, d->vocab_l, H, d->vocab_l);
+        st = norm_proj(d, 1, d->final_norm, &hj, 1, batch, s);
+        if (st != QMM_OK && st != QMM_ERR_UNSUPPORTED) return st;
+    }
+    if (st != QMM_OK) {
+        TRY(add_norm(d, 1, d->final_norm, batch, s));
+        TRY(qmatvec_launch_strided(c.type_head, d->head, d->xq_h, lg, d->vocab_l, batch, d->vocab_l, H, s));
+    }
     float* bv = best_out ? best_out : d->best_val;
     TRY(launch_pdl(argmax_partial_kernel, dim3(ARGMAX_PARTS, batch), dim3(256), 0, s, (const float*)lg, d->argmax_cand, d->vocab_l));
     TRY(launch_pdl(argmax_final_kernel, dim3(batch), dim3(256), 0, s, (const Candidate*)d->argmax_cand, ARGMAX_PARTS, next_tokens,

@@ -44,13 +44,25 @@ struct JobDesc {
     long push_word;       // tensor parallel: slot index of this job's y[0][0] in the exchange areas, or -1: plain stores to y
 };
 
+// How the activations of a list are made when the kernel builds them itself (all jobs then share them):
+//   JOBS_X_NORM  xq = Q8_1( rmsnorm(x_in + x_add) * gamma ), the sum also written to x_out by CTA 0: the residual
+//                update, the norm and the quantization that precede the projections of a block, without a launch
+//                of their own (each CTA repeats them for the one row it needs: 2 x hidden floats out of L2)
+//   JOBS_X_GLU   xq = Q8_1( act(gate) * up ) from the fused [gate | up] output of the preceding projection
+// (XBuild and the mode constants are declared in api.cu, the first file of the translation unit:
+//   x_in   NORM: residual (m, k); GLU: gate_up (m, 2k)      x_add  NORM: output of the preceding projection to add, or NULL
+//   gamma  NORM: gains, or NULL                              x_out  NORM: where the updated residual goes (not x_in), or NULL)
+constexpr int JOBS_X_GLOBAL = 0;
+
 struct JobList {
     JobDesc job[JOBS_MAX];
     int n_jobs, m;
     int nst, slot_bytes, pstage_max;
     int x_off, partial_off, ring_off;
     int n_consumers, any_sel;
+    int x_mode;           // JOBS_X_*
     TpPush push;          // used by the jobs with push_word >= 0
+    XBuild xb;
 };
 static_assert(sizeof(JobList) <= 4096, "the job list travels as a kernel parameter");
 
@@ -59,6 +71,7 @@ struct __align__(16) JobsSmemHeader {
     uint64_t empty[JOBS_MAX_STAGES];
     uint64_t xfull;
     int abort_flag;
+    float red[JOBS_MAX_WARPS];  // sum-of-squares partials of the activation builder
 };
 
 // rows of job J owned by CTA bx
@@ -104,6 +117,7 @@ struct JobArgs {
     int kw, rg, units, row_bytes, xq_row_bytes, rows_stage, n_rows;
     int m, nst, slot_bytes, pstage_max;
     uint32_t w_lo, x_parity;
+    int x_wait;   // 0: the activations were built by the kernel itself and are in place
 };
 
 // All stages of one job for one consumer warp.  st.ok = 0 after a timeout (the CTA unwinds).
@@ -123,7 +137,7 @@ __device__ __noinline__ ConsumerState consume_job(const JobArgs a, JobsSmemHeade
     typename F::XRegs x[M];
     // Every warp waits for every job's activations, also one without a share in this job: a warp that
     // skipped a phase of this barrier could not tell the next phase from the one before it.
-    if (!mbar_wait_bounded(smem_u32(&hdr->xfull), a.x_parity, cta_abort)) {
+    if (a.x_wait && !mbar_wait_bounded(smem_u32(&hdr->xfull), a.x_parity, cta_abort)) {
         if (lane == 0 && !*cta_abort) {
             atomicExch(&g_device_status, DEV_TIMEOUT_FULL);
             *cta_abort = 1;
@@ -207,6 +221,98 @@ __device__ __forceinline__ ConsumerState consume_job_rb(int rb, const JobArgs& a
     return consume_job<TYPE, M, 1>(a, hdr, ring_s, partial, xs, warp, lane, st, cta_abort);
 }
 
+__device__ __forceinline__ void consumers_sync(int n_threads) { asm volatile("bar.sync 1, %0;" ::"r"(n_threads) : "memory"); }
+
+// One Q8_1 block into shared memory from the 32 values held one per lane (the arithmetic of quantize_q8_kernel).
+__device__ __forceinline__ void warp_q8_1_to_smem(float v, uint8_t* blk, int lane) {
+    float amax = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const uint16_t dh = __half_as_ushort(__float2half_rn(fminf(__fdiv_rn(amax, 127.0f), 65504.0f)));
+    const float df = f16_bits_to_f32(dh);
+    int q = (df > 0.0f) ? (int)roundf(__fdiv_rn(v, df)) : 0;
+    q = q < -127 ? -127 : (q > 127 ? 127 : q);
+    blk[4 + lane] = (uint8_t)(int8_t)q;
+    int sum = q;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) {
+        *reinterpret_cast<uint16_t*>(blk) = dh;
+        *reinterpret_cast<uint16_t*>(blk + 2) = __half_as_ushort(__float2half_rn(__fmul_rn(df, (float)sum)));
+    }
+}
+
+// The consumer warps of a CTA build the activations of the whole list in the staging area (see XBuild).
+// A warp owns whole blocks of 32 consecutive elements (block w, w + n_warps, ...); all of a lane's loads are
+// issued before the first use, so the builder costs one round trip to L2, not one per element.
+constexpr int XB_MAX_BLOCKS = 20;  // blocks per warp the norm builder keeps in registers (K <= 20 * 32 * warps)
+constexpr int XB_GLU_CHUNK = 8;
+__device__ __noinline__ void build_activations(const XBuild xb, int mode, int m, uint8_t* xs, float* red, int warp, int lane, int n_warps,
+                                               bool writes_residual) {
+    const int k = xb.k, n_thr = n_warps * 32, n_blk = k / 32;
+    const int xq_row_bytes = n_blk * Q8_1_BYTES;
+    for (int mi = 0; mi < m; ++mi) {
+        uint8_t* xrow = xs + (size_t)mi * xq_row_bytes;
+        if (mode == JOBS_X_NORM) {
+            const float* xi = xb.x_in + (size_t)mi * k;
+            const float* xa = xb.x_add ? xb.x_add + (size_t)mi * k : nullptr;
+            float v[XB_MAX_BLOCKS], a[XB_MAX_BLOCKS], g[XB_MAX_BLOCKS];
+#pragma unroll
+            for (int j = 0; j < XB_MAX_BLOCKS; ++j) {
+                const int blk = warp + j * n_warps;
+                const int e = blk * 32 + lane;
+                const bool in = blk < n_blk;
+                v[j] = in ? xi[e] : 0.f;
+                a[j] = (in && xa) ? xa[e] : 0.f;
+                g[j] = (in && xb.gamma) ? xb.gamma[e] : 1.f;
+            }
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < XB_MAX_BLOCKS; ++j) {
+                v[j] += a[j];
+                ss += v[j] * v[j];
+            }
+            ss = warp_sum(ss);
+            consumers_sync(n_thr);  // red[] of the previous row has been read
+            if (lane == 0) red[warp] = ss;
+            consumers_sync(n_thr);
+            float tot = 0.f;
+            for (int w = 0; w < n_warps; ++w) tot += red[w];  // fixed order
+            const float inv = rsqrtf(tot / (float)k + xb.eps);
+#pragma unroll
+            for (int j = 0; j < XB_MAX_BLOCKS; ++j) {
+                const int blk = warp + j * n_warps;
+                if (blk < n_blk) {
+                    if (writes_residual && xb.x_out) xb.x_out[(size_t)mi * k + blk * 32 + lane] = v[j];
+                    warp_q8_1_to_smem(v[j] * inv * g[j], xrow + (size_t)blk * Q8_1_BYTES, lane);
+                }
+            }
+        } else {
+            const float* gu = xb.x_in + (size_t)mi * 2 * k;
+            for (int b0 = warp; b0 < n_blk; b0 += n_warps * XB_GLU_CHUNK) {
+                float gg[XB_GLU_CHUNK], uu[XB_GLU_CHUNK];
+#pragma unroll
+                for (int j = 0; j < XB_GLU_CHUNK; ++j) {
+                    const int blk = b0 + j * n_warps;
+                    gg[j] = blk < n_blk ? gu[blk * 32 + lane] : 0.f;
+                    uu[j] = blk < n_blk ? gu[k + blk * 32 + lane] : 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < XB_GLU_CHUNK; ++j) {
+                    const int blk = b0 + j * n_warps;
+                    if (blk < n_blk) {
+                        const float gv = gg[j];
+                        const float av = xb.act == 0 ? 0.5f * gv * (1.0f + tanhf(0.7978845608028654f * (gv + 0.044715f * gv * gv * gv)))
+                                                      : gv / (1.0f + __expf(-gv));
+                        warp_q8_1_to_smem(av * uu[j], xrow + (size_t)blk * Q8_1_BYTES, lane);
+                    }
+                }
+            }
+        }
+    }
+    consumers_sync(n_thr);  // every block of the staging area is written
+}
+
 template <int M>
 __global__ void __launch_bounds__((JOBS_MAX_WARPS + 1) * 32, 1) qmatvec_jobs_kernel(const __grid_constant__ JobList L) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -283,7 +389,8 @@ __global__ void __launch_bounds__((JOBS_MAX_WARPS + 1) * 32, 1) qmatvec_jobs_ker
         if (!L.any_sel) pdl_wait_prior_grids();  // activations come from the preceding kernel, y may still be read by it
         const unsigned push_seq = L.push.tp > 0 ? tp_next_seq(L.push.counter) : 0u;
         int x_issued = 0;  // activation copies issued
-        if (fo.j < L.n_jobs) {
+        const bool copies_x = L.x_mode == JOBS_X_GLOBAL;
+        if (copies_x && fo.j < L.n_jobs) {
             if (lane == 0) issue_x(fo.j);
             x_issued = 1;
         }
@@ -300,7 +407,7 @@ __global__ void __launch_bounds__((JOBS_MAX_WARPS + 1) * 32, 1) qmatvec_jobs_ker
                 break;
             }
             const JobDesc& J = L.job[fo.j];
-            if (fo.it == 0) {
+            if (copies_x && fo.it == 0) {
                 // every warp holds this job's activations in registers: the staging area is free for the next job's
                 JobCursor nx = fo;
                 nx.it = nx.n_it;  // step to the next job in which this CTA owns rows
@@ -368,6 +475,10 @@ __global__ void __launch_bounds__((JOBS_MAX_WARPS + 1) * 32, 1) qmatvec_jobs_ker
     const uint32_t ring_s = smem_u32(ring);
     ConsumerState st = {0, 0, 0u, 1};
     uint32_t x_parity = 0;
+    if (L.x_mode != JOBS_X_GLOBAL) {
+        pdl_wait_prior_grids();  // the inputs of the builder come from the preceding kernel
+        build_activations(L.xb, L.x_mode, L.m, xs, hdr->red, warp, lane, L.n_consumers, bx == 0);
+    }
     for (int j = 0; j < L.n_jobs; ++j) {
         const JobDesc& J = L.job[j];
         long row_begin;
@@ -381,6 +492,7 @@ __global__ void __launch_bounds__((JOBS_MAX_WARPS + 1) * 32, 1) qmatvec_jobs_ker
         // low address bits of this CTA's first row (a selector moves the matrix by a multiple of 16 bytes)
         a.w_lo = (uint32_t)((reinterpret_cast<uintptr_t>(J.w) + (size_t)row_begin * J.row_bytes) & 15);
         a.x_parity = x_parity;
+        a.x_wait = L.x_mode == JOBS_X_GLOBAL;
         const int type = J.type, rb = J.rb;
         if (type == QMM_TYPE_Q4_K)
             st = consume_job_rb<QMM_TYPE_Q4_K, M>(rb, a, hdr, ring_s, partial, xs, warp, lane, st, cta_abort);
@@ -400,12 +512,18 @@ static int g_jobs_warps = 14;
 static int g_jobs_ring = 150 * 1024;
 static int g_jobs_stage = 48 * 1024;
 static int g_jobs_rotate = 1;
+// decode engine at batch <= 2 on one GPU (default 0: every operator its own launch): 1 = Q|K and V as one job list; 2 = also the norms built inside the matvec
+// launches; 3 = also the gated activation (all three measured slower than the separate launches: 2 and 3 repeat the small operator in every CTA;
+// kept for experiments)
+static int g_decoder_fuse = 0;
+int decoder_fusion() { return g_decoder_fuse; }
 int jobs_tune(const char* key, int value) {
     const std::string k(key ? key : "");
     if (k == "jobs_warps" && value >= 1 && value <= JOBS_MAX_WARPS) return g_jobs_warps = value, QMM_OK;
     if (k == "jobs_ring_bytes" && value >= 8 * 1024 && value <= 190 * 1024) return g_jobs_ring = value, QMM_OK;
     if (k == "jobs_stage_bytes" && value >= 1024 && value <= 48 * 1024) return g_jobs_stage = value, QMM_OK;
     if (k == "jobs_rotate" && (value == 0 || value == 1)) return g_jobs_rotate = value, QMM_OK;
+    if (k == "decoder_fuse" && value >= 0 && value <= 3) return g_decoder_fuse = value, QMM_OK;
     return QMM_ERR_UNSUPPORTED;
 }
 
@@ -445,16 +563,27 @@ static int job_geometry(int type, int& block_elems, int& block_bytes, int& w_ali
 // Validates the jobs, then launches them in groups of up to JOBS_MAX.  Shapes the persistent kernel does
 // not take (see the head of this file) run as one single-matrix launch per job instead; a job with a
 // device-side selector has no such fallback and is rejected with QMM_ERR_UNSUPPORTED.
-int qmatvec_jobs_launch_push(const qmm_matvec_job* jobs, int n_jobs, int m, const TpPush* push, const long* push_words, cudaStream_t stream);
+int qmatvec_jobs_launch_ex(const qmm_matvec_job* jobs, int n_jobs, int m, const TpPush* push, const long* push_words, int x_mode,
+                           const XBuild* xb, cudaStream_t stream);
+int qmatvec_jobs_launch_push(const qmm_matvec_job* jobs, int n_jobs, int m, const TpPush* push, const long* push_words, cudaStream_t stream) {
+    return qmatvec_jobs_launch_ex(jobs, n_jobs, m, push, push_words, JOBS_X_GLOBAL, nullptr, stream);
+}
 int qmatvec_jobs_launch(const qmm_matvec_job* jobs, int n_jobs, int m, cudaStream_t stream) {
-    return qmatvec_jobs_launch_push(jobs, n_jobs, m, nullptr, nullptr, stream);
+    return qmatvec_jobs_launch_ex(jobs, n_jobs, m, nullptr, nullptr, JOBS_X_GLOBAL, nullptr, stream);
 }
 
 // push / push_words (tensor parallel, both or neither): job i with push_words[i] >= 0 sends its outputs to slot
 // push_words[i] + mi * y_stride + row of every rank's exchange area instead of storing them to its y.  Such a
 // list has no per-job fallback: QMM_ERR_UNSUPPORTED when it does not fit the persistent kernel.
-int qmatvec_jobs_launch_push(const qmm_matvec_job* jobs, int n_jobs, int m, const TpPush* push, const long* push_words, cudaStream_t stream) {
+// x_mode != JOBS_X_GLOBAL: the kernel builds the activations itself (xb; every job must have K = xb->k, the
+// jobs' xq pointers are not used); such a list has no fallback either and must fit one launch.
+int qmatvec_jobs_launch_ex(const qmm_matvec_job* jobs, int n_jobs, int m, const TpPush* push, const long* push_words, int x_mode,
+                           const XBuild* xb, cudaStream_t stream) {
     if (!jobs) return QMM_ERR_NULL;
+    const bool builds = x_mode != JOBS_X_GLOBAL;
+    if (builds && (!xb || !xb->x_in)) return QMM_ERR_NULL;
+    if (builds && (n_jobs > JOBS_MAX || xb->k % 32 != 0)) return QMM_ERR_UNSUPPORTED;
+    if (x_mode == JOBS_X_NORM && xb->k > XB_MAX_BLOCKS * 32 * g_jobs_warps) return QMM_ERR_UNSUPPORTED;
     if (n_jobs <= 0 || m <= 0) return QMM_ERR_SHAPE;
     const int sms = sm_count();
     const int nw = g_jobs_warps;
@@ -462,13 +591,15 @@ int qmatvec_jobs_launch_push(const qmm_matvec_job* jobs, int n_jobs, int m, cons
     bool any_sel = false;
     for (int i = 0; i < n_jobs; ++i) {
         const qmm_matvec_job& q = jobs[i];
-        if (!q.w || !q.xq || !q.y) return QMM_ERR_NULL;
+        if (!q.w || (!q.xq && !builds) || !q.y) return QMM_ERR_NULL;
+        if (builds && q.k != xb->k) return QMM_ERR_SHAPE;
         int be, bb, wa;
         if (int st = job_geometry(q.type, be, bb, wa)) return st;
         if (q.n <= 0 || q.k <= 0 || q.k % be != 0) return QMM_ERR_SHAPE;
         const long ys = q.y_stride ? q.y_stride : q.n;
         if (ys < q.n || ys > 0x7fffffffl) return QMM_ERR_SHAPE;
-        if (reinterpret_cast<uintptr_t>(q.w) % wa != 0 || reinterpret_cast<uintptr_t>(q.xq) % 4 != 0 || reinterpret_cast<uintptr_t>(q.y) % 4 != 0)
+        if (reinterpret_cast<uintptr_t>(q.w) % wa != 0 || (!builds && reinterpret_cast<uintptr_t>(q.xq) % 4 != 0) ||
+            reinterpret_cast<uintptr_t>(q.y) % 4 != 0)
             return QMM_ERR_ALIGN;
         const long row_bytes = (long)q.k / be * bb;
         if (row_bytes > 48 * 1024) return QMM_ERR_UNSUPPORTED;
@@ -478,11 +609,12 @@ int qmatvec_jobs_launch_push(const qmm_matvec_job* jobs, int n_jobs, int m, cons
         }
         const int xq_row = q.k / QK8 * Q8_1_BYTES;
         const int units = q.k / (q.type == QMM_TYPE_Q8_0 ? 32 : 64);
-        if (reinterpret_cast<uintptr_t>(q.xq) % 16 != 0 || ((long)m * xq_row) % 16 != 0 || (units + 31) / 32 > nw || (long)m * xq_row > 64 * 1024)
+        if ((!builds && (reinterpret_cast<uintptr_t>(q.xq) % 16 != 0 || ((long)m * xq_row) % 16 != 0)) || (units + 31) / 32 > nw ||
+            (long)m * xq_row > 64 * 1024)
             fits = false;
     }
     if (!fits) {
-        if (any_sel || push) return QMM_ERR_UNSUPPORTED;
+        if (any_sel || push || builds) return QMM_ERR_UNSUPPORTED;
         for (int i = 0; i < n_jobs; ++i) {
             const qmm_matvec_job& q = jobs[i];
             if (int st = qmatvec_launch_strided(q.type, q.w, q.xq, q.y, q.y_stride ? q.y_stride : q.n, m, q.n, q.k, stream)) return st;
@@ -498,6 +630,8 @@ int qmatvec_jobs_launch_push(const qmm_matvec_job* jobs, int n_jobs, int m, cons
         L.n_consumers = nw;
         L.any_sel = 0;
         if (push) L.push = *push;
+        L.x_mode = x_mode;
+        if (builds) L.xb = *xb;
         int slot_max = 0, pstage_max = 0, x_max = 0;
         for (int i = 0; i < nj; ++i) {
             const qmm_matvec_job& q = jobs[j0 + i];

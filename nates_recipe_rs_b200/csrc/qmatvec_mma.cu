@@ -591,10 +591,40 @@ static int mma_launch_inst(const CUtensorMap& wmap, const MmaParams& p, int grid
     return QMM_OK;
 }
 
+static int qmatvec_mma_launch_rows(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
+                                   unsigned long long* trace, const TpPush* push, cudaStream_t stream);
+
 // Returns QMM_ERR_UNSUPPORTED (nothing launched) when the type or shape does not fit this kernel; the
-// caller then uses the dp4a kernel.  m <= 16.
+// caller then uses the dp4a kernel.  m <= 16.  A matrix with several K chunks keeps the running sums of all
+// the tiles of a CTA in shared memory; when a tall matrix (an output head) has more tiles per CTA than fit,
+// it is launched in row blocks instead of falling back.
 int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                        unsigned long long* trace, const TpPush* push, cudaStream_t stream) {
+    int st = qmatvec_mma_launch_rows(type, w, xq, y, y_stride, m, n, k, cta_limit, trace, push, stream);
+    if (st != QMM_ERR_UNSUPPORTED || n < 4096) return st;
+    const long row_bytes = qmm_row_bytes(type, k);
+    if (row_bytes <= 0 || row_bytes % 16 != 0) return QMM_ERR_UNSUPPORTED;
+    const int sms = sm_count();
+    for (int parts = 2; parts <= 16; parts *= 2) {
+        // whole 16-row tiles per block, the same number for every CTA
+        int rows = ((n + parts - 1) / parts + 16 * sms - 1) / (16 * sms) * (16 * sms);
+        if (rows >= n) continue;
+        for (int r0 = 0; r0 < n; r0 += rows) {
+            const int nr = n - r0 < rows ? n - r0 : rows;
+            TpPush sub = {};
+            if (push) sub = *push, sub.word0 += r0;
+            st = qmatvec_mma_launch_rows(type, static_cast<const uint8_t*>(w) + (size_t)r0 * row_bytes, xq, y + r0, y_stride, m, nr, k, cta_limit,
+                                         trace, push ? &sub : nullptr, stream);
+            if (st == QMM_ERR_UNSUPPORTED && r0 == 0) break;  // still too many tiles per CTA: try smaller blocks
+            if (st) return st;
+        }
+        if (st == QMM_OK) return QMM_OK;
+    }
+    return QMM_ERR_UNSUPPORTED;
+}
+
+static int qmatvec_mma_launch_rows(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
+                                   unsigned long long* trace, const TpPush* push, cudaStream_t stream) {
     if ((type != QMM_TYPE_Q4_K && type != QMM_TYPE_Q6_K) || m < 1 || m > 16 || k % QKK != 0) return QMM_ERR_UNSUPPORTED;
     // 16-byte asynchronous copies of the activations, tensor copies of the weights
     if (reinterpret_cast<uintptr_t>(xq) % 16 != 0 || reinterpret_cast<uintptr_t>(w) % 16 != 0) return QMM_ERR_UNSUPPORTED;

@@ -23,7 +23,7 @@ __all__ = [
     "Q8_0", "Q8_1", "Q4_K", "Q6_K", "row_bytes", "check_launch",
     "gpu_quantize_q8_1_into", "gpu_quantize_q8_1", "gpu_quantize_weights_into", "gpu_quantize_weights",
     "gpu_dequantize_into", "gpu_dequantize", "gpu_qmatvec_into", "gpu_qmatvec", "gpu_qblock_dots",
-    "MatvecJobs", "gpu_qmatvec_batch_into", "TpComm", "gpu_qmatvec_tp_into", "gpu_qmatvec_batch_tp_into",
+    "MatvecJobs", "gpu_qmatvec_batch_into", "gpu_norm_qmatvec_batch_into", "gpu_glu_qmatvec_batch_into", "TpComm", "gpu_qmatvec_tp_into", "gpu_qmatvec_batch_tp_into",
     "gpu_qgemm_q4_k_bf16_into", "gpu_qgemm_q4_k_bf16",
     "gpu_qlinear",
     "gpu_rmsnorm_q8_1_into", "gpu_rope_kv_append", "gpu_glu_act_q8_1_into", "gpu_embed_rows_into", "gpu_argmax_rows",
@@ -37,6 +37,10 @@ def _ptr(t):
 
 def _stream():
     return torch.cuda.current_stream().cuda_stream
+
+
+def _opt(t):
+    return _ptr(t) if t is not None else None
 
 
 def _need(t, nbytes, name):
@@ -141,7 +145,7 @@ class MatvecJobs:
         """out(m,n) = xq(m,k) . w(n,k)^T, as gpu_qmatvec_into; `select` (int32 device tensor) makes the
         matrix w + select[0] * select_stride_bytes, resolved on the device when the kernel runs; tp_sum
         (gpu_qmatvec_batch_tp_into only): the outputs are summed over the tensor-parallel ranks."""
-        self._jobs.append(_lib.MatvecJob(qtype, n, k, _ptr(w), _ptr(xq), _ptr(out), y_stride,
+        self._jobs.append(_lib.MatvecJob(qtype, n, k, _ptr(w), _opt(xq), _ptr(out), y_stride,
                                          _ptr(select) if select is not None else None, select_stride_bytes, 1 if tp_sum else 0))
         self._keep.append((w, xq, out, select))
         return self
@@ -159,6 +163,20 @@ def gpu_qmatvec_batch_into(jobs, m):
     input (examples/gemma4.rs:653-667, 675-678, 726-742)."""
     arr = jobs.array()
     check(lib().launch_qmatvec_batch(arr, len(jobs), m, _stream()), "launch_qmatvec_batch")
+
+
+def gpu_norm_qmatvec_batch_into(x_in, x_add, gamma, x_out, eps, jobs, m):
+    """Residual add + RMSNorm + Q8_1 built inside the job-list launch that consumes them (the jobs' xq is
+    not used): examples/gemma4.rs:646-667 as one launch.  x_out (or None) receives x_in + x_add."""
+    arr = jobs.array()
+    check(lib().launch_norm_qmatvec_batch(_ptr(x_in), _opt(x_add), _opt(gamma), _opt(x_out), eps, arr, len(jobs), m, _stream()),
+          "launch_norm_qmatvec_batch")
+
+
+def gpu_glu_qmatvec_batch_into(gate_up, act, jobs, m):
+    """Gated activation + Q8_1 built inside the job-list launch that consumes them (examples/gemma4.rs:677-678)."""
+    arr = jobs.array()
+    check(lib().launch_glu_qmatvec_batch(_ptr(gate_up), act, arr, len(jobs), m, _stream()), "launch_glu_qmatvec_batch")
 
 
 class TpComm:
@@ -245,10 +263,6 @@ def gpu_qlinear(qtype, w, x, n, k):
 
 
 # ---- the small per-layer operators -----------------------------------------------------
-def _opt(t):
-    return _ptr(t) if t is not None else None
-
-
 def gpu_rmsnorm_q8_1_into(x, gamma, xq, rows, cols, eps, add=None, out_f32=None):
     """x (rows, cols) f32 [+= add, in place] -> xq = Q8_1(rmsnorm(x) * gamma); the upstream's
     gpu_rmsnorm_f64_into (gpu-core/src/infer_ops.rs:117-139) fused with the residual add before it and

@@ -241,3 +241,33 @@ def test_gguf_decoder_rejects_what_it_cannot_run(dec, tmp_path):
     with pytest.raises(QmmError) as e:
         dec.Decoder(dec.DecoderConfig(max_batch=1, ctx_len=16, tp_rank=0, tp_size=1), gguf_path=tmp_path / "none.gguf")
     assert e.value.status == -8
+
+
+def test_fused_and_separate_launches_agree(dec):
+    """Batch 1-2 on one GPU: the levels of the tunable decoder_fuse (Q|K and V as one job list; norms and
+    gated activations built inside the matvec launches) against every operator as its own launch (0)."""
+    from nates_recipe_rs_b200 import quant_ops as ops
+    from nates_recipe_rs_b200._lib import check, lib
+    cfg = tiny_cfg(dec, n_layers=3, hidden=1024, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn=2048, vocab=2048, max_batch=2)
+    results = []
+    for fuse in (3, 2, 1, 0):
+        check(lib().qmm_tune(b"decoder_fuse", fuse), "qmm_tune")
+        try:
+            d = dec.Decoder(cfg)
+            toks = torch.tensor([9, 1500], dtype=torch.int32, device="cuda")
+            seq = []
+            for pos in range(5):
+                lg = torch.empty(2, cfg.vocab, device="cuda")
+                d.tokens.copy_(toks)
+                d.step(2, pos, lg)
+                ops.check_launch()
+                seq.append(lg.cpu().numpy())
+                toks = torch.tensor([100 + pos, 200 + pos], dtype=torch.int32, device="cuda")
+            results.append(seq)
+            d.close()
+        finally:
+            check(lib().qmm_tune(b"decoder_fuse", 1), "qmm_tune")
+    for level, seq in zip((3, 2, 1), results[:3]):
+        for pos, (a, b) in enumerate(zip(seq, results[3])):
+            scale = np.abs(b).max()
+            assert np.abs(a - b).max() <= (1e-5 if pos == 0 else 2e-2) * scale, (level, pos, float(np.abs(a - b).max()), float(scale))

@@ -209,3 +209,51 @@ def test_tp_exchange_with_one_rank_equals_plain_launches(ops):
         assert L.launch_qmatvec_tp(comm, Q4, big.data_ptr(), big.data_ptr(), big.data_ptr(), 32, 4096, 256, stream) == -7
     finally:
         check(L.qmm_tp_comm_destroy(comm), "qmm_tp_comm_destroy")
+
+
+@pytest.mark.parametrize("m", [1, 2])
+@pytest.mark.parametrize("k,with_add", [(4096, True), (1024, False), (8192, True)])
+def test_norm_built_inside_the_job_launch(ops, m, k, with_add):
+    """launch_norm_qmatvec_batch: residual add + RMSNorm + Q8_1 inside the launch, shared by the jobs."""
+    x = oracle.fill_normal(m * k, 1, 1.3).reshape(m, k)
+    add = oracle.fill_normal(m * k, 2, 0.6).reshape(m, k) if with_add else None
+    gamma = oracle.fill_normal(k, 3, 0.1) + np.float32(1.0)
+    xs = x + add if with_add else x
+    xq = oracle.quantize(oracle.Q8_1, oracle.rmsnorm(xs, gamma, 1e-6))
+    specs = [(Q4, 700, k), (Q6, 260, k), (Q8, 129, k)]
+    jobs = ops.MatvecJobs()
+    outs, wants = [], []
+    for i, (qtype, n, _) in enumerate(specs):
+        w = oracle.quantize(qtype, oracle.fill_normal(n * k, 20 + i, 0.02).reshape(n, k))
+        y = torch.full((m, n), float("nan"), device="cuda")
+        jobs.add(qtype, dev(w), None, y, n, k)
+        outs.append(y)
+        wants.append(oracle.matvec(qtype, w, xq, k))
+    x_out = torch.full((m, k), float("nan"), device="cuda") if with_add else None
+    ops.gpu_norm_qmatvec_batch_into(dev(x), dev(add) if with_add else None, dev(gamma), x_out, 1e-6, jobs, m)
+    torch.cuda.synchronize()
+    ops.check_launch()
+    if with_add:
+        assert np.array_equal(x_out.cpu().numpy(), xs), "updated residual"
+    for i, (y, want) in enumerate(zip(outs, wants)):
+        # the sum of squares is added in another order than on the host: an activation code may differ by one
+        err = np.abs(y.cpu().numpy() - want)
+        assert (err <= 1e-4 + 1e-3 * np.abs(want) + 2e-3 * np.abs(want).max()).all(), (i, float(err.max()))
+        assert np.median(err / (np.abs(want) + 1e-6)) < 1e-4
+
+
+@pytest.mark.parametrize("act", [0, 1])
+def test_gated_activation_built_inside_the_job_launch(ops, act):
+    m, k, n = 2, 3584, 1000
+    gu = oracle.fill_normal(m * 2 * k, 5, 1.5).reshape(m, 2 * k)
+    fn = oracle.gelu_mul if act == 0 else oracle.silu_mul
+    xq = oracle.quantize(oracle.Q8_1, fn(gu[:, :k].copy(), gu[:, k:].copy()))
+    w = oracle.quantize(Q6, oracle.fill_normal(n * k, 6, 0.02).reshape(n, k))
+    y = torch.full((m, n), float("nan"), device="cuda")
+    jobs = ops.MatvecJobs().add(Q6, dev(w), None, y, n, k)
+    ops.gpu_glu_qmatvec_batch_into(dev(gu), act, jobs, m)
+    torch.cuda.synchronize()
+    ops.check_launch()
+    want = oracle.matvec(Q6, w, xq, k)
+    err = np.abs(y.cpu().numpy() - want)
+    assert (err <= 1e-4 + 1e-3 * np.abs(want) + 2e-3 * np.abs(want).max()).all(), float(err.max())

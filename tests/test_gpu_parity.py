@@ -204,6 +204,36 @@ def test_tensor_parallel_shard_shapes_both_kernels(ops, qtype, n, k):
         _lib.check(L.qmm_tune(b"mma_min_m", 3), "tune")
 
 
+def test_tall_head_with_several_k_chunks_takes_the_tensor_core_kernel_in_row_blocks(ops):
+    """The 70B-class output head (128256 x 8192, Q6_K) at 16 activation rows: two K chunks and 55 row tiles per CTA,
+    more running sums than fit in shared memory at once, so the launcher cuts the matrix into row blocks.  Against
+    the dp4a kernel on every output and against the oracle on a row sample (also across a block boundary)."""
+    from nates_recipe_rs_b200 import _lib
+    L = _lib.lib()
+    qtype, n, k, m = oracle.Q6_K, 128256, 8192, 16
+    gen = torch.Generator(device="cuda").manual_seed(99)
+    w = torch.empty(n * oracle.row_bytes(qtype, k), dtype=torch.uint8, device="cuda")
+    rb = oracle.row_bytes(qtype, k)
+    for r0 in range(0, n, 16032):   # quantized in pieces: the f32 source of the whole matrix would be 4 GB
+        ops.gpu_quantize_weights_into(qtype, torch.randn(16032, k, device="cuda", generator=gen) * 0.02, w[r0 * rb:(r0 + 16032) * rb], 16032, k)
+    xq = ops.gpu_quantize_q8_1(torch.randn(m, k, device="cuda", generator=gen))
+    try:
+        _lib.check(L.qmm_tune(b"mma_min_m", 0), "tune")
+        y_dp4a = ops.gpu_qmatvec(qtype, w, xq, m, n, k)
+        _lib.check(L.qmm_tune(b"mma_min_m", 3), "tune")
+        y = torch.full((m, n), float("nan"), device="cuda")
+        ops.gpu_qmatvec_into(qtype, w, xq, y, m, n, k)
+        ops.check_launch()
+    finally:
+        _lib.check(L.qmm_tune(b"mma_min_m", 3), "tune")
+    assert not torch.isnan(y).any()
+    assert_close(y.cpu().numpy(), y_dp4a.cpu().numpy(), "all rows")
+    rows = np.concatenate([np.arange(0, n, 4099), np.arange(66290, 66320), [n - 1]])
+    wn = w.cpu().numpy().reshape(n, rb)[rows]
+    want = oracle.matvec(qtype, wn, xq.cpu().numpy(), k)
+    assert_close(y.cpu().numpy()[:, rows], want, "row sample")
+
+
 @pytest.mark.parametrize("qtype", TYPES)
 @pytest.mark.parametrize("m", [2, 8, 16])
 def test_matvec_random_byte_weights(ops, qtype, m):
