@@ -124,6 +124,11 @@ int launch_qmatvec_q8_0(const void* w, const void* xq, float* y, int m, int n, i
 int launch_qmatvec_q4_k(const void* w, const void* xq, float* y, int m, int n, int k, void* stream);
 int launch_qmatvec_q6_k(const void* w, const void* xq, float* y, int m, int n, int k, void* stream);
 int launch_qmatvec(int type, const void* w, const void* xq, float* y, int m, int n, int k, void* stream);
+/* The same with the weight rows row_pitch_bytes apart instead of back to back (row_pitch_bytes >= the packed row,
+ * even; 0 = back to back).  Q6_K and Q8_0 rows are in general not a multiple of 16 bytes long; a loader that pads
+ * them (Q6_K: to a multiple of 48 bytes) makes every shape eligible for the tensor-core kernel.  The padding is
+ * read and ignored. */
+int launch_qmatvec_pitched(int type, const void* w, long row_pitch_bytes, const void* xq, float* y, int m, int n, int k, void* stream);
 
 /* ---- several independent decode projections in ONE launch.  The upstream issues the projections
  * that share an input one launch after the other (q, k, v: examples/gemma4.rs:653-667; gate and up:

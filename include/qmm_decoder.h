@@ -59,7 +59,10 @@ int qmm_decoder_export_gguf(void* handle, const char* path, const char* architec
 int qmm_decoder_destroy(void* handle);
 /* packed weight bytes this rank streams per decoded token (all layers + head) */
 long qmm_decoder_weight_bytes(void* handle);
-/* device pointer and byte size of a tensor (norm weights are f32, matrices packed blocks) */
+/* device pointer and packed byte size of a tensor (norm weights are f32, matrices packed blocks).  On a
+ * tensor-parallel rank the rows of a Q6_K O or down shard may lie further apart on the device than their
+ * packed length (padded to 16-byte boundaries for the tensor-core matvec): read such a tensor with
+ * qmm_decoder_read_tensor, which packs the rows. */
 int qmm_decoder_get_tensor(void* handle, int layer, int which, void** ptr, long* bytes);
 /* copies a tensor to host memory (synchronises the device); capacity in bytes */
 int qmm_decoder_read_tensor(void* handle, int layer, int which, void* host_dst, long capacity);

@@ -53,6 +53,7 @@ SIGNATURES = {
     "launch_qmatvec_q4_k": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "launch_qmatvec_q6_k": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "launch_qmatvec": (i32, [i32, vp, vp, vp, i32, i32, i32, vp]),
+    "launch_qmatvec_pitched": (i32, [i32, vp, i64, vp, vp, i32, i32, i32, vp]),
     "launch_qmatvec_batch": (i32, [C.POINTER(MatvecJob), i32, i32, vp]),
     "qmm_tp_comm_create": (i32, [i32, i32, i64, C.POINTER(vp)]),
     "qmm_tp_comm_destroy": (i32, [vp]),

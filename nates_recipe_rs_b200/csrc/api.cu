@@ -26,6 +26,8 @@ static int g_overlap = 1;
 bool overlap_enabled() { return g_overlap != 0; }
 
 int qmatvec_launch(int type, const void* w, const void* xq, float* y, int m, int n, int k, cudaStream_t stream);
+int qmatvec_launch_pitched(int type, const void* w, long row_pitch, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
+                           const TpPush* push, cudaStream_t stream);
 int qblock_dots_launch(int type, const void* w, const void* xq, int32_t* out, int n, int k, cudaStream_t stream);
 int quantize_q8_1_launch(const float* x, void* xq, int m, int k, cudaStream_t stream);
 int quantize_weights_launch(int type, const float* w, void* out, long rows, int k, cudaStream_t stream);
@@ -135,6 +137,10 @@ int launch_dequantize_q6_k_bf16(const void* w, void* out, long n, void* s) { ret
 
 int launch_qmatvec(int type, const void* w, const void* xq, float* y, int m, int n, int k, void* stream) {
     return qmatvec_launch(type, w, xq, y, m, n, k, as_stream(stream));
+}
+int launch_qmatvec_pitched(int type, const void* w, long row_pitch_bytes, const void* xq, float* y, int m, int n, int k, void* stream) {
+    if (row_pitch_bytes < 0) return QMM_ERR_SHAPE;
+    return qmatvec_launch_pitched(type, w, row_pitch_bytes, xq, y, n, m, n, k, 0, nullptr, as_stream(stream));
 }
 int launch_qmatvec_q8_0(const void* w, const void* xq, float* y, int m, int n, int k, void* s) { return qmatvec_launch(QMM_TYPE_Q8_0, w, xq, y, m, n, k, as_stream(s)); }
 int launch_qmatvec_q4_k(const void* w, const void* xq, float* y, int m, int n, int k, void* s) { return qmatvec_launch(QMM_TYPE_Q4_K, w, xq, y, m, n, k, as_stream(s)); }

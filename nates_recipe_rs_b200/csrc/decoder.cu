@@ -20,6 +20,8 @@ int qmatvec_launch_limited(int type, const void* w, const void* xq, float* y, lo
 int quantize_weights_launch(int type, const float* w, void* out, long rows, int k, cudaStream_t stream);
 int qmatvec_launch_push(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                         const TpPush* push, cudaStream_t stream);
+int qmatvec_launch_pitched(int type, const void* w, long row_pitch, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
+                           const TpPush* push, cudaStream_t stream);
 int decoder_fusion();
 
 constexpr int ARGMAX_PARTS = 256;
@@ -28,6 +30,15 @@ struct LayerWeights {
     float *attn_norm, *ffn_norm;
     uint8_t *wqk, *wv, *wo, *wgu, *wdown;
 };
+// Row pitch of a row-parallel shard: a tensor-parallel rank holds columns [r*K/tp, (r+1)*K/tp) of O and down as
+// a matrix of its own; Q6_K rows of such a shard (210 bytes per 256 columns) need not be a multiple of 16 bytes
+// long, which the tensor-core matvec's tensor copies require of every row start, so the shard's rows are padded
+// to the next multiple of 48 bytes (a whole number of that kernel's 48-byte groups).  0 = rows back to back.
+static long shard_pitch(int type, long k, int tp_size) {
+    const long rb = type == QMM_TYPE_Q8_0 ? k / 32 * Q8_0_BYTES : (type == QMM_TYPE_Q4_K ? k / 256 * Q4_K_BYTES : k / 256 * Q6_K_BYTES);
+    if (tp_size <= 1 || type != QMM_TYPE_Q6_K || rb % 48 == 0) return 0;
+    return (rb + 47) / 48 * 48;
+}
 
 struct Decoder {
     qmm_decoder_config c;
@@ -47,6 +58,7 @@ struct Decoder {
     float* part[2] = {nullptr, nullptr};
     TpComm* comm = nullptr;                    // tensor parallel only
     Candidate* argmax_cand = nullptr;          // argmax stage-one candidates: max_batch x ARGMAX_PARTS
+    long o_pitch = 0, down_pitch = 0;          // row pitch of the O and down shards (0: rows back to back)
     int attn_splits = 1, attn_chunk = 0;
     std::vector<void*> allocs;
     // second stream for the V projection when its type differs from Q|K's (it then runs beside the Q|K
@@ -212,6 +224,29 @@ static void destroy(Decoder* d) {
     delete d;
 }
 
+// A row-parallel shard (hidden rows, k columns out of k_full): rows back to back, or `pitch` bytes apart
+// (filled densely into a staging allocation first, then spread; the padding is zeroed).
+static int fill_row_parallel(Decoder* d, WeightSource* src, uint8_t** dst, int type, int layer, int which, int k, int col0, int k_full, long pitch,
+                             cudaStream_t s) {
+    const int H = d->c.hidden;
+    const size_t rb = (size_t)type_row_bytes(type, k);
+    if (!pitch) {
+        if (int st = dev_alloc(d, dst, (size_t)H * rb)) return st;
+        return src->matrix(d, *dst, type, layer, which, H, k, 0, col0, k_full, s);
+    }
+    if (int st = dev_alloc(d, dst, (size_t)H * pitch)) return st;
+    void* dense = nullptr;
+    QMM_CUDA_TRY(cudaMalloc(&dense, (size_t)H * rb));
+    int st = src->matrix(d, static_cast<uint8_t*>(dense), type, layer, which, H, k, 0, col0, k_full, s);
+    cudaError_t e = cudaSuccess;
+    if (!st) e = cudaMemsetAsync(*dst, 0, (size_t)H * pitch, s);
+    if (!st && e == cudaSuccess) e = cudaMemcpy2DAsync(*dst, (size_t)pitch, dense, rb, rb, (size_t)H, cudaMemcpyDeviceToDevice, s);
+    if (!st && e == cudaSuccess) e = cudaStreamSynchronize(s);
+    cudaFree(dense);
+    if (!st && e != cudaSuccess) st = cuda_fail(e);
+    return st;
+}
+
 static int create(const qmm_decoder_config* cfg, WeightSource* src, Decoder** out) {
     const qmm_decoder_config& c = *cfg;
     if (c.n_layers <= 0 || c.hidden <= 0 || c.head_dim <= 0 || c.n_q_heads <= 0 || c.n_kv_heads <= 0 || c.ffn <= 0 || c.vocab <= 0 ||
@@ -256,6 +291,8 @@ static int create(const qmm_decoder_config* cfg, WeightSource* src, Decoder** ou
         seeded->tmp = tmp;
     }
     const int r = c.tp_rank;
+    d->o_pitch = shard_pitch(c.type_attn_o, ao, c.tp_size);
+    d->down_pitch = shard_pitch(c.type_ffn_down, d->ffn_l, c.tp_size);
     d->layers.resize(c.n_layers);
     long per_token = 0;
     for (int l = 0; l < c.n_layers; ++l) {
@@ -280,16 +317,14 @@ static int create(const qmm_decoder_config* cfg, WeightSource* src, Decoder** ou
         }
         TRY(src->matrix(d, L.wv, c.type_attn_v, l, QMM_T_WV, d->v_rows, H, (long)r * d->v_rows, 0, H, s));
         const size_t o_b = (size_t)H * type_row_bytes(c.type_attn_o, ao);
-        TRY(dev_alloc(d, &L.wo, o_b));
-        TRY(src->matrix(d, L.wo, c.type_attn_o, l, QMM_T_WO, H, ao, 0, r * ao, c.n_q_heads * hd, s));
+        TRY(fill_row_parallel(d, src, &L.wo, c.type_attn_o, l, QMM_T_WO, ao, r * ao, c.n_q_heads * hd, d->o_pitch, s));
         const size_t gu_b = (size_t)2 * d->ffn_l * type_row_bytes(c.type_ffn_gate_up, H);
         TRY(dev_alloc(d, &L.wgu, gu_b));
         TRY(src->matrix(d, L.wgu, c.type_ffn_gate_up, l, QMM_T_WGATE, d->ffn_l, H, (long)r * d->ffn_l, 0, H, s));
         TRY(src->matrix(d, L.wgu + (size_t)d->ffn_l * type_row_bytes(c.type_ffn_gate_up, H), c.type_ffn_gate_up, l, QMM_T_WUP, d->ffn_l, H,
                         (long)r * d->ffn_l, 0, H, s));
         const size_t dn_b = (size_t)H * type_row_bytes(c.type_ffn_down, d->ffn_l);
-        TRY(dev_alloc(d, &L.wdown, dn_b));
-        TRY(src->matrix(d, L.wdown, c.type_ffn_down, l, QMM_T_WDOWN, H, d->ffn_l, 0, r * d->ffn_l, c.ffn, s));
+        TRY(fill_row_parallel(d, src, &L.wdown, c.type_ffn_down, l, QMM_T_WDOWN, d->ffn_l, r * d->ffn_l, c.ffn, d->down_pitch, s));
         per_token += (long)(qk_b + v_b + o_b + gu_b + dn_b);
     }
     TRY(dev_alloc(d, &d->final_norm, H * sizeof(float)));
@@ -388,9 +423,10 @@ static int add_norm(Decoder* d, int which, const float* gamma, int batch, cudaSt
 // rank's exchange area, where the next add_norm finds the partial outputs of all ranks
 static int row_parallel(Decoder* d, int type, const uint8_t* w, const uint8_t* xq, int which, int batch, int k, cudaStream_t s) {
     const int H = d->c.hidden;
-    if (!d->comm) return qmatvec_launch_strided(type, w, xq, d->part[which], H, batch, H, k, s);
+    const long pitch = which == 0 ? d->o_pitch : d->down_pitch;
+    if (!d->comm) return qmatvec_launch_pitched(type, w, pitch, xq, d->part[which], H, batch, H, k, 0, nullptr, s);
     const TpPush push = tp_comm_push(d->comm, 0);
-    return qmatvec_launch_push(type, w, xq, d->part[which], H, batch, H, k, 0, &push, s);
+    return qmatvec_launch_pitched(type, w, pitch, xq, d->part[which], H, batch, H, k, 0, &push, s);
 }
 
 // Small batches on one GPU: the residual add + norm + quantization before a block's projections, and the
@@ -736,6 +772,13 @@ int qmm_decoder_read_tensor(void* handle, int layer, int which, void* host_dst, 
     if (int st = qmm_decoder_get_tensor(handle, layer, which, &p, &n)) return st;
     if (n > capacity) return QMM_ERR_SHAPE;
     QMM_CUDA_TRY(cudaDeviceSynchronize());
+    Decoder* d = static_cast<Decoder*>(handle);
+    const long pitch = layer >= 0 ? (which == QMM_T_WO ? d->o_pitch : (which == QMM_T_WDOWN ? d->down_pitch : 0)) : 0;
+    if (pitch) {  // the rows lie `pitch` bytes apart on the device: the copy packs them
+        const size_t rb = (size_t)n / d->c.hidden;
+        QMM_CUDA_TRY(cudaMemcpy2D(host_dst, rb, p, (size_t)pitch, rb, (size_t)d->c.hidden, cudaMemcpyDeviceToHost));
+        return QMM_OK;
+    }
     QMM_CUDA_TRY(cudaMemcpy(host_dst, p, (size_t)n, cudaMemcpyDeviceToHost));
     return QMM_OK;
 }

@@ -305,7 +305,7 @@ void gemm_set_probe(int v);
 int mma_set_min_m(int v);
 int attn_set_tc_min_batch(int v);
 int mma_min_m();
-int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
+int qmatvec_mma_launch(int type, const void* w, long row_pitch, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                        unsigned long long* trace, const TpPush* push, cudaStream_t stream);
 int matvec_tune(const char* key, int value) {
     const std::string k(key ? key : "");
@@ -373,6 +373,8 @@ int qmatvec_launch_limited(int type, const void* w, const void* xq, float* y, lo
                            cudaStream_t stream);
 int qmatvec_launch_push(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                         const TpPush* push, cudaStream_t stream);
+int qmatvec_launch_pitched(int type, const void* w, long row_pitch, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
+                           const TpPush* push, cudaStream_t stream);
 int qmatvec_launch(int type, const void* w, const void* xq, float* y, int m, int n, int k, cudaStream_t stream) {
     return qmatvec_launch_strided(type, w, xq, y, n, m, n, k, stream);
 }
@@ -393,6 +395,14 @@ int qmatvec_launch_limited(int type, const void* w, const void* xq, float* y, lo
 // rank's exchange area instead of y (y must still be a valid pointer; it is not written)
 int qmatvec_launch_push(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                         const TpPush* push, cudaStream_t stream) {
+    return qmatvec_launch_pitched(type, w, 0, xq, y, y_stride, m, n, k, cta_limit, push, stream);
+}
+
+// row_pitch: bytes from one weight row to the next (0 = the packed row bytes: rows back to back).  A pitch
+// lets a loader pad rows so that each starts on a 16-byte boundary (Q6_K rows of 210 * k/256 bytes do not
+// in general), which the tensor-core kernel's tensor copies need; the padding is streamed and ignored.
+int qmatvec_launch_pitched(int type, const void* w, long row_pitch, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
+                           const TpPush* push, cudaStream_t stream) {
     if (!w || !xq || !y) return QMM_ERR_NULL;
     if (y_stride < n) return QMM_ERR_SHAPE;
     int block_elems, block_bytes, unit_elems, w_align;
@@ -407,6 +417,10 @@ int qmatvec_launch_push(int type, const void* w, const void* xq, float* y, long 
     p.n = n;
     p.k = k;
     p.row_bytes = k / block_elems * block_bytes;
+    if (row_pitch) {
+        if (row_pitch < p.row_bytes || row_pitch % 2 != 0 || row_pitch > STAGE_MAX_BYTES) return QMM_ERR_SHAPE;
+        p.row_bytes = (int)row_pitch;  // all addressing goes by the pitch; the units of a row come from k
+    }
     p.xq_row_bytes = k / QK8 * Q8_1_BYTES;
     p.probe = g_probe;
     p.trace = g_trace ? g_trace + (size_t)(g_trace_count++) * g_trace_stride : nullptr;
@@ -432,7 +446,7 @@ int qmatvec_launch_push(int type, const void* w, const void* xq, float* y, long 
             const int mg = m - m_done < 16 ? m - m_done : 16;
             TpPush sub = {};
             if (push) sub = *push, sub.word0 += (long)m_done * y_stride;
-            const int st = qmatvec_mma_launch(type, w, static_cast<const uint8_t*>(xq) + (size_t)m_done * p.xq_row_bytes,
+            const int st = qmatvec_mma_launch(type, w, row_pitch, static_cast<const uint8_t*>(xq) + (size_t)m_done * p.xq_row_bytes,
                                               y + (size_t)m_done * y_stride, y_stride, mg, n, k, cta_limit, p.trace, push ? &sub : nullptr, stream);
             if (st == QMM_ERR_UNSUPPORTED) break;
             if (st) return st;

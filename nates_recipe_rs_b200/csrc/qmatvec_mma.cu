@@ -591,18 +591,18 @@ static int mma_launch_inst(const CUtensorMap& wmap, const MmaParams& p, int grid
     return QMM_OK;
 }
 
-static int qmatvec_mma_launch_rows(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
-                                   unsigned long long* trace, const TpPush* push, cudaStream_t stream);
+static int qmatvec_mma_launch_rows(int type, const void* w, long row_pitch, const void* xq, float* y, long y_stride, int m, int n, int k,
+                                   int cta_limit, unsigned long long* trace, const TpPush* push, cudaStream_t stream);
 
 // Returns QMM_ERR_UNSUPPORTED (nothing launched) when the type or shape does not fit this kernel; the
 // caller then uses the dp4a kernel.  m <= 16.  A matrix with several K chunks keeps the running sums of all
 // the tiles of a CTA in shared memory; when a tall matrix (an output head) has more tiles per CTA than fit,
 // it is launched in row blocks instead of falling back.
-int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
+int qmatvec_mma_launch(int type, const void* w, long row_pitch, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                        unsigned long long* trace, const TpPush* push, cudaStream_t stream) {
-    int st = qmatvec_mma_launch_rows(type, w, xq, y, y_stride, m, n, k, cta_limit, trace, push, stream);
+    int st = qmatvec_mma_launch_rows(type, w, row_pitch, xq, y, y_stride, m, n, k, cta_limit, trace, push, stream);
     if (st != QMM_ERR_UNSUPPORTED || n < 4096) return st;
-    const long row_bytes = qmm_row_bytes(type, k);
+    const long row_bytes = row_pitch ? row_pitch : qmm_row_bytes(type, k);
     if (row_bytes <= 0 || row_bytes % 16 != 0) return QMM_ERR_UNSUPPORTED;
     const int sms = sm_count();
     for (int parts = 2; parts <= 16; parts *= 2) {
@@ -613,8 +613,8 @@ int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y
             const int nr = n - r0 < rows ? n - r0 : rows;
             TpPush sub = {};
             if (push) sub = *push, sub.word0 += r0;
-            st = qmatvec_mma_launch_rows(type, static_cast<const uint8_t*>(w) + (size_t)r0 * row_bytes, xq, y + r0, y_stride, m, nr, k, cta_limit,
-                                         trace, push ? &sub : nullptr, stream);
+            st = qmatvec_mma_launch_rows(type, static_cast<const uint8_t*>(w) + (size_t)r0 * row_bytes, row_pitch, xq, y + r0, y_stride, m, nr, k,
+                                         cta_limit, trace, push ? &sub : nullptr, stream);
             if (st == QMM_ERR_UNSUPPORTED && r0 == 0) break;  // still too many tiles per CTA: try smaller blocks
             if (st) return st;
         }
@@ -623,8 +623,8 @@ int qmatvec_mma_launch(int type, const void* w, const void* xq, float* y, long y
     return QMM_ERR_UNSUPPORTED;
 }
 
-static int qmatvec_mma_launch_rows(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
-                                   unsigned long long* trace, const TpPush* push, cudaStream_t stream) {
+static int qmatvec_mma_launch_rows(int type, const void* w, long row_pitch, const void* xq, float* y, long y_stride, int m, int n, int k,
+                                   int cta_limit, unsigned long long* trace, const TpPush* push, cudaStream_t stream) {
     if ((type != QMM_TYPE_Q4_K && type != QMM_TYPE_Q6_K) || m < 1 || m > 16 || k % QKK != 0) return QMM_ERR_UNSUPPORTED;
     // 16-byte asynchronous copies of the activations, tensor copies of the weights
     if (reinterpret_cast<uintptr_t>(xq) % 16 != 0 || reinterpret_cast<uintptr_t>(w) % 16 != 0) return QMM_ERR_UNSUPPORTED;
@@ -642,16 +642,20 @@ static int qmatvec_mma_launch_rows(int type, const void* w, const void* xq, floa
     p.k_blocks = k / QKK;
     p.row_bytes = p.k_blocks * block_bytes;
     p.xq_row_bytes = k / QK8 * Q8_1_BYTES;
+    const long pitch_bytes = row_pitch ? row_pitch : p.row_bytes;  // bytes from one weight row to the next
+    if (pitch_bytes < p.row_bytes) return QMM_ERR_SHAPE;
     const int nt = m > 8 ? 2 : 1;
     // The weights arrive by tensor copies whose innermost extent is a group of GROUP bytes; a row and a
     // chunk of columns must both be whole groups.  Q4_K: 96 bytes (even column counts), Q6_K: 48 bytes
     // (multiples of eight columns).
     const int group = q4 ? 96 : 48;
     const int col_step = q4 ? 2 : 8;
-    if (p.k_blocks % col_step != 0) return QMM_ERR_UNSUPPORTED;
+    // rows a whole number of groups apart (a dense matrix: the row itself; a padded one: its pitch)
+    if (pitch_bytes % group != 0 || pitch_bytes % 16 != 0) return QMM_ERR_UNSUPPORTED;
     // consumer warps = columns per chunk: a divisor of the super-blocks per row in 12..16 if there is one
-    // (no ragged last chunk), else 16
-    int cw = p.k_blocks < MMA_MAX_CW ? p.k_blocks : MMA_MAX_CW;
+    // (no ragged last chunk), else 16; a short row takes the next multiple of col_step (a chunk of columns
+    // is whole groups), the warps past the end of the row idle
+    int cw = p.k_blocks < MMA_MAX_CW ? (p.k_blocks + col_step - 1) / col_step * col_step : MMA_MAX_CW;
     for (int c = MMA_MAX_CW; c >= 12; c -= col_step)
         if (p.k_blocks >= c && p.k_blocks % c == 0) {
             cw = c;
@@ -680,8 +684,8 @@ static int qmatvec_mma_launch_rows(int type, const void* w, const void* xq, floa
     if (!enc) return cuda_fail(cudaErrorNotSupported);
     CUtensorMap wmap;
     {
-        const cuuint64_t dims[3] = {(cuuint64_t)(group / 4), (cuuint64_t)(p.row_bytes / group), (cuuint64_t)n};
-        const cuuint64_t strides[2] = {(cuuint64_t)group, (cuuint64_t)p.row_bytes};
+        const cuuint64_t dims[3] = {(cuuint64_t)(group / 4), (cuuint64_t)(pitch_bytes / group), (cuuint64_t)n};
+        const cuuint64_t strides[2] = {(cuuint64_t)group, (cuuint64_t)pitch_bytes};
         const cuuint32_t box[3] = {(cuuint32_t)(group / 4), (cuuint32_t)(p.pitch / group), 16};
         const cuuint32_t estr[3] = {1, 1, 1};
         if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,

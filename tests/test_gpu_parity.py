@@ -234,6 +234,33 @@ def test_tall_head_with_several_k_chunks_takes_the_tensor_core_kernel_in_row_blo
     assert_close(y.cpu().numpy()[:, rows], want, "row sample")
 
 
+@pytest.mark.parametrize("qtype,n,k,pitch_to", [(oracle.Q6_K, 300, 7168, 48), (oracle.Q6_K, 513, 1792, 48), (oracle.Q6_K, 200, 3584, 48),
+                                                (oracle.Q8_0, 129, 4224, 16), (oracle.Q4_K, 64, 2048, 256), (oracle.Q6_K, 64, 2048, 48)])
+def test_matvec_with_padded_rows(ops, qtype, n, k, pitch_to):
+    """launch_qmatvec_pitched: the rows of the matrix lie further apart than their packed length (the padding
+    filled with 0xFF).  Q6_K shards of a tensor-parallel down projection (K = 14336 / 2, / 4, / 8) are padded to a
+    multiple of 48 bytes so that the tensor-core kernel can fetch them; results as for back-to-back rows."""
+    from nates_recipe_rs_b200._lib import check, lib
+    rb = oracle.row_bytes(qtype, k)
+    pitch = (rb + pitch_to - 1) // pitch_to * pitch_to + (pitch_to if qtype == oracle.Q4_K else 0)
+    w = oracle.quantize(qtype, oracle.fill_normal(n * k, 31, 0.02).reshape(n, k))
+    padded = np.full((n, pitch), 0xFF, dtype=np.uint8)
+    padded[:, :rb] = w
+    wd, wp = dev(w), dev(padded)
+    for m in (1, 2, 5, 16, 32):
+        x = oracle.fill_normal(m * k, 32 + m, 1.0).reshape(m, k)
+        xq = oracle.quantize(oracle.Q8_1, x)
+        xqd = dev(xq)
+        y = torch.full((m, n), float("nan"), device="cuda")
+        check(lib().launch_qmatvec_pitched(qtype, wp.data_ptr(), pitch, xqd.data_ptr(), y.data_ptr(), m, n, k, torch.cuda.current_stream().cuda_stream),
+              "launch_qmatvec_pitched")
+        ops.check_launch()
+        assert not torch.isnan(y).any()
+        assert_close(y.cpu().numpy(), oracle.matvec(qtype, w, xq, k), f"m={m} against the oracle")
+        assert_close(y.cpu().numpy(), ops.gpu_qmatvec(qtype, wd, xqd, m, n, k).cpu().numpy(), f"m={m} against back-to-back rows")
+    assert lib().launch_qmatvec_pitched(qtype, wp.data_ptr(), rb - 2, xqd.data_ptr(), y.data_ptr(), 1, n, k, None) == -2
+
+
 @pytest.mark.parametrize("qtype", TYPES)
 @pytest.mark.parametrize("m", [2, 8, 16])
 def test_matvec_random_byte_weights(ops, qtype, m):
