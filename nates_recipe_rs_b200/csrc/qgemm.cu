@@ -37,6 +37,7 @@ struct GemmParams {
     int m, n, k;
     int row_bytes;
     int probe;            // tuning aid: 0 normal, 1 = unpack arithmetic skipped, 2 = tensor-core work skipped
+    int mb_per_cta;       // 128-row blocks of x per CTA (1..GEMM_MB_MAX): fewer when the column tiles alone do not fill the GPU
 };
 
 struct __align__(16) GemmSmemHeader {
@@ -112,8 +113,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * GEMM_BN;
-    const int m0 = blockIdx.y * (128 * GEMM_MB_MAX);
-    const int mb_count = min(GEMM_MB_MAX, (p.m - m0 + 127) / 128);
+    const int m0 = blockIdx.y * (128 * p.mb_per_cta);
+    const int mb_count = min(p.mb_per_cta, (p.m - m0 + 127) / 128);
     const int kt = p.k / GEMM_BK;
 
     if (threadIdx.x == 0) {
@@ -346,6 +347,12 @@ static EncodeTiledFn encode_tiled_fn() {
 
 static int g_gemm_probe = 0;
 void gemm_set_probe(int v) { g_gemm_probe = v; }
+static int g_gemm_mb = 0;  // tunable "gemm_mb": row blocks per CTA, 0 = automatic
+int gemm_set_mb(int v) {
+    if (v < 0 || v > GEMM_MB_MAX || v == 3) return QMM_ERR_UNSUPPORTED;
+    g_gemm_mb = v;
+    return QMM_OK;
+}
 
 int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, int n, int k, cudaStream_t stream) {
     if (!w || !x || (!y && !yf)) return QMM_ERR_NULL;
@@ -379,7 +386,20 @@ int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, in
         QMM_CUDA_TRY(cudaFuncSetAttribute(qgemm_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    const dim3 grid((n + GEMM_BN - 1) / GEMM_BN, (m + 128 * GEMM_MB_MAX - 1) / (128 * GEMM_MB_MAX));
+    // Row blocks of x per CTA.  Measured on B200 at K = 4096: a CTA takes about 36 us (its whole weight tile is
+    // unpacked whatever the rows) plus 18.5 us per row block (the tensor-core side), and the grid runs in waves
+    // of one CTA per SM; take the count with the smallest modelled time ("gemm_mb" overrides).
+    const int col_tiles = (n + GEMM_BN - 1) / GEMM_BN, row_blocks = (m + 127) / 128;
+    int mb = GEMM_MB_MAX;
+    double best = 0.0;
+    for (int cand = GEMM_MB_MAX; cand >= 1; cand /= 2) {
+        const long ctas = (long)col_tiles * ((row_blocks + cand - 1) / cand);
+        const double t = (double)((ctas + sm_count() - 1) / sm_count()) * (36.0 + 18.5 * cand);
+        if (cand == GEMM_MB_MAX || t < best) best = t, mb = cand;
+    }
+    if (g_gemm_mb >= 1 && g_gemm_mb <= GEMM_MB_MAX) mb = g_gemm_mb;
+    p.mb_per_cta = mb;
+    const dim3 grid(col_tiles, (row_blocks + mb - 1) / mb);
     qgemm_q4k_kernel<<<grid, GEMM_THREADS, smem, stream>>>(map, p);
     QMM_CUDA_TRY(cudaGetLastError());
     return QMM_OK;

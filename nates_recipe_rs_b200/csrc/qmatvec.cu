@@ -302,6 +302,7 @@ static int g_trace_stride = 0, g_trace_count = 0;
 // tuning aid: the next launches write 4 time stamps per CTA at trace + launch_index * stride
 void matvec_set_trace(unsigned long long* buf, int stride_words) { g_trace = buf; g_trace_stride = stride_words; g_trace_count = 0; }
 void gemm_set_probe(int v);
+int gemm_set_mb(int v);
 int mma_set_min_m(int v);
 int attn_set_tc_min_batch(int v);
 int mma_min_m();
@@ -320,6 +321,7 @@ int matvec_tune(const char* key, int value) {
     if (k == "rb_max" && (value == 1 || value == 2 || value == 4)) return g_rb_max = value, QMM_OK;
     if (k == "ctas_per_sm" && value >= 1 && value <= 2) return g_ctas_per_sm = value, QMM_OK;
     if (k == "mma_min_m") return mma_set_min_m(value);
+    if (k == "gemm_mb") return gemm_set_mb(value);
     if (k == "attn_tc_min_batch") return attn_set_tc_min_batch(value);
     return QMM_ERR_UNSUPPORTED;
 }
