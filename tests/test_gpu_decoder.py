@@ -147,7 +147,9 @@ def test_step_rejects_bad_arguments(dec):
 
 @pytest.mark.parametrize("batch,nqh,nkv,hd,length", [(1, 4, 2, 64, 1), (2, 8, 2, 128, 70), (3, 32, 8, 128, 300), (1, 8, 8, 32, 129),
                                                      (4, 8, 2, 128, 70), (5, 32, 8, 128, 300), (4, 8, 8, 64, 129), (6, 64, 8, 128, 1),
-                                                     (4, 16, 4, 96, 200)])
+                                                     (4, 16, 4, 96, 200),
+                                                     # more work items than persistent CTAs: several chunks per CTA through the ring of buffers
+                                                     (16, 32, 8, 128, 700), (8, 8, 1, 128, 4096), (4, 4, 2, 256, 100), (32, 8, 1, 128, 1300)])
 def test_attention_entry_matches_oracle(dec, batch, nqh, nkv, hd, length):
     """launch_attn_decode through the C ABI against the oracle's straight-loop attention.  From four
     sequences on the library computes scores and outputs on the f16 tensor cores with q and the
