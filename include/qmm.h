@@ -83,7 +83,7 @@ int qmm_set_overlap(int on);
  * job-list matvec "jobs_warps" (1..24), "jobs_ring_bytes", "jobs_stage_bytes", "jobs_rotate" (0/1); "decoder_fuse"
  * (0..3, decode engine at batch 1-2: default 0 = every operator its own launch, 1 = Q|K and V as one job list, 2 = also norms built inside the matvec
  * launches, 3 = also the gated activation).
- * "gemm_mb" (0 = automatic, 1, 2, 4: 128-row blocks of x per CTA of the prefill GEMM).
+ * "gemm_mb" (0 = automatic, 1, 2: 256-row blocks of x per CTA of the prefill GEMM).
  * Every setting computes the same results.  Not thread-safe against concurrent launches.
  * (A library built with -DQMM_TUNING also has instrumentation that is not part of this interface:
  * stream-only probe modes and a per-CTA time-stamp trace, declared in csrc/qmm_tuning.h.) */

@@ -306,6 +306,8 @@ int gemm_set_mb(int v);
 int mma_set_min_m(int v);
 int attn_set_tc_min_batch(int v);
 int mma_min_m();
+int mma_acc_set(const char* key, int v);
+int mma_group_rows();
 int qmatvec_mma_launch(int type, const void* w, long row_pitch, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                        unsigned long long* trace, const TpPush* push, cudaStream_t stream);
 int matvec_tune(const char* key, int value) {
@@ -321,6 +323,7 @@ int matvec_tune(const char* key, int value) {
     if (k == "rb_max" && (value == 1 || value == 2 || value == 4)) return g_rb_max = value, QMM_OK;
     if (k == "ctas_per_sm" && value >= 1 && value <= 2) return g_ctas_per_sm = value, QMM_OK;
     if (k == "mma_min_m") return mma_set_min_m(value);
+    if (k.rfind("mma_acc", 0) == 0) return mma_acc_set(key, value);
     if (k == "gemm_mb") return gemm_set_mb(value);
     if (k == "attn_tc_min_batch") return attn_set_tc_min_batch(value);
     return QMM_ERR_UNSUPPORTED;
@@ -445,7 +448,7 @@ int qmatvec_launch_pitched(int type, const void* w, long row_pitch, const void* 
     int m_done = 0;
     if (mma_min_m() > 0 && !g_probe) {
         while (m - m_done >= mma_min_m()) {
-            const int mg = m - m_done < 16 ? m - m_done : 16;
+            const int mg = m - m_done < mma_group_rows() ? m - m_done : mma_group_rows();
             TpPush sub = {};
             if (push) sub = *push, sub.word0 += (long)m_done * y_stride;
             const int st = qmatvec_mma_launch(type, w, row_pitch, static_cast<const uint8_t*>(xq) + (size_t)m_done * p.xq_row_bytes,

@@ -137,6 +137,8 @@ SHAPES = [
     # eight activation rows, one or several K chunks, ragged last row tile and last chunk), else dp4a
     (8, 300, 4096), (16, 1000, 4096), (13, 257, 14336), (21, 100, 8192), (16, 40, 28672), (7, 17, 256),
     (6, 50, 1024), (12, 50, 1024), (3, 4099, 2048), (10, 333, 4608),
+    # 17..32 rows in one pass of the tensor-core kernel (four tiles of eight), more rows in groups of 32
+    (17, 300, 4096), (32, 1000, 4096), (25, 257, 14336), (32, 2500, 2048), (40, 130, 4096), (70, 64, 1024),
 ]
 
 
@@ -172,6 +174,35 @@ def test_small_batch_tensor_core_kernel_matches_dp4a_kernel(ops, qtype, m, n, k)
     assert_close(y_mma.cpu().numpy(), y_dp4a.cpu().numpy())
 
 
+@pytest.mark.parametrize("qtype", [oracle.Q4_K, oracle.Q6_K])
+@pytest.mark.parametrize("m,n,k", [(5, 20000, 2048), (16, 20000, 1024), (29, 20000, 1024), (8, 3000, 14336), (32, 700, 8192)])
+def test_tensor_core_kernel_tiles_per_pass(ops, qtype, m, n, k):
+    """Every instantiation of the tensor-core kernel (2, 4 or 8 weight tiles per pass; 8 or 16 warps for up
+    to eight rows) against the oracle; the tall matrices have nine row tiles per CTA, more than any pass takes."""
+    from nates_recipe_rs_b200 import _lib
+    L = _lib.lib()
+    w = seeded_weights(qtype, n, k, 31 + n)
+    xq = oracle.quantize(oracle.Q8_1, oracle.fill_normal(m * k, 32 + k, 1.0).reshape(m, k))
+    want = oracle.matvec(qtype, w, xq, k)
+    wd, xd = dev(w), dev(xq)
+    try:
+        for warps in (8, 16):
+            _lib.check(L.qmm_tune(b"mma_acc_w1", warps), "tune")
+            for tp in (2, 4, 8):
+                for key in (b"mma_acc_tp1", b"mma_acc_tp2"):
+                    _lib.check(L.qmm_tune(key, tp), "tune")
+                _lib.check(L.qmm_tune(b"mma_acc_tp4", min(tp, 4)), "tune")
+                y = torch.full((m, n), float("nan"), device="cuda")
+                ops.gpu_qmatvec_into(qtype, wd, xd, y, m, n, k)
+                ops.check_launch()
+                assert_close(y.cpu().numpy(), want, f"warps {warps} tiles/pass {tp}")
+    finally:
+        _lib.check(L.qmm_tune(b"mma_acc_w1", 16), "tune")
+        _lib.check(L.qmm_tune(b"mma_acc_tp1", 8), "tune")
+        _lib.check(L.qmm_tune(b"mma_acc_tp2", 8), "tune")
+        _lib.check(L.qmm_tune(b"mma_acc_tp4", 4), "tune")
+
+
 # per-rank projection shapes of the 8B- and 70B-class stacks under tensor parallelism 4 and 8
 TP_SHARD_SHAPES = [
     (oracle.Q4_K, 1280, 4096), (oracle.Q6_K, 256, 4096), (oracle.Q4_K, 4096, 1024), (oracle.Q4_K, 7168, 4096), (oracle.Q6_K, 4096, 3584),
@@ -204,10 +235,9 @@ def test_tensor_parallel_shard_shapes_both_kernels(ops, qtype, n, k):
         _lib.check(L.qmm_tune(b"mma_min_m", 3), "tune")
 
 
-def test_tall_head_with_several_k_chunks_takes_the_tensor_core_kernel_in_row_blocks(ops):
-    """The 70B-class output head (128256 x 8192, Q6_K) at 16 activation rows: two K chunks and 55 row tiles per CTA,
-    more running sums than fit in shared memory at once, so the launcher cuts the matrix into row blocks.  Against
-    the dp4a kernel on every output and against the oracle on a row sample (also across a block boundary)."""
+def test_tall_head_with_several_k_chunks_takes_the_tensor_core_kernel(ops):
+    """The 70B-class output head (128256 x 8192, Q6_K) at 16 activation rows: several K chunks and 55 row tiles per CTA,
+    i.e. seven passes of eight tiles.  Against the dp4a kernel on every output and against the oracle on a row sample."""
     from nates_recipe_rs_b200 import _lib
     L = _lib.lib()
     qtype, n, k, m = oracle.Q6_K, 128256, 8192, 16
