@@ -252,7 +252,6 @@ __global__ void __launch_bounds__(MAXW * 32, 1) qmv_mma_kernel(const __grid_cons
         r_advance();
     }
 
-
     const int q = lane >> 2, pq = lane & 3;
     const int cthreads = p.cw * 32;
     pdl_wait_prior_grids();  // activations come from the preceding kernel, y may still be read by it
