@@ -78,12 +78,15 @@ int qmm_set_overlap(int on);
  * 1, 2, 4: 32-byte groups of a Q4_K super-block per lane), "rb_max" (1, 2, 4: rows reduced together per warp),
  * "ctas_per_sm" (1, 2: persistent CTAs per SM of the single-matrix dp4a matvec; 2 needs "ring_bytes" and
  * "consumer_warps" small enough to fit twice), "mma_min_m" (0..16: fewest activation rows that take the
- * tensor-core matvec where type and shape allow it; 0 = never; default 3), "attn_tc_min_batch" (fewest
+ * tensor-core matvec where type and shape allow it; 0 = never; default 3), "mma_acc_tp1" / "mma_acc_tp2" /
+ * "mma_acc_tp4" (2, 4, 8: weight tiles per pass of the tensor-core matvec at up to 8 / 16 / 32 activation rows) and
+ * "mma_acc_w1" (8, 16: its warps at up to 8 rows), "attn_tc_min_batch" (fewest
  * sequences from which the decode attention runs on the f16 tensor cores; 0 = never; default 4), and for the
  * job-list matvec "jobs_warps" (1..24), "jobs_ring_bytes", "jobs_stage_bytes", "jobs_rotate" (0/1); "decoder_fuse"
  * (0..3, decode engine at batch 1-2: default 0 = every operator its own launch, 1 = Q|K and V as one job list, 2 = also norms built inside the matvec
  * launches, 3 = also the gated activation).
- * "gemm_mb" (0 = automatic, 1, 2: 256-row blocks of x per CTA of the prefill GEMM).
+ * "gemm_mb" (0 = automatic, 1, 2: 256-row blocks of x per CTA of the prefill GEMM), "gemm_ksplit" (0 = automatic,
+ * 1, 2: CTAs of a cluster that share one output tile of the prefill GEMM, each with a part of K).
  * Every setting computes the same results.  Not thread-safe against concurrent launches.
  * (A library built with -DQMM_TUNING also has instrumentation that is not part of this interface:
  * stream-only probe modes and a per-CTA time-stamp trace, declared in csrc/qmm_tuning.h.) */

@@ -57,6 +57,7 @@ struct GemmParams {
     int row_bytes;
     int probe;            // tuning aid: 0 normal, 1 = unpack arithmetic skipped, 2 = tensor-core work skipped
     int nb_per_cta;       // 256-row blocks of x per CTA (1..GEMM_NB_MAX)
+    int ksplit;           // CTAs of a cluster that share one output tile, each with a contiguous part of K (1 or 2)
 };
 
 struct __align__(16) GemmSmemHeader {
@@ -83,6 +84,11 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// barrier over all threads of all CTAs of the cluster, with release/acquire ordering of (distributed) shared memory
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -140,7 +146,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
     const int m0 = blockIdx.y * (GEMM_BX * p.nb_per_cta);
     const int nb = min(p.nb_per_cta, (p.m - m0 + GEMM_BX - 1) / GEMM_BX);
     const int xs_slots = GEMM_XT / p.nb_per_cta;  // k-steps of x in the ring
-    const int kt = p.k / GEMM_BK;
+    // K range of this CTA: whole super-blocks; blockIdx.z is the rank in the cluster of p.ksplit CTAs
+    const int split = (int)blockIdx.z;
+    const int sb0 = split * (p.k / QKK) / p.ksplit, n_sb = (split + 1) * (p.k / QKK) / p.ksplit - sb0;
+    const int kt = n_sb * (QKK / GEMM_BK), ks0 = sb0 * (QKK / GEMM_BK);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GEMM_SW; ++s) mbar_init(smem_u32(&hdr->w_full[s]), GEMM_DEQ_WARPS);
@@ -170,7 +179,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
     };
     // k-step ks has retired on the tensor cores (its commit has arrived)
     auto wait_done = [&](int ks) { return mbar_wait_bounded(smem_u32(&hdr->done[ks % GEMM_ND]), (ks / GEMM_ND) & 1, cta_abort); };
-    const int n_sb = p.k / QKK;
+    bool role_ok = true;  // unpack warps: the main loop ran to its end
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (x tiles)
@@ -185,7 +194,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
                 const uint32_t bar = smem_u32(&hdr->x_full[slot]);
                 mbar_arrive_expect_tx(bar, (uint32_t)nb * GEMM_X_BYTES);
                 for (int b = 0; b < nb; ++b)  // rows past m are filled with zeros
-                    tma_load_2d(smem_u32(x_ring + (slot * p.nb_per_cta + b) * GEMM_X_BYTES), &xmap, ks * GEMM_BK, m0 + b * GEMM_BX, bar);
+                    tma_load_2d(smem_u32(x_ring + (slot * p.nb_per_cta + b) * GEMM_X_BYTES), &xmap, (ks0 + ks) * GEMM_BK, m0 + b * GEMM_BX, bar);
             }
             if (*cta_abort) {
                 // copies that were issued but perhaps not consumed: wait (bounded) for them to land
@@ -234,7 +243,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
                 }
                 const uint32_t bar = smem_u32(&hdr->p_full[slot]);
                 mbar_arrive_expect_tx(bar, GEMM_P_BYTES);
-                tma_load_2d(smem_u32(p_ring + slot * GEMM_P_BYTES), &wmap, sb * Q4_K_BYTES, n0, bar);  // rows past n: zeros
+                tma_load_2d(smem_u32(p_ring + slot * GEMM_P_BYTES), &wmap, (sb0 + sb) * Q4_K_BYTES, n0, bar);  // rows past n: zeros
             }
             if (*cta_abort) {
                 for (int i = max(0, issued - GEMM_SP); i < issued; ++i) {
@@ -310,13 +319,48 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
                 }
             }
         }
-        // ---- epilogue: TMEM -> registers -> bf16 -> global.  Lane = weight row, column = row of x.
-        if (ok && mbar_wait_bounded(smem_u32(&hdr->acc_full), 0, cta_abort) && !*cta_abort) {
-            tc_fence_after();
-            const int q = warp & 3;                 // TMEM lane quarter this warp may read
-            const int cq = (warp - 2) >> 2;         // the four warps of a quarter split the columns
-            const int cols_w = nb * GEMM_BX / 4;    // columns per warp: 64 or 128
-            const int gcol = n0 + 32 * q + lane;    // this lane's output column of y
+        role_ok = ok;
+    }
+
+    // ---- epilogue (the unpack warps): TMEM -> registers -> bf16 -> global.  Lane = weight row, column = row of x.
+    const bool is_unpack = warp >= 2 && warp < 2 + GEMM_DEQ_WARPS;
+    bool acc_ok = false;
+    if (is_unpack) {
+        acc_ok = role_ok && mbar_wait_bounded(smem_u32(&hdr->acc_full), 0, cta_abort) && !*cta_abort;
+        if (!acc_ok && role_ok && lane == 0) give_up(DEV_TIMEOUT_MMA);
+        tc_fence_after();
+    }
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int cq = (warp - 2) >> 2;         // the four warps of a quarter split the columns
+    const int cols_w = nb * GEMM_BX / 4;    // columns per warp: 64 or 128
+    const int wrow_l = 32 * q + lane;       // this lane's weight row within the tile
+    if (p.ksplit > 1) {
+        // Split K: the CTAs of the cluster hold partial sums of the same tile.  Once every CTA's tensor-core work
+        // has retired (first cluster barrier: the rings are idle everywhere) rank 1 stores its accumulators into
+        // rank 0's x ring (128 KB = 128 x 256 floats) through distributed shared memory; after the second barrier
+        // rank 0 adds them to its own (fixed order: reruns are bit identical) and writes the tile.  Every thread of
+        // the cluster reaches both barriers on every path (a failed wait only skips work).
+        cluster_sync_all();
+        if (is_unpack && split != 0 && acc_ok) {
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(x_ring)), "r"(0));
+            for (int c = cq * cols_w; c < (cq + 1) * cols_w; c += 32) {
+                if (m0 + c >= p.m) break;
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c, r);
+                const uint32_t rowb = remote + (uint32_t)(((c >> 5) * GEMM_BW + wrow_l) * 128);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)  // 16-byte pieces, rotated by the row so that eight lanes hit eight bank groups
+                    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowb + (uint32_t)((j ^ (wrow_l & 7)) << 4)), "r"(r[4 * j]),
+                                 "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
+                                 : "memory");
+            }
+        }
+        cluster_sync_all();
+    }
+    if (is_unpack && split == 0) {
+        if (acc_ok) {
+            const int gcol = n0 + wrow_l;    // this lane's output column of y
             // bf16 output with rows of y a multiple of 16 bytes: the warp turns its 32 x 32 block through a
             // private 2 KB of the (now idle) weight ring, so a lane stores 16 bytes = 8 outputs of one row
             const bool wide = p.y && !p.yf && p.n % 8 == 0 && reinterpret_cast<uintptr_t>(p.y) % 16 == 0;
@@ -325,6 +369,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
                 if (m0 + c >= p.m) break;  // rows of x past m (the blocks of a CTA are consecutive, so are their columns)
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c, r);
+                if (p.ksplit > 1) {
+                    const uint8_t* rowp = x_ring + ((c >> 5) * GEMM_BW + wrow_l) * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 v = *reinterpret_cast<const float4*>(rowp + ((j ^ (wrow_l & 7)) << 4));
+                        r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v.x);
+                        r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
+                        r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
+                        r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
+                    }
+                }
                 if (wide) {
                     __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stg);
 #pragma unroll
@@ -352,8 +407,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
                     }
                 }
             }
-        } else if (ok && lane == 0) {
-            give_up(DEV_TIMEOUT_MMA);
         }
     }
     tc_fence_before();
@@ -383,6 +436,12 @@ static EncodeTiledFn encode_tiled_fn() {
 
 static int g_gemm_probe = 0;
 void gemm_set_probe(int v) { g_gemm_probe = v; }
+static int g_gemm_ksplit = 0;  // tunable "gemm_ksplit": 0 = automatic, 1, 2
+int gemm_set_ksplit(int v) {
+    if (v < 0 || v > 2) return QMM_ERR_UNSUPPORTED;
+    g_gemm_ksplit = v;
+    return QMM_OK;
+}
 static int g_gemm_mb = 0;  // tunable "gemm_mb": 256-row blocks of x per CTA, 0 = automatic
 int gemm_set_mb(int v) {
     if (v < 0 || v > GEMM_NB_MAX) return QMM_ERR_UNSUPPORTED;
@@ -447,9 +506,31 @@ int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, in
     }
     if (g_gemm_mb >= 1 && g_gemm_mb <= GEMM_NB_MAX) nbc = g_gemm_mb;
     p.nb_per_cta = nbc;
-    const dim3 grid(col_tiles, (x_blocks + nbc - 1) / nbc);
-    qgemm_q4k_kernel<<<grid, GEMM_THREADS, smem, stream>>>(map, wmap, p);
-    QMM_CUDA_TRY(cudaGetLastError());
+    // Few tiles (a narrow matrix at a few hundred rows): two CTAs per tile, each with half of K, joined through
+    // distributed shared memory.  Only with one block of x per CTA (the partial tile must fit the x ring).
+    const long ctas = (long)col_tiles * ((x_blocks + nbc - 1) / nbc);
+    int ksplit = (nbc == 1 && 2 * ctas <= sm_count() && k >= 8 * QKK) ? 2 : 1;
+    if (g_gemm_ksplit == 1 || (g_gemm_ksplit == 2 && nbc == 1 && k >= 2 * QKK)) ksplit = g_gemm_ksplit;
+    p.ksplit = ksplit;
+    const dim3 grid(col_tiles, (x_blocks + nbc - 1) / nbc, ksplit);
+    if (ksplit == 1) {
+        qgemm_q4k_kernel<<<grid, GEMM_THREADS, smem, stream>>>(map, wmap, p);
+        QMM_CUDA_TRY(cudaGetLastError());
+        return QMM_OK;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned)ksplit;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, qgemm_q4k_kernel, map, wmap, p));
     return QMM_OK;
 }
 

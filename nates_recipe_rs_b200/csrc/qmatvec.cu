@@ -303,6 +303,7 @@ static int g_trace_stride = 0, g_trace_count = 0;
 void matvec_set_trace(unsigned long long* buf, int stride_words) { g_trace = buf; g_trace_stride = stride_words; g_trace_count = 0; }
 void gemm_set_probe(int v);
 int gemm_set_mb(int v);
+int gemm_set_ksplit(int v);
 int mma_set_min_m(int v);
 int attn_set_tc_min_batch(int v);
 int mma_min_m();
@@ -325,6 +326,7 @@ int matvec_tune(const char* key, int value) {
     if (k == "mma_min_m") return mma_set_min_m(value);
     if (k.rfind("mma_acc", 0) == 0) return mma_acc_set(key, value);
     if (k == "gemm_mb") return gemm_set_mb(value);
+    if (k == "gemm_ksplit") return gemm_set_ksplit(value);
     if (k == "attn_tc_min_batch") return attn_set_tc_min_batch(value);
     return QMM_ERR_UNSUPPORTED;
 }

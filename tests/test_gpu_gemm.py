@@ -53,6 +53,34 @@ def test_gemm_matches_oracle(ops, m, n, k):
     assert (np.abs(oracle.bf16_bits_to_f32(got) - oracle.bf16_bits_to_f32(y_ref)) <= step).all()
 
 
+@pytest.mark.parametrize("m,n,k", [(100, 300, 1024), (256, 128, 2048), (77, 200, 512), (129, 384, 4096), (300, 256, 1024)])
+@pytest.mark.parametrize("ksplit", [1, 2])
+def test_gemm_split_k_over_a_cluster(ops, m, n, k, ksplit):
+    """K split over the two CTAs of a cluster (partial tiles joined through distributed shared memory) and not
+    split, forced by the tunable: both against the oracle, reruns bit identical, f32 and bf16 outputs."""
+    from nates_recipe_rs_b200 import _lib
+    L = _lib.lib()
+    w, x = make_case(m, n, k, 500 + m + n)
+    y_ref, yf_ref = oracle.gemm_bf16(oracle.Q4_K, w, x, k)
+    wd, xd = torch.from_numpy(w).cuda(), bf16_tensor(x)
+    try:
+        _lib.check(L.qmm_tune(b"gemm_mb", 1), "tune")
+        _lib.check(L.qmm_tune(b"gemm_ksplit", ksplit), "tune")
+        yf = ops.gpu_qgemm_q4_k_bf16(wd, xd, n, k, torch.float32)
+        yf2 = ops.gpu_qgemm_q4_k_bf16(wd, xd, n, k, torch.float32)
+        y = ops.gpu_qgemm_q4_k_bf16(wd, xd, n, k)
+        ops.check_launch()
+    finally:
+        _lib.check(L.qmm_tune(b"gemm_mb", 0), "tune")
+        _lib.check(L.qmm_tune(b"gemm_ksplit", 0), "tune")
+    assert torch.equal(yf, yf2)
+    got_f = yf.cpu().numpy()
+    err = np.abs(got_f.astype(np.float64) - yf_ref.astype(np.float64))
+    assert (err <= ABS_TOL + REL_TOL * np.abs(yf_ref)).all(), f"max err {err.max():.3e}"
+    got = y.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, oracle.f32_to_bf16_bits(got_f))
+
+
 def test_gemm_weights_are_the_bf16_dequant(ops):
     """With x = identity rows the GEMM returns the bf16 weights themselves: bit-exact vs the oracle."""
     n, k = 128, 256
