@@ -274,6 +274,26 @@ long qmm_argmax_scratch_bytes(int batch);
 int launch_argmax_rows(const float* logits, void* scratch, int* out_index, float* out_value, int batch, int vocab, void* stream);
 int launch_scale_f32(float* x, float scalar, long n, void* stream);
 
+/* ---- quantized dense layer: y(m,n) = act( x(m,k) . w(n,k)^T + bias(n) ), x and y f32, w packed blocks of
+ * `type`.  The counterpart of LayerKind::Dense in the upstream's forward pass (recipe-infer/src/forward.rs:
+ * 372-431: gpu_linear_into, gpu-core/src/kernels.rs:2589-2640, then one activation launch), the place where a
+ * quantized weight plugs into its LayerParams (recipe-infer/src/params.rs:35-59: w, b, in_dim = k,
+ * out_dim = n, act, palpha).  Three launches: x -> Q8_1 into xq_scratch (m * k/32 * 36 bytes, 4-byte
+ * aligned), the matvec, bias + activation in place.  bias may be NULL.  alpha: the negative slope of
+ * LEAKY_RELU (upstream: 0.01) and PRELU (the learned scalar), ELU's alpha (upstream: 1.0); ignored otherwise. */
+#define QMM_DENSE_LINEAR 0
+#define QMM_DENSE_RELU 1
+#define QMM_DENSE_SIGMOID 2
+#define QMM_DENSE_LEAKY_RELU 3
+#define QMM_DENSE_PRELU 4
+#define QMM_DENSE_ELU 5
+#define QMM_DENSE_SELU 6
+#define QMM_DENSE_TANH 7
+#define QMM_DENSE_SILU 8
+#define QMM_DENSE_GELU 9
+int launch_qdense(int type, const void* w, const float* x, const float* bias, float* y, void* xq_scratch, int m, int n, int k, int act,
+                  float alpha, void* stream);
+
 /* ---- mixture-of-experts branch of a decode step, on the device.  The upstream example routes on the host:
  * it downloads the activations, computes router logits, softmax and top-k per token in f64 loops, gathers the
  * tokens of every chosen expert, uploads them and runs the experts one after the other

@@ -6,6 +6,8 @@
 //   launch_embed_rows         host-side embedding gather of the upstream example, examples/gemma4.rs:951-958
 //   launch_argmax_rows        host-side pick of the next token, examples/gemma4.rs:1021-1046 (greedy here)
 //   launch_scale_f32          launch_scale_f64       gpu-core/src/kernels/gemm_f64.hip:57-65, infer_ops.rs:242-248
+//   launch_qdense             LayerKind::Dense of the upstream's forward pass: gpu_linear_into + one activation launch,
+//                             recipe-infer/src/forward.rs:372-431, with the weight in packed blocks
 #include "qmm_formats.cuh"
 
 namespace qmm {
@@ -16,6 +18,33 @@ __global__ void scale_f32_kernel(float* __restrict__ x, float scalar, long n) {
 }
 
 constexpr int ARGMAX_ENTRY_PARTS = 256;
+
+// y = act(y + bias) in place, the epilogue of a quantized dense layer.  The activations are the upstream's
+// (recipe-infer/src/forward.rs:388-431; elementwise.hip, gapact.hip): leaky ReLU / PReLU with slope alpha,
+// ELU with alpha, SELU with its two constants, tanh-form GELU.
+__device__ __forceinline__ float dense_act(float z, int act, float alpha) {
+    switch (act) {
+    case QMM_DENSE_RELU: return fmaxf(z, 0.f);
+    case QMM_DENSE_SIGMOID: return 1.f / (1.f + expf(-z));
+    case QMM_DENSE_LEAKY_RELU:
+    case QMM_DENSE_PRELU: return z > 0.f ? z : alpha * z;
+    case QMM_DENSE_ELU: return z > 0.f ? z : alpha * (expf(z) - 1.f);
+    case QMM_DENSE_SELU: return 1.0507009873554804934f * (z > 0.f ? z : 1.6732632423543772848f * (expf(z) - 1.f));
+    case QMM_DENSE_TANH: return tanhf(z);
+    case QMM_DENSE_SILU: return z / (1.f + expf(-z));
+    case QMM_DENSE_GELU: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    }
+    return z;
+}
+__global__ void dense_bias_act_kernel(float* __restrict__ y, const float* __restrict__ bias, long total, int n, int act, float alpha) {
+    pdl_wait_prior_grids();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) {
+        float z = y[i];
+        if (bias) z += bias[i % n];
+        y[i] = dense_act(z, act, alpha);
+    }
+}
 
 }  // namespace qmm
 
@@ -86,6 +115,21 @@ int launch_argmax_rows(const float* logits, void* scratch, int* out_index, float
     argmax_partial_kernel<<<dim3(ARGMAX_ENTRY_PARTS, batch), 256, 0, s>>>(logits, cand, vocab);
     argmax_final_kernel<<<batch, 256, 0, s>>>(cand, ARGMAX_ENTRY_PARTS, out_index, 0, out_value);
     QMM_CUDA_TRY(cudaGetLastError());
+    return QMM_OK;
+}
+
+int launch_qdense(int type, const void* w, const float* x, const float* bias, float* y, void* xq_scratch, int m, int n, int k, int act,
+                  float alpha, void* stream) {
+    if (!w || !x || !y || !xq_scratch) return QMM_ERR_NULL;
+    if (act < QMM_DENSE_LINEAR || act > QMM_DENSE_GELU) return QMM_ERR_UNSUPPORTED;
+    cudaStream_t s = as_stream(stream);
+    if (int st = launch_quantize_q8_1(x, xq_scratch, m, k, stream)) return st;
+    if (int st = launch_qmatvec(type, w, xq_scratch, y, m, n, k, stream)) return st;
+    if (bias || act != QMM_DENSE_LINEAR) {
+        const long total = (long)m * n;
+        dense_bias_act_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(y, bias, total, n, act, alpha);
+        QMM_CUDA_TRY(cudaGetLastError());
+    }
     return QMM_OK;
 }
 

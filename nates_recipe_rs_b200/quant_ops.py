@@ -24,7 +24,7 @@ __all__ = [
     "gpu_quantize_q8_1_into", "gpu_quantize_q8_1", "gpu_quantize_weights_into", "gpu_quantize_weights",
     "gpu_dequantize_into", "gpu_dequantize", "gpu_qmatvec_into", "gpu_qmatvec", "gpu_qblock_dots",
     "MatvecJobs", "gpu_qmatvec_batch_into", "gpu_norm_qmatvec_batch_into", "gpu_glu_qmatvec_batch_into", "TpComm", "gpu_qmatvec_tp_into", "gpu_qmatvec_batch_tp_into",
-    "gpu_qgemm_q4_k_bf16_into", "gpu_qgemm_q4_k_bf16",
+    "gpu_qgemm_q4_k_bf16_into", "gpu_qgemm_q4_k_bf16", "gpu_qdense_into", "DENSE_ACTS",
     "gpu_qlinear",
     "gpu_rmsnorm_q8_1_into", "gpu_rope_kv_append", "gpu_glu_act_q8_1_into", "gpu_embed_rows_into", "gpu_argmax_rows",
     "gpu_scale_f32_inplace", "gpu_moe_router_topk", "gpu_moe_experts_into",
@@ -309,6 +309,25 @@ def gpu_argmax_rows(logits):
 def gpu_scale_f32_inplace(x, scalar):
     """x *= scalar: the upstream's gpu_scale_f64_inplace (gpu-core/src/infer_ops.rs:242-248)."""
     check(lib().launch_scale_f32(_ptr(x), scalar, x.numel(), _stream()), "launch_scale_f32")
+
+
+# ---- quantized dense layer ---------------------------------------------------------------
+DENSE_ACTS = {"linear": 0, "relu": 1, "sigmoid": 2, "leaky_relu": 3, "prelu": 4, "elu": 5, "selu": 6, "tanh": 7, "silu": 8, "gelu": 9}
+
+
+def gpu_qdense_into(qtype, w, x, bias, out, m, n, k, act="linear", alpha=0.0, xq_scratch=None):
+    """out(m,n) = act(x(m,k) . w(n,k)^T + bias): LayerKind::Dense of the upstream's forward pass
+    (recipe-infer/src/forward.rs:372-431) with the weight in packed `qtype` blocks.  x, out f32."""
+    _need(w, n * row_bytes(qtype, k), "w")
+    _need(x, m * k * 4, "x")
+    _need(out, m * n * 4, "out")
+    if bias is not None:
+        _need(bias, n * 4, "bias")
+    if xq_scratch is None:
+        xq_scratch = torch.empty(m * row_bytes(Q8_1, k), dtype=torch.uint8, device=x.device)
+    _need(xq_scratch, m * row_bytes(Q8_1, k), "xq_scratch")
+    check(lib().launch_qdense(qtype, _ptr(w), _ptr(x), _ptr(bias) if bias is not None else None, _ptr(out), _ptr(xq_scratch), m, n, k,
+                              DENSE_ACTS[act] if isinstance(act, str) else int(act), float(alpha), _stream()), "launch_qdense")
 
 
 # ---- mixture of experts ---------------------------------------------------------------------

@@ -187,6 +187,41 @@ def silu_mul(gate, up):
     return out
 
 
+DENSE_ACTS = ("linear", "relu", "sigmoid", "leaky_relu", "prelu", "elu", "selu", "tanh", "silu", "gelu")
+
+
+def dense(qtype, w, x, bias, act, alpha, k):
+    """Quantized dense layer y = act(x . w^T + bias): the composition the upstream runs for LayerKind::Dense
+    (recipe-infer/src/forward.rs:372-431) with the product taken through the Q8_1 form of x and the packed
+    weight (quantize + matvec above).  The activations follow the upstream's kernels (elementwise.hip:1521-1560,
+    gapact.hip:6-18), evaluated in float64 and rounded to float32."""
+    x = _c(x, np.float32)
+    y = matvec(qtype, w, quantize(Q8_1, x), k)
+    z = y if bias is None else (y + _c(bias, np.float32)[None, :]).astype(np.float32)
+    z = z.astype(np.float64)
+    if act == "linear":
+        r = z
+    elif act == "relu":
+        r = np.maximum(z, 0.0)
+    elif act == "sigmoid":
+        r = 1.0 / (1.0 + np.exp(-z))
+    elif act in ("leaky_relu", "prelu"):
+        r = np.where(z > 0, z, alpha * z)
+    elif act == "elu":
+        r = np.where(z > 0, z, alpha * (np.exp(z) - 1.0))
+    elif act == "selu":
+        r = 1.0507009873554804934193349852946 * np.where(z > 0, z, 1.6732632423543772848170429916717 * (np.exp(z) - 1.0))
+    elif act == "tanh":
+        r = np.tanh(z)
+    elif act == "silu":
+        r = z / (1.0 + np.exp(-z))
+    elif act == "gelu":
+        r = 0.5 * z * (1.0 + np.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+    else:
+        raise ValueError(act)
+    return r.astype(np.float32)
+
+
 def attn_decode(q, kc, vc, nqh, nkv, hd, length):
     """q (nqh, hd) f32; kc/vc (cap, nkv, hd) fp16 bit patterns (uint16 or float16)."""
     q = _c(q, np.float32)
