@@ -278,9 +278,12 @@ int launch_scale_f32(float* x, float scalar, long n, void* stream);
  * `type`.  The counterpart of LayerKind::Dense in the upstream's forward pass (recipe-infer/src/forward.rs:
  * 372-431: gpu_linear_into, gpu-core/src/kernels.rs:2589-2640, then one activation launch), the place where a
  * quantized weight plugs into its LayerParams (recipe-infer/src/params.rs:35-59: w, b, in_dim = k,
- * out_dim = n, act, palpha).  Three launches: x -> Q8_1 into xq_scratch (m * k/32 * 36 bytes, 4-byte
- * aligned), the matvec, bias + activation in place.  bias may be NULL.  alpha: the negative slope of
- * LEAKY_RELU (upstream: 0.01) and PRELU (the learned scalar), ELU's alpha (upstream: 1.0); ignored otherwise. */
+ * out_dim = n, act, palpha).  Three launches: x -> Q8_1 into xq_scratch, the matvec, bias + activation in
+ * place.  From 64 rows on a Q4_K layer takes the tensor-core GEMM instead: x rounded to bf16 into xq_scratch
+ * (16-byte aligned), launch_qgemm_q4_k_bf16_f32acc, bias + activation; the product then differs from the
+ * small-batch one by the rounding of x (bf16 instead of Q8_1 blocks).  xq_scratch: qmm_qdense_scratch_bytes
+ * bytes of caller-owned device memory.  bias may be NULL.  alpha: the negative slope of LEAKY_RELU (upstream:
+ * 0.01) and PRELU (the learned scalar), ELU's alpha (upstream: 1.0); ignored otherwise. */
 #define QMM_DENSE_LINEAR 0
 #define QMM_DENSE_RELU 1
 #define QMM_DENSE_SIGMOID 2
@@ -291,6 +294,7 @@ int launch_scale_f32(float* x, float scalar, long n, void* stream);
 #define QMM_DENSE_TANH 7
 #define QMM_DENSE_SILU 8
 #define QMM_DENSE_GELU 9
+long qmm_qdense_scratch_bytes(int type, int m, int k);
 int launch_qdense(int type, const void* w, const float* x, const float* bias, float* y, void* xq_scratch, int m, int n, int k, int act,
                   float alpha, void* stream);
 

@@ -36,6 +36,11 @@ __device__ __forceinline__ float dense_act(float z, int act, float alpha) {
     }
     return z;
 }
+__global__ void f32_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, long n) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2bfloat16_rn(x[i]);
+}
+constexpr int QDENSE_GEMM_MIN_M = 64;  // rows from which a Q4_K dense layer takes the tensor-core GEMM
 __global__ void dense_bias_act_kernel(float* __restrict__ y, const float* __restrict__ bias, long total, int n, int act, float alpha) {
     pdl_wait_prior_grids();
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -118,13 +123,28 @@ int launch_argmax_rows(const float* logits, void* scratch, int* out_index, float
     return QMM_OK;
 }
 
+long qmm_qdense_scratch_bytes(int type, int m, int k) {
+    if (m <= 0 || k <= 0) return 0;
+    const long q8 = (long)m * (k / 32) * Q8_1_BYTES, bf = (long)m * k * 2;
+    return (type == QMM_TYPE_Q4_K && m >= QDENSE_GEMM_MIN_M && k % 256 == 0) ? (bf > q8 ? bf : q8) : q8;
+}
+
 int launch_qdense(int type, const void* w, const float* x, const float* bias, float* y, void* xq_scratch, int m, int n, int k, int act,
                   float alpha, void* stream) {
     if (!w || !x || !y || !xq_scratch) return QMM_ERR_NULL;
     if (act < QMM_DENSE_LINEAR || act > QMM_DENSE_GELU) return QMM_ERR_UNSUPPORTED;
+    if (m <= 0 || n <= 0 || k <= 0) return QMM_ERR_SHAPE;
     cudaStream_t s = as_stream(stream);
-    if (int st = launch_quantize_q8_1(x, xq_scratch, m, k, stream)) return st;
-    if (int st = launch_qmatvec(type, w, xq_scratch, y, m, n, k, stream)) return st;
+    if (type == QMM_TYPE_Q4_K && m >= QDENSE_GEMM_MIN_M && k % 256 == 0 && reinterpret_cast<uintptr_t>(xq_scratch) % 16 == 0) {
+        // many rows: x rounded to bf16, the prefill GEMM with its f32 accumulators as the output
+        const long total = (long)m * k;
+        f32_to_bf16_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(x, static_cast<__nv_bfloat16*>(xq_scratch), total);
+        QMM_CUDA_TRY(cudaGetLastError());
+        if (int st = launch_qgemm_q4_k_bf16_f32acc(w, xq_scratch, y, m, n, k, stream)) return st;
+    } else {
+        if (int st = launch_quantize_q8_1(x, xq_scratch, m, k, stream)) return st;
+        if (int st = launch_qmatvec(type, w, xq_scratch, y, m, n, k, stream)) return st;
+    }
     if (bias || act != QMM_DENSE_LINEAR) {
         const long total = (long)m * n;
         dense_bias_act_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(y, bias, total, n, act, alpha);

@@ -65,7 +65,8 @@ class Scratch:
     def __init__(self, layers, n, device="cuda"):
         self.n = n
         self.acts = [torch.empty(n, l.out_dim, dtype=torch.float32, device=device) for l in layers]
-        self.xq = torch.empty(n * max(ops.row_bytes(Q8_1, l.in_dim) for l in layers), dtype=torch.uint8, device=device)
+        from ._lib import lib
+        self.xq = torch.empty(max(lib().qmm_qdense_scratch_bytes(l.qtype, n, l.in_dim) for l in layers), dtype=torch.uint8, device=device)
 
 
 def forward_into(layers, x, scratch):

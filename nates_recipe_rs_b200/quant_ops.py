@@ -317,15 +317,17 @@ DENSE_ACTS = {"linear": 0, "relu": 1, "sigmoid": 2, "leaky_relu": 3, "prelu": 4,
 
 def gpu_qdense_into(qtype, w, x, bias, out, m, n, k, act="linear", alpha=0.0, xq_scratch=None):
     """out(m,n) = act(x(m,k) . w(n,k)^T + bias): LayerKind::Dense of the upstream's forward pass
-    (recipe-infer/src/forward.rs:372-431) with the weight in packed `qtype` blocks.  x, out f32."""
+    (recipe-infer/src/forward.rs:372-431) with the weight in packed `qtype` blocks.  x, out f32.  Up to 63 rows
+    (and every type but Q4_K) through the Q8_1 matvec, from 64 rows on Q4_K through the bf16 tensor-core GEMM."""
     _need(w, n * row_bytes(qtype, k), "w")
     _need(x, m * k * 4, "x")
     _need(out, m * n * 4, "out")
     if bias is not None:
         _need(bias, n * 4, "bias")
+    need = lib().qmm_qdense_scratch_bytes(qtype, m, k)
     if xq_scratch is None:
-        xq_scratch = torch.empty(m * row_bytes(Q8_1, k), dtype=torch.uint8, device=x.device)
-    _need(xq_scratch, m * row_bytes(Q8_1, k), "xq_scratch")
+        xq_scratch = torch.empty(need, dtype=torch.uint8, device=x.device)
+    _need(xq_scratch, need, "xq_scratch")
     check(lib().launch_qdense(qtype, _ptr(w), _ptr(x), _ptr(bias) if bias is not None else None, _ptr(out), _ptr(xq_scratch), m, n, k,
                               DENSE_ACTS[act] if isinstance(act, str) else int(act), float(alpha), _stream()), "launch_qdense")
 

@@ -190,13 +190,16 @@ def silu_mul(gate, up):
 DENSE_ACTS = ("linear", "relu", "sigmoid", "leaky_relu", "prelu", "elu", "selu", "tanh", "silu", "gelu")
 
 
-def dense(qtype, w, x, bias, act, alpha, k):
+def dense(qtype, w, x, bias, act, alpha, k, via="q8_1"):
     """Quantized dense layer y = act(x . w^T + bias): the composition the upstream runs for LayerKind::Dense
     (recipe-infer/src/forward.rs:372-431) with the product taken through the Q8_1 form of x and the packed
-    weight (quantize + matvec above).  The activations follow the upstream's kernels (elementwise.hip:1521-1560,
+    weight (quantize + matvec above), or through bf16(x) and the bf16 form of the weight (via="bf16").  The activations follow the upstream's kernels (elementwise.hip:1521-1560,
     gapact.hip:6-18), evaluated in float64 and rounded to float32."""
     x = _c(x, np.float32)
-    y = matvec(qtype, w, quantize(Q8_1, x), k)
+    if via == "bf16":   # many rows: x rounded to bf16, exact products, f32 accumulators (gemm_bf16 above)
+        y = gemm_bf16(qtype, w, f32_to_bf16_bits(x), k)[1]
+    else:
+        y = matvec(qtype, w, quantize(Q8_1, x), k)
     z = y if bias is None else (y + _c(bias, np.float32)[None, :]).astype(np.float32)
     z = z.astype(np.float64)
     if act == "linear":

@@ -40,6 +40,21 @@ def test_dense_matches_oracle(ops, act, qtype, m, n, k):
     assert ok, f"{act}: max err {worst:.3e}"
 
 
+@pytest.mark.parametrize("act", ["linear", "gelu", "selu"])
+@pytest.mark.parametrize("m,n,k", [(64, 300, 1024), (200, 129, 512), (700, 256, 768)])
+def test_dense_many_rows_takes_the_gemm(ops, act, m, n, k):
+    """From 64 rows on a Q4_K layer runs on the tcgen05 GEMM with x rounded to bf16."""
+    w = oracle.quantize(oracle.Q4_K, oracle.fill_normal(n * k, 90 + n, 0.05).reshape(n, k))
+    x = oracle.fill_normal(m * k, 91 + k, 1.0).reshape(m, k)
+    bias = oracle.fill_normal(n, 92, 0.5)
+    want = oracle.dense(oracle.Q4_K, w, x, bias, act, 0.0, k, via="bf16")
+    out = torch.full((m, n), float("nan"), device="cuda")
+    ops.gpu_qdense_into(oracle.Q4_K, torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda(), torch.from_numpy(bias).cuda(), out, m, n, k, act)
+    ops.check_launch()
+    ok, worst = close(out.cpu().numpy(), want)
+    assert ok, f"{act}: max err {worst:.3e}"
+
+
 def test_dense_without_bias_is_the_matvec(ops):
     m, n, k = 3, 257, 1024
     w = oracle.quantize(oracle.Q4_K, oracle.fill_normal(n * k, 7, 0.05).reshape(n, k))
