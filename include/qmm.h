@@ -274,6 +274,18 @@ long qmm_argmax_scratch_bytes(int batch);
 int launch_argmax_rows(const float* logits, void* scratch, int* out_index, float* out_value, int batch, int vocab, void* stream);
 int launch_scale_f32(float* x, float scalar, long n, void* stream);
 
+/* ---- attention over a whole sequence: the counterpart of the upstream's gpu_gqa_attn_into
+ * (gpu-core/src/infer_ops.rs:160-189 -> launch_gqa_masked_attn, gpu-core/src/kernels/f64_infer.hip:42-100).
+ * q (t, n_q_heads*head_dim), k and v (t, n_kv_heads*head_dim), out (t, n_q_heads*head_dim), all f32 row-major
+ * (the upstream's are f64); query head h reads kv head h / (n_q_heads / n_kv_heads).  Positions p < prefix are
+ * causal (attend sp <= p), positions p >= prefix attend the whole sequence; prefix = t is plain causal
+ * attention, prefix = 0 bidirectional.  Scores are q.k * kq_scale (the upstream folds its scale into q: 1).
+ * `out` must be distinct from q, k and v (every CTA reads the whole sequence, as upstream).  head_dim 32, 64, 96,
+ * 128 or 256; q, k, v 16-byte aligned.  Scores and outputs run on the f16 tensor cores with q (scaled), k, v and
+ * the probabilities rounded to f16 (about 1e-3 relative); the t x t scores are never stored. */
+int launch_attn_prefill(const float* q, const float* k, const float* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim,
+                        int prefix, float kq_scale, void* stream);
+
 /* ---- quantized dense layer: y(m,n) = act( x(m,k) . w(n,k)^T + bias(n) ), x and y f32, w packed blocks of
  * `type`.  The counterpart of LayerKind::Dense in the upstream's forward pass (recipe-infer/src/forward.rs:
  * 372-431: gpu_linear_into, gpu-core/src/kernels.rs:2589-2640, then one activation launch), the place where a

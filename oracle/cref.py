@@ -31,8 +31,7 @@ _lib = None
 def lib():
     global _lib
     if _lib is None:
-        if not os.path.exists(_SO):
-            build()
+        build()  # compiles only when the shared object is missing or older than its sources
         L = C.CDLL(_SO)
         vp, i64, i32, f32, u64 = C.c_void_p, C.c_long, C.c_int, C.c_float, C.c_uint64
         L.qo_fill_normal.argtypes = [vp, i64, u64, f32, i64]
@@ -49,6 +48,7 @@ def lib():
         L.qo_gelu_mul.argtypes = [vp, vp, vp, i64]
         L.qo_silu_mul.argtypes = [vp, vp, vp, i64]
         L.qo_attn_decode.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64]
+        L.qo_attn_prefill.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, C.c_double]
         L.qo_f32_to_f16.argtypes = [f32]
         L.qo_f32_to_f16.restype = C.c_uint16
         L.qo_f16_to_f32.argtypes = [C.c_uint16]
@@ -184,6 +184,15 @@ def silu_mul(gate, up):
     g, u = _c(gate, np.float32), _c(up, np.float32)
     out = np.empty_like(g)
     lib().qo_silu_mul(_p(g), _p(u), _p(out), g.size)
+    return out
+
+
+def attn_prefill(q, k, v, nqh, nkv, hd, prefix, kq_scale=1.0):
+    """q (t, nqh*hd), k, v (t, nkv*hd) f32 -> out (t, nqh*hd): the upstream's gqa_masked_attn."""
+    q, k, v = _c(q, np.float32), _c(k, np.float32), _c(v, np.float32)
+    t = q.shape[0]
+    out = np.empty((t, nqh * hd), dtype=np.float32)
+    lib().qo_attn_prefill(_p(q), _p(k), _p(v), _p(out), t, nqh, nkv, hd, prefix, float(kq_scale))
     return out
 
 

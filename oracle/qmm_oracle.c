@@ -603,3 +603,32 @@ void qo_attn_decode(const float* q, const uint16_t* kc, const uint16_t* vc, floa
     }
     free(p);
 }
+
+/* Attention over a whole sequence, the upstream's gqa_masked_attn restated (gpu-core/src/kernels/f64_infer.hip:42-91):
+ * one softmax per (position p, head h) over all t keys in double precision; a masked score (p < prefix and
+ * sp > p) is -1e30 as upstream; scores are q.k * kq_scale. */
+void qo_attn_prefill(const float* q, const float* k, const float* v, float* out, long t, long nqh, long nkv, long hd,
+                     long prefix, double kq_scale) {
+    long group = nqh / nkv, qd = nqh * hd, kd = nkv * hd;
+    double* sc = (double*)malloc((size_t)t * sizeof(double));
+    for (long p = 0; p < t; p++)
+        for (long h = 0; h < nqh; h++) {
+            long kv = h / group;
+            const float* qrow = q + p * qd + h * hd;
+            double m = -1e300;
+            for (long sp = 0; sp < t; sp++) {
+                double dot = 0.0;
+                for (long x = 0; x < hd; x++) dot += (double)qrow[x] * (double)k[sp * kd + kv * hd + x];
+                sc[sp] = (p < prefix && sp > p) ? -1e30 : dot * kq_scale;
+                if (sc[sp] > m) m = sc[sp];
+            }
+            double sum = 0.0;
+            for (long sp = 0; sp < t; sp++) { sc[sp] = exp(sc[sp] - m); sum += sc[sp]; }
+            for (long x = 0; x < hd; x++) {
+                double acc = 0.0;
+                for (long sp = 0; sp < t; sp++) acc += sc[sp] * (double)v[sp * kd + kv * hd + x];
+                out[p * qd + h * hd + x] = (float)(acc / sum);
+            }
+        }
+    free(sc);
+}

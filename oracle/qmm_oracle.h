@@ -94,6 +94,8 @@ void qo_silu_mul(const float* gate, const float* up, float* out, long n);
  * q (nqh, hd) f32; kc, vc (ctx_cap, nkv, hd) fp16; attends to positions [0, len) */
 void qo_attn_decode(const float* q, const uint16_t* kc, const uint16_t* vc, float* out,
                     long nqh, long nkv, long hd, long len);
+void qo_attn_prefill(const float* q, const float* k, const float* v, float* out, long t, long nqh, long nkv, long hd,
+                     long prefix, double kq_scale);
 
 int qo_num_threads(void);
 void qo_set_num_threads(int n);

@@ -141,3 +141,39 @@ def test_entries_reject_bad_arguments(ops):
     assert L.launch_embed_rows(77, 16, 16, 16, 1, 256, 10, None) == -5
     assert L.launch_argmax_rows(16, None, 16, None, 1, 10, None) == -1
     assert L.launch_scale_f32(None, 1.0, 5, None) == -1
+
+
+@pytest.mark.parametrize("t,nqh,nkv,hd,prefix", [(1, 4, 2, 64, 1), (70, 8, 2, 128, 70), (130, 4, 4, 32, 0), (200, 8, 2, 128, 77), (300, 16, 4, 96, 300),
+                                                  (129, 2, 1, 256, 64), (513, 4, 1, 128, 400), (64, 4, 2, 64, 10)])
+def test_sequence_attention_matches_oracle(ops, t, nqh, nkv, hd, prefix):
+    """launch_attn_prefill (the upstream's gqa_masked_attn: causal below `prefix`, bidirectional from it on) against the
+    oracle's double-precision loops.  q, k, v and the probabilities pass through f16 on the tensor cores (2^-11 each)."""
+    rng = np.random.default_rng(t * 7 + hd)
+    q = rng.normal(size=(t, nqh * hd)).astype(np.float32)
+    k = rng.normal(size=(t, nkv * hd)).astype(np.float32)
+    v = rng.normal(size=(t, nkv * hd)).astype(np.float32)
+    scale = 1.0 / np.sqrt(hd)
+    want = oracle.attn_prefill(q, k, v, nqh, nkv, hd, prefix, scale)
+    out = torch.full((t, nqh * hd), float("nan"), device="cuda")
+    ops.gpu_gqa_attn_into(torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(), out, t, nqh, nkv, hd, prefix, scale)
+    ops.check_launch()
+    got = out.cpu().numpy()
+    assert not np.isnan(got).any()
+    assert np.abs(got - want).max() <= 1e-4 + 4e-3 * np.abs(want).max()
+    # twice: identical bits
+    out2 = torch.empty_like(out)
+    ops.gpu_gqa_attn_into(torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(), out2, t, nqh, nkv, hd, prefix, scale)
+    assert torch.equal(out, out2)
+
+
+def test_sequence_attention_rejects_bad_arguments(ops):
+    from nates_recipe_rs_b200._lib import lib
+    L = lib()
+    x = torch.zeros(64 * 64, device="cuda")
+    o = torch.zeros(64 * 64, device="cuda")
+    p = lambda a: a.data_ptr()
+    assert L.launch_attn_prefill(p(x), p(x), p(x), p(o), 4, 4, 3, 64, 0, 1.0, None) == -2      # heads do not divide
+    assert L.launch_attn_prefill(p(x), p(x), p(x), p(x), 4, 4, 2, 64, 0, 1.0, None) == -2      # out aliases an input
+    assert L.launch_attn_prefill(p(x), p(x), p(x), p(o), 4, 4, 2, 80, 0, 1.0, None) == -3      # head_dim not instantiated
+    assert L.launch_attn_prefill(None, p(x), p(x), p(o), 4, 4, 2, 64, 0, 1.0, None) == -1
+    ops.check_launch()
