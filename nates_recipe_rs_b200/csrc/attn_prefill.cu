@@ -58,16 +58,29 @@ __global__ void __launch_bounds__(128 * GH) attn_prefill_kernel(const float* __r
     const int kt_end = (q0 + PF_BQ <= prefix) ? min(n_kt, qt + 1) : n_kt;
     for (int kt = 0; kt < kt_end; ++kt) {
         __syncthreads();  // the previous tile is consumed (first pass: the query tile is written)
-        for (int i = tid; i < PF_BK * (HD / 4); i += PF_THREADS) {
-            const int r = i / (HD / 4), c = (i - r * (HD / 4)) * 4;
-            const int sp = kt * PF_BK + r;
-            float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-            if (sp < t) {
-                a = *reinterpret_cast<const float4*>(k + (size_t)sp * kd + (size_t)kvh * HD + c);
-                b = *reinterpret_cast<const float4*>(v + (size_t)sp * kd + (size_t)kvh * HD + c);
+        // the tile's keys and values: up to eight loads per matrix in flight per thread (one round trip to L2 for
+        // them together), then convert and store
+        constexpr int KV_IT = PF_BK * (HD / 4) / PF_THREADS;  // float4 pieces per thread and matrix (whole: HD is a multiple of 32)
+        constexpr int KV_CH = KV_IT < 8 ? KV_IT : 8;
+#pragma unroll 1
+        for (int base = 0; base < KV_IT; base += KV_CH) {
+            float4 ka[KV_CH], va[KV_CH];
+#pragma unroll
+            for (int it = 0; it < KV_CH; ++it) {
+                const int i = tid + (base + it) * PF_THREADS, r = i / (HD / 4), c = (i - r * (HD / 4)) * 4;
+                const int sp = kt * PF_BK + r;
+                ka[it] = va[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (sp < t) {
+                    ka[it] = *reinterpret_cast<const float4*>(k + (size_t)sp * kd + (size_t)kvh * HD + c);
+                    va[it] = *reinterpret_cast<const float4*>(v + (size_t)sp * kd + (size_t)kvh * HD + c);
+                }
             }
-            *reinterpret_cast<uint2*>(ks + r * PITCH + c) = make_uint2(pack_h2(a.x, a.y), pack_h2(a.z, a.w));
-            *reinterpret_cast<uint2*>(vs + r * PITCH + c) = make_uint2(pack_h2(b.x, b.y), pack_h2(b.z, b.w));
+#pragma unroll
+            for (int it = 0; it < KV_CH; ++it) {
+                const int i = tid + (base + it) * PF_THREADS, r = i / (HD / 4), c = (i - r * (HD / 4)) * 4;
+                *reinterpret_cast<uint2*>(ks + r * PITCH + c) = make_uint2(pack_h2(ka[it].x, ka[it].y), pack_h2(ka[it].z, ka[it].w));
+                *reinterpret_cast<uint2*>(vs + r * PITCH + c) = make_uint2(pack_h2(va[it].x, va[it].y), pack_h2(va[it].z, va[it].w));
+            }
         }
         __syncthreads();
 
