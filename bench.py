@@ -29,6 +29,8 @@ CPU implementation there is: the upstream has none) on the host cores.
     --case jobs:<q4k|ffn>[:launches]                          one job-list launch (24 Q4_K / 32 FFN jobs)
     --case gemm:<n>:<k>:<m>[:launches]                        Q4_K x bf16 prefill GEMM
     --case decode:<8b|70b>:<batch>[:steps[:layers]]           eager decode steps of a (cut) stack
+    --case shard:<8b|70b>:<tp>:<batch>                        step time of a decoder with the per-rank shapes of a
+                                                              tensor-parallel layout, on one GPU (no exchange)
 """
 import argparse
 import json
@@ -703,6 +705,43 @@ def run_case(spec):
         for i in range(steps):   # eager launches, so that a launch list attributes the step to its kernels
             d.step(batch, pos0 + i)
             d.tokens.copy_(d.next_tokens)
+    elif kind == "shard":
+        # shard:<8b|70b>:<tp>:<batch>: a decoder with the per-rank shapes of a tensor-parallel layout on ONE GPU,
+        # i.e. the step without any exchange (what an N-GPU step is compared with); graph replays, device-timed
+        from nates_recipe_rs_b200 import decoder as dec
+        name, tp, batch = parts[1], int(parts[2]), int(parts[3])
+        cfg = (dec.config_8b if name == "8b" else dec.config_70b)(max_batch=batch)
+        cfg.n_q_heads //= tp
+        cfg.n_kv_heads = max(1, cfg.n_kv_heads // tp)
+        cfg.ffn //= tp
+        cfg.vocab //= tp
+        d = dec.Decoder(cfg)
+        d.fill_cache(3)
+        steps, reps = 8, 4
+        pos0 = cfg.ctx_len - steps - 1
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            d.tokens.fill_(11)
+
+            def body():
+                for i in range(steps):
+                    d.step(batch, pos0 + i)
+                    d.tokens.copy_(d.next_tokens)
+            body()
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                body()
+            g.replay()
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                g.replay()
+            e1.record(stream)
+            stream.synchronize()
+        ms = e0.elapsed_time(e1) / (reps * steps)
+        print(json.dumps({"case": spec, "ms_per_step": ms, "us_per_layer": ms * 1e3 / cfg.n_layers, "weight_bytes": d.weight_bytes}))
     else:
         raise SystemExit(f"unknown --case {spec!r}")
     torch.cuda.synchronize()
