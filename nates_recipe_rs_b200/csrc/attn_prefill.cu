@@ -56,33 +56,47 @@ __global__ void __launch_bounds__(128 * GH) attn_prefill_kernel(const float* __r
     // key tiles: a tile of queries that is causal throughout stops at its own diagonal tile
     const int n_kt = (t + PF_BK - 1) / PF_BK;
     const int kt_end = (q0 + PF_BQ <= prefix) ? min(n_kt, qt + 1) : n_kt;
+    // Keys and values of a tile: float4 pieces, KV_IT per thread and matrix.  When a thread's pieces of a tile fit
+    // its registers (KV_IT <= 8) the NEXT tile's loads are issued before the current tile's arithmetic, so their round
+    // trip to L2 hides under the mma; otherwise a tile is loaded in chunks of eight pieces right before its use.
+    constexpr int KV_IT = PF_BK * (HD / 4) / PF_THREADS;  // (whole: HD is a multiple of 32)
+    constexpr bool PREFETCH = KV_IT <= 8;
+    constexpr int KV_CH = KV_IT < 8 ? KV_IT : 8;
+    float4 ka[KV_CH], va[KV_CH];
+    auto load_kv = [&](int kt, int base) {
+#pragma unroll
+        for (int it = 0; it < KV_CH; ++it) {
+            const int i = tid + (base + it) * PF_THREADS, r = i / (HD / 4), c = (i - r * (HD / 4)) * 4;
+            const int sp = kt * PF_BK + r;
+            ka[it] = va[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (sp < t) {
+                ka[it] = *reinterpret_cast<const float4*>(k + (size_t)sp * kd + (size_t)kvh * HD + c);
+                va[it] = *reinterpret_cast<const float4*>(v + (size_t)sp * kd + (size_t)kvh * HD + c);
+            }
+        }
+    };
+    auto store_kv = [&](int base) {
+#pragma unroll
+        for (int it = 0; it < KV_CH; ++it) {
+            const int i = tid + (base + it) * PF_THREADS, r = i / (HD / 4), c = (i - r * (HD / 4)) * 4;
+            *reinterpret_cast<uint2*>(ks + r * PITCH + c) = make_uint2(pack_h2(ka[it].x, ka[it].y), pack_h2(ka[it].z, ka[it].w));
+            *reinterpret_cast<uint2*>(vs + r * PITCH + c) = make_uint2(pack_h2(va[it].x, va[it].y), pack_h2(va[it].z, va[it].w));
+        }
+    };
+    if (PREFETCH && kt_end > 0) load_kv(0, 0);
     for (int kt = 0; kt < kt_end; ++kt) {
         __syncthreads();  // the previous tile is consumed (first pass: the query tile is written)
-        // the tile's keys and values: up to eight loads per matrix in flight per thread (one round trip to L2 for
-        // them together), then convert and store
-        constexpr int KV_IT = PF_BK * (HD / 4) / PF_THREADS;  // float4 pieces per thread and matrix (whole: HD is a multiple of 32)
-        constexpr int KV_CH = KV_IT < 8 ? KV_IT : 8;
+        if constexpr (PREFETCH) {
+            store_kv(0);
+        } else {
 #pragma unroll 1
-        for (int base = 0; base < KV_IT; base += KV_CH) {
-            float4 ka[KV_CH], va[KV_CH];
-#pragma unroll
-            for (int it = 0; it < KV_CH; ++it) {
-                const int i = tid + (base + it) * PF_THREADS, r = i / (HD / 4), c = (i - r * (HD / 4)) * 4;
-                const int sp = kt * PF_BK + r;
-                ka[it] = va[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (sp < t) {
-                    ka[it] = *reinterpret_cast<const float4*>(k + (size_t)sp * kd + (size_t)kvh * HD + c);
-                    va[it] = *reinterpret_cast<const float4*>(v + (size_t)sp * kd + (size_t)kvh * HD + c);
-                }
-            }
-#pragma unroll
-            for (int it = 0; it < KV_CH; ++it) {
-                const int i = tid + (base + it) * PF_THREADS, r = i / (HD / 4), c = (i - r * (HD / 4)) * 4;
-                *reinterpret_cast<uint2*>(ks + r * PITCH + c) = make_uint2(pack_h2(ka[it].x, ka[it].y), pack_h2(ka[it].z, ka[it].w));
-                *reinterpret_cast<uint2*>(vs + r * PITCH + c) = make_uint2(pack_h2(va[it].x, va[it].y), pack_h2(va[it].z, va[it].w));
+            for (int base = 0; base < KV_IT; base += KV_CH) {
+                load_kv(kt, base);
+                store_kv(base);
             }
         }
         __syncthreads();
+        if (PREFETCH && kt + 1 < kt_end) load_kv(kt + 1, 0);
 
         // scores of the warp's 16 query rows against the 64 keys: 8 n-tiles of 8 keys
         float s[PF_BK / 8][4];
