@@ -212,6 +212,15 @@ int launch_qmatvec_batch_tp(void* comm, const qmm_matvec_job* jobs, int n_jobs, 
 int launch_qgemm_q4_k_bf16(const void* w, const void* x, void* y, int m, int n, int k, void* stream);
 int launch_qgemm_q4_k_bf16_f32acc(const void* w, const void* x, float* yf, int m, int n, int k, void* stream);
 
+/* ---- out(m,n) = a(m,k) . b(n,k)^T with a and b bf16 (row-major), fp32 accumulation: the upstream's
+ * gpu_gemm_bt_f64_into (gpu-core/src/infer_ops.rs:224-240, kernels/gemm_f64.hip:14-54) on a DECODED weight
+ * window in bf16 - what a caller uses for a weight type that has no fused GEMM here (dequantize with
+ * launch_dequantize_*_bf16, then this).  The same tcgen05 kernel as launch_qgemm_q4_k_bf16 with the weight
+ * tiles fetched by TMA instead of unpacked.  out bf16, or f32 accumulators (_f32acc).  k a multiple of 256;
+ * a, b 16-byte aligned. */
+int launch_gemm_bt_bf16(const void* a, const void* b, void* out, int m, int n, int k, void* stream);
+int launch_gemm_bt_bf16_f32acc(const void* a, const void* b, float* out, int m, int n, int k, void* stream);
+
 /* ---- decode attention: one query token per sequence against an fp16 KV cache, grouped-query.
  * Counterpart of launch_gqa_masked_attn (gpu-core/src/kernels/f64_infer.hip:49-100; Rust
  * gpu_gqa_attn_into, gpu-core/src/infer_ops.rs:11-55) for the decode case: qkv (batch, (n_q_heads +

@@ -82,6 +82,19 @@ int qmm_decoder_ipc_export(void* handle, void* out_handle_64_bytes);
 int qmm_decoder_ipc_import(void* handle, int peer_rank, const void* handle_64_bytes);
 int qmm_decoder_tp_ready(void* handle); /* call once after all imports (uploads the pointer tables) */
 
+/* The prompt path: all n_tokens positions of a prompt through every layer at once, the way the upstream's layer
+ * function runs a sequence (examples/gemma4.rs:638-742: every projection one gpu_gemm_bt_f64_into over the t rows,
+ * the attention one gpu_gqa_attn_into).  Projections are launch_qdense without bias or activation (the tcgen05
+ * GEMM on bf16(x) for Q4_K weights from 64 rows on, the Q8_1 matvec otherwise), the attention launch_attn_prefill
+ * (causal), the small operators the decode path's kernels with one row per position.  Fills the KV cache of
+ * sequence `seq` for positions 0..n_tokens-1 and writes the greedy token after the last position to next_token[0]
+ * (device), its logits to logits_out (device, vocab floats; may be NULL); decoding continues with
+ * qmm_decoder_step at pos = n_tokens.  tokens: device pointer.  Its activation buffers are allocated on first use
+ * for the longest prompt so far (freed with the decoder).  One GPU only (QMM_ERR_UNSUPPORTED with tp_size > 1).
+ * The logits differ from feeding the prompt token by token through qmm_decoder_step by the rounding of the
+ * activations (bf16 / f16 here, Q8_1 blocks there). */
+int qmm_decoder_prefill(void* handle, const int* tokens, int n_tokens, int seq, int* next_token, float* logits_out, void* stream);
+
 /* One decode step: tokens (device, batch ints) at position pos -> next_tokens (device, batch ints,
  * greedy).  logits (optional, device, batch x vocab_local f32) receives this rank's slice of the
  * logits.  With tensor parallelism the ranks exchange their slice's best candidate inside the

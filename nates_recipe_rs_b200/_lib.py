@@ -77,6 +77,8 @@ SIGNATURES = {
     "qmm_argmax_scratch_bytes": (i64, [i32]),
     "launch_argmax_rows": (i32, [vp, vp, vp, vp, i32, i32, vp]),
     "launch_scale_f32": (i32, [vp, C.c_float, i64, vp]),
+    "launch_gemm_bt_bf16": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "launch_gemm_bt_bf16_f32acc": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "launch_attn_prefill": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, C.c_float, vp]),
     "qmm_qdense_scratch_bytes": (i64, [i32, i32, i32]),
     "launch_qdense": (i32, [i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, C.c_float, vp]),

@@ -34,6 +34,7 @@ int quantize_weights_launch(int type, const float* w, void* out, long rows, int 
 int dequantize_f32_launch(int type, const void* w, float* out, long n_elems, cudaStream_t stream);
 int dequantize_bf16_launch(int type, const void* w, void* out, long n_elems, cudaStream_t stream);
 int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, int n, int k, cudaStream_t stream);
+int gemm_bt_bf16_launch(const void* a, const void* b, void* y, float* yf, int m, int n, int k, cudaStream_t stream);
 int matvec_tune(const char* key, int value);
 int jobs_tune(const char* key, int value);
 int qmatvec_jobs_launch(const qmm_matvec_job* jobs, int n_jobs, int m, cudaStream_t stream);
@@ -175,6 +176,15 @@ int launch_qgemm_q4_k_bf16(const void* w, const void* x, void* y, int m, int n, 
 int launch_qgemm_q4_k_bf16_f32acc(const void* w, const void* x, float* yf, int m, int n, int k, void* stream) {
     if (!yf) return QMM_ERR_NULL;
     return qgemm_q4k_launch(w, x, nullptr, yf, m, n, k, as_stream(stream));
+}
+
+int launch_gemm_bt_bf16(const void* a, const void* b, void* out, int m, int n, int k, void* stream) {
+    if (!out) return QMM_ERR_NULL;
+    return gemm_bt_bf16_launch(a, b, out, nullptr, m, n, k, as_stream(stream));
+}
+int launch_gemm_bt_bf16_f32acc(const void* a, const void* b, float* out, int m, int n, int k, void* stream) {
+    if (!out) return QMM_ERR_NULL;
+    return gemm_bt_bf16_launch(a, b, nullptr, out, m, n, k, as_stream(stream));
 }
 
 int launch_qblock_dots(int type, const void* w, const void* xq, int32_t* out, int n, int k, void* stream) {

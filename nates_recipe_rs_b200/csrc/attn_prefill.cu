@@ -23,7 +23,8 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 // HD: head dimension (a multiple of 16 up to 256).  GH: query heads of one kv head per CTA (1 or 2), four warps each.
 template <int HD, int GH>
 __global__ void __launch_bounds__(128 * GH) attn_prefill_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
-                                                                  float* __restrict__ out, int t, int nqh, int nkv, int prefix, float kq_scale) {
+                                                                  float* __restrict__ out, int t, int nqh, int nkv, int prefix, float kq_scale,
+                                                                  long q_stride, long k_stride, long v_stride, long o_stride) {
     extern __shared__ __align__(16) uint8_t pf_raw[];
     constexpr int PITCH = HD + 8;  // halves: rows 16 bytes apart modulo 128, so the 8 rows of an ldmatrix hit all banks
     constexpr int PF_THREADS = 128 * GH;
@@ -34,7 +35,7 @@ __global__ void __launch_bounds__(128 * GH) attn_prefill_kernel(const float* __r
     const int hl = wall >> 2, warp = wall & 3;  // head within the CTA, 16-row block of the query tile
     const int qt = blockIdx.x, h = blockIdx.y * GH + hl, kvh = (blockIdx.y * GH) / (nqh / nkv);
     __half* qs = qs_all + hl * PF_BQ * PITCH;
-    const size_t qd = (size_t)nqh * HD, kd = (size_t)nkv * HD;
+    const size_t qd = (size_t)q_stride, kd = (size_t)k_stride, vd = (size_t)v_stride, od = (size_t)o_stride;  // floats between rows
     const int q0 = qt * PF_BQ;
 
     // the query tiles, scaled, as f16 (rows past t as zeros)
@@ -71,7 +72,7 @@ __global__ void __launch_bounds__(128 * GH) attn_prefill_kernel(const float* __r
             ka[it] = va[it] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (sp < t) {
                 ka[it] = *reinterpret_cast<const float4*>(k + (size_t)sp * kd + (size_t)kvh * HD + c);
-                va[it] = *reinterpret_cast<const float4*>(v + (size_t)sp * kd + (size_t)kvh * HD + c);
+                va[it] = *reinterpret_cast<const float4*>(v + (size_t)sp * vd + (size_t)kvh * HD + c);
             }
         }
     };
@@ -162,14 +163,14 @@ __global__ void __launch_bounds__(128 * GH) attn_prefill_kernel(const float* __r
     const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n) {
-        if (p0 < t) *reinterpret_cast<float2*>(out + (size_t)p0 * qd + (size_t)h * HD + 8 * n + 2 * pq) = make_float2(o[n][0] * i0, o[n][1] * i0);
-        if (p1 < t) *reinterpret_cast<float2*>(out + (size_t)p1 * qd + (size_t)h * HD + 8 * n + 2 * pq) = make_float2(o[n][2] * i1, o[n][3] * i1);
+        if (p0 < t) *reinterpret_cast<float2*>(out + (size_t)p0 * od + (size_t)h * HD + 8 * n + 2 * pq) = make_float2(o[n][0] * i0, o[n][1] * i0);
+        if (p1 < t) *reinterpret_cast<float2*>(out + (size_t)p1 * od + (size_t)h * HD + 8 * n + 2 * pq) = make_float2(o[n][2] * i1, o[n][3] * i1);
     }
 }
 
 template <int HD, int GH>
 static int attn_prefill_inst(const float* q, const float* k, const float* v, float* out, int t, int nqh, int nkv, int prefix, float kq_scale,
-                             cudaStream_t s) {
+                             long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s) {
     const size_t smem = (size_t)(GH * PF_BQ + 2 * PF_BK) * (HD + 8) * sizeof(__half);
     static std::mutex mu;
     static bool configured[64] = {};
@@ -182,29 +183,30 @@ static int attn_prefill_inst(const float* q, const float* k, const float* v, flo
             if (dev >= 0 && dev < 64) configured[dev] = true;
         }
     }
-    attn_prefill_kernel<HD, GH><<<dim3((t + PF_BQ - 1) / PF_BQ, nqh / GH), 128 * GH, smem, s>>>(q, k, v, out, t, nqh, nkv, prefix, kq_scale);
+    attn_prefill_kernel<HD, GH><<<dim3((t + PF_BQ - 1) / PF_BQ, nqh / GH), 128 * GH, smem, s>>>(q, k, v, out, t, nqh, nkv, prefix, kq_scale, q_stride, k_stride,
+                                                                                                 v_stride, o_stride);
     QMM_CUDA_TRY(cudaGetLastError());
     return QMM_OK;
 }
 
-}  // namespace qmm
-
-using namespace qmm;
-
-extern "C" int launch_attn_prefill(const float* q, const float* k, const float* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim,
-                                   int prefix, float kq_scale, void* stream) {
+// q, k, v, out with their own row strides (floats; multiples of 4): the projections of a layer write [q | k] and v
+// side by side
+int attn_prefill_launch(const float* q, const float* k, const float* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim, int prefix,
+                        float kq_scale, long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s) {
     if (!q || !k || !v || !out) return QMM_ERR_NULL;
     if (t <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads != 0 || prefix < 0) return QMM_ERR_SHAPE;
+    if (q_stride < (long)n_q_heads * head_dim || o_stride < (long)n_q_heads * head_dim || k_stride < (long)n_kv_heads * head_dim ||
+        v_stride < (long)n_kv_heads * head_dim || q_stride % 4 || k_stride % 4 || v_stride % 4 || o_stride % 2)
+        return QMM_ERR_SHAPE;
     if (out == q || out == k || out == v) return QMM_ERR_SHAPE;  // every CTA reads the whole sequence (as upstream)
     if (reinterpret_cast<uintptr_t>(q) % 16 || reinterpret_cast<uintptr_t>(k) % 16 || reinterpret_cast<uintptr_t>(v) % 16 ||
         reinterpret_cast<uintptr_t>(out) % 8)
         return QMM_ERR_ALIGN;
-    cudaStream_t s = as_stream(stream);
     const bool two = (n_q_heads / n_kv_heads) % 2 == 0;  // two query heads of a kv head per CTA
-#define QMM_PF_CASE(HD_)                                                                                                     \
-    case HD_:                                                                                                                 \
-        return two ? attn_prefill_inst<HD_, 2>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, s)                  \
-                   : attn_prefill_inst<HD_, 1>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, s)
+#define QMM_PF_CASE(HD_)                                                                                                                              \
+    case HD_:                                                                                                                                          \
+        return two ? attn_prefill_inst<HD_, 2>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, s)   \
+                   : attn_prefill_inst<HD_, 1>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, s)
     switch (head_dim) {
         QMM_PF_CASE(32);
         QMM_PF_CASE(64);
@@ -214,4 +216,14 @@ extern "C" int launch_attn_prefill(const float* q, const float* k, const float* 
     }
 #undef QMM_PF_CASE
     return QMM_ERR_UNSUPPORTED;
+}
+
+}  // namespace qmm
+
+using namespace qmm;
+
+extern "C" int launch_attn_prefill(const float* q, const float* k, const float* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim,
+                                   int prefix, float kq_scale, void* stream) {
+    const long qd = (long)n_q_heads * head_dim, kd = (long)n_kv_heads * head_dim;
+    return attn_prefill_launch(q, k, v, out, t, n_q_heads, n_kv_heads, head_dim, prefix, kq_scale, qd, kd, kd, qd, as_stream(stream));
 }

@@ -20,6 +20,10 @@ int qmatvec_launch_limited(int type, const void* w, const void* xq, float* y, lo
 int quantize_weights_launch(int type, const float* w, void* out, long rows, int k, cudaStream_t stream);
 int qmatvec_launch_push(int type, const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                         const TpPush* push, cudaStream_t stream);
+int gemm_bt_bf16_launch(const void* a, const void* b, void* y, float* yf, int m, int n, int k, cudaStream_t stream);
+int dequantize_bf16_launch(int type, const void* w, void* out, long n_elems, cudaStream_t stream);
+int attn_prefill_launch(const float* q, const float* k, const float* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim, int prefix,
+                        float kq_scale, long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s);
 int qmatvec_launch_pitched(int type, const void* w, long row_pitch, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                            const TpPush* push, cudaStream_t stream);
 int decoder_fusion();
@@ -67,6 +71,14 @@ struct Decoder {
     cudaEvent_t fork = nullptr, join = nullptr;
     int sms = 0;
     long weight_bytes_per_token = 0;
+    // buffers of the prompt path (prefill), allocated on first use for the longest prompt seen so far
+    struct Prefill {
+        int cap = 0;
+        float *x = nullptr, *xn = nullptr, *qk = nullptr, *v = nullptr, *att = nullptr, *part = nullptr, *gu = nullptr, *act = nullptr;
+        uint8_t *xq = nullptr, *q8 = nullptr;
+        __nv_bfloat16* wb = nullptr;  // a weight matrix decoded to bf16 (types without a fused GEMM)
+        size_t wb_elems = 0;
+    } pf;
 };
 
 static int type_row_bytes(int type, long k) {
@@ -214,8 +226,10 @@ struct GgufSource : WeightSource {
     }
 };
 
+static void prefill_free(Decoder* d);
 static void destroy(Decoder* d) {
     if (!d) return;
+    prefill_free(d);
     tp_comm_destroy(d->comm);
     for (void* p : d->allocs) cudaFree(p);
     if (d->fork) cudaEventDestroy(d->fork);
@@ -579,6 +593,132 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
     return QMM_OK;
 }
 
+// ---- the prompt path: all positions of a prompt through every layer at once, as the upstream's layer function does
+// (examples/gemma4.rs:638-742: every projection is one gpu_gemm_bt_f64_into over the t rows, the attention one
+// gpu_gqa_attn_into).  Projections: launch_qdense without bias or activation, i.e. the tcgen05 GEMM on bf16(x) for
+// Q4_K weights from 64 rows on and the Q8_1 matvec otherwise; attention: the sequence kernel, causal; the small
+// operators are the decode path's kernels with one row per position.  Fills the KV cache of sequence `seq` for
+// positions 0..t-1 and returns the greedy token after the last position.  One GPU only.
+static void prefill_free(Decoder* d) {
+    Decoder::Prefill& f = d->pf;
+    void* ptrs[] = {f.x, f.xn, f.qk, f.v, f.att, f.part, f.gu, f.act, f.xq, f.q8, f.wb};
+    for (void* p : ptrs)
+        if (p) cudaFree(p);
+    f = Decoder::Prefill{};
+}
+static int prefill_reserve(Decoder* d, int t) {
+    Decoder::Prefill& f = d->pf;
+    if (t <= f.cap) return QMM_OK;
+    prefill_free(d);
+    const qmm_decoder_config& c = d->c;
+    const size_t H = c.hidden, T = (size_t)t, ao = (size_t)d->nq * c.head_dim, ffn = d->ffn_l;
+    const size_t kmax = std::max(std::max(H, ao), ffn);
+    const size_t dense_scratch = std::max(T * kmax * 2, T * (kmax / 32) * Q8_1_BYTES);  // bf16 or Q8_1 form of a projection's input
+    struct { void** p; size_t bytes; } want[] = {
+        {(void**)&f.x, T * H * 4},      {(void**)&f.xn, T * H * 4},        {(void**)&f.qk, T * (size_t)d->qkv_cols * 4}, {(void**)&f.v, T * (size_t)d->v_rows * 4},
+        {(void**)&f.att, T * ao * 4},   {(void**)&f.part, T * H * 4},      {(void**)&f.gu, T * 2 * ffn * 4},             {(void**)&f.act, T * ffn * 4},
+        {(void**)&f.xq, dense_scratch}, {(void**)&f.q8, T * (kmax / 32) * Q8_1_BYTES}};
+    for (auto& w : want)
+        if (cudaMalloc(w.p, w.bytes) != cudaSuccess) {
+            prefill_free(d);
+            return cuda_fail(cudaErrorMemoryAllocation);
+        }
+    // the largest matrix of a type without a fused GEMM, decoded to bf16 one at a time
+    size_t wb = 0;
+    auto note = [&](int type, size_t n, size_t k) {
+        if (type != QMM_TYPE_Q4_K) wb = std::max(wb, n * k);
+    };
+    note(c.type_attn_qk, (size_t)d->qk_rows + (c.type_attn_v == c.type_attn_qk ? d->v_rows : 0), H);
+    note(c.type_attn_v, d->v_rows, H);
+    note(c.type_attn_o, H, ao);
+    note(c.type_ffn_gate_up, 2 * ffn, H);
+    note(c.type_ffn_down, H, ffn);
+    if (wb && cudaMalloc((void**)&f.wb, wb * 2) != cudaSuccess) {
+        prefill_free(d);
+        return cuda_fail(cudaErrorMemoryAllocation);
+    }
+    f.wb_elems = wb;
+    f.cap = t;
+    return QMM_OK;
+}
+
+__global__ void prefill_f32_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, long n) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2bfloat16_rn(x[i]);
+}
+
+// One projection of the prompt path: y(t, n) = x(t, k) . w(n, k)^T.  Q4_K: launch_qdense (the fused GEMM from 64 rows
+// on).  Other types from 64 rows on: the matrix is decoded to bf16 (bit-identical to launch_dequantize_*_bf16) and
+// multiplied by the same tcgen05 kernel with TMA-fed weight tiles; fewer rows: the Q8_1 matvec.
+static int prefill_dense(Decoder* d, int type, const uint8_t* w, const float* x, float* y, int t, int n, int k, cudaStream_t s) {
+    Decoder::Prefill& f = d->pf;
+    if (type == QMM_TYPE_Q4_K || t < 64 || k % 256 != 0 || (size_t)n * k > f.wb_elems)
+        return launch_qdense(type, w, x, nullptr, y, f.xq, t, n, k, QMM_DENSE_LINEAR, 0.f, s);
+    if (int st = dequantize_bf16_launch(type, w, f.wb, (long)n * k, s)) return st;
+    const long total = (long)t * k;
+    prefill_f32_to_bf16_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(x, reinterpret_cast<__nv_bfloat16*>(f.xq), total);
+    QMM_CUDA_TRY(cudaGetLastError());
+    return gemm_bt_bf16_launch(f.xq, f.wb, nullptr, y, t, n, k, s);
+}
+
+static int prefill(Decoder* d, const int* tokens, int t, int seq, int* next_token, float* logits_out, cudaStream_t s) {
+    const qmm_decoder_config& c = d->c;
+    if (!tokens || !next_token) return QMM_ERR_NULL;
+    if (d->comm || c.tp_size != 1) return QMM_ERR_UNSUPPORTED;
+    if (t <= 0 || t > c.ctx_len || seq < 0 || seq >= c.max_batch) return QMM_ERR_SHAPE;
+    int st;
+#define TRY(e) \
+    do {       \
+        if ((st = (e)) != 0) return st; \
+    } while (0)
+    TRY(prefill_reserve(d, t));
+    Decoder::Prefill& f = d->pf;
+    const int H = c.hidden, hd = c.head_dim, nq = d->nq, nkv = d->nkv, ao = nq * hd, ffn = d->ffn_l;
+    const bool v_fused = c.type_attn_v == c.type_attn_qk;  // V's rows follow K's in the same matrix
+    const long qk_stride = v_fused ? d->qkv_cols : d->qk_rows;
+    const float* vbuf = v_fused ? f.qk + d->qk_rows : f.v;
+    const long v_stride = v_fused ? d->qkv_cols : d->v_rows;
+    const TpRecv none = {};
+    {   // embedding
+        const int rb = type_row_bytes(c.type_head, H);
+        const dim3 grid((H + 255) / 256, t);
+        if (c.type_head == QMM_TYPE_Q6_K) embed_rows_kernel<QMM_TYPE_Q6_K><<<grid, 256, 0, s>>>(d->embed, tokens, f.x, H, rb, c.vocab, (unsigned*)nullptr);
+        else if (c.type_head == QMM_TYPE_Q4_K) embed_rows_kernel<QMM_TYPE_Q4_K><<<grid, 256, 0, s>>>(d->embed, tokens, f.x, H, rb, c.vocab, (unsigned*)nullptr);
+        else embed_rows_kernel<QMM_TYPE_Q8_0><<<grid, 256, 0, s>>>(d->embed, tokens, f.x, H, rb, c.vocab, (unsigned*)nullptr);
+        QMM_CUDA_TRY(cudaGetLastError());
+    }
+    const size_t cache_layer = (size_t)c.max_batch * c.ctx_len * nkv * hd;
+    PartPtrs parts = {};
+    parts.p[0] = f.part;
+    for (int l = 0; l < c.n_layers; ++l) {
+        const LayerWeights& L = d->layers[l];
+        // x += down output of the previous layer; xn = RMSNorm(x) * gamma
+        TRY(add_rmsnorm_launch(f.x, parts, l > 0 ? 1 : 0, (long)H, L.attn_norm, f.q8, H, c.rms_eps, none, f.xn, t, false, s));
+        TRY(prefill_dense(d, c.type_attn_qk, L.wqk, f.xn, f.qk, t, v_fused ? d->qk_rows + d->v_rows : d->qk_rows, H, s));
+        if (!v_fused) TRY(prefill_dense(d, c.type_attn_v, L.wv, f.xn, f.v, t, d->v_rows, H, s));
+        rope_seq_append_kernel<<<dim3(8, t), 256, 0, s>>>(f.qk, qk_stride, vbuf, v_stride, d->kcache + (size_t)l * cache_layer,
+                                                            d->vcache + (size_t)l * cache_layer, nq, nkv, hd, 0, seq, c.ctx_len, c.rope_theta);
+        QMM_CUDA_TRY(cudaGetLastError());
+        TRY(attn_prefill_launch(f.qk, f.qk + (size_t)nq * hd, vbuf, f.att, t, nq, nkv, hd, t, rsqrtf((float)hd), qk_stride, qk_stride, v_stride, ao, s));
+        TRY(prefill_dense(d, c.type_attn_o, L.wo, f.att, f.part, t, H, ao, s));
+        TRY(add_rmsnorm_launch(f.x, parts, 1, (long)H, L.ffn_norm, f.q8, H, c.rms_eps, none, f.xn, t, false, s));
+        TRY(prefill_dense(d, c.type_ffn_gate_up, L.wgu, f.xn, f.gu, t, 2 * ffn, H, s));
+        act_mul_q8_kernel<<<dim3((ffn / 32 + 3) / 4, t), 128, 0, s>>>((const float*)f.gu, f.q8, ffn, c.act, f.act);
+        QMM_CUDA_TRY(cudaGetLastError());
+        TRY(prefill_dense(d, c.type_ffn_down, L.wdown, f.act, f.part, t, H, ffn, s));
+    }
+    // the last position only: residual, final norm, head, greedy token
+    PartPtrs last = {};
+    last.p[0] = f.part + (size_t)(t - 1) * H;
+    TRY(add_rmsnorm_launch(f.x + (size_t)(t - 1) * H, last, 1, (long)H, d->final_norm, d->xq_h, H, c.rms_eps, none, nullptr, 1, false, s));
+    float* lg = logits_out ? logits_out : d->logits;
+    TRY(qmatvec_launch_strided(c.type_head, d->head, d->xq_h, lg, d->vocab_l, 1, d->vocab_l, H, s));
+    TRY(launch_pdl(argmax_partial_kernel, dim3(ARGMAX_PARTS, 1), dim3(256), 0, s, (const float*)lg, d->argmax_cand, d->vocab_l));
+    TRY(launch_pdl(argmax_final_kernel, dim3(1), dim3(256), 0, s, (const Candidate*)d->argmax_cand, ARGMAX_PARTS, next_token, 0, d->best_val));
+#undef TRY
+    return QMM_OK;
+}
+
 }  // namespace qmm
 
 using namespace qmm;
@@ -827,6 +967,12 @@ int qmm_decoder_tp_ready(void* handle) {
     if (!handle) return QMM_ERR_NULL;
     Decoder* d = static_cast<Decoder*>(handle);
     return d->comm ? tp_comm_ready(d->comm) : QMM_OK;
+}
+
+int qmm_decoder_prefill(void* handle, const int* tokens, int n_tokens, int seq, int* next_token, float* logits_out, void* stream) {
+    if (!handle) return QMM_ERR_NULL;
+    Decoder* d = static_cast<Decoder*>(handle);
+    return prefill(d, tokens, n_tokens, seq, next_token, logits_out, static_cast<cudaStream_t>(stream));
 }
 
 int qmm_decoder_step(void* handle, const int* tokens, int batch, int pos, int* next_tokens, float* logits, float* best, void* stream) {

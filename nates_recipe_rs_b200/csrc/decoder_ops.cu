@@ -303,6 +303,39 @@ inline int add_rmsnorm_launch(float* x, const PartPtrs& parts, int n_parts, long
     return QMM_OK;
 }
 
+// The same for a whole sequence (the prefill of a prompt): row r of the buffers is position pos0 + r of sequence
+// `seq`.  q and k (columns [0, nqh*hd) and [nqh*hd, (nqh+nkv)*hd) of a row of qk) are rotated in place (f32: the
+// sequence attention reads them there), k (rotated) and v also go to the fp16 cache.
+__global__ void rope_seq_append_kernel(float* __restrict__ qk, long qk_stride, const float* __restrict__ v, long v_stride,
+                                       __half* __restrict__ kcache, __half* __restrict__ vcache, int nqh, int nkv, int hd, int pos0, int seq,
+                                       int ctx_cap, float theta) {
+    const int r = blockIdx.y, pos = pos0 + r;
+    const int half = hd / 2;
+    const int pairs = (nqh + nkv) * half;
+    float* row = qk + (size_t)r * qk_stride;
+    const float* vrow = v + (size_t)r * v_stride;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < pairs + nkv * hd; idx += gridDim.x * blockDim.x) {
+        if (idx < pairs) {
+            const int head = idx / half, i = idx - head * half;
+            float sn, cs;
+            sincosf((float)pos * powf(theta, -2.0f * (float)i / (float)hd), &sn, &cs);
+            float* h = row + (size_t)head * hd;
+            const float a = h[i], c = h[i + half];
+            const float ra = a * cs - c * sn, rc = a * sn + c * cs;
+            h[i] = ra;
+            h[i + half] = rc;
+            if (head >= nqh) {
+                __half* dst = kcache + (((size_t)seq * ctx_cap + pos) * nkv + (head - nqh)) * hd;
+                dst[i] = __float2half_rn(ra);
+                dst[i + half] = __float2half_rn(rc);
+            }
+        } else {
+            const int j = idx - pairs;
+            vcache[((size_t)seq * ctx_cap + pos) * nkv * hd + j] = __float2half_rn(vrow[j]);
+        }
+    }
+}
+
 // NeoX rotary embedding of q (in place, fp32) and k, then k and v appended to the fp16 cache at `pos`.
 // qkv row layout: [q: nqh*hd | k: nkv*hd | v: nkv*hd].  cache layout: (batch, ctx_cap, nkv, hd).
 __global__ void rope_kv_append_kernel(float* __restrict__ qkv, __half* __restrict__ kcache, __half* __restrict__ vcache, int nqh, int nkv,

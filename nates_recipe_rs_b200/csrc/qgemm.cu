@@ -58,6 +58,7 @@ struct GemmParams {
     int probe;            // tuning aid: 0 normal, 1 = unpack arithmetic skipped, 2 = tensor-core work skipped
     int nb_per_cta;       // 256-row blocks of x per CTA (1..GEMM_NB_MAX)
     int ksplit;           // CTAs of a cluster that share one output tile, each with a contiguous part of K (1 or 2)
+    int w_bf16;           // 1: the weights are bf16 rows (n, k) and reach the weight ring by TMA; nothing is unpacked
 };
 
 struct __align__(16) GemmSmemHeader {
@@ -152,7 +153,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
     const int kt = n_sb * (QKK / GEMM_BK), ks0 = sb0 * (QKK / GEMM_BK);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < GEMM_SW; ++s) mbar_init(smem_u32(&hdr->w_full[s]), GEMM_DEQ_WARPS);
+        for (int s = 0; s < GEMM_SW; ++s) mbar_init(smem_u32(&hdr->w_full[s]), p.w_bf16 ? 1 : GEMM_DEQ_WARPS);
         for (int s = 0; s < GEMM_ND; ++s) mbar_init(smem_u32(&hdr->done[s]), nb);  // one commit per block and k-step
         for (int s = 0; s < GEMM_XT; ++s) mbar_init(smem_u32(&hdr->x_full[s]), 1);
         for (int s = 0; s < GEMM_SP; ++s) mbar_init(smem_u32(&hdr->p_full[s]), 1), mbar_init(smem_u32(&hdr->p_empty[s]), GEMM_DEQ_WARPS);
@@ -232,8 +233,31 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
             umma_commit(smem_u32(&hdr->acc_full));  // also on the give-up path, so the epilogue warps are released
         }
     } else if (warp == GEMM_WARP_PACKED) {
-        // ------------------------------------------------------------ TMA producer (packed super-blocks)
-        if (lane == 0) {
+        // ------------------------------------------------------------ TMA producer (packed super-blocks, or bf16 weight tiles)
+        if (lane == 0 && p.w_bf16) {
+            // plain bf16 weights: one 128 x 64 tile per k-step straight into the weight ring (128-byte swizzle, as x)
+            int issued = 0;
+            for (int ks = 0; ks < kt; ++ks, ++issued) {
+                if (ks >= GEMM_SW && !wait_done(ks - GEMM_SW)) {
+                    give_up(DEV_TIMEOUT_EMPTY);
+                    break;
+                }
+                const uint32_t bar = smem_u32(&hdr->w_full[ks % GEMM_SW]);
+                mbar_arrive_expect_tx(bar, GEMM_W_BYTES);
+                tma_load_2d(smem_u32(w_ring + (ks % GEMM_SW) * GEMM_W_BYTES), &wmap, (ks0 + ks) * GEMM_BK, n0, bar);  // rows past n: zeros
+            }
+            if (*cta_abort) {
+                for (int i = max(0, issued - GEMM_SW); i < issued; ++i) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(smem_u32(&hdr->w_full[i % GEMM_SW]), (i / GEMM_SW) & 1)) {
+                        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                            atomicExch(&g_device_status, DEV_TIMEOUT_DRAIN);
+                            break;
+                        }
+                    }
+                }
+            }
+        } else if (lane == 0) {
             int issued = 0;
             for (int sb = 0; sb < n_sb; ++sb, ++issued) {
                 const int slot = sb % GEMM_SP;
@@ -265,7 +289,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) qgemm_q4k_kernel(const __grid
         const int row = t & 127, part = t >> 7;  // part 0..3
         const uint32_t row_off = (uint32_t)row * 128u, swz = (uint32_t)(row & 7);
         bool ok = true;
-        for (int sb = 0; sb < n_sb && ok; ++sb) {
+        for (int sb = 0; sb < (p.w_bf16 ? 0 : n_sb) && ok; ++sb) {
             // this row's super-block from the packed ring: header and this thread's 8 bytes of each group
             const int ps = sb % GEMM_SP;
             if (!mbar_wait_bounded(smem_u32(&hdr->p_full[ps]), (sb / GEMM_SP) & 1, cta_abort)) {
@@ -449,7 +473,7 @@ int gemm_set_mb(int v) {
     return QMM_OK;
 }
 
-int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, int n, int k, cudaStream_t stream) {
+static int gemm_launch(const void* w, bool w_bf16, const void* x, void* y, float* yf, int m, int n, int k, cudaStream_t stream) {
     if (!w || !x || (!y && !yf)) return QMM_ERR_NULL;
     if (m <= 0 || n <= 0 || k <= 0 || k % 256 != 0) return QMM_ERR_SHAPE;
     if (reinterpret_cast<uintptr_t>(w) % 16 != 0 || reinterpret_cast<uintptr_t>(x) % 16 != 0 ||
@@ -466,9 +490,17 @@ int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, in
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cuda_fail(cudaErrorInvalidValue);
 
-    // the packed weights as a 2-D byte tensor (row bytes, rows): one box = one super-block of 128 rows
+    // the packed weights as a 2-D byte tensor (row bytes, rows): one box = one super-block of 128 rows; bf16 weights as
+    // a (k, n) bf16 tensor: one box = one 128 x 64 tile, swizzled like the x tiles
     CUtensorMap wmap;
-    {
+    if (w_bf16) {
+        const cuuint64_t wdims[2] = {(cuuint64_t)k, (cuuint64_t)n};
+        const cuuint64_t wstrides[1] = {(cuuint64_t)k * 2};
+        const cuuint32_t wbox[2] = {GEMM_BK, GEMM_BW};
+        if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(w), wdims, wstrides, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cuda_fail(cudaErrorInvalidValue);
+    } else {
         const cuuint64_t wdims[2] = {(cuuint64_t)(k / 256 * Q4_K_BYTES), (cuuint64_t)n};
         const cuuint64_t wstrides[1] = {(cuuint64_t)(k / 256 * Q4_K_BYTES)};
         const cuuint32_t wbox[2] = {Q4_K_BYTES, GEMM_BW};
@@ -484,6 +516,7 @@ int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, in
     p.m = m, p.n = n, p.k = k;
     p.row_bytes = k / 256 * Q4_K_BYTES;
     p.probe = g_gemm_probe;
+    p.w_bf16 = w_bf16 ? 1 : 0;
     const size_t smem = (size_t)GEMM_SW * GEMM_W_BYTES + (size_t)GEMM_XT * GEMM_X_BYTES + (size_t)GEMM_SP * GEMM_P_BYTES + sizeof(GemmSmemHeader) + 1024;
     static bool configured[64] = {};
     int dev = 0;
@@ -532,6 +565,14 @@ int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, in
     cfg.numAttrs = 1;
     QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, qgemm_q4k_kernel, map, wmap, p));
     return QMM_OK;
+}
+
+int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, int n, int k, cudaStream_t stream) {
+    return gemm_launch(w, false, x, y, yf, m, n, k, stream);
+}
+// out(m, n) = a(m, k) . b(n, k)^T with a and b bf16: the upstream's gemm_bt on a decoded (bf16) weight window
+int gemm_bt_bf16_launch(const void* a, const void* b, void* y, float* yf, int m, int n, int k, cudaStream_t stream) {
+    return gemm_launch(b, true, a, y, yf, m, n, k, stream);
 }
 
 }  // namespace qmm

@@ -57,6 +57,7 @@ def _bind():
         L.qmm_decoder_ipc_import.argtypes = [vp, i32, vp]
         L.qmm_decoder_tp_ready.argtypes = [vp]
         L.qmm_decoder_step.argtypes = [vp, vp, i32, i32, vp, vp, vp, vp]
+        L.qmm_decoder_prefill.argtypes = [vp, vp, i32, i32, vp, vp, vp]
         L.qmm_decoder_create_from_gguf.argtypes = [C.c_char_p, i32, i32, i32, i32, C.POINTER(vp)]
         L.qmm_decoder_export_gguf.argtypes = [vp, C.c_char_p, C.c_char_p]
         _bound = True
@@ -119,6 +120,17 @@ class Decoder:
         check(self.L.qmm_decoder_step(self.h, self.tokens.data_ptr(), batch, pos, self.next_tokens.data_ptr(),
                                       logits.data_ptr() if logits is not None else None, self.best.data_ptr(),
                                       torch.cuda.current_stream().cuda_stream), "qmm_decoder_step")
+
+    def prefill(self, prompt, seq=0, logits=None):
+        """All positions of `prompt` (int32 CUDA tensor) through the stack at once; fills the KV cache of sequence
+        `seq` for positions 0..len-1 and returns the greedy token after the last position (int32 CUDA tensor of one
+        element); `logits` (vocab floats) optionally receives that position's logits.  Decode goes on with
+        step(batch, pos=len(prompt))."""
+        out = torch.empty(1, dtype=torch.int32, device=prompt.device)
+        check(self.L.qmm_decoder_prefill(self.h, prompt.data_ptr(), prompt.numel(), seq, out.data_ptr(),
+                                         logits.data_ptr() if logits is not None else None, torch.cuda.current_stream().cuda_stream),
+              "qmm_decoder_prefill")
+        return out
 
     def close(self):
         if self.h:

@@ -24,7 +24,7 @@ __all__ = [
     "gpu_quantize_q8_1_into", "gpu_quantize_q8_1", "gpu_quantize_weights_into", "gpu_quantize_weights",
     "gpu_dequantize_into", "gpu_dequantize", "gpu_qmatvec_into", "gpu_qmatvec", "gpu_qblock_dots",
     "MatvecJobs", "gpu_qmatvec_batch_into", "gpu_norm_qmatvec_batch_into", "gpu_glu_qmatvec_batch_into", "TpComm", "gpu_qmatvec_tp_into", "gpu_qmatvec_batch_tp_into",
-    "gpu_qgemm_q4_k_bf16_into", "gpu_qgemm_q4_k_bf16", "gpu_qdense_into", "DENSE_ACTS", "gpu_gqa_attn_into",
+    "gpu_qgemm_q4_k_bf16_into", "gpu_qgemm_q4_k_bf16", "gpu_qdense_into", "DENSE_ACTS", "gpu_gqa_attn_into", "gpu_gemm_bt_bf16_into",
     "gpu_qlinear",
     "gpu_rmsnorm_q8_1_into", "gpu_rope_kv_append", "gpu_glu_act_q8_1_into", "gpu_embed_rows_into", "gpu_argmax_rows",
     "gpu_scale_f32_inplace", "gpu_moe_router_topk", "gpu_moe_experts_into",
@@ -309,6 +309,16 @@ def gpu_argmax_rows(logits):
 def gpu_scale_f32_inplace(x, scalar):
     """x *= scalar: the upstream's gpu_scale_f64_inplace (gpu-core/src/infer_ops.rs:242-248)."""
     check(lib().launch_scale_f32(_ptr(x), scalar, x.numel(), _stream()), "launch_scale_f32")
+
+
+def gpu_gemm_bt_bf16_into(a, b, out, m, n, k):
+    """out(m,n) = a(m,k) . b(n,k)^T, a and b bf16, out bf16 or f32: the upstream's gpu_gemm_bt_f64_into
+    (gpu-core/src/infer_ops.rs:224-240) on a bf16 weight window."""
+    _need(a, m * k * 2, "a")
+    _need(b, n * k * 2, "b")
+    _need(out, m * n * out.element_size(), "out")
+    name = "launch_gemm_bt_bf16" if out.dtype == torch.bfloat16 else "launch_gemm_bt_bf16_f32acc"
+    check(getattr(lib(), name)(_ptr(a), _ptr(b), _ptr(out), m, n, k, _stream()), name)
 
 
 def gpu_gqa_attn_into(q, k, v, out, t, nqh, nkv, hd, prefix, kq_scale=1.0):

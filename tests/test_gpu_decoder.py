@@ -273,3 +273,97 @@ def test_fused_and_separate_launches_agree(dec):
         for pos, (a, b) in enumerate(zip(seq, results[3])):
             scale = np.abs(b).max()
             assert np.abs(a - b).max() <= (1e-5 if pos == 0 else 2e-2) * scale, (level, pos, float(np.abs(a - b).max()), float(scale))
+
+
+def ref_prefill(ref, tokens):
+    """The prompt path restated from oracle pieces: every projection a quantized dense over all positions (bf16 GEMM
+    route from 64 rows on - fused for Q4_K, on the decoded bf16 matrix for the other types - and the Q8_1 matvec route
+    below), attention over the whole sequence, causal.  Fills the reference cache of sequence 0 and returns the
+    logits of the last position."""
+    c = ref.c
+    t = len(tokens)
+    H, hd, nq, nkv, ffn = c.hidden, c.head_dim, c.n_q_heads, c.n_kv_heads, c.ffn
+
+    def dense(qt, w, x, k):
+        via = "bf16" if (t >= 64 and k % 256 == 0) else "q8_1"
+        return oracle.dense(qt, w, x, None, "linear", 0.0, k, via=via)
+
+    rb = oracle.row_bytes(c.type_head, H)
+    x = np.stack([oracle.dequantize(c.type_head, ref.head[tok * rb:(tok + 1) * rb], H).reshape(-1) for tok in tokens]).astype(np.float32)
+    for l, L in enumerate(ref.layers):
+        xn = oracle.rmsnorm(x, L["attn_norm"], c.rms_eps)
+        qk = dense(c.type_attn_qk, L["wqk"], xn, H)
+        v = dense(c.type_attn_v, L["wv"], xn, H)
+        q = oracle.rope_neox(qk[:, :nq * hd].copy(), hd, nq, 0, c.rope_theta).reshape(t, nq * hd)
+        k = oracle.rope_neox(qk[:, nq * hd:].copy(), hd, nkv, 0, c.rope_theta).reshape(t, nkv * hd)
+        ref.kc[l, 0, :t] = k.reshape(t, nkv, hd).astype(np.float16)
+        ref.vc[l, 0, :t] = v.reshape(t, nkv, hd).astype(np.float16)
+        att = oracle.attn_prefill(q, k, v, nq, nkv, hd, t, 1.0 / np.sqrt(hd))
+        x = x + dense(c.type_attn_o, L["wo"], att, nq * hd)
+        xn = oracle.rmsnorm(x, L["ffn_norm"], c.rms_eps)
+        gu = dense(c.type_ffn_gate_up, L["wgu"], xn, H)
+        act = oracle.gelu_mul if c.act == ref.dec.ACT_GELU_TANH else oracle.silu_mul
+        x = x + dense(c.type_ffn_down, L["wdown"], act(gu[:, :ffn].copy(), gu[:, ffn:].copy()), ffn)
+    xq = ref.q8(oracle.rmsnorm(x[-1:], ref.final_norm, c.rms_eps)[0])
+    return oracle.matvec(c.type_head, ref.head, xq, H)[0]
+
+
+@pytest.mark.parametrize("t", [1, 20, 70, 130])
+def test_prefill_matches_reference_and_decode_continues(dec, t):
+    """qmm_decoder_prefill on a prompt of t tokens (below and above the 64 rows from which Q4_K projections take the
+    tensor-core GEMM) against the oracle composition; then one decode step from the filled cache."""
+    from nates_recipe_rs_b200 import quant_ops as ops
+    d = dec.Decoder(tiny_cfg(dec, ctx_len=160, max_batch=2))
+    c = d.cfg
+    ref = RefModel(d, dec)
+    rng = np.random.default_rng(t)
+    prompt = rng.integers(0, c.vocab, size=t).astype(np.int32)
+    logits = torch.empty(c.vocab, device="cuda")
+    nxt = d.prefill(torch.from_numpy(prompt).cuda(), 0, logits)
+    ops.check_launch()
+    want = ref_prefill(ref, prompt)
+    got = logits.cpu().numpy()
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() <= 2e-2 * scale, (float(np.abs(got - want).max()), float(scale))
+    assert int(nxt.item()) == int(got.argmax())
+    # the cache the engine filled continues the sequence: one decode step at position t
+    tok = int(nxt.item())
+    d.tokens[:1] = tok
+    step_logits = torch.empty(c.max_batch, c.vocab, device="cuda")
+    d.step(1, t, step_logits)
+    ops.check_launch()
+    want2 = ref.step(0, tok, t)
+    got2 = step_logits[0].cpu().numpy()
+    assert np.abs(got2 - want2).max() <= 2e-2 * np.abs(want2).max()
+    d.close()
+
+
+def test_prefill_agrees_with_token_by_token_decoding(dec):
+    """The same prompt through the decode path one token at a time: the logits after the last token agree with the
+    prompt path within the difference of the activation formats (bf16 / f16 against Q8_1 blocks)."""
+    from nates_recipe_rs_b200 import quant_ops as ops
+    t = 80
+    d = dec.Decoder(tiny_cfg(dec, ctx_len=96, max_batch=2))
+    c = d.cfg
+    prompt = np.random.default_rng(5).integers(0, c.vocab, size=t).astype(np.int32)
+    a = torch.empty(c.vocab, device="cuda")
+    d.prefill(torch.from_numpy(prompt).cuda(), 1, a)      # sequence 1
+    b = torch.empty(c.max_batch, c.vocab, device="cuda")
+    for pos in range(t):
+        d.tokens[:1] = int(prompt[pos])
+        d.step(1, pos, b)                                  # sequence 0
+    ops.check_launch()
+    scale = float(b[0].abs().max())
+    assert float((a - b[0]).abs().max()) <= 5e-2 * scale
+    d.close()
+
+
+def test_prefill_rejects_bad_arguments(dec):
+    from nates_recipe_rs_b200._lib import QmmError
+    d = dec.Decoder(tiny_cfg(dec))
+    toks = torch.zeros(100, dtype=torch.int32, device="cuda")
+    with pytest.raises(QmmError):
+        d.prefill(toks, 0)            # longer than the context (48)
+    with pytest.raises(QmmError):
+        d.prefill(toks[:4], 7)        # no such sequence
+    d.close()

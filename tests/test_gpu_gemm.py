@@ -116,3 +116,24 @@ def test_gemm_full_size_against_torch(ops, m, n, k):
     ref = x.float() @ wb.float().T
     mag = x.float().abs() @ wb.float().abs().T
     assert bool(((yf - ref).abs() <= ABS_TOL + REL_TOL * mag).all()), float((yf - ref).abs().max())
+
+
+@pytest.mark.parametrize("qtype", [oracle.Q6_K, oracle.Q8_0, oracle.Q4_K])
+@pytest.mark.parametrize("m,n,k", [(70, 300, 1024), (512, 256, 768), (129, 128, 256)])
+def test_gemm_bt_on_a_bf16_weight_window(ops, qtype, m, n, k):
+    """launch_gemm_bt_bf16 on weights dequantised to bf16 by the library (the route of a block type without a fused
+    GEMM) against the oracle's GEMM on the same packed weights: the bf16 weights are bit-identical by construction."""
+    w = oracle.quantize(qtype, oracle.fill_normal(n * k, 300 + n, 0.02).reshape(n, k))
+    x = oracle.f32_to_bf16_bits(oracle.fill_normal(m * k, 301 + m, 1.0).reshape(m, k))
+    y_ref, yf_ref = oracle.gemm_bf16(qtype, w, x, k)
+    wb = ops.gpu_dequantize(qtype, torch.from_numpy(w).cuda(), n * k, torch.bfloat16)
+    xd = bf16_tensor(x)
+    yf = torch.full((m, n), float("nan"), device="cuda")
+    ops.gpu_gemm_bt_bf16_into(xd, wb, yf, m, n, k)
+    y = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    ops.gpu_gemm_bt_bf16_into(xd, wb, y, m, n, k)
+    ops.check_launch()
+    got_f = yf.cpu().numpy()
+    err = np.abs(got_f.astype(np.float64) - yf_ref.astype(np.float64))
+    assert (err <= ABS_TOL + REL_TOL * np.abs(yf_ref)).all(), f"max err {err.max():.3e}"
+    assert np.array_equal(y.view(torch.int16).cpu().numpy().view(np.uint16), oracle.f32_to_bf16_bits(got_f))
