@@ -458,6 +458,8 @@ def run_ours(args):
         out.update(sections)
         if decode is not None:
             out["decode"] = decode
+            if PREFILL:
+                out["prefill"] = PREFILL
         if tp_par is not None:
             out["tp_parity"] = tp_par
             out["tp_exchange"] = {"fused_vs_nccl_max_rel_diff": sum_diff, "fused_pass_us": elapsed_ms * 1e3 / n_pass,
@@ -567,6 +569,9 @@ def gemm_section(torch, ops, timer, dev, layers, tensor_peak):
     return out
 
 
+PREFILL = []   # filled by run_decode on one GPU: time to run a whole prompt through the stack
+
+
 def run_decode(world, rank, dev, quick):
     """Greedy decode tok/s of the random-init 8B- and 70B-class stacks (BASELINE configs[3], [4]):
     whole steps (embedding .. argmax) captured as a CUDA graph, KV cache filled with seeded values,
@@ -632,6 +637,28 @@ def run_decode(world, rank, dev, quick):
             out.append({"stack": name, "batch": batch, "context": cfg.ctx_len, "ms_per_step": sec * 1e3, "tok_s": batch / sec,
                         "weight_GB_per_token": wb / 1e9, "weight_GBps": wb / sec / 1e9, "tp": world})
             del graph
+        if world == 1:
+            # the prompt path: all positions of a prompt at once (GEMM projections, sequence attention); eager launches
+            for t in (512, 2048):
+                if t > cfg.ctx_len:
+                    continue
+                note(f"prefill {name}: {t} tokens")
+                prompt = torch.randint(0, cfg.vocab, (t,), dtype=torch.int32, device=dev)
+                try:
+                    d.prefill(prompt, 0)   # allocates the prompt path's buffers
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(2):
+                        d.prefill(prompt, 0)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ops.check_launch()
+                    sec = e0.elapsed_time(e1) * 1e-3 / 2
+                    PREFILL.append({"stack": name, "tokens": t, "ms": sec * 1e3, "tok_s": t / sec,
+                                    "weight_flops": 2.0 * t * (d.weight_bytes / 0.62), "note": "flops ~ 2 x tokens x weights (0.62 B per weight on average)"})
+                except Exception as e:
+                    PREFILL.append({"stack": name, "tokens": t, "error": f"{type(e).__name__}: {e}"[:120]})
         d.close()
         del d
         torch.cuda.empty_cache()
