@@ -29,6 +29,7 @@ CPU implementation there is: the upstream has none) on the host cores.
     --case jobs:<q4k|ffn>[:launches]                          one job-list launch (24 Q4_K / 32 FFN jobs)
     --case gemm:<n>:<k>:<m>[:launches]                        Q4_K x bf16 prefill GEMM
     --case decode:<8b|70b>:<batch>[:steps[:layers]]           eager decode steps of a (cut) stack
+    --case prefill:<8b|70b>:<tokens>[:layers]                 a prompt through a (cut) stack at once, twice
     --case shard:<8b|70b>:<tp>:<batch>                        step time of a decoder with the per-rank shapes of a
                                                               tensor-parallel layout, on one GPU (no exchange)
 """
@@ -732,6 +733,18 @@ def run_case(spec):
         for i in range(steps):   # eager launches, so that a launch list attributes the step to its kernels
             d.step(batch, pos0 + i)
             d.tokens.copy_(d.next_tokens)
+    elif kind == "prefill":
+        # prefill:<8b|70b>:<tokens>[:layers]: one prompt through a (cut) stack, eager launches (for a launch list)
+        from nates_recipe_rs_b200 import decoder as dec
+        name, t = parts[1], int(parts[2])
+        cfg = (dec.config_8b if name == "8b" else dec.config_70b)(max_batch=1)
+        if len(parts) > 3:
+            cfg.n_layers = int(parts[3])
+        d = dec.Decoder(cfg)
+        prompt = torch.randint(0, cfg.vocab, (t,), dtype=torch.int32, device=dev)
+        d.prefill(prompt, 0)
+        torch.cuda.synchronize()
+        d.prefill(prompt, 0)
     elif kind == "shard":
         # shard:<8b|70b>:<tp>:<batch>: a decoder with the per-rank shapes of a tensor-parallel layout on ONE GPU,
         # i.e. the step without any exchange (what an N-GPU step is compared with); graph replays, device-timed

@@ -703,8 +703,11 @@ static int prefill(Decoder* d, const int* tokens, int t, int seq, int* next_toke
         TRY(prefill_dense(d, c.type_attn_o, L.wo, f.att, f.part, t, H, ao, s));
         TRY(add_rmsnorm_launch(f.x, parts, 1, (long)H, L.ffn_norm, f.q8, H, c.rms_eps, none, f.xn, t, false, s));
         TRY(prefill_dense(d, c.type_ffn_gate_up, L.wgu, f.xn, f.gu, t, 2 * ffn, H, s));
-        act_mul_q8_kernel<<<dim3((ffn / 32 + 3) / 4, t), 128, 0, s>>>((const float*)f.gu, f.q8, ffn, c.act, f.act);
-        QMM_CUDA_TRY(cudaGetLastError());
+        {
+            const long quads = (long)t * (ffn / 4);
+            act_mul_f32_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, s>>>((const float*)f.gu, f.act, ffn, c.act, quads);
+            QMM_CUDA_TRY(cudaGetLastError());
+        }
         TRY(prefill_dense(d, c.type_ffn_down, L.wdown, f.act, f.part, t, H, ffn, s));
     }
     // the last position only: residual, final norm, head, greedy token

@@ -279,7 +279,9 @@ inline int add_rmsnorm_launch(float* x, const PartPtrs& parts, int n_parts, long
         attr[na].val.programmaticStreamSerializationAllowed = 1;
         ++na;
     }
-    const bool clustered = hidden % (NORM_CLUSTER * 32) == 0 && hidden / NORM_CLUSTER <= NORM_CL_THREADS * NORM_CL_PER_THREAD;
+    // a cluster of eight CTAs per row cuts the latency of a few rows (decode); with many rows (a prompt) one CTA per
+    // row fills the GPU anyway and the 16 k tiny CTAs of the clustered form cost 200 instead of 20 us at 2048 rows
+    const bool clustered = rows <= 64 && hidden % (NORM_CLUSTER * 32) == 0 && hidden / NORM_CLUSTER <= NORM_CL_THREADS * NORM_CL_PER_THREAD;
     if (clustered) {
         attr[na].id = cudaLaunchAttributeClusterDimension;
         attr[na].val.clusterDim.x = NORM_CLUSTER;
@@ -756,6 +758,23 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
 }
 
 // gated activation on the fused [gate | up] projection output + Q8_1: act(gate) * up -> xq (ffn per row)
+// out = act(gate) * up for many rows (the prompt path: only the f32 values are needed), four elements per thread
+__global__ void act_mul_f32_kernel(const float* __restrict__ gate_up, float* __restrict__ out, int ffn, int act, long quads) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= quads) return;
+    const int per_row = ffn / 4;
+    const long b = i / per_row;
+    const int c = (int)(i - b * per_row) * 4;
+    const float* row = gate_up + (size_t)b * 2 * ffn;
+    const float4 g = *reinterpret_cast<const float4*>(row + c), u = *reinterpret_cast<const float4*>(row + ffn + c);
+    float4 r;
+    r.x = (act == 0 ? gelu_tanh_f(g.x) : g.x / (1.0f + __expf(-g.x))) * u.x;
+    r.y = (act == 0 ? gelu_tanh_f(g.y) : g.y / (1.0f + __expf(-g.y))) * u.y;
+    r.z = (act == 0 ? gelu_tanh_f(g.z) : g.z / (1.0f + __expf(-g.z))) * u.z;
+    r.w = (act == 0 ? gelu_tanh_f(g.w) : g.w / (1.0f + __expf(-g.w))) * u.w;
+    *reinterpret_cast<float4*>(out + (size_t)b * ffn + c) = r;
+}
+
 __global__ void act_mul_q8_kernel(const float* __restrict__ gate_up, uint8_t* __restrict__ xq, int ffn, int act, float* __restrict__ out_f32) {
     pdl_release_dependents();
     pdl_wait_prior_grids();
