@@ -744,7 +744,12 @@ def run_case(spec):
         prompt = torch.randint(0, cfg.vocab, (t,), dtype=torch.int32, device=dev)
         d.prefill(prompt, 0)
         torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
         d.prefill(prompt, 0)
+        e1.record()
+        torch.cuda.synchronize()
+        print(json.dumps({"case": spec, "layers": cfg.n_layers, "ms": e0.elapsed_time(e1)}))
     elif kind == "shard":
         # shard:<8b|70b>:<tp>:<batch>: a decoder with the per-rank shapes of a tensor-parallel layout on ONE GPU,
         # i.e. the step without any exchange (what an N-GPU step is compared with); graph replays, device-timed

@@ -24,7 +24,8 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 template <int HD, int GH>
 __global__ void __launch_bounds__(128 * GH) attn_prefill_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                                                                   float* __restrict__ out, int t, int nqh, int nkv, int prefix, float kq_scale,
-                                                                  long q_stride, long k_stride, long v_stride, long o_stride) {
+                                                                  long q_stride, long k_stride, long v_stride, long o_stride,
+                                                                  __nv_bfloat16* __restrict__ out_bf16) {
     extern __shared__ __align__(16) uint8_t pf_raw[];
     constexpr int PITCH = HD + 8;  // halves: rows 16 bytes apart modulo 128, so the 8 rows of an ldmatrix hit all banks
     constexpr int PF_THREADS = 128 * GH;
@@ -163,14 +164,19 @@ __global__ void __launch_bounds__(128 * GH) attn_prefill_kernel(const float* __r
     const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n) {
-        if (p0 < t) *reinterpret_cast<float2*>(out + (size_t)p0 * od + (size_t)h * HD + 8 * n + 2 * pq) = make_float2(o[n][0] * i0, o[n][1] * i0);
-        if (p1 < t) *reinterpret_cast<float2*>(out + (size_t)p1 * od + (size_t)h * HD + 8 * n + 2 * pq) = make_float2(o[n][2] * i1, o[n][3] * i1);
+        if (out_bf16) {  // the same layout as out, as bf16 (the input of a GEMM)
+            if (p0 < t) *reinterpret_cast<__nv_bfloat162*>(out_bf16 + (size_t)p0 * od + (size_t)h * HD + 8 * n + 2 * pq) = __floats2bfloat162_rn(o[n][0] * i0, o[n][1] * i0);
+            if (p1 < t) *reinterpret_cast<__nv_bfloat162*>(out_bf16 + (size_t)p1 * od + (size_t)h * HD + 8 * n + 2 * pq) = __floats2bfloat162_rn(o[n][2] * i1, o[n][3] * i1);
+        } else {
+            if (p0 < t) *reinterpret_cast<float2*>(out + (size_t)p0 * od + (size_t)h * HD + 8 * n + 2 * pq) = make_float2(o[n][0] * i0, o[n][1] * i0);
+            if (p1 < t) *reinterpret_cast<float2*>(out + (size_t)p1 * od + (size_t)h * HD + 8 * n + 2 * pq) = make_float2(o[n][2] * i1, o[n][3] * i1);
+        }
     }
 }
 
 template <int HD, int GH>
 static int attn_prefill_inst(const float* q, const float* k, const float* v, float* out, int t, int nqh, int nkv, int prefix, float kq_scale,
-                             long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s) {
+                             long q_stride, long k_stride, long v_stride, long o_stride, __nv_bfloat16* out_bf16, cudaStream_t s) {
     const size_t smem = (size_t)(GH * PF_BQ + 2 * PF_BK) * (HD + 8) * sizeof(__half);
     static std::mutex mu;
     static bool configured[64] = {};
@@ -184,7 +190,7 @@ static int attn_prefill_inst(const float* q, const float* k, const float* v, flo
         }
     }
     attn_prefill_kernel<HD, GH><<<dim3((t + PF_BQ - 1) / PF_BQ, nqh / GH), 128 * GH, smem, s>>>(q, k, v, out, t, nqh, nkv, prefix, kq_scale, q_stride, k_stride,
-                                                                                                 v_stride, o_stride);
+                                                                                                 v_stride, o_stride, out_bf16);
     QMM_CUDA_TRY(cudaGetLastError());
     return QMM_OK;
 }
@@ -192,21 +198,21 @@ static int attn_prefill_inst(const float* q, const float* k, const float* v, flo
 // q, k, v, out with their own row strides (floats; multiples of 4): the projections of a layer write [q | k] and v
 // side by side
 int attn_prefill_launch(const float* q, const float* k, const float* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim, int prefix,
-                        float kq_scale, long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s) {
-    if (!q || !k || !v || !out) return QMM_ERR_NULL;
+                        float kq_scale, long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s, __nv_bfloat16* out_bf16) {
+    if (!q || !k || !v || (!out && !out_bf16)) return QMM_ERR_NULL;
     if (t <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads != 0 || prefix < 0) return QMM_ERR_SHAPE;
     if (q_stride < (long)n_q_heads * head_dim || o_stride < (long)n_q_heads * head_dim || k_stride < (long)n_kv_heads * head_dim ||
         v_stride < (long)n_kv_heads * head_dim || q_stride % 4 || k_stride % 4 || v_stride % 4 || o_stride % 2)
         return QMM_ERR_SHAPE;
     if (out == q || out == k || out == v) return QMM_ERR_SHAPE;  // every CTA reads the whole sequence (as upstream)
     if (reinterpret_cast<uintptr_t>(q) % 16 || reinterpret_cast<uintptr_t>(k) % 16 || reinterpret_cast<uintptr_t>(v) % 16 ||
-        reinterpret_cast<uintptr_t>(out) % 8)
+        reinterpret_cast<uintptr_t>(out) % 8 || reinterpret_cast<uintptr_t>(out_bf16) % 4)
         return QMM_ERR_ALIGN;
     const bool two = (n_q_heads / n_kv_heads) % 2 == 0;  // two query heads of a kv head per CTA
 #define QMM_PF_CASE(HD_)                                                                                                                              \
     case HD_:                                                                                                                                          \
-        return two ? attn_prefill_inst<HD_, 2>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, s)   \
-                   : attn_prefill_inst<HD_, 1>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, s)
+        return two ? attn_prefill_inst<HD_, 2>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, s)   \
+                   : attn_prefill_inst<HD_, 1>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, s)
     switch (head_dim) {
         QMM_PF_CASE(32);
         QMM_PF_CASE(64);
@@ -225,5 +231,6 @@ using namespace qmm;
 extern "C" int launch_attn_prefill(const float* q, const float* k, const float* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim,
                                    int prefix, float kq_scale, void* stream) {
     const long qd = (long)n_q_heads * head_dim, kd = (long)n_kv_heads * head_dim;
-    return attn_prefill_launch(q, k, v, out, t, n_q_heads, n_kv_heads, head_dim, prefix, kq_scale, qd, kd, kd, qd, as_stream(stream));
+    if (!out) return QMM_ERR_NULL;
+    return attn_prefill_launch(q, k, v, out, t, n_q_heads, n_kv_heads, head_dim, prefix, kq_scale, qd, kd, kd, qd, as_stream(stream), nullptr);
 }

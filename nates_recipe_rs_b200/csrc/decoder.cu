@@ -23,7 +23,8 @@ int qmatvec_launch_push(int type, const void* w, const void* xq, float* y, long 
 int gemm_bt_bf16_launch(const void* a, const void* b, void* y, float* yf, int m, int n, int k, cudaStream_t stream);
 int dequantize_bf16_launch(int type, const void* w, void* out, long n_elems, cudaStream_t stream);
 int attn_prefill_launch(const float* q, const float* k, const float* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim, int prefix,
-                        float kq_scale, long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s);
+                        float kq_scale, long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s, __nv_bfloat16* out_bf16);
+int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, int n, int k, cudaStream_t stream);
 int qmatvec_launch_pitched(int type, const void* w, long row_pitch, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                            const TpPush* push, cudaStream_t stream);
 int decoder_fusion();
@@ -76,6 +77,7 @@ struct Decoder {
         int cap = 0;
         float *x = nullptr, *xn = nullptr, *qk = nullptr, *v = nullptr, *att = nullptr, *part = nullptr, *gu = nullptr, *act = nullptr;
         uint8_t *xq = nullptr, *q8 = nullptr;
+        __nv_bfloat16* xb = nullptr;  // the bf16 form of a projection's input, written by the kernel that produces it
         __nv_bfloat16* wb = nullptr;  // a weight matrix decoded to bf16 (types without a fused GEMM)
         size_t wb_elems = 0;
     } pf;
@@ -601,7 +603,7 @@ static int step(Decoder* d, const int* tokens, int batch, int pos, int* next_tok
 // positions 0..t-1 and returns the greedy token after the last position.  One GPU only.
 static void prefill_free(Decoder* d) {
     Decoder::Prefill& f = d->pf;
-    void* ptrs[] = {f.x, f.xn, f.qk, f.v, f.att, f.part, f.gu, f.act, f.xq, f.q8, f.wb};
+    void* ptrs[] = {f.x, f.xn, f.qk, f.v, f.att, f.part, f.gu, f.act, f.xq, f.q8, f.wb, f.xb};
     for (void* p : ptrs)
         if (p) cudaFree(p);
     f = Decoder::Prefill{};
@@ -617,7 +619,7 @@ static int prefill_reserve(Decoder* d, int t) {
     struct { void** p; size_t bytes; } want[] = {
         {(void**)&f.x, T * H * 4},      {(void**)&f.xn, T * H * 4},        {(void**)&f.qk, T * (size_t)d->qkv_cols * 4}, {(void**)&f.v, T * (size_t)d->v_rows * 4},
         {(void**)&f.att, T * ao * 4},   {(void**)&f.part, T * H * 4},      {(void**)&f.gu, T * 2 * ffn * 4},             {(void**)&f.act, T * ffn * 4},
-        {(void**)&f.xq, dense_scratch}, {(void**)&f.q8, T * (kmax / 32) * Q8_1_BYTES}};
+        {(void**)&f.xq, dense_scratch}, {(void**)&f.q8, T * (kmax / 32) * Q8_1_BYTES}, {(void**)&f.xb, T * kmax * 2}};
     for (auto& w : want)
         if (cudaMalloc(w.p, w.bytes) != cudaSuccess) {
             prefill_free(d);
@@ -642,23 +644,16 @@ static int prefill_reserve(Decoder* d, int t) {
     return QMM_OK;
 }
 
-__global__ void prefill_f32_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, long n) {
-    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = __float2bfloat16_rn(x[i]);
-}
-
 // One projection of the prompt path: y(t, n) = x(t, k) . w(n, k)^T.  Q4_K: launch_qdense (the fused GEMM from 64 rows
 // on).  Other types from 64 rows on: the matrix is decoded to bf16 (bit-identical to launch_dequantize_*_bf16) and
 // multiplied by the same tcgen05 kernel with TMA-fed weight tiles; fewer rows: the Q8_1 matvec.
 static int prefill_dense(Decoder* d, int type, const uint8_t* w, const float* x, float* y, int t, int n, int k, cudaStream_t s) {
     Decoder::Prefill& f = d->pf;
-    if (type == QMM_TYPE_Q4_K || t < 64 || k % 256 != 0 || (size_t)n * k > f.wb_elems)
-        return launch_qdense(type, w, x, nullptr, y, f.xq, t, n, k, QMM_DENSE_LINEAR, 0.f, s);
+    const bool gemm = t >= 64 && k % 256 == 0;   // then f.xb holds bf16(x), written by the kernel that produced x
+    if (gemm && type == QMM_TYPE_Q4_K) return qgemm_q4k_launch(w, f.xb, nullptr, y, t, n, k, s);
+    if (!gemm || (size_t)n * k > f.wb_elems) return launch_qdense(type, w, x, nullptr, y, f.xq, t, n, k, QMM_DENSE_LINEAR, 0.f, s);
     if (int st = dequantize_bf16_launch(type, w, f.wb, (long)n * k, s)) return st;
-    const long total = (long)t * k;
-    prefill_f32_to_bf16_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(x, reinterpret_cast<__nv_bfloat16*>(f.xq), total);
-    QMM_CUDA_TRY(cudaGetLastError());
-    return gemm_bt_bf16_launch(f.xq, f.wb, nullptr, y, t, n, k, s);
+    return gemm_bt_bf16_launch(f.xb, f.wb, nullptr, y, t, n, k, s);
 }
 
 static int prefill(Decoder* d, const int* tokens, int t, int seq, int* next_token, float* logits_out, cudaStream_t s) {
@@ -679,6 +674,10 @@ static int prefill(Decoder* d, const int* tokens, int t, int seq, int* next_toke
     const float* vbuf = v_fused ? f.qk + d->qk_rows : f.v;
     const long v_stride = v_fused ? d->qkv_cols : d->v_rows;
     const TpRecv none = {};
+    // From 64 positions on every projection is a GEMM on a bf16 input: the kernels that produce those inputs write bf16 (f.xb)
+    // and skip the f32 copy.
+    float* const xn_f32 = (t >= 64 && H % 256 == 0) ? nullptr : f.xn;
+    const bool seq_norm = !xn_f32 && add_rmsnorm_bf16_fits(H, (long)H);  // then neither the f32 nor the Q8_1 form of the norm is read
     {   // embedding
         const int rb = type_row_bytes(c.type_head, H);
         const dim3 grid((H + 255) / 256, t);
@@ -693,19 +692,25 @@ static int prefill(Decoder* d, const int* tokens, int t, int seq, int* next_toke
     for (int l = 0; l < c.n_layers; ++l) {
         const LayerWeights& L = d->layers[l];
         // x += down output of the previous layer; xn = RMSNorm(x) * gamma
-        TRY(add_rmsnorm_launch(f.x, parts, l > 0 ? 1 : 0, (long)H, L.attn_norm, f.q8, H, c.rms_eps, none, f.xn, t, false, s));
+        if (seq_norm) TRY(add_rmsnorm_bf16_launch(f.x, l > 0 ? f.part : nullptr, (long)H, L.attn_norm, H, c.rms_eps, f.xb, t, s));
+        else TRY(add_rmsnorm_launch(f.x, parts, l > 0 ? 1 : 0, (long)H, L.attn_norm, f.q8, H, c.rms_eps, none, xn_f32, t, false, s, f.xb));
         TRY(prefill_dense(d, c.type_attn_qk, L.wqk, f.xn, f.qk, t, v_fused ? d->qk_rows + d->v_rows : d->qk_rows, H, s));
         if (!v_fused) TRY(prefill_dense(d, c.type_attn_v, L.wv, f.xn, f.v, t, d->v_rows, H, s));
         rope_seq_append_kernel<<<dim3(8, t), 256, 0, s>>>(f.qk, qk_stride, vbuf, v_stride, d->kcache + (size_t)l * cache_layer,
                                                             d->vcache + (size_t)l * cache_layer, nq, nkv, hd, 0, seq, c.ctx_len, c.rope_theta);
         QMM_CUDA_TRY(cudaGetLastError());
-        TRY(attn_prefill_launch(f.qk, f.qk + (size_t)nq * hd, vbuf, f.att, t, nq, nkv, hd, t, rsqrtf((float)hd), qk_stride, qk_stride, v_stride, ao, s));
+        // (from 64 positions on the O projection is a GEMM and reads the attention's output as bf16)
+        TRY(attn_prefill_launch(f.qk, f.qk + (size_t)nq * hd, vbuf, f.att, t, nq, nkv, hd, t, rsqrtf((float)hd), qk_stride, qk_stride, v_stride, ao, s,
+                                (t >= 64 && ao % 256 == 0) ? f.xb : nullptr));
         TRY(prefill_dense(d, c.type_attn_o, L.wo, f.att, f.part, t, H, ao, s));
-        TRY(add_rmsnorm_launch(f.x, parts, 1, (long)H, L.ffn_norm, f.q8, H, c.rms_eps, none, f.xn, t, false, s));
+        if (seq_norm) TRY(add_rmsnorm_bf16_launch(f.x, f.part, (long)H, L.ffn_norm, H, c.rms_eps, f.xb, t, s));
+        else TRY(add_rmsnorm_launch(f.x, parts, 1, (long)H, L.ffn_norm, f.q8, H, c.rms_eps, none, xn_f32, t, false, s, f.xb));
         TRY(prefill_dense(d, c.type_ffn_gate_up, L.wgu, f.xn, f.gu, t, 2 * ffn, H, s));
         {
             const long quads = (long)t * (ffn / 4);
-            act_mul_f32_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, s>>>((const float*)f.gu, f.act, ffn, c.act, quads);
+            const bool gemm = t >= 64 && ffn % 256 == 0;  // then the down projection reads bf16
+            act_mul_f32_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, s>>>((const float*)f.gu, gemm ? nullptr : f.act, gemm ? f.xb : nullptr, ffn,
+                                                                             c.act, quads);
             QMM_CUDA_TRY(cudaGetLastError());
         }
         TRY(prefill_dense(d, c.type_ffn_down, L.wdown, f.act, f.part, t, H, ffn, s));

@@ -100,7 +100,7 @@ struct PartPtrs {
 };
 __global__ void __launch_bounds__(1024) add_rmsnorm_q8_kernel(float* __restrict__ x, const PartPtrs parts, int n_parts, long part_stride,
                                       const float* __restrict__ gamma, uint8_t* __restrict__ xq, int hidden, float eps, const TpRecv rcv,
-                                      float* __restrict__ out_f32) {
+                                      float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_bf16) {
     __shared__ float red[32];
     __shared__ int give_up;
     pdl_release_dependents();
@@ -154,6 +154,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_q8_kernel(float* __restrict_
             if (exchange || n_parts > 0) xr[e] = v[i];
             const float nv = v[i] * inv * gm[i];
             if (out_f32) out_f32[(size_t)b * hidden + e] = nv;
+            if (out_bf16) out_bf16[(size_t)b * hidden + e] = __float2bfloat16_rn(nv);
             warp_store_q8_1(nv, qrow + (size_t)(e >> 5) * Q8_1_BYTES, lane);
         }
     }
@@ -171,7 +172,7 @@ constexpr int NORM_CL_PER_THREAD = 4;   // slice <= 1024 elements
 __global__ void __launch_bounds__(NORM_CL_THREADS) add_rmsnorm_q8_cluster_kernel(float* __restrict__ x, const PartPtrs parts, int n_parts,
                                                                                 long part_stride, const float* __restrict__ gamma,
                                                                                 uint8_t* __restrict__ xq, int hidden, float eps, const TpRecv rcv,
-                                                                                float* __restrict__ out_f32) {
+                                                                                float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_bf16) {
     __shared__ float red[32];
     __shared__ float cl_ss;     // this CTA's sum of squares, read by the other CTAs of the cluster
     __shared__ int cl_bad;      // this CTA gave up on a peer
@@ -262,14 +263,68 @@ __global__ void __launch_bounds__(NORM_CL_THREADS) add_rmsnorm_q8_cluster_kernel
             if (exchange || n_parts > 0) xr[e] = v[i];
             const float nv = v[i] * inv * gm[i];
             if (out_f32) out_f32[(size_t)b * hidden + e] = nv;
+            if (out_bf16) out_bf16[(size_t)b * hidden + e] = __float2bfloat16_rn(nv);
             warp_store_q8_1(nv, qrow + (size_t)(e >> 5) * Q8_1_BYTES, lane);
         }
     }
 }
 
+// The prompt-path form of the operator: many rows at once, the normalised row wanted only as bf16 (the input of a
+// GEMM).  One CTA of 256 threads per row, four consecutive elements per thread per pass (hidden a multiple of 4, at
+// most 8192), the row held in registers between the sum of squares and the scaling; no Q8_1 blocks, no exchange.
+constexpr int NORM_SEQ_THREADS = 256;
+constexpr int NORM_SEQ_PASSES = 8;
+__global__ void __launch_bounds__(NORM_SEQ_THREADS) add_rmsnorm_bf16_kernel(float* __restrict__ x, const float* __restrict__ part, long part_stride,
+                                                                            const float* __restrict__ gamma, int hidden, float eps,
+                                                                            __nv_bfloat16* __restrict__ out_bf16) {
+    __shared__ float red[32];
+    const int b = blockIdx.x, quads = hidden >> 2;
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)b * hidden);
+    const float4* pr = part ? reinterpret_cast<const float4*>(part + (size_t)b * part_stride) : nullptr;
+    float4 v[NORM_SEQ_PASSES];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_SEQ_PASSES; ++i) {
+        const int q = i * NORM_SEQ_THREADS + threadIdx.x;
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (q < quads) {
+            v[i] = xr[q];
+            if (pr) {
+                const float4 p = pr[q];
+                v[i].x += p.x, v[i].y += p.y, v[i].z += p.z, v[i].w += p.w;
+                xr[q] = v[i];
+            }
+            ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        }
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)hidden + eps);
+    uint2* orow = reinterpret_cast<uint2*>(out_bf16 + (size_t)b * hidden);
+#pragma unroll
+    for (int i = 0; i < NORM_SEQ_PASSES; ++i) {
+        const int q = i * NORM_SEQ_THREADS + threadIdx.x;
+        if (q < quads) {
+            const float4 g = gamma ? reinterpret_cast<const float4*>(gamma)[q] : make_float4(1.f, 1.f, 1.f, 1.f);
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v[i].x * inv * g.x, v[i].y * inv * g.y);
+            const __nv_bfloat162 hi = __floats2bfloat162_rn(v[i].z * inv * g.z, v[i].w * inv * g.w);
+            orow[q] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+        }
+    }
+}
+inline bool add_rmsnorm_bf16_fits(int hidden, long part_stride) {
+    return hidden % 4 == 0 && part_stride % 4 == 0 && hidden <= 4 * NORM_SEQ_THREADS * NORM_SEQ_PASSES;
+}
+inline int add_rmsnorm_bf16_launch(float* x, const float* part, long part_stride, const float* gamma, int hidden, float eps, __nv_bfloat16* out_bf16,
+                                   int rows, cudaStream_t stream) {
+    add_rmsnorm_bf16_kernel<<<rows, NORM_SEQ_THREADS, 0, stream>>>(x, part, part_stride, gamma, hidden, eps, out_bf16);
+    QMM_CUDA_TRY(cudaGetLastError());
+    return QMM_OK;
+}
+
 // Launches the residual + norm + Q8_1 operator: the cluster form when the row splits evenly, else one CTA per row.
 inline int add_rmsnorm_launch(float* x, const PartPtrs& parts, int n_parts, long part_stride, const float* gamma, uint8_t* xq, int hidden,
-                              float eps, const TpRecv& rcv, float* out_f32, int rows, bool pdl, cudaStream_t stream) {
+                              float eps, const TpRecv& rcv, float* out_f32, int rows, bool pdl, cudaStream_t stream,
+                              __nv_bfloat16* out_bf16 = nullptr) {
     cudaLaunchConfig_t cfg = {};
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -292,7 +347,7 @@ inline int add_rmsnorm_launch(float* x, const PartPtrs& parts, int n_parts, long
         cfg.blockDim = dim3(NORM_CL_THREADS);
         cfg.attrs = attr;
         cfg.numAttrs = na;
-        QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, add_rmsnorm_q8_cluster_kernel, x, parts, n_parts, part_stride, gamma, xq, hidden, eps, rcv, out_f32));
+        QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, add_rmsnorm_q8_cluster_kernel, x, parts, n_parts, part_stride, gamma, xq, hidden, eps, rcv, out_f32, out_bf16));
         return QMM_OK;
     }
     const int passes = (hidden + 1023) / 1024;
@@ -301,7 +356,7 @@ inline int add_rmsnorm_launch(float* x, const PartPtrs& parts, int n_parts, long
     cfg.blockDim = dim3(threads);
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, add_rmsnorm_q8_kernel, x, parts, n_parts, part_stride, gamma, xq, hidden, eps, rcv, out_f32));
+    QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, add_rmsnorm_q8_kernel, x, parts, n_parts, part_stride, gamma, xq, hidden, eps, rcv, out_f32, out_bf16));
     return QMM_OK;
 }
 
@@ -759,7 +814,8 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
 
 // gated activation on the fused [gate | up] projection output + Q8_1: act(gate) * up -> xq (ffn per row)
 // out = act(gate) * up for many rows (the prompt path: only the f32 values are needed), four elements per thread
-__global__ void act_mul_f32_kernel(const float* __restrict__ gate_up, float* __restrict__ out, int ffn, int act, long quads) {
+__global__ void act_mul_f32_kernel(const float* __restrict__ gate_up, float* __restrict__ out, __nv_bfloat16* __restrict__ out_bf16, int ffn, int act,
+                                   long quads) {
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= quads) return;
     const int per_row = ffn / 4;
@@ -772,7 +828,11 @@ __global__ void act_mul_f32_kernel(const float* __restrict__ gate_up, float* __r
     r.y = (act == 0 ? gelu_tanh_f(g.y) : g.y / (1.0f + __expf(-g.y))) * u.y;
     r.z = (act == 0 ? gelu_tanh_f(g.z) : g.z / (1.0f + __expf(-g.z))) * u.z;
     r.w = (act == 0 ? gelu_tanh_f(g.w) : g.w / (1.0f + __expf(-g.w))) * u.w;
-    *reinterpret_cast<float4*>(out + (size_t)b * ffn + c) = r;
+    if (out) *reinterpret_cast<float4*>(out + (size_t)b * ffn + c) = r;
+    if (out_bf16) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(r.x, r.y), hi = __floats2bfloat162_rn(r.z, r.w);
+        *reinterpret_cast<uint2*>(out_bf16 + (size_t)b * ffn + c) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    }
 }
 
 __global__ void act_mul_q8_kernel(const float* __restrict__ gate_up, uint8_t* __restrict__ xq, int ffn, int act, float* __restrict__ out_f32) {
