@@ -196,6 +196,78 @@ __global__ void dequantize_kernel(const uint8_t* __restrict__ w, OUT* __restrict
         out[idx] = __float2bfloat16_rn(v);
 }
 
+// ---- the same values, eight consecutive elements per thread: 16-bit loads of the packed bytes (a block is only
+// 2-byte aligned in general), one 16- or 32-byte store.  Every element goes through the arithmetic of dequant_elem.
+template <int TYPE>
+__device__ __forceinline__ void dequant8(const uint8_t* blk, int e0, float (&v)[8]);
+template <>
+__device__ __forceinline__ void dequant8<QMM_TYPE_Q8_0>(const uint8_t* blk, int e0, float (&v)[8]) {
+    const float d = f16_bits_to_f32(ld_u16(blk));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const unsigned w = ld_u16(blk + 2 + e0 + 2 * i);
+        v[2 * i] = __fmul_rn(d, (float)(int8_t)(w & 0xFFu));
+        v[2 * i + 1] = __fmul_rn(d, (float)(int8_t)(w >> 8));
+    }
+}
+template <>
+__device__ __forceinline__ void dequant8<QMM_TYPE_Q4_K>(const uint8_t* blk, int e0, float (&v)[8]) {
+    const int j = e0 >> 5, l = e0 & 31;
+    const uint8_t* s = blk + 4;
+    int sc, m;
+    if (j < 4) {
+        sc = s[j] & 63;
+        m = s[j + 4] & 63;
+    } else {
+        sc = (s[j + 4] & 15) | ((s[j - 4] >> 6) << 4);
+        m = (s[j + 4] >> 4) | ((s[j] >> 6) << 4);
+    }
+    const float ds = __fmul_rn(f16_bits_to_f32(ld_u16(blk)), (float)sc), mm = __fmul_rn(f16_bits_to_f32(ld_u16(blk + 2)), (float)m);
+    const int sh = (j & 1) ? 4 : 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const unsigned w = ld_u16(blk + 16 + 32 * (j >> 1) + l + 2 * i);
+        v[2 * i] = __fsub_rn(__fmul_rn(ds, (float)((w >> sh) & 15u)), mm);
+        v[2 * i + 1] = __fsub_rn(__fmul_rn(ds, (float)((w >> (8 + sh)) & 15u)), mm);
+    }
+}
+template <>
+__device__ __forceinline__ void dequant8<QMM_TYPE_Q6_K>(const uint8_t* blk, int e0, float (&v)[8]) {
+    const int h = e0 >> 7, r = e0 & 127, t = r >> 5, l = r & 31;
+    const float ds = __fmul_rn(f16_bits_to_f32(ld_u16(blk + 208)), (float)(int8_t)blk[192 + (e0 >> 4)]);
+    const int lsh = (t < 2) ? 0 : 4, hsh = 2 * t;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const unsigned wl = ld_u16(blk + 64 * h + l + 32 * (t & 1) + 2 * i), wh = ld_u16(blk + 128 + 32 * h + l + 2 * i);
+        const int q0 = (int)(((wl >> lsh) & 15u) | (((wh >> hsh) & 3u) << 4)) - 32;
+        const int q1 = (int)(((wl >> (8 + lsh)) & 15u) | (((wh >> (8 + hsh)) & 3u) << 4)) - 32;
+        v[2 * i] = __fmul_rn(ds, (float)q0);
+        v[2 * i + 1] = __fmul_rn(ds, (float)q1);
+    }
+}
+template <int TYPE, typename OUT>
+__global__ void __launch_bounds__(256) dequantize8_kernel(const uint8_t* __restrict__ w, OUT* __restrict__ out, long n_octets) {
+    using F = Fmt<TYPE, 1>;
+    const long o = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (o >= n_octets) return;
+    const long idx = o * 8, blk = idx / F::BLOCK_ELEMS;
+    float v[8];
+    dequant8<TYPE>(w + blk * F::BLOCK_BYTES, (int)(idx - blk * F::BLOCK_ELEMS), v);
+    if constexpr (sizeof(OUT) == 4) {
+        float4* d = reinterpret_cast<float4*>(out + idx);
+        d[0] = make_float4(v[0], v[1], v[2], v[3]);
+        d[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+        uint32_t p[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            p[i] = *reinterpret_cast<const uint32_t*>(&b);
+        }
+        *reinterpret_cast<uint4*>(out + idx) = make_uint4(p[0], p[1], p[2], p[3]);
+    }
+}
+
 // ------------------------------------------------------------------- host side
 int quantize_q8_1_launch(const float* x, void* xq, int m, int k, cudaStream_t stream) {
     if (!x || !xq) return QMM_ERR_NULL;
@@ -250,8 +322,20 @@ static int dequantize_launch_t(int type, const void* w, OUT* out, long n_elems, 
     if (n_elems <= 0 || n_elems % be != 0) return QMM_ERR_SHAPE;
     if (reinterpret_cast<uintptr_t>(w) % 2 != 0) return QMM_ERR_ALIGN;
     const int threads = 256;
-    const unsigned grid = (unsigned)((n_elems + threads - 1) / threads);
     const uint8_t* wb = static_cast<const uint8_t*>(w);
+    if (reinterpret_cast<uintptr_t>(out) % 16 == 0) {  // eight elements per thread, whole 16-byte stores
+        const long n_octets = n_elems / 8;
+        const unsigned grid8 = (unsigned)((n_octets + threads - 1) / threads);
+        switch (type) {
+        case QMM_TYPE_Q8_0: dequantize8_kernel<QMM_TYPE_Q8_0, OUT><<<grid8, threads, 0, stream>>>(wb, out, n_octets); break;
+        case QMM_TYPE_Q4_K: dequantize8_kernel<QMM_TYPE_Q4_K, OUT><<<grid8, threads, 0, stream>>>(wb, out, n_octets); break;
+        case QMM_TYPE_Q6_K: dequantize8_kernel<QMM_TYPE_Q6_K, OUT><<<grid8, threads, 0, stream>>>(wb, out, n_octets); break;
+        default: return QMM_ERR_TYPE;
+        }
+        QMM_CUDA_TRY(cudaGetLastError());
+        return QMM_OK;
+    }
+    const unsigned grid = (unsigned)((n_elems + threads - 1) / threads);
     switch (type) {
     case QMM_TYPE_Q8_0: dequantize_kernel<QMM_TYPE_Q8_0, OUT><<<grid, threads, 0, stream>>>(wb, out, n_elems); break;
     case QMM_TYPE_Q4_K: dequantize_kernel<QMM_TYPE_Q4_K, OUT><<<grid, threads, 0, stream>>>(wb, out, n_elems); break;

@@ -117,6 +117,20 @@ def test_dequantize_bit_exact(ops, qtype, maker):
     assert np.array_equal(got16, oracle.dequantize_bf16(qtype, w, k).reshape(-1))
 
 
+@pytest.mark.parametrize("qtype", TYPES)
+def test_dequantize_into_an_unaligned_window(ops, qtype):
+    """An output that does not start on a 16-byte line takes the one-element-per-thread kernel: the same bits."""
+    n, k = 8, 1024
+    w = random_byte_weights(qtype, n, k, 321)
+    for dtype, want in ((torch.float32, oracle.dequantize(qtype, w, k).reshape(-1).view(np.uint32)),
+                        (torch.bfloat16, oracle.dequantize_bf16(qtype, w, k).reshape(-1))):
+        buf = torch.zeros(n * k + 1, dtype=dtype, device="cuda")
+        ops.gpu_dequantize_into(qtype, dev(w), buf[1:], n * k)
+        got = buf[1:].contiguous().view(torch.int32 if dtype == torch.float32 else torch.int16).cpu().numpy()
+        assert np.array_equal(got.view(want.dtype), want)
+        assert float(buf[0]) == 0.0
+
+
 # ------------------------------------------------------------------ integer block sums
 @pytest.mark.parametrize("qtype", TYPES)
 @pytest.mark.parametrize("maker", [seeded_weights, random_byte_weights])
