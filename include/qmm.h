@@ -294,6 +294,11 @@ int launch_scale_f32(float* x, float scalar, long n, void* stream);
  * the probabilities rounded to f16 (about 1e-3 relative); the t x t scores are never stored. */
 int launch_attn_prefill(const float* q, const float* k, const float* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim,
                         int prefix, float kq_scale, void* stream);
+/* The same with k and v already f16 (2 bytes per element, row-major (t, n_kv_heads*head_dim), 16-byte aligned, n_kv_heads*head_dim
+ * a multiple of 8): the rows of a KV cache.  The values the f32 form would round k and v to are read as they are, so both forms
+ * give the same bits for k16 = f16(k), v16 = f16(v); the tiles go to shared memory with cp.async, half the traffic, no conversion. */
+int launch_attn_prefill_f16kv(const float* q, const void* k16, const void* v16, float* out, int t, int n_q_heads, int n_kv_heads,
+                              int head_dim, int prefix, float kq_scale, void* stream);
 
 /* ---- quantized dense layer: y(m,n) = act( x(m,k) . w(n,k)^T + bias(n) ), x and y f32, w packed blocks of
  * `type`.  The counterpart of LayerKind::Dense in the upstream's forward pass (recipe-infer/src/forward.rs:

@@ -9,6 +9,9 @@
 // f16, about 1e-3 relative, everything else is f32.  The t x t score matrix is never stored.  When two query heads
 // share a kv head the CTA takes both (eight warps), so a tile of keys and values is fetched and converted once for
 // the two: the kernel is bound by that traffic (f32 k and v from L2 for every tile of queries), not by the mma.
+// KV16: k and v are already f16 (the rows of a KV cache, strides in halves): their tiles go from global to shared
+// memory with cp.async, the next tile's copy in flight under the current tile's arithmetic (two stages), no
+// conversion and half the traffic.
 #include "qmm_formats.cuh"
 
 namespace qmm {
@@ -20,9 +23,17 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
 // HD: head dimension (a multiple of 16 up to 256).  GH: query heads of one kv head per CTA (1 or 2), four warps each.
-template <int HD, int GH>
-__global__ void __launch_bounds__(128 * GH) attn_prefill_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+template <int HD, int GH, bool KV16>
+__global__ void __launch_bounds__(128 * GH, (KV16 && HD <= 128) ? 2 : 1) attn_prefill_kernel(const float* __restrict__ q, const void* __restrict__ k_, const void* __restrict__ v_,
                                                                   float* __restrict__ out, int t, int nqh, int nkv, int prefix, float kq_scale,
                                                                   long q_stride, long k_stride, long v_stride, long o_stride,
                                                                   __nv_bfloat16* __restrict__ out_bf16) {
@@ -30,11 +41,20 @@ __global__ void __launch_bounds__(128 * GH) attn_prefill_kernel(const float* __r
     constexpr int PITCH = HD + 8;  // halves: rows 16 bytes apart modulo 128, so the 8 rows of an ldmatrix hit all banks
     constexpr int PF_THREADS = 128 * GH;
     __half* qs_all = reinterpret_cast<__half*>(pf_raw);  // GH query tiles
-    __half* ks = qs_all + GH * PF_BQ * PITCH;
-    __half* vs = ks + PF_BK * PITCH;
+    constexpr int KV_STAGES = KV16 ? 2 : 1;
+    __half* ks_all = qs_all + GH * PF_BQ * PITCH;            // KV_STAGES key tiles, then as many value tiles
+    __half* vs_all = ks_all + KV_STAGES * PF_BK * PITCH;
+    const float* k = static_cast<const float*>(k_);
+    const float* v = static_cast<const float*>(v_);
+    const __half* k16 = static_cast<const __half*>(k_);
+    const __half* v16 = static_cast<const __half*>(v_);
     const int tid = threadIdx.x, wall = tid >> 5, lane = tid & 31, qr = lane >> 2, pq = lane & 3;
     const int hl = wall >> 2, warp = wall & 3;  // head within the CTA, 16-row block of the query tile
-    const int qt = blockIdx.x, h = blockIdx.y * GH + hl, kvh = (blockIdx.y * GH) / (nqh / nkv);
+    // Causal tiles of queries cost in proportion to their position, and CTAs start in grid order (x fastest): the grid is
+    // (head group, tile of queries) with the LAST tile of queries first, so the long CTAs start first and the short ones
+    // fill the end of the run (started in increasing order the longest CTAs would begin when most of the GPU is idle).
+    const int hg = blockIdx.x, qt = gridDim.y - 1 - blockIdx.y;
+    const int h = hg * GH + hl, kvh = (hg * GH) / (nqh / nkv);
     __half* qs = qs_all + hl * PF_BQ * PITCH;
     const size_t qd = (size_t)q_stride, kd = (size_t)k_stride, vd = (size_t)v_stride, od = (size_t)o_stride;  // floats between rows
     const int q0 = qt * PF_BQ;
@@ -44,7 +64,7 @@ __global__ void __launch_bounds__(128 * GH) attn_prefill_kernel(const float* __r
         const int hh = i / (PF_BQ * (HD / 4)), j = i - hh * (PF_BQ * (HD / 4));
         const int r = j / (HD / 4), c = (j - r * (HD / 4)) * 4;
         float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (q0 + r < t) x = *reinterpret_cast<const float4*>(q + (size_t)(q0 + r) * qd + (size_t)(blockIdx.y * GH + hh) * HD + c);
+        if (q0 + r < t) x = *reinterpret_cast<const float4*>(q + (size_t)(q0 + r) * qd + (size_t)(hg * GH + hh) * HD + c);
         *reinterpret_cast<uint2*>(qs_all + (hh * PF_BQ + r) * PITCH + c) = make_uint2(pack_h2(x.x * kq_scale, x.y * kq_scale), pack_h2(x.z * kq_scale, x.w * kq_scale));
     }
 
@@ -62,7 +82,7 @@ __global__ void __launch_bounds__(128 * GH) attn_prefill_kernel(const float* __r
     // its registers (KV_IT <= 8) the NEXT tile's loads are issued before the current tile's arithmetic, so their round
     // trip to L2 hides under the mma; otherwise a tile is loaded in chunks of eight pieces right before its use.
     constexpr int KV_IT = PF_BK * (HD / 4) / PF_THREADS;  // (whole: HD is a multiple of 32)
-    constexpr bool PREFETCH = KV_IT <= 8;
+    constexpr bool PREFETCH = !KV16 && KV_IT <= 8;
     constexpr int KV_CH = KV_IT < 8 ? KV_IT : 8;
     float4 ka[KV_CH], va[KV_CH];
     auto load_kv = [&](int kt, int base) {
@@ -81,55 +101,91 @@ __global__ void __launch_bounds__(128 * GH) attn_prefill_kernel(const float* __r
 #pragma unroll
         for (int it = 0; it < KV_CH; ++it) {
             const int i = tid + (base + it) * PF_THREADS, r = i / (HD / 4), c = (i - r * (HD / 4)) * 4;
-            *reinterpret_cast<uint2*>(ks + r * PITCH + c) = make_uint2(pack_h2(ka[it].x, ka[it].y), pack_h2(ka[it].z, ka[it].w));
-            *reinterpret_cast<uint2*>(vs + r * PITCH + c) = make_uint2(pack_h2(va[it].x, va[it].y), pack_h2(va[it].z, va[it].w));
+            *reinterpret_cast<uint2*>(ks_all + r * PITCH + c) = make_uint2(pack_h2(ka[it].x, ka[it].y), pack_h2(ka[it].z, ka[it].w));
+            *reinterpret_cast<uint2*>(vs_all + r * PITCH + c) = make_uint2(pack_h2(va[it].x, va[it].y), pack_h2(va[it].z, va[it].w));
         }
     };
-    if (PREFETCH && kt_end > 0) load_kv(0, 0);
-    for (int kt = 0; kt < kt_end; ++kt) {
-        __syncthreads();  // the previous tile is consumed (first pass: the query tile is written)
-        if constexpr (PREFETCH) {
-            store_kv(0);
-        } else {
-#pragma unroll 1
-            for (int base = 0; base < KV_IT; base += KV_CH) {
-                load_kv(kt, base);
-                store_kv(base);
+    // KV16: 16-byte pieces (8 halves) of a key and a value tile straight into stage `stage`; rows past t as zeros
+    auto copy_kv16 = [&](int kt, int stage) {
+        __half* kd_s = ks_all + stage * PF_BK * PITCH;
+        __half* vd_s = vs_all + stage * PF_BK * PITCH;
+        for (int i = tid; i < PF_BK * (HD / 8); i += PF_THREADS) {
+            const int r = i / (HD / 8), c = (i - r * (HD / 8)) * 8;
+            const int sp = kt * PF_BK + r;
+            if (sp < t) {
+                cp_async_16(smem_u32(kd_s + r * PITCH + c), k16 + (size_t)sp * kd + (size_t)kvh * HD + c);
+                cp_async_16(smem_u32(vd_s + r * PITCH + c), v16 + (size_t)sp * vd + (size_t)kvh * HD + c);
+            } else {
+                *reinterpret_cast<uint4*>(kd_s + r * PITCH + c) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(vd_s + r * PITCH + c) = make_uint4(0u, 0u, 0u, 0u);
             }
         }
-        __syncthreads();
-        if (PREFETCH && kt + 1 < kt_end) load_kv(kt + 1, 0);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (PREFETCH && kt_end > 0) load_kv(0, 0);
+    if (KV16 && kt_end > 0) copy_kv16(0, 0);
+    for (int kt = 0; kt < kt_end; ++kt) {
+        if constexpr (KV16) {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's pieces of tile kt
+            __syncthreads();  // everyone's pieces; and the tile before is consumed (first pass: the query tile is written)
+            if (kt + 1 < kt_end) copy_kv16(kt + 1, (kt + 1) & 1);
+        } else {
+            __syncthreads();  // the previous tile is consumed (first pass: the query tile is written)
+            if constexpr (PREFETCH) {
+                store_kv(0);
+            } else {
+#pragma unroll 1
+                for (int base = 0; base < KV_IT; base += KV_CH) {
+                    load_kv(kt, base);
+                    store_kv(base);
+                }
+            }
+            __syncthreads();
+            if (PREFETCH && kt + 1 < kt_end) load_kv(kt + 1, 0);
+        }
+        const __half* ks = ks_all + (KV16 ? (kt & 1) : 0) * PF_BK * PITCH;
+        const __half* vs = vs_all + (KV16 ? (kt & 1) : 0) * PF_BK * PITCH;
 
         // scores of the warp's 16 query rows against the 64 keys: 8 n-tiles of 8 keys
         float s[PF_BK / 8][4];
 #pragma unroll
         for (int n = 0; n < PF_BK / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
-        const __half* qa = qs + (16 * warp + qr) * PITCH + 2 * pq;
+        // fragments by ldmatrix.x4: lane l addresses row (l & 7) of 8x8 matrix l >> 3.  A (queries): matrices = (rows 0-7 |
+        // 8-15) x (columns kk.. | kk+8..); B (keys): the two column halves of key rows 8n..8n+7, then of 8n+8..8n+15
+        const uint32_t qa = smem_u32(qs + (16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8) * PITCH + ((lane >> 4) & 1) * 8);
+        const uint32_t kb = smem_u32(ks + ((lane & 7) + ((lane >> 4) & 1) * 8) * PITCH + ((lane >> 3) & 1) * 8);
 #pragma unroll
         for (int kk = 0; kk < HD; kk += 16) {
-            const uint32_t a0 = *reinterpret_cast<const uint32_t*>(qa + kk), a1 = *reinterpret_cast<const uint32_t*>(qa + 8 * PITCH + kk);
-            const uint32_t a2 = *reinterpret_cast<const uint32_t*>(qa + kk + 8), a3 = *reinterpret_cast<const uint32_t*>(qa + 8 * PITCH + kk + 8);
+            uint32_t a0, a1, a2, a3;
+            ldmatrix_x4(a0, a1, a2, a3, qa + kk * 2);
 #pragma unroll
-            for (int n = 0; n < PF_BK / 8; ++n) {
-                const __half* kb = ks + (8 * n + qr) * PITCH + 2 * pq + kk;
-                mma_f16_k16(s[n], a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(kb), *reinterpret_cast<const uint32_t*>(kb + 8));
+            for (int n = 0; n < PF_BK / 8; n += 2) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(b0, b1, b2, b3, kb + (8 * n * PITCH + kk) * 2);
+                mma_f16_k16(s[n], a0, a1, a2, a3, b0, b1);
+                mma_f16_k16(s[n + 1], a0, a1, a2, a3, b2, b3);
             }
         }
         // mask (the upstream writes -1e30 into a masked score; a key past the end does not exist), running softmax
-        float mx0 = -INFINITY, mx1 = -INFINITY;
+        // (only a tile that reaches past the end or past the diagonal of this warp's first row has anything to mask)
+        const int w0 = q0 + 16 * warp;
+        if (kt * PF_BK + PF_BK > t || (w0 < prefix && kt * PF_BK + PF_BK - 1 > w0)) {
 #pragma unroll
-        for (int n = 0; n < PF_BK / 8; ++n) {
+            for (int n = 0; n < PF_BK / 8; ++n) {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int sp = kt * PF_BK + 8 * n + 2 * pq + e;
-                if (sp >= t) s[n][e] = -INFINITY, s[n][2 + e] = -INFINITY;
-                else {
-                    if (p0 < prefix && sp > p0) s[n][e] = -1e30f;
-                    if (p1 < prefix && sp > p1) s[n][2 + e] = -1e30f;
+                for (int e = 0; e < 2; ++e) {
+                    const int sp = kt * PF_BK + 8 * n + 2 * pq + e;
+                    if (sp >= t) s[n][e] = -INFINITY, s[n][2 + e] = -INFINITY;
+                    else {
+                        if (p0 < prefix && sp > p0) s[n][e] = -1e30f;
+                        if (p1 < prefix && sp > p1) s[n][2 + e] = -1e30f;
+                    }
                 }
-                mx0 = fmaxf(mx0, s[n][e]), mx1 = fmaxf(mx1, s[n][2 + e]);
             }
         }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < PF_BK / 8; ++n) mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1])), mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)), mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)), mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);  // finite: every tile holds at least one existing key
@@ -153,11 +209,12 @@ __global__ void __launch_bounds__(128 * GH) attn_prefill_kernel(const float* __r
 #pragma unroll
         for (int j = 0; j < PF_BK / 16; ++j) {
 #pragma unroll
-            for (int n = 0; n < HD / 8; ++n) {
-                const uint32_t addr = smem_u32(vs + (16 * j + (lane & 15)) * PITCH + 8 * n);
-                uint32_t b0, b1;
-                asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+            for (int n = 0; n < HD / 8; n += 2) {  // (transposed: key rows 16j..16j+7 | +8..15 of columns 8n.., then of 8n+8..)
+                const uint32_t addr = smem_u32(vs + (16 * j + (lane & 15)) * PITCH + 8 * n + ((lane >> 4) & 1) * 8);
+                uint32_t b0, b1, b2, b3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(addr));
                 mma_f16_k16(o[n], pa[j][0], pa[j][1], pa[j][2], pa[j][3], b0, b1);
+                mma_f16_k16(o[n + 1], pa[j][0], pa[j][1], pa[j][2], pa[j][3], b2, b3);
             }
         }
     }
@@ -174,10 +231,10 @@ __global__ void __launch_bounds__(128 * GH) attn_prefill_kernel(const float* __r
     }
 }
 
-template <int HD, int GH>
-static int attn_prefill_inst(const float* q, const float* k, const float* v, float* out, int t, int nqh, int nkv, int prefix, float kq_scale,
+template <int HD, int GH, bool KV16>
+static int attn_prefill_inst(const float* q, const void* k, const void* v, float* out, int t, int nqh, int nkv, int prefix, float kq_scale,
                              long q_stride, long k_stride, long v_stride, long o_stride, __nv_bfloat16* out_bf16, cudaStream_t s) {
-    const size_t smem = (size_t)(GH * PF_BQ + 2 * PF_BK) * (HD + 8) * sizeof(__half);
+    const size_t smem = (size_t)(GH * PF_BQ + (KV16 ? 4 : 2) * PF_BK) * (HD + 8) * sizeof(__half);
     static std::mutex mu;
     static bool configured[64] = {};
     int dev = 0;
@@ -185,11 +242,11 @@ static int attn_prefill_inst(const float* q, const float* k, const float* v, flo
     if (smem > 48 * 1024) {
         std::lock_guard<std::mutex> g(mu);
         if (dev < 0 || dev >= 64 || !configured[dev]) {
-            QMM_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_kernel<HD, GH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            QMM_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_kernel<HD, GH, KV16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             if (dev >= 0 && dev < 64) configured[dev] = true;
         }
     }
-    attn_prefill_kernel<HD, GH><<<dim3((t + PF_BQ - 1) / PF_BQ, nqh / GH), 128 * GH, smem, s>>>(q, k, v, out, t, nqh, nkv, prefix, kq_scale, q_stride, k_stride,
+    attn_prefill_kernel<HD, GH, KV16><<<dim3(nqh / GH, (t + PF_BQ - 1) / PF_BQ), 128 * GH, smem, s>>>(q, k, v, out, t, nqh, nkv, prefix, kq_scale, q_stride, k_stride,
                                                                                                  v_stride, o_stride, out_bf16);
     QMM_CUDA_TRY(cudaGetLastError());
     return QMM_OK;
@@ -197,22 +254,26 @@ static int attn_prefill_inst(const float* q, const float* k, const float* v, flo
 
 // q, k, v, out with their own row strides (floats; multiples of 4): the projections of a layer write [q | k] and v
 // side by side
-int attn_prefill_launch(const float* q, const float* k, const float* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim, int prefix,
-                        float kq_scale, long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s, __nv_bfloat16* out_bf16) {
+// (kv_f16: k and v are f16 rows, their strides in halves and multiples of 8)
+int attn_prefill_launch(const float* q, const void* k, const void* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim, int prefix,
+                        float kq_scale, long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s, __nv_bfloat16* out_bf16, bool kv_f16) {
     if (!q || !k || !v || (!out && !out_bf16)) return QMM_ERR_NULL;
     if (t <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads != 0 || prefix < 0) return QMM_ERR_SHAPE;
     if (q_stride < (long)n_q_heads * head_dim || o_stride < (long)n_q_heads * head_dim || k_stride < (long)n_kv_heads * head_dim ||
-        v_stride < (long)n_kv_heads * head_dim || q_stride % 4 || k_stride % 4 || v_stride % 4 || o_stride % 2)
+        v_stride < (long)n_kv_heads * head_dim || q_stride % 4 || k_stride % (kv_f16 ? 8 : 4) || v_stride % (kv_f16 ? 8 : 4) || o_stride % 2)
         return QMM_ERR_SHAPE;
-    if (out == q || out == k || out == v) return QMM_ERR_SHAPE;  // every CTA reads the whole sequence (as upstream)
+    if (out == q || static_cast<const void*>(out) == k || static_cast<const void*>(out) == v) return QMM_ERR_SHAPE;  // every CTA reads the whole sequence (as upstream)
     if (reinterpret_cast<uintptr_t>(q) % 16 || reinterpret_cast<uintptr_t>(k) % 16 || reinterpret_cast<uintptr_t>(v) % 16 ||
         reinterpret_cast<uintptr_t>(out) % 8 || reinterpret_cast<uintptr_t>(out_bf16) % 4)
         return QMM_ERR_ALIGN;
     const bool two = (n_q_heads / n_kv_heads) % 2 == 0;  // two query heads of a kv head per CTA
 #define QMM_PF_CASE(HD_)                                                                                                                              \
     case HD_:                                                                                                                                          \
-        return two ? attn_prefill_inst<HD_, 2>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, s)   \
-                   : attn_prefill_inst<HD_, 1>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, s)
+        if (kv_f16)                                                                                                                                    \
+            return two ? attn_prefill_inst<HD_, 2, true>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, s) \
+                       : attn_prefill_inst<HD_, 1, true>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, s); \
+        return two ? attn_prefill_inst<HD_, 2, false>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, s)   \
+                   : attn_prefill_inst<HD_, 1, false>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, s)
     switch (head_dim) {
         QMM_PF_CASE(32);
         QMM_PF_CASE(64);
@@ -232,5 +293,12 @@ extern "C" int launch_attn_prefill(const float* q, const float* k, const float* 
                                    int prefix, float kq_scale, void* stream) {
     const long qd = (long)n_q_heads * head_dim, kd = (long)n_kv_heads * head_dim;
     if (!out) return QMM_ERR_NULL;
-    return attn_prefill_launch(q, k, v, out, t, n_q_heads, n_kv_heads, head_dim, prefix, kq_scale, qd, kd, kd, qd, as_stream(stream), nullptr);
+    return attn_prefill_launch(q, k, v, out, t, n_q_heads, n_kv_heads, head_dim, prefix, kq_scale, qd, kd, kd, qd, as_stream(stream), nullptr, false);
+}
+
+extern "C" int launch_attn_prefill_f16kv(const float* q, const void* k, const void* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim,
+                                         int prefix, float kq_scale, void* stream) {
+    const long qd = (long)n_q_heads * head_dim, kd = (long)n_kv_heads * head_dim;
+    if (!out) return QMM_ERR_NULL;
+    return attn_prefill_launch(q, k, v, out, t, n_q_heads, n_kv_heads, head_dim, prefix, kq_scale, qd, kd, kd, qd, as_stream(stream), nullptr, true);
 }

@@ -22,8 +22,8 @@ int qmatvec_launch_push(int type, const void* w, const void* xq, float* y, long 
                         const TpPush* push, cudaStream_t stream);
 int gemm_bt_bf16_launch(const void* a, const void* b, void* y, float* yf, int m, int n, int k, cudaStream_t stream);
 int dequantize_bf16_launch(int type, const void* w, void* out, long n_elems, cudaStream_t stream);
-int attn_prefill_launch(const float* q, const float* k, const float* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim, int prefix,
-                        float kq_scale, long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s, __nv_bfloat16* out_bf16);
+int attn_prefill_launch(const float* q, const void* k, const void* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim, int prefix,
+                        float kq_scale, long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s, __nv_bfloat16* out_bf16, bool kv_f16);
 int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, int n, int k, cudaStream_t stream);
 int qmatvec_launch_pitched(int type, const void* w, long row_pitch, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                            const TpPush* push, cudaStream_t stream);
@@ -700,8 +700,11 @@ static int prefill(Decoder* d, const int* tokens, int t, int seq, int* next_toke
                                                             d->vcache + (size_t)l * cache_layer, nq, nkv, hd, 0, seq, c.ctx_len, c.rope_theta);
         QMM_CUDA_TRY(cudaGetLastError());
         // (from 64 positions on the O projection is a GEMM and reads the attention's output as bf16)
-        TRY(attn_prefill_launch(f.qk, f.qk + (size_t)nq * hd, vbuf, f.att, t, nq, nkv, hd, t, rsqrtf((float)hd), qk_stride, qk_stride, v_stride, ao, s,
-                                (t >= 64 && ao % 256 == 0) ? f.xb : nullptr));
+        {   // keys and values: the f16 rows that the kernel above has just appended to the cache (row = position)
+            const size_t seq_off = (size_t)l * cache_layer + (size_t)seq * c.ctx_len * nkv * hd;
+            TRY(attn_prefill_launch(f.qk, d->kcache + seq_off, d->vcache + seq_off, f.att, t, nq, nkv, hd, t, rsqrtf((float)hd), qk_stride,
+                                    (long)nkv * hd, (long)nkv * hd, ao, s, (t >= 64 && ao % 256 == 0) ? f.xb : nullptr, (nkv * hd) % 8 == 0));
+        }
         TRY(prefill_dense(d, c.type_attn_o, L.wo, f.att, f.part, t, H, ao, s));
         if (seq_norm) TRY(add_rmsnorm_bf16_launch(f.x, f.part, (long)H, L.ffn_norm, H, c.rms_eps, f.xb, t, s));
         else TRY(add_rmsnorm_launch(f.x, parts, 1, (long)H, L.ffn_norm, f.q8, H, c.rms_eps, none, xn_f32, t, false, s, f.xb));

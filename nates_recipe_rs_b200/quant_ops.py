@@ -323,12 +323,16 @@ def gpu_gemm_bt_bf16_into(a, b, out, m, n, k):
 
 def gpu_gqa_attn_into(q, k, v, out, t, nqh, nkv, hd, prefix, kq_scale=1.0):
     """Attention over a whole sequence into a caller-owned out (t, nqh*hd), the upstream's gpu_gqa_attn_into
-    (gpu-core/src/infer_ops.rs:160-189): positions below `prefix` causal, the others bidirectional.  f32."""
+    (gpu-core/src/infer_ops.rs:160-189): positions below `prefix` causal, the others bidirectional.  q and out f32;
+    k and v f32, or both float16 (the rows of a KV cache)."""
+    if k.dtype != v.dtype or k.dtype not in (torch.float32, torch.float16):
+        raise TypeError("k and v must both be float32 or both float16")
     _need(q, t * nqh * hd * 4, "q")
-    _need(k, t * nkv * hd * 4, "k")
-    _need(v, t * nkv * hd * 4, "v")
+    _need(k, t * nkv * hd * k.element_size(), "k")
+    _need(v, t * nkv * hd * v.element_size(), "v")
     _need(out, t * nqh * hd * 4, "out")
-    check(lib().launch_attn_prefill(_ptr(q), _ptr(k), _ptr(v), _ptr(out), t, nqh, nkv, hd, prefix, float(kq_scale), _stream()), "launch_attn_prefill")
+    name = "launch_attn_prefill" if k.dtype == torch.float32 else "launch_attn_prefill_f16kv"
+    check(getattr(lib(), name)(_ptr(q), _ptr(k), _ptr(v), _ptr(out), t, nqh, nkv, hd, prefix, float(kq_scale), _stream()), name)
 
 
 # ---- quantized dense layer ---------------------------------------------------------------

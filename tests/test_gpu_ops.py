@@ -164,6 +164,11 @@ def test_sequence_attention_matches_oracle(ops, t, nqh, nkv, hd, prefix):
     out2 = torch.empty_like(out)
     ops.gpu_gqa_attn_into(torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(), out2, t, nqh, nkv, hd, prefix, scale)
     assert torch.equal(out, out2)
+    # k and v handed over as f16 (the rows of a KV cache): the values the f32 form rounds to, so the same bits
+    out3 = torch.full_like(out, float("nan"))
+    ops.gpu_gqa_attn_into(torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda().half(), torch.from_numpy(v).cuda().half(), out3, t, nqh, nkv, hd, prefix, scale)
+    ops.check_launch()
+    assert torch.equal(out, out3)
 
 
 def test_sequence_attention_rejects_bad_arguments(ops):
@@ -176,4 +181,6 @@ def test_sequence_attention_rejects_bad_arguments(ops):
     assert L.launch_attn_prefill(p(x), p(x), p(x), p(x), 4, 4, 2, 64, 0, 1.0, None) == -2      # out aliases an input
     assert L.launch_attn_prefill(p(x), p(x), p(x), p(o), 4, 4, 2, 80, 0, 1.0, None) == -3      # head_dim not instantiated
     assert L.launch_attn_prefill(None, p(x), p(x), p(o), 4, 4, 2, 64, 0, 1.0, None) == -1
+    assert L.launch_attn_prefill_f16kv(p(x), p(x), None, p(o), 4, 4, 2, 64, 0, 1.0, None) == -1
+    assert L.launch_attn_prefill_f16kv(p(x), p(x), p(x), p(o), 4, 4, 2, 80, 0, 1.0, None) == -3
     ops.check_launch()
