@@ -666,6 +666,7 @@ static int prefill(Decoder* d, const int* tokens, int t, int seq, int* next_toke
     do {       \
         if ((st = (e)) != 0) return st; \
     } while (0)
+    if (c.head_dim / 2 > 256 || (d->nkv * c.head_dim) % 4 || d->qk_rows % 4 || d->v_rows % 4) return QMM_ERR_UNSUPPORTED;  // rope_seq_append_kernel
     TRY(prefill_reserve(d, t));
     Decoder::Prefill& f = d->pf;
     const int H = c.hidden, hd = c.head_dim, nq = d->nq, nkv = d->nkv, ao = nq * hd, ffn = d->ffn_l;
@@ -696,7 +697,7 @@ static int prefill(Decoder* d, const int* tokens, int t, int seq, int* next_toke
         else TRY(add_rmsnorm_launch(f.x, parts, l > 0 ? 1 : 0, (long)H, L.attn_norm, f.q8, H, c.rms_eps, none, xn_f32, t, false, s, f.xb));
         TRY(prefill_dense(d, c.type_attn_qk, L.wqk, f.xn, f.qk, t, v_fused ? d->qk_rows + d->v_rows : d->qk_rows, H, s));
         if (!v_fused) TRY(prefill_dense(d, c.type_attn_v, L.wv, f.xn, f.v, t, d->v_rows, H, s));
-        rope_seq_append_kernel<<<dim3(8, t), 256, 0, s>>>(f.qk, qk_stride, vbuf, v_stride, d->kcache + (size_t)l * cache_layer,
+        rope_seq_append_kernel<<<t, 256, 0, s>>>(f.qk, qk_stride, vbuf, v_stride, d->kcache + (size_t)l * cache_layer,
                                                             d->vcache + (size_t)l * cache_layer, nq, nkv, hd, 0, seq, c.ctx_len, c.rope_theta);
         QMM_CUDA_TRY(cudaGetLastError());
         // (from 64 positions on the O projection is a GEMM and reads the attention's output as bf16)

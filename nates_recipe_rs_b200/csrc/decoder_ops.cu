@@ -363,33 +363,39 @@ inline int add_rmsnorm_launch(float* x, const PartPtrs& parts, int n_parts, long
 // The same for a whole sequence (the prefill of a prompt): row r of the buffers is position pos0 + r of sequence
 // `seq`.  q and k (columns [0, nqh*hd) and [nqh*hd, (nqh+nkv)*hd) of a row of qk) are rotated in place (f32: the
 // sequence attention reads them there), k (rotated) and v also go to the fp16 cache.
+// One CTA per position: a thread keeps one rotation (sine and cosine of pos * theta^(-2i/hd), the costly part) and
+// applies it to element pair i of every head of its group of heads.
 __global__ void rope_seq_append_kernel(float* __restrict__ qk, long qk_stride, const float* __restrict__ v, long v_stride,
                                        __half* __restrict__ kcache, __half* __restrict__ vcache, int nqh, int nkv, int hd, int pos0, int seq,
                                        int ctx_cap, float theta) {
-    const int r = blockIdx.y, pos = pos0 + r;
+    const int r = blockIdx.x, pos = pos0 + r;
     const int half = hd / 2;
-    const int pairs = (nqh + nkv) * half;
     float* row = qk + (size_t)r * qk_stride;
     const float* vrow = v + (size_t)r * v_stride;
-    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < pairs + nkv * hd; idx += gridDim.x * blockDim.x) {
-        if (idx < pairs) {
-            const int head = idx / half, i = idx - head * half;
-            float sn, cs;
-            sincosf((float)pos * powf(theta, -2.0f * (float)i / (float)hd), &sn, &cs);
+    const size_t cache_row = ((size_t)seq * ctx_cap + pos) * nkv * hd;
+    const int groups = blockDim.x / half;  // (the launcher keeps half <= blockDim.x)
+    const int i = threadIdx.x % half, g = threadIdx.x / half;
+    if (g < groups) {
+        float sn, cs;
+        sincosf((float)pos * powf(theta, -2.0f * (float)i / (float)hd), &sn, &cs);
+        for (int head = g; head < nqh + nkv; head += groups) {
             float* h = row + (size_t)head * hd;
             const float a = h[i], c = h[i + half];
             const float ra = a * cs - c * sn, rc = a * sn + c * cs;
             h[i] = ra;
             h[i + half] = rc;
             if (head >= nqh) {
-                __half* dst = kcache + (((size_t)seq * ctx_cap + pos) * nkv + (head - nqh)) * hd;
+                __half* dst = kcache + cache_row + (size_t)(head - nqh) * hd;
                 dst[i] = __float2half_rn(ra);
                 dst[i + half] = __float2half_rn(rc);
             }
-        } else {
-            const int j = idx - pairs;
-            vcache[((size_t)seq * ctx_cap + pos) * nkv * hd + j] = __float2half_rn(vrow[j]);
         }
+    }
+    const int nv = nkv * hd;  // (a multiple of 4: hd is even and the launcher checks the rest)
+    for (int j = threadIdx.x * 4; j < nv; j += blockDim.x * 4) {
+        const float4 x = *reinterpret_cast<const float4*>(vrow + j);
+        const __half2 lo = __floats2half2_rn(x.x, x.y), hi = __floats2half2_rn(x.z, x.w);
+        *reinterpret_cast<uint2*>(vcache + cache_row + j) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
     }
 }
 
