@@ -311,6 +311,10 @@ int mma_acc_set(const char* key, int v);
 int mma_group_rows();
 int qmatvec_mma_launch(int type, const void* w, long row_pitch, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                        unsigned long long* trace, const TpPush* push, cudaStream_t stream);
+int umv_set_min_m(int v);
+int umv_set_ksplit(int v);
+int umv_min_m();
+int qmatvec_umma_launch(const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, cudaStream_t stream);
 int matvec_tune(const char* key, int value) {
     const std::string k(key ? key : "");
 #ifdef QMM_TUNING  // wrong results by design: development builds only
@@ -324,6 +328,8 @@ int matvec_tune(const char* key, int value) {
     if (k == "rb_max" && (value == 1 || value == 2 || value == 4)) return g_rb_max = value, QMM_OK;
     if (k == "ctas_per_sm" && value >= 1 && value <= 2) return g_ctas_per_sm = value, QMM_OK;
     if (k == "mma_min_m") return mma_set_min_m(value);
+    if (k == "umma_min_m") return umv_set_min_m(value);
+    if (k == "umma_ksplit") return umv_set_ksplit(value);
     if (k.rfind("mma_acc", 0) == 0) return mma_acc_set(key, value);
     if (k == "gemm_mb") return gemm_set_mb(value);
     if (k == "gemm_ksplit") return gemm_set_ksplit(value);
@@ -448,6 +454,17 @@ int qmatvec_launch_pitched(int type, const void* w, long row_pitch, const void* 
     // From mma_min_m activation rows on, groups of up to 16 rows go to the tensor-core kernel where it
     // supports the shape; what is left (fewer rows, other types and shapes) takes the dp4a kernel below.
     int m_done = 0;
+    // Q4_K rows back to back, from umma_min_m activation rows on: groups of up to 32 rows through the tcgen05 integer kernel
+    if (type == QMM_TYPE_Q4_K && !push && !g_probe && umv_min_m() > 0 && (row_pitch == 0 || row_pitch == (long)k / block_elems * block_bytes)) {
+        while (m - m_done >= umv_min_m()) {
+            const int mg = m - m_done < 32 ? m - m_done : 32;
+            const int st = qmatvec_umma_launch(w, static_cast<const uint8_t*>(xq) + (size_t)m_done * p.xq_row_bytes, y + (size_t)m_done * y_stride, y_stride,
+                                               mg, n, k, stream);
+            if (st == QMM_ERR_UNSUPPORTED) break;
+            if (st) return st;
+            m_done += mg;
+        }
+    }
     if (mma_min_m() > 0 && !g_probe) {
         while (m - m_done >= mma_min_m()) {
             const int mg = m - m_done < mma_group_rows() ? m - m_done : mma_group_rows();
