@@ -217,6 +217,34 @@ def test_tensor_core_kernel_tiles_per_pass(ops, qtype, m, n, k):
         _lib.check(L.qmm_tune(b"mma_acc_tp4", 4), "tune")
 
 
+@pytest.mark.parametrize("maker", [seeded_weights, random_byte_weights])
+@pytest.mark.parametrize("m,n,k", [(17, 1000, 1024), (32, 4096, 4096), (24, 300, 14336), (12, 2048, 2048), (40, 640, 8192)])
+def test_tcgen05_integer_matvec(ops, maker, m, n, k):
+    """The tcgen05 kind::i8 form of the Q4_K matvec (int32 sums in tensor memory, scales in the epilogue) against the
+    oracle: both widths of the instruction (16 and 32 activation rows; 12 rows reach it through the tunable), ragged
+    last tiles, K split over clusters of 1, 2 and 4 CTAs, a second group of rows past 32; reruns give the same bits."""
+    from nates_recipe_rs_b200 import _lib
+    L = _lib.lib()
+    w = maker(oracle.Q4_K, n, k, 77 + n)
+    xq = oracle.quantize(oracle.Q8_1, oracle.fill_normal(m * k, 78 + k, 1.0).reshape(m, k))
+    want = oracle.matvec(oracle.Q4_K, w, xq, k)
+    wd, xd = dev(w), dev(xq)
+    try:
+        _lib.check(L.qmm_tune(b"umma_min_m", 8), "tune")
+        for ksplit in (0, 1, 2, 4):
+            _lib.check(L.qmm_tune(b"umma_ksplit", ksplit), "tune")
+            y = torch.full((m, n), float("nan"), device="cuda")
+            ops.gpu_qmatvec_into(oracle.Q4_K, wd, xd, y, m, n, k)
+            y2 = torch.full((m, n), float("nan"), device="cuda")
+            ops.gpu_qmatvec_into(oracle.Q4_K, wd, xd, y2, m, n, k)
+            ops.check_launch()
+            assert_close(y.cpu().numpy(), want, f"ksplit {ksplit}")
+            assert torch.equal(y, y2)
+    finally:
+        _lib.check(L.qmm_tune(b"umma_min_m", 17), "tune")
+        _lib.check(L.qmm_tune(b"umma_ksplit", 0), "tune")
+
+
 # per-rank projection shapes of the 8B- and 70B-class stacks under tensor parallelism 4 and 8
 TP_SHARD_SHAPES = [
     (oracle.Q4_K, 1280, 4096), (oracle.Q6_K, 256, 4096), (oracle.Q4_K, 4096, 1024), (oracle.Q4_K, 7168, 4096), (oracle.Q6_K, 4096, 3584),
