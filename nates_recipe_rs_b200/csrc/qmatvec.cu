@@ -314,7 +314,7 @@ int qmatvec_mma_launch(int type, const void* w, long row_pitch, const void* xq, 
 int umv_set_min_m(int v);
 int umv_set_ksplit(int v);
 int umv_min_m();
-int qmatvec_umma_launch(const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, cudaStream_t stream);
+int qmatvec_umma_launch(const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, const TpPush* push, cudaStream_t stream);
 int matvec_tune(const char* key, int value) {
     const std::string k(key ? key : "");
 #ifdef QMM_TUNING  // wrong results by design: development builds only
@@ -455,11 +455,13 @@ int qmatvec_launch_pitched(int type, const void* w, long row_pitch, const void* 
     // supports the shape; what is left (fewer rows, other types and shapes) takes the dp4a kernel below.
     int m_done = 0;
     // Q4_K rows back to back, from umma_min_m activation rows on: groups of up to 32 rows through the tcgen05 integer kernel
-    if (type == QMM_TYPE_Q4_K && !push && !g_probe && umv_min_m() > 0 && (row_pitch == 0 || row_pitch == (long)k / block_elems * block_bytes)) {
+    if (type == QMM_TYPE_Q4_K && !g_probe && umv_min_m() > 0 && (row_pitch == 0 || row_pitch == (long)k / block_elems * block_bytes)) {
         while (m - m_done >= umv_min_m()) {
             const int mg = m - m_done < 32 ? m - m_done : 32;
+            TpPush sub = {};
+            if (push) sub = *push, sub.word0 += (long)m_done * y_stride;
             const int st = qmatvec_umma_launch(w, static_cast<const uint8_t*>(xq) + (size_t)m_done * p.xq_row_bytes, y + (size_t)m_done * y_stride, y_stride,
-                                               mg, n, k, stream);
+                                               mg, n, k, push ? &sub : nullptr, stream);
             if (st == QMM_ERR_UNSUPPORTED) break;
             if (st) return st;
             m_done += mg;

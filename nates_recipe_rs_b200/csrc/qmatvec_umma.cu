@@ -50,6 +50,7 @@ struct UmvParams {
     int m, n, k;
     int xq_row_bytes;
     int ksplit;         // CTAs of a cluster that share a tile of rows, each with a contiguous part of K
+    TpPush push;        // tensor parallel: the outputs go to every rank's exchange area instead of y
 };
 
 struct __align__(16) UmvSmemHeader {
@@ -431,11 +432,12 @@ __global__ void __launch_bounds__(UMV_THREADS, 1) qmv_umma_kernel(const __grid_c
         }
     }
     if (is_epi0 && split == 0 && epi_ok && !*cta_abort) {
-        pdl_wait_prior_grids();  // y may still be read by the preceding kernel
+        pdl_wait_prior_grids();  // y may still be read by the preceding kernel; the exchange counter belongs to it too
+        const unsigned push_seq = p.push.tp > 0 ? tp_next_seq(p.push.counter) : 0u;
         if (n0 + row < p.n) {
 #pragma unroll
             for (int c = 0; c < NC; ++c)
-                if (c < p.m) p.y[(size_t)c * p.y_stride + n0 + row] = acc[c];  // the lanes of a warp: 32 consecutive outputs
+                if (c < p.m) tp_store_out(p.push, push_seq, p.y, p.y_stride, c, (long)n0 + row, acc[c]);  // a warp: 32 consecutive outputs
         }
     }
     tc_fence_before();
@@ -461,8 +463,8 @@ int umv_set_ksplit(int v) {
 }
 
 // Q4_K rows back to back, up to 32 activation rows, k a multiple of 256; QMM_ERR_UNSUPPORTED for anything else
-// (the caller falls back to the mma.sync kernel)
-int qmatvec_umma_launch(const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, cudaStream_t stream) {
+// (the caller falls back to the mma.sync kernel).  push (tensor parallel): as in the other matvec kernels.
+int qmatvec_umma_launch(const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, const TpPush* push, cudaStream_t stream) {
     if (m <= 0 || m > 32 || k % QKK != 0 || reinterpret_cast<uintptr_t>(w) % 16 != 0 || reinterpret_cast<uintptr_t>(xq) % 16 != 0) return QMM_ERR_UNSUPPORTED;
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return QMM_ERR_UNSUPPORTED;
@@ -489,6 +491,8 @@ int qmatvec_umma_launch(const void* w, const void* xq, float* y, long y_stride, 
     p.y = y;
     p.y_stride = y_stride;
     p.m = m, p.n = n, p.k = k;
+    p.push = TpPush{};
+    if (push) p.push = *push;
     p.xq_row_bytes = k / QK8 * Q8_1_BYTES;
     const int tiles = (n + UMV_BW - 1) / UMV_BW;
     // few tiles: split K over a cluster so that most SMs have a CTA (each part at least four super-blocks)
