@@ -704,7 +704,7 @@ static int prefill(Decoder* d, const int* tokens, int t, int seq, int* next_toke
         {   // keys and values: the f16 rows that the kernel above has just appended to the cache (row = position)
             const size_t seq_off = (size_t)l * cache_layer + (size_t)seq * c.ctx_len * nkv * hd;
             TRY(attn_prefill_launch(f.qk, d->kcache + seq_off, d->vcache + seq_off, f.att, t, nq, nkv, hd, t, rsqrtf((float)hd), qk_stride,
-                                    (long)nkv * hd, (long)nkv * hd, ao, s, (t >= 64 && ao % 256 == 0) ? f.xb : nullptr, (nkv * hd) % 8 == 0));
+                                    (long)nkv * hd, (long)nkv * hd, ao, s, (t >= 64 && ao % 256 == 0) ? f.xb : nullptr, true));  // (head_dim is a multiple of 32: 16-byte rows)
         }
         TRY(prefill_dense(d, c.type_attn_o, L.wo, f.att, f.part, t, H, ao, s));
         if (seq_norm) TRY(add_rmsnorm_bf16_launch(f.x, f.part, (long)H, L.ffn_norm, H, c.rms_eps, f.xb, t, s));

@@ -361,8 +361,8 @@ inline int add_rmsnorm_launch(float* x, const PartPtrs& parts, int n_parts, long
 }
 
 // The same for a whole sequence (the prefill of a prompt): row r of the buffers is position pos0 + r of sequence
-// `seq`.  q and k (columns [0, nqh*hd) and [nqh*hd, (nqh+nkv)*hd) of a row of qk) are rotated in place (f32: the
-// sequence attention reads them there), k (rotated) and v also go to the fp16 cache.
+// `seq`.  q (columns [0, nqh*hd) of a row of qk) is rotated in place (f32: the sequence attention reads it there); k
+// (columns [nqh*hd, (nqh+nkv)*hd)) is rotated into the fp16 cache, where v goes too and where the attention reads both.
 // One CTA per position: a thread keeps one rotation (sine and cosine of pos * theta^(-2i/hd), the costly part) and
 // applies it to element pair i of every head of its group of heads.
 __global__ void rope_seq_append_kernel(float* __restrict__ qk, long qk_stride, const float* __restrict__ v, long v_stride,
@@ -382,9 +382,10 @@ __global__ void rope_seq_append_kernel(float* __restrict__ qk, long qk_stride, c
             float* h = row + (size_t)head * hd;
             const float a = h[i], c = h[i + half];
             const float ra = a * cs - c * sn, rc = a * sn + c * cs;
-            h[i] = ra;
-            h[i + half] = rc;
-            if (head >= nqh) {
+            if (head < nqh) {
+                h[i] = ra;
+                h[i + half] = rc;
+            } else {
                 __half* dst = kcache + cache_row + (size_t)(head - nqh) * hd;
                 dst[i] = __float2half_rn(ra);
                 dst[i + half] = __float2half_rn(rc);
