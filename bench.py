@@ -30,6 +30,8 @@ CPU implementation there is: the upstream has none) on the host cores.
     --case gemm:<n>:<k>:<m>[:launches]                        Q4_K x bf16 prefill GEMM
     --case decode:<8b|70b>:<batch>[:steps[:layers]]           eager decode steps of a (cut) stack
     --case prefill:<8b|70b>:<tokens>[:layers]                 a prompt through a (cut) stack at once, twice
+    --case seqattn:<t>:<q heads>:<kv heads>:<head dim>[:f32]  causal attention over a sequence (k, v f16 rows of a cache,
+                                                              or f32), a few launches, device-timed
     --case shard:<8b|70b>:<tp>:<batch>                        step time of a decoder with the per-rank shapes of a
                                                               tensor-parallel layout, on one GPU (no exchange)
 """
@@ -733,6 +735,25 @@ def run_case(spec):
         for i in range(steps):   # eager launches, so that a launch list attributes the step to its kernels
             d.step(batch, pos0 + i)
             d.tokens.copy_(d.next_tokens)
+    elif kind == "seqattn":
+        t, nqh, nkv, hd = (int(v) for v in parts[1:5])
+        kv_dtype = torch.float32 if len(parts) > 5 and parts[5] == "f32" else torch.float16
+        q = torch.randn(t, nqh * hd, device=dev)
+        k = torch.randn(t, nkv * hd, device=dev).to(kv_dtype)
+        v = torch.randn(t, nkv * hd, device=dev).to(kv_dtype)
+        out = torch.empty(t, nqh * hd, device=dev)
+        for _ in range(2):
+            ops.gpu_gqa_attn_into(q, k, v, out, t, nqh, nkv, hd, t, hd ** -0.5)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            ops.gpu_gqa_attn_into(q, k, v, out, t, nqh, nkv, hd, t, hd ** -0.5)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / 3
+        flops = 4.0 * hd * nqh * (t * (t + 1) / 2)
+        print(json.dumps({"case": spec, "us_per_launch": us, "useful_TFLOPs": flops / us / 1e6}))
     elif kind == "prefill":
         # prefill:<8b|70b>:<tokens>[:layers]: one prompt through a (cut) stack, eager launches (for a launch list)
         from nates_recipe_rs_b200 import decoder as dec
