@@ -302,6 +302,11 @@ int launch_attn_prefill(const float* q, const float* k, const float* v, float* o
  * give the same bits for k16 = f16(k), v16 = f16(v); the tiles go to shared memory with cp.async, half the traffic, no conversion. */
 int launch_attn_prefill_f16kv(const float* q, const void* k16, const void* v16, float* out, int t, int n_q_heads, int n_kv_heads,
                               int head_dim, int prefix, float kq_scale, void* stream);
+/* ... and for t queries that continue a sequence: row r of q and out is position q_pos0 + r, k16 and v16 hold positions
+ * 0..t_kv-1 (q_pos0 + t <= t_kv); `prefix` counts positions of the sequence as above.  Row for row the same bits as the
+ * rows q_pos0.. of one call over the whole sequence. */
+int launch_attn_prefill_f16kv_at(const float* q, const void* k16, const void* v16, float* out, int t, int t_kv, int q_pos0, int n_q_heads,
+                                 int n_kv_heads, int head_dim, int prefix, float kq_scale, void* stream);
 
 /* ---- quantized dense layer: y(m,n) = act( x(m,k) . w(n,k)^T + bias(n) ), x and y f32, w packed blocks of
  * `type`.  The counterpart of LayerKind::Dense in the upstream's forward pass (recipe-infer/src/forward.rs:

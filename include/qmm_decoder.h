@@ -94,6 +94,12 @@ int qmm_decoder_tp_ready(void* handle); /* call once after all imports (uploads 
  * The logits differ from feeding the prompt token by token through qmm_decoder_step by the rounding of the
  * activations (bf16 / f16 here, Q8_1 blocks there). */
 int qmm_decoder_prefill(void* handle, const int* tokens, int n_tokens, int seq, int* next_token, float* logits_out, void* stream);
+/* The same for tokens that CONTINUE sequence `seq`: tokens[0] is position pos0 and the cache already holds positions
+ * 0..pos0-1 (from an earlier prompt call or from decode steps).  A long prompt can be fed in pieces, a conversation
+ * extended turn by turn; every query attends to the cached positions and causally to its own piece.  pos0 = 0 is
+ * qmm_decoder_prefill.  pos0 + n_tokens <= ctx_len. */
+int qmm_decoder_prefill_at(void* handle, const int* tokens, int n_tokens, int seq, int pos0, int* next_token, float* logits_out,
+                           void* stream);
 
 /* One decode step: tokens (device, batch ints) at position pos -> next_tokens (device, batch ints,
  * greedy).  logits (optional, device, batch x vocab_local f32) receives this rank's slice of the

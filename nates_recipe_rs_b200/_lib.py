@@ -81,6 +81,7 @@ SIGNATURES = {
     "launch_gemm_bt_bf16_f32acc": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "launch_attn_prefill": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, C.c_float, vp]),
     "launch_attn_prefill_f16kv": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, C.c_float, vp]),
+    "launch_attn_prefill_f16kv_at": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, C.c_float, vp]),
     "qmm_qdense_scratch_bytes": (i64, [i32, i32, i32]),
     "launch_qdense": (i32, [i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, C.c_float, vp]),
     "launch_moe_router_topk": (i32, [vp, vp, vp, i32, i32, i32, i32, C.c_float, C.c_float, vp, vp, vp, vp]),

@@ -36,7 +36,7 @@ template <int HD, int GH, bool KV16>
 __global__ void __launch_bounds__(128 * GH, (KV16 && HD <= 128) ? 2 : 1) attn_prefill_kernel(const float* __restrict__ q, const void* __restrict__ k_, const void* __restrict__ v_,
                                                                   float* __restrict__ out, int t, int nqh, int nkv, int prefix, float kq_scale,
                                                                   long q_stride, long k_stride, long v_stride, long o_stride,
-                                                                  __nv_bfloat16* __restrict__ out_bf16) {
+                                                                  __nv_bfloat16* __restrict__ out_bf16, int t_kv, int q_pos0) {
     extern __shared__ __align__(16) uint8_t pf_raw[];
     constexpr int PITCH = HD + 8;  // halves: rows 16 bytes apart modulo 128, so the 8 rows of an ldmatrix hit all banks
     constexpr int PF_THREADS = 128 * GH;
@@ -69,15 +69,17 @@ __global__ void __launch_bounds__(128 * GH, (KV16 && HD <= 128) ? 2 : 1) attn_pr
     }
 
     // this thread's two query rows and their running softmax state
-    const int p0 = q0 + 16 * warp + qr, p1 = p0 + 8;
+    // (row r of q and out is position q_pos0 + r of the sequence; the keys and values are positions 0 .. t_kv-1)
+    const int r0 = q0 + 16 * warp + qr, r1 = r0 + 8;
+    const int p0 = q_pos0 + r0, p1 = p0 + 8;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     float o[HD / 8][4];
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
     // key tiles: a tile of queries that is causal throughout stops at its own diagonal tile
-    const int n_kt = (t + PF_BK - 1) / PF_BK;
-    const int kt_end = (q0 + PF_BQ <= prefix) ? min(n_kt, qt + 1) : n_kt;
+    const int n_kt = (t_kv + PF_BK - 1) / PF_BK;
+    const int kt_end = (q_pos0 + q0 + PF_BQ <= prefix) ? min(n_kt, (q_pos0 + q0 + PF_BQ - 1) / PF_BK + 1) : n_kt;
     // Keys and values of a tile: float4 pieces, KV_IT per thread and matrix.  When a thread's pieces of a tile fit
     // its registers (KV_IT <= 8) the NEXT tile's loads are issued before the current tile's arithmetic, so their round
     // trip to L2 hides under the mma; otherwise a tile is loaded in chunks of eight pieces right before its use.
@@ -91,7 +93,7 @@ __global__ void __launch_bounds__(128 * GH, (KV16 && HD <= 128) ? 2 : 1) attn_pr
             const int i = tid + (base + it) * PF_THREADS, r = i / (HD / 4), c = (i - r * (HD / 4)) * 4;
             const int sp = kt * PF_BK + r;
             ka[it] = va[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (sp < t) {
+            if (sp < t_kv) {
                 ka[it] = *reinterpret_cast<const float4*>(k + (size_t)sp * kd + (size_t)kvh * HD + c);
                 va[it] = *reinterpret_cast<const float4*>(v + (size_t)sp * vd + (size_t)kvh * HD + c);
             }
@@ -112,7 +114,7 @@ __global__ void __launch_bounds__(128 * GH, (KV16 && HD <= 128) ? 2 : 1) attn_pr
         for (int i = tid; i < PF_BK * (HD / 8); i += PF_THREADS) {
             const int r = i / (HD / 8), c = (i - r * (HD / 8)) * 8;
             const int sp = kt * PF_BK + r;
-            if (sp < t) {
+            if (sp < t_kv) {
                 cp_async_16(smem_u32(kd_s + r * PITCH + c), k16 + (size_t)sp * kd + (size_t)kvh * HD + c);
                 cp_async_16(smem_u32(vd_s + r * PITCH + c), v16 + (size_t)sp * vd + (size_t)kvh * HD + c);
             } else {
@@ -168,14 +170,14 @@ __global__ void __launch_bounds__(128 * GH, (KV16 && HD <= 128) ? 2 : 1) attn_pr
         }
         // mask (the upstream writes -1e30 into a masked score; a key past the end does not exist), running softmax
         // (only a tile that reaches past the end or past the diagonal of this warp's first row has anything to mask)
-        const int w0 = q0 + 16 * warp;
-        if (kt * PF_BK + PF_BK > t || (w0 < prefix && kt * PF_BK + PF_BK - 1 > w0)) {
+        const int w0 = q_pos0 + q0 + 16 * warp;
+        if (kt * PF_BK + PF_BK > t_kv || (w0 < prefix && kt * PF_BK + PF_BK - 1 > w0)) {
 #pragma unroll
             for (int n = 0; n < PF_BK / 8; ++n) {
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int sp = kt * PF_BK + 8 * n + 2 * pq + e;
-                    if (sp >= t) s[n][e] = -INFINITY, s[n][2 + e] = -INFINITY;
+                    if (sp >= t_kv) s[n][e] = -INFINITY, s[n][2 + e] = -INFINITY;
                     else {
                         if (p0 < prefix && sp > p0) s[n][e] = -1e30f;
                         if (p1 < prefix && sp > p1) s[n][2 + e] = -1e30f;
@@ -222,18 +224,18 @@ __global__ void __launch_bounds__(128 * GH, (KV16 && HD <= 128) ? 2 : 1) attn_pr
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n) {
         if (out_bf16) {  // the same layout as out, as bf16 (the input of a GEMM)
-            if (p0 < t) *reinterpret_cast<__nv_bfloat162*>(out_bf16 + (size_t)p0 * od + (size_t)h * HD + 8 * n + 2 * pq) = __floats2bfloat162_rn(o[n][0] * i0, o[n][1] * i0);
-            if (p1 < t) *reinterpret_cast<__nv_bfloat162*>(out_bf16 + (size_t)p1 * od + (size_t)h * HD + 8 * n + 2 * pq) = __floats2bfloat162_rn(o[n][2] * i1, o[n][3] * i1);
+            if (r0 < t) *reinterpret_cast<__nv_bfloat162*>(out_bf16 + (size_t)r0 * od + (size_t)h * HD + 8 * n + 2 * pq) = __floats2bfloat162_rn(o[n][0] * i0, o[n][1] * i0);
+            if (r1 < t) *reinterpret_cast<__nv_bfloat162*>(out_bf16 + (size_t)r1 * od + (size_t)h * HD + 8 * n + 2 * pq) = __floats2bfloat162_rn(o[n][2] * i1, o[n][3] * i1);
         } else {
-            if (p0 < t) *reinterpret_cast<float2*>(out + (size_t)p0 * od + (size_t)h * HD + 8 * n + 2 * pq) = make_float2(o[n][0] * i0, o[n][1] * i0);
-            if (p1 < t) *reinterpret_cast<float2*>(out + (size_t)p1 * od + (size_t)h * HD + 8 * n + 2 * pq) = make_float2(o[n][2] * i1, o[n][3] * i1);
+            if (r0 < t) *reinterpret_cast<float2*>(out + (size_t)r0 * od + (size_t)h * HD + 8 * n + 2 * pq) = make_float2(o[n][0] * i0, o[n][1] * i0);
+            if (r1 < t) *reinterpret_cast<float2*>(out + (size_t)r1 * od + (size_t)h * HD + 8 * n + 2 * pq) = make_float2(o[n][2] * i1, o[n][3] * i1);
         }
     }
 }
 
 template <int HD, int GH, bool KV16>
 static int attn_prefill_inst(const float* q, const void* k, const void* v, float* out, int t, int nqh, int nkv, int prefix, float kq_scale,
-                             long q_stride, long k_stride, long v_stride, long o_stride, __nv_bfloat16* out_bf16, cudaStream_t s) {
+                             long q_stride, long k_stride, long v_stride, long o_stride, __nv_bfloat16* out_bf16, int t_kv, int q_pos0, cudaStream_t s) {
     const size_t smem = (size_t)(GH * PF_BQ + (KV16 ? 4 : 2) * PF_BK) * (HD + 8) * sizeof(__half);
     static std::mutex mu;
     static bool configured[64] = {};
@@ -247,7 +249,7 @@ static int attn_prefill_inst(const float* q, const void* k, const void* v, float
         }
     }
     attn_prefill_kernel<HD, GH, KV16><<<dim3(nqh / GH, (t + PF_BQ - 1) / PF_BQ), 128 * GH, smem, s>>>(q, k, v, out, t, nqh, nkv, prefix, kq_scale, q_stride, k_stride,
-                                                                                                 v_stride, o_stride, out_bf16);
+                                                                                                 v_stride, o_stride, out_bf16, t_kv, q_pos0);
     QMM_CUDA_TRY(cudaGetLastError());
     return QMM_OK;
 }
@@ -256,9 +258,11 @@ static int attn_prefill_inst(const float* q, const void* k, const void* v, float
 // side by side
 // (kv_f16: k and v are f16 rows, their strides in halves and multiples of 8)
 int attn_prefill_launch(const float* q, const void* k, const void* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim, int prefix,
-                        float kq_scale, long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s, __nv_bfloat16* out_bf16, bool kv_f16) {
+                        float kq_scale, long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s, __nv_bfloat16* out_bf16, bool kv_f16, int t_kv, int q_pos0) {
     if (!q || !k || !v || (!out && !out_bf16)) return QMM_ERR_NULL;
     if (t <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads != 0 || prefix < 0) return QMM_ERR_SHAPE;
+    if (t_kv <= 0) t_kv = t;  // (0: as many keys as queries, the first query at position 0)
+    if (q_pos0 < 0 || q_pos0 + t > t_kv) return QMM_ERR_SHAPE;  // every query position has its own key
     if (q_stride < (long)n_q_heads * head_dim || o_stride < (long)n_q_heads * head_dim || k_stride < (long)n_kv_heads * head_dim ||
         v_stride < (long)n_kv_heads * head_dim || q_stride % 4 || k_stride % (kv_f16 ? 8 : 4) || v_stride % (kv_f16 ? 8 : 4) || o_stride % 2)
         return QMM_ERR_SHAPE;
@@ -270,10 +274,10 @@ int attn_prefill_launch(const float* q, const void* k, const void* v, float* out
 #define QMM_PF_CASE(HD_)                                                                                                                              \
     case HD_:                                                                                                                                          \
         if (kv_f16)                                                                                                                                    \
-            return two ? attn_prefill_inst<HD_, 2, true>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, s) \
-                       : attn_prefill_inst<HD_, 1, true>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, s); \
-        return two ? attn_prefill_inst<HD_, 2, false>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, s)   \
-                   : attn_prefill_inst<HD_, 1, false>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, s)
+            return two ? attn_prefill_inst<HD_, 2, true>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, t_kv, q_pos0, s) \
+                       : attn_prefill_inst<HD_, 1, true>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, t_kv, q_pos0, s); \
+        return two ? attn_prefill_inst<HD_, 2, false>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, t_kv, q_pos0, s)   \
+                   : attn_prefill_inst<HD_, 1, false>(q, k, v, out, t, n_q_heads, n_kv_heads, prefix, kq_scale, q_stride, k_stride, v_stride, o_stride, out_bf16, t_kv, q_pos0, s)
     switch (head_dim) {
         QMM_PF_CASE(32);
         QMM_PF_CASE(64);
@@ -293,12 +297,23 @@ extern "C" int launch_attn_prefill(const float* q, const float* k, const float* 
                                    int prefix, float kq_scale, void* stream) {
     const long qd = (long)n_q_heads * head_dim, kd = (long)n_kv_heads * head_dim;
     if (!out) return QMM_ERR_NULL;
-    return attn_prefill_launch(q, k, v, out, t, n_q_heads, n_kv_heads, head_dim, prefix, kq_scale, qd, kd, kd, qd, as_stream(stream), nullptr, false);
+    return attn_prefill_launch(q, k, v, out, t, n_q_heads, n_kv_heads, head_dim, prefix, kq_scale, qd, kd, kd, qd, as_stream(stream), nullptr, false, 0, 0);
 }
 
 extern "C" int launch_attn_prefill_f16kv(const float* q, const void* k, const void* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim,
                                          int prefix, float kq_scale, void* stream) {
     const long qd = (long)n_q_heads * head_dim, kd = (long)n_kv_heads * head_dim;
     if (!out) return QMM_ERR_NULL;
-    return attn_prefill_launch(q, k, v, out, t, n_q_heads, n_kv_heads, head_dim, prefix, kq_scale, qd, kd, kd, qd, as_stream(stream), nullptr, true);
+    return attn_prefill_launch(q, k, v, out, t, n_q_heads, n_kv_heads, head_dim, prefix, kq_scale, qd, kd, kd, qd, as_stream(stream), nullptr, true, 0, 0);
+}
+
+// Queries at positions q_pos0 .. q_pos0+t-1 of a sequence whose keys and values 0 .. t_kv-1 are f16 rows (a KV cache that
+// already holds the earlier positions): the continuation of a prompt.  Row for row the same arithmetic as the whole
+// sequence in one call.
+extern "C" int launch_attn_prefill_f16kv_at(const float* q, const void* k, const void* v, float* out, int t, int t_kv, int q_pos0, int n_q_heads,
+                                            int n_kv_heads, int head_dim, int prefix, float kq_scale, void* stream) {
+    const long qd = (long)n_q_heads * head_dim, kd = (long)n_kv_heads * head_dim;
+    if (!out) return QMM_ERR_NULL;
+    if (t_kv <= 0) return QMM_ERR_SHAPE;
+    return attn_prefill_launch(q, k, v, out, t, n_q_heads, n_kv_heads, head_dim, prefix, kq_scale, qd, kd, kd, qd, as_stream(stream), nullptr, true, t_kv, q_pos0);
 }

@@ -23,7 +23,7 @@ int qmatvec_launch_push(int type, const void* w, const void* xq, float* y, long 
 int gemm_bt_bf16_launch(const void* a, const void* b, void* y, float* yf, int m, int n, int k, cudaStream_t stream);
 int dequantize_bf16_launch(int type, const void* w, void* out, long n_elems, cudaStream_t stream);
 int attn_prefill_launch(const float* q, const void* k, const void* v, float* out, int t, int n_q_heads, int n_kv_heads, int head_dim, int prefix,
-                        float kq_scale, long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s, __nv_bfloat16* out_bf16, bool kv_f16);
+                        float kq_scale, long q_stride, long k_stride, long v_stride, long o_stride, cudaStream_t s, __nv_bfloat16* out_bf16, bool kv_f16, int t_kv, int q_pos0);
 int qgemm_q4k_launch(const void* w, const void* x, void* y, float* yf, int m, int n, int k, cudaStream_t stream);
 int qmatvec_launch_pitched(int type, const void* w, long row_pitch, const void* xq, float* y, long y_stride, int m, int n, int k, int cta_limit,
                            const TpPush* push, cudaStream_t stream);
@@ -656,11 +656,12 @@ static int prefill_dense(Decoder* d, int type, const uint8_t* w, const float* x,
     return gemm_bt_bf16_launch(f.xb, f.wb, nullptr, y, t, n, k, s);
 }
 
-static int prefill(Decoder* d, const int* tokens, int t, int seq, int* next_token, float* logits_out, cudaStream_t s) {
+// pos0: the position of tokens[0]; the cache of sequence `seq` already holds positions 0 .. pos0-1
+static int prefill(Decoder* d, const int* tokens, int t, int seq, int pos0, int* next_token, float* logits_out, cudaStream_t s) {
     const qmm_decoder_config& c = d->c;
     if (!tokens || !next_token) return QMM_ERR_NULL;
     if (d->comm || c.tp_size != 1) return QMM_ERR_UNSUPPORTED;
-    if (t <= 0 || t > c.ctx_len || seq < 0 || seq >= c.max_batch) return QMM_ERR_SHAPE;
+    if (t <= 0 || pos0 < 0 || (long)pos0 + t > c.ctx_len || seq < 0 || seq >= c.max_batch) return QMM_ERR_SHAPE;
     int st;
 #define TRY(e) \
     do {       \
@@ -698,13 +699,14 @@ static int prefill(Decoder* d, const int* tokens, int t, int seq, int* next_toke
         TRY(prefill_dense(d, c.type_attn_qk, L.wqk, f.xn, f.qk, t, v_fused ? d->qk_rows + d->v_rows : d->qk_rows, H, s));
         if (!v_fused) TRY(prefill_dense(d, c.type_attn_v, L.wv, f.xn, f.v, t, d->v_rows, H, s));
         rope_seq_append_kernel<<<t, 256, 0, s>>>(f.qk, qk_stride, vbuf, v_stride, d->kcache + (size_t)l * cache_layer,
-                                                            d->vcache + (size_t)l * cache_layer, nq, nkv, hd, 0, seq, c.ctx_len, c.rope_theta);
+                                                            d->vcache + (size_t)l * cache_layer, nq, nkv, hd, pos0, seq, c.ctx_len, c.rope_theta);
         QMM_CUDA_TRY(cudaGetLastError());
         // (from 64 positions on the O projection is a GEMM and reads the attention's output as bf16)
         {   // keys and values: the f16 rows that the kernel above has just appended to the cache (row = position)
             const size_t seq_off = (size_t)l * cache_layer + (size_t)seq * c.ctx_len * nkv * hd;
-            TRY(attn_prefill_launch(f.qk, d->kcache + seq_off, d->vcache + seq_off, f.att, t, nq, nkv, hd, t, rsqrtf((float)hd), qk_stride,
-                                    (long)nkv * hd, (long)nkv * hd, ao, s, (t >= 64 && ao % 256 == 0) ? f.xb : nullptr, true));  // (head_dim is a multiple of 32: 16-byte rows)
+            // (head_dim is a multiple of 32: 16-byte rows; causal throughout: prefix = the sequence's length so far)
+            TRY(attn_prefill_launch(f.qk, d->kcache + seq_off, d->vcache + seq_off, f.att, t, nq, nkv, hd, pos0 + t, rsqrtf((float)hd), qk_stride,
+                                    (long)nkv * hd, (long)nkv * hd, ao, s, (t >= 64 && ao % 256 == 0) ? f.xb : nullptr, true, pos0 + t, pos0));
         }
         TRY(prefill_dense(d, c.type_attn_o, L.wo, f.att, f.part, t, H, ao, s));
         if (seq_norm) TRY(add_rmsnorm_bf16_launch(f.x, f.part, (long)H, L.ffn_norm, H, c.rms_eps, f.xb, t, s));
@@ -984,7 +986,13 @@ int qmm_decoder_tp_ready(void* handle) {
 int qmm_decoder_prefill(void* handle, const int* tokens, int n_tokens, int seq, int* next_token, float* logits_out, void* stream) {
     if (!handle) return QMM_ERR_NULL;
     Decoder* d = static_cast<Decoder*>(handle);
-    return prefill(d, tokens, n_tokens, seq, next_token, logits_out, static_cast<cudaStream_t>(stream));
+    return prefill(d, tokens, n_tokens, seq, 0, next_token, logits_out, static_cast<cudaStream_t>(stream));
+}
+
+int qmm_decoder_prefill_at(void* handle, const int* tokens, int n_tokens, int seq, int pos0, int* next_token, float* logits_out, void* stream) {
+    if (!handle) return QMM_ERR_NULL;
+    Decoder* d = static_cast<Decoder*>(handle);
+    return prefill(d, tokens, n_tokens, seq, pos0, next_token, logits_out, static_cast<cudaStream_t>(stream));
 }
 
 int qmm_decoder_step(void* handle, const int* tokens, int batch, int pos, int* next_tokens, float* logits, float* best, void* stream) {

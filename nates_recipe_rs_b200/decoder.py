@@ -58,6 +58,7 @@ def _bind():
         L.qmm_decoder_tp_ready.argtypes = [vp]
         L.qmm_decoder_step.argtypes = [vp, vp, i32, i32, vp, vp, vp, vp]
         L.qmm_decoder_prefill.argtypes = [vp, vp, i32, i32, vp, vp, vp]
+        L.qmm_decoder_prefill_at.argtypes = [vp, vp, i32, i32, i32, vp, vp, vp]
         L.qmm_decoder_create_from_gguf.argtypes = [C.c_char_p, i32, i32, i32, i32, C.POINTER(vp)]
         L.qmm_decoder_export_gguf.argtypes = [vp, C.c_char_p, C.c_char_p]
         _bound = True
@@ -121,15 +122,15 @@ class Decoder:
                                       logits.data_ptr() if logits is not None else None, self.best.data_ptr(),
                                       torch.cuda.current_stream().cuda_stream), "qmm_decoder_step")
 
-    def prefill(self, prompt, seq=0, logits=None):
+    def prefill(self, prompt, seq=0, logits=None, pos0=0):
         """All positions of `prompt` (int32 CUDA tensor) through the stack at once; fills the KV cache of sequence
-        `seq` for positions 0..len-1 and returns the greedy token after the last position (int32 CUDA tensor of one
-        element); `logits` (vocab floats) optionally receives that position's logits.  Decode goes on with
-        step(batch, pos=len(prompt))."""
+        `seq` for positions pos0..pos0+len-1 (the cache must already hold 0..pos0-1) and returns the greedy token
+        after the last position (int32 CUDA tensor of one element); `logits` (vocab floats) optionally receives that
+        position's logits.  Decode goes on with step(batch, pos=pos0+len(prompt))."""
         out = torch.empty(1, dtype=torch.int32, device=prompt.device)
-        check(self.L.qmm_decoder_prefill(self.h, prompt.data_ptr(), prompt.numel(), seq, out.data_ptr(),
-                                         logits.data_ptr() if logits is not None else None, torch.cuda.current_stream().cuda_stream),
-              "qmm_decoder_prefill")
+        check(self.L.qmm_decoder_prefill_at(self.h, prompt.data_ptr(), prompt.numel(), seq, pos0, out.data_ptr(),
+                                            logits.data_ptr() if logits is not None else None, torch.cuda.current_stream().cuda_stream),
+              "qmm_decoder_prefill_at")
         return out
 
     def close(self):

@@ -24,7 +24,7 @@ __all__ = [
     "gpu_quantize_q8_1_into", "gpu_quantize_q8_1", "gpu_quantize_weights_into", "gpu_quantize_weights",
     "gpu_dequantize_into", "gpu_dequantize", "gpu_qmatvec_into", "gpu_qmatvec", "gpu_qblock_dots",
     "MatvecJobs", "gpu_qmatvec_batch_into", "gpu_norm_qmatvec_batch_into", "gpu_glu_qmatvec_batch_into", "TpComm", "gpu_qmatvec_tp_into", "gpu_qmatvec_batch_tp_into",
-    "gpu_qgemm_q4_k_bf16_into", "gpu_qgemm_q4_k_bf16", "gpu_qdense_into", "DENSE_ACTS", "gpu_gqa_attn_into", "gpu_gemm_bt_bf16_into",
+    "gpu_qgemm_q4_k_bf16_into", "gpu_qgemm_q4_k_bf16", "gpu_qdense_into", "DENSE_ACTS", "gpu_gqa_attn_into", "gpu_gqa_attn_at_into", "gpu_gemm_bt_bf16_into",
     "gpu_qlinear",
     "gpu_rmsnorm_q8_1_into", "gpu_rope_kv_append", "gpu_glu_act_q8_1_into", "gpu_embed_rows_into", "gpu_argmax_rows",
     "gpu_scale_f32_inplace", "gpu_moe_router_topk", "gpu_moe_experts_into",
@@ -333,6 +333,19 @@ def gpu_gqa_attn_into(q, k, v, out, t, nqh, nkv, hd, prefix, kq_scale=1.0):
     _need(out, t * nqh * hd * 4, "out")
     name = "launch_attn_prefill" if k.dtype == torch.float32 else "launch_attn_prefill_f16kv"
     check(getattr(lib(), name)(_ptr(q), _ptr(k), _ptr(v), _ptr(out), t, nqh, nkv, hd, prefix, float(kq_scale), _stream()), name)
+
+
+def gpu_gqa_attn_at_into(q, k16, v16, out, t, t_kv, q_pos0, nqh, nkv, hd, prefix, kq_scale=1.0):
+    """The same for t queries that continue a sequence: row r of q / out is position q_pos0 + r, k16 and v16 (float16)
+    hold positions 0..t_kv-1 (the rows of a KV cache)."""
+    _need(q, t * nqh * hd * 4, "q")
+    _need(k16, t_kv * nkv * hd * 2, "k16")
+    _need(v16, t_kv * nkv * hd * 2, "v16")
+    _need(out, t * nqh * hd * 4, "out")
+    if k16.dtype != torch.float16 or v16.dtype != torch.float16:
+        raise TypeError("k16 and v16 must be float16")
+    check(lib().launch_attn_prefill_f16kv_at(_ptr(q), _ptr(k16), _ptr(v16), _ptr(out), t, t_kv, q_pos0, nqh, nkv, hd, prefix, float(kq_scale), _stream()),
+          "launch_attn_prefill_f16kv_at")
 
 
 # ---- quantized dense layer ---------------------------------------------------------------

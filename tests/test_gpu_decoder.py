@@ -358,6 +358,38 @@ def test_prefill_agrees_with_token_by_token_decoding(dec):
     d.close()
 
 
+@pytest.mark.parametrize("pieces", [(70, 70), (60, 64, 30), (20, 30), (64, 1, 75)])
+def test_prefill_in_pieces_continues_the_cache(dec, pieces):
+    """A prompt fed in pieces (qmm_decoder_prefill_at: each piece attends to the cached positions before it) against the
+    same prompt in one call: the last position's logits agree (the pieces may take the matvec route where the whole
+    prompt takes the GEMM route, hence the decoder tolerance), and decode continues from either cache alike."""
+    from nates_recipe_rs_b200 import quant_ops as ops
+    t = sum(pieces)
+    d = dec.Decoder(tiny_cfg(dec, ctx_len=160, max_batch=2))
+    c = d.cfg
+    prompt = torch.from_numpy(np.random.default_rng(t).integers(0, c.vocab, size=t).astype(np.int32)).cuda()
+    whole = torch.empty(c.vocab, device="cuda")
+    nxt_whole = d.prefill(prompt, 0, whole)                       # sequence 0: one call
+    part = torch.empty(c.vocab, device="cuda")
+    pos = 0
+    for n in pieces:                                              # sequence 1: piece by piece
+        nxt_part = d.prefill(prompt[pos:pos + n].contiguous(), 1, part, pos0=pos)
+        pos += n
+    ops.check_launch()
+    scale = float(whole.abs().max())
+    same_route = all((n >= 64) == (t >= 64) for n in pieces)
+    assert float((whole - part).abs().max()) <= (2e-3 if same_route else 5e-2) * scale
+    if same_route:
+        assert int(nxt_whole.item()) == int(nxt_part.item())
+    # one decode step for both sequences from their caches
+    d.tokens[:2] = int(nxt_whole.item())
+    step_logits = torch.empty(c.max_batch, c.vocab, device="cuda")
+    d.step(2, t, step_logits)
+    ops.check_launch()
+    assert float((step_logits[0] - step_logits[1]).abs().max()) <= (2e-3 if same_route else 5e-2) * float(step_logits[0].abs().max())
+    d.close()
+
+
 def test_prefill_rejects_bad_arguments(dec):
     from nates_recipe_rs_b200._lib import QmmError
     d = dec.Decoder(tiny_cfg(dec))
@@ -366,4 +398,8 @@ def test_prefill_rejects_bad_arguments(dec):
         d.prefill(toks, 0)            # longer than the context (48)
     with pytest.raises(QmmError):
         d.prefill(toks[:4], 7)        # no such sequence
+    with pytest.raises(QmmError):
+        d.prefill(toks[:10], 0, pos0=40)   # runs past the context (48)
+    with pytest.raises(QmmError):
+        d.prefill(toks[:4], 0, pos0=-1)
     d.close()

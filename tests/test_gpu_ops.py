@@ -171,6 +171,30 @@ def test_sequence_attention_matches_oracle(ops, t, nqh, nkv, hd, prefix):
     assert torch.equal(out, out3)
 
 
+@pytest.mark.parametrize("t_kv,q_pos0,t,nqh,nkv,hd,prefix", [(200, 64, 136, 8, 2, 128, 200), (200, 77, 100, 8, 2, 128, 200), (513, 500, 13, 4, 1, 64, 513),
+                                                          (300, 100, 150, 4, 4, 32, 120), (130, 129, 1, 2, 1, 256, 130)])
+def test_sequence_attention_continuing_a_cache(ops, t_kv, q_pos0, t, nqh, nkv, hd, prefix):
+    """Queries that continue a sequence whose earlier keys and values sit in an f16 cache: row for row the bits of one
+    call over the whole sequence (also when the piece does not start on a tile of 64 positions)."""
+    rng = np.random.default_rng(t_kv + q_pos0)
+    q = torch.from_numpy(rng.normal(size=(t_kv, nqh * hd)).astype(np.float32)).cuda()
+    k = torch.from_numpy(rng.normal(size=(t_kv, nkv * hd)).astype(np.float32)).cuda().half()
+    v = torch.from_numpy(rng.normal(size=(t_kv, nkv * hd)).astype(np.float32)).cuda().half()
+    scale = 1.0 / np.sqrt(hd)
+    whole = torch.empty(t_kv, nqh * hd, device="cuda")
+    ops.gpu_gqa_attn_into(q, k, v, whole, t_kv, nqh, nkv, hd, prefix, scale)
+    # the piece sees only the keys up to its own end when it is causal throughout; with bidirectional positions it needs all
+    kv_len = t_kv if prefix < t_kv else q_pos0 + t
+    piece = torch.full((t, nqh * hd), float("nan"), device="cuda")
+    ops.gpu_gqa_attn_at_into(q[q_pos0:q_pos0 + t].contiguous(), k[:kv_len].contiguous(), v[:kv_len].contiguous(), piece, t, kv_len, q_pos0, nqh, nkv, hd,
+                             prefix, scale)
+    ops.check_launch()
+    assert torch.equal(piece, whole[q_pos0:q_pos0 + t])
+    from nates_recipe_rs_b200._lib import lib
+    L = lib()
+    assert L.launch_attn_prefill_f16kv_at(q.data_ptr(), k.data_ptr(), v.data_ptr(), piece.data_ptr(), t, q_pos0 + t - 1, q_pos0, nqh, nkv, hd, prefix, 1.0, None) == -2
+
+
 def test_sequence_attention_rejects_bad_arguments(ops):
     from nates_recipe_rs_b200._lib import lib
     L = lib()
