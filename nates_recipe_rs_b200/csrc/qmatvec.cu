@@ -314,6 +314,8 @@ int qmatvec_mma_launch(int type, const void* w, long row_pitch, const void* xq, 
 int umv_set_min_m(int v);
 int umv_set_ksplit(int v);
 int umv_min_m();
+int umv_min_k();
+int umv_set_min_k(int v);
 int qmatvec_umma_launch(const void* w, const void* xq, float* y, long y_stride, int m, int n, int k, const TpPush* push, cudaStream_t stream);
 int matvec_tune(const char* key, int value) {
     const std::string k(key ? key : "");
@@ -330,6 +332,7 @@ int matvec_tune(const char* key, int value) {
     if (k == "mma_min_m") return mma_set_min_m(value);
     if (k == "umma_min_m") return umv_set_min_m(value);
     if (k == "umma_ksplit") return umv_set_ksplit(value);
+    if (k == "umma_min_k") return umv_set_min_k(value);
     if (k.rfind("mma_acc", 0) == 0) return mma_acc_set(key, value);
     if (k == "gemm_mb") return gemm_set_mb(value);
     if (k == "gemm_ksplit") return gemm_set_ksplit(value);
@@ -454,8 +457,11 @@ int qmatvec_launch_pitched(int type, const void* w, long row_pitch, const void* 
     // From mma_min_m activation rows on, groups of up to 16 rows go to the tensor-core kernel where it
     // supports the shape; what is left (fewer rows, other types and shapes) takes the dp4a kernel below.
     int m_done = 0;
-    // Q4_K rows back to back, from umma_min_m activation rows on: groups of up to 32 rows through the tcgen05 integer kernel
-    if (type == QMM_TYPE_Q4_K && !g_probe && umv_min_m() > 0 && (row_pitch == 0 || row_pitch == (long)k / block_elems * block_bytes)) {
+    // Q4_K rows back to back, from umma_min_m activation rows on: groups of up to 32 rows through the tcgen05 integer kernel.
+    // Not for short rows (the column shards of a tensor-parallel O or down projection): its launch has about 6 us of fixed
+    // cost, and below 16 super-blocks per row the mma.sync kernel measured faster (70B batch 32 on 8 GPUs: 2232 against
+    // 2118 tok/s).  It takes no CTA limit: a tile of 128 rows per CTA is its grid.
+    if (type == QMM_TYPE_Q4_K && !g_probe && umv_min_m() > 0 && k >= umv_min_k() && (row_pitch == 0 || row_pitch == (long)k / block_elems * block_bytes)) {
         while (m - m_done >= umv_min_m()) {
             const int mg = m - m_done < 32 ? m - m_done : 32;
             TpPush sub = {};

@@ -455,6 +455,13 @@ int umv_set_min_m(int v) {
     return QMM_OK;
 }
 int umv_min_m() { return g_umv_min_m; }
+static int g_umv_min_k = 4096;  // tunable "umma_min_k": shortest rows (elements) that take this kernel
+int umv_set_min_k(int v) {
+    if (v < QKK || v % QKK) return QMM_ERR_UNSUPPORTED;
+    g_umv_min_k = v;
+    return QMM_OK;
+}
+int umv_min_k() { return g_umv_min_k; }
 static int g_umv_ksplit = 0;  // tunable "umma_ksplit": 0 = automatic
 int umv_set_ksplit(int v) {
     if (v < 0 || v > UMV_KSPLIT_MAX || v == 3) return QMM_ERR_UNSUPPORTED;

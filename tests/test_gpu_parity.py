@@ -231,6 +231,7 @@ def test_tcgen05_integer_matvec(ops, maker, m, n, k):
     wd, xd = dev(w), dev(xq)
     try:
         _lib.check(L.qmm_tune(b"umma_min_m", 8), "tune")
+        _lib.check(L.qmm_tune(b"umma_min_k", 256), "tune")
         for ksplit in (0, 1, 2, 4):
             _lib.check(L.qmm_tune(b"umma_ksplit", ksplit), "tune")
             y = torch.full((m, n), float("nan"), device="cuda")
@@ -242,6 +243,7 @@ def test_tcgen05_integer_matvec(ops, maker, m, n, k):
             assert torch.equal(y, y2)
     finally:
         _lib.check(L.qmm_tune(b"umma_min_m", 17), "tune")
+        _lib.check(L.qmm_tune(b"umma_min_k", 4096), "tune")
         _lib.check(L.qmm_tune(b"umma_ksplit", 0), "tune")
 
 
