@@ -81,7 +81,8 @@ int qmm_set_overlap(int on);
  * tensor-core matvec where type and shape allow it; 0 = never; default 3), "mma_acc_tp1" / "mma_acc_tp2" /
  * "mma_acc_tp4" (2, 4, 8: weight tiles per pass of the tensor-core matvec at up to 8 / 16 / 32 activation rows) and
  * "mma_acc_w1" (8, 16: its warps at up to 8 rows), "umma_min_m" (0..33: fewest activation rows from which Q4_K
- * rows stored back to back take the tcgen05 integer matvec, in groups of up to 32 rows; 0 = never; default 17), "umma_min_k" (a multiple of 256, default 4096: shortest rows that take it) and
+ * rows stored back to back take the tcgen05 integer matvec, in groups of up to 32 rows; 0 = never; default 17), "umma_min_k" (a multiple of 256, default 4096: shortest rows that take it; the matrix must also hold
+ * 2 * umma_min_k^2 weights) and
  * "umma_ksplit" (0 = automatic, 1, 2, 4: CTAs of a cluster that share its tile of 128 weight rows, each with a
  * part of K), "attn_tc_min_batch" (fewest
  * sequences from which the decode attention runs on the f16 tensor cores; 0 = never; default 4), and for the

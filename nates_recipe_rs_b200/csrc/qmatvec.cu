@@ -459,9 +459,10 @@ int qmatvec_launch_pitched(int type, const void* w, long row_pitch, const void* 
     int m_done = 0;
     // Q4_K rows back to back, from umma_min_m activation rows on: groups of up to 32 rows through the tcgen05 integer kernel.
     // Not for short rows (the column shards of a tensor-parallel O or down projection): its launch has about 6 us of fixed
-    // cost, and below 16 super-blocks per row the mma.sync kernel measured faster (70B batch 32 on 8 GPUs: 2232 against
-    // 2118 tok/s).  It takes no CTA limit: a tile of 128 rows per CTA is its grid.
-    if (type == QMM_TYPE_Q4_K && !g_probe && umv_min_m() > 0 && k >= umv_min_k() && (row_pitch == 0 || row_pitch == (long)k / block_elems * block_bytes)) {
+    // cost, and below 16 super-blocks per row, or for a matrix under 32 M weights (few tiles, K split over clusters), the
+    // mma.sync kernel measured as fast or faster (70B batch 32 on 8 GPUs: 2232 against 2118 tok/s).  It takes no CTA
+    // limit: a tile of 128 rows per CTA is its grid.
+    if (type == QMM_TYPE_Q4_K && !g_probe && umv_min_m() > 0 && k >= umv_min_k() && (long)n * k >= 2l * umv_min_k() * umv_min_k() && (row_pitch == 0 || row_pitch == (long)k / block_elems * block_bytes)) {
         while (m - m_done >= umv_min_m()) {
             const int mg = m - m_done < 32 ? m - m_done : 32;
             TpPush sub = {};

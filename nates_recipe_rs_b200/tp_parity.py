@@ -84,7 +84,7 @@ def tp_matvec_parity(verbose=False):
     from ._lib import Q8_0
     rank, world = dist.get_rank(), dist.get_world_size()
     dev = torch.device("cuda", torch.cuda.current_device())
-    n_max, m_max = 4096, 32
+    n_max, m_max = 8192, 32
     comm = ops.TpComm(4 * m_max * n_max)
     ok, cases = True, 0
 
@@ -110,7 +110,7 @@ def tp_matvec_parity(verbose=False):
 
     for seed, (qt, n, kl, m) in enumerate([(Q4_K, 4096, 1792, 1), (Q6_K, 4096, 1792, 1), (Q4_K, 512, 3584, 2), (Q8_0, 300, 512, 1),
                                            (Q4_K, 4096, 2048, 5), (Q6_K, 2048, 2048, 16), (Q6_K, 1000, 1792, 9), (Q4_K, 37, 256, 3),
-                                           (Q4_K, 4096, 2048, 32), (Q4_K, 1000, 1792, 20), (Q4_K, 2048, 4096, 32), (Q4_K, 1000, 4096, 20)]):
+                                           (Q4_K, 4096, 2048, 32), (Q4_K, 1000, 1792, 20), (Q4_K, 8192, 4096, 32), (Q4_K, 1000, 4096, 20)]):
         w, xq = shard(qt, n, kl, rank, seed)
         for rep in range(2):   # two exchanges in a row use the two alternating buffers
             y = torch.full((m, n), float("nan"), device=dev)
