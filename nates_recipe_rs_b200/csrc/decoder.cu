@@ -644,9 +644,10 @@ static int prefill_reserve(Decoder* d, int t) {
     return QMM_OK;
 }
 
-// One projection of the prompt path: y(t, n) = x(t, k) . w(n, k)^T.  Q4_K: launch_qdense (the fused GEMM from 64 rows
-// on).  Other types from 64 rows on: the matrix is decoded to bf16 (bit-identical to launch_dequantize_*_bf16) and
-// multiplied by the same tcgen05 kernel with TMA-fed weight tiles; fewer rows: the Q8_1 matvec.
+// One projection of the prompt path: y(t, n) = x(t, k) . w(n, k)^T.  From 64 rows on the input is read as bf16 from
+// f.xb (written by the kernel that produced x; `x` itself may then be stale): Q4_K through the fused tcgen05 GEMM, other
+// types decoded to bf16 (bit-identical to launch_dequantize_*_bf16) and multiplied by the same kernel with TMA-fed
+// weight tiles.  Fewer rows: launch_qdense on the f32 input (the Q8_1 matvec).
 static int prefill_dense(Decoder* d, int type, const uint8_t* w, const float* x, float* y, int t, int n, int k, cudaStream_t s) {
     Decoder::Prefill& f = d->pf;
     const bool gemm = t >= 64 && k % 256 == 0;   // then f.xb holds bf16(x), written by the kernel that produced x
